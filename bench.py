@@ -1,0 +1,316 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: RWKV-4 7B-shape uint8 batch-1 decode, tokens/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--shape 7b]
+
+One "step" is one decode step (one token through 32 layers + head) of one stream per GPU.
+With N > 1 (launched by torchrun, one rank per GPU) every rank holds a replica of the
+weights and decodes its own stream: data-parallel replicas, no collective on the data path
+(weak scaling).  Rank 0 prints ONE JSON line.
+
+Keys beyond the basic contract:
+  e2e        tokens/s through the public API with HOST tokens: per step an H2D copy of the
+             token from pinned memory, the forward, a D2H copy of the logits, host argmax.
+  roofline   HBM roofline of the streaming GEMV kernel (129 of the 130 launches per step):
+             algorithmic bytes per launch / average launch duration vs the measured copy
+             bandwidth of this pool's B200s.
+  kernels    the same kernel timed alone (CUDA events around single launches), per matrix shape.
+  cpu_baseline / --impl reference
+             the CPU oracle (a port of the reference's FASTQUANT CPU path) timed on the host
+             cores on a bounded sample: one 7B-shape block + the head, extrapolated to 32 blocks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+from rwkvstic_b200.synth import SHAPES, VOCAB  # noqa: E402
+
+METRIC = "rwkv4_7b_int8_decode_tokens_per_s_b1"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+def decode_bytes_per_token(L, D, V=VOCAB, F=None):
+    """Algorithmic HBM bytes of one decode step: uint8 weights + fp32 scale/offset per input
+    feature of every matrix + fp32 vector parameters + state read and write + embedding row."""
+    F = 4 * D if F is None else F
+    w8 = L * (5 * D * D + 2 * D * F) + V * D
+    quant_vec = L * 8 * (6 * D + F) + 8 * D
+    vec = L * 44 * D + 16 * D
+    state = 40 * D * L
+    return w8, w8 + quant_vec + vec + state + 4 * D
+
+
+# ----------------------------------------------------------------------------------- clocks
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.path = tempfile.mktemp(prefix="clocks_", suffix=".csv")
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self, gpu_indices):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        with open(self.path) as f:
+            for line in f:
+                p = [c.strip() for c in line.split(",")]
+                if len(p) < 9 or not p[0].isdigit() or int(p[0]) not in gpu_indices:
+                    continue
+                try:
+                    sm.append(float(p[1])); mx.append(float(p[2]))
+                except ValueError:
+                    continue
+                for name, val in zip(names, p[5:9]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ----------------------------------------------------------------------------------- CPU reference arm
+def cpu_reference(shape, steps, warmup):
+    """tokens/s of the CPU oracle at this shape, from a bounded sample (one block + head)."""
+    from oracle.fastquant_oracle import OracleRWKV
+    from rwkvstic_b200.synth import synth_checkpoint
+    L, D = SHAPES[shape]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ck = synth_checkpoint(1, D, seed=1234)
+    model = OracleRWKV(ck)
+    del ck
+    state = model.emptyState.clone()
+    x = torch.randn(1, D, dtype=torch.float64)
+    tok = torch.tensor([17])
+    for _ in range(max(1, min(warmup, 2))):
+        model.forward(tok, state)
+        model.head(x)
+    n = max(2, min(steps, 8))
+    t0 = time.perf_counter()
+    for _ in range(n):
+        model.forward(tok, state)
+    t_model = (time.perf_counter() - t0) / n
+    t0 = time.perf_counter()
+    for _ in range(n):
+        model.head(x)
+    t_head = (time.perf_counter() - t0) / n
+    t_block = max(t_model - t_head, 1e-9)
+    t_token = L * t_block + t_head
+    return {"value": 1.0 / t_token, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"oracle port of the reference FASTQUANT CPU path (uint8 weights cast to fp32 per call, "
+                      f"fp32 matmul, fp64 vectors), {n} decode steps of a 1-block D={D} model + head: "
+                      f"{t_block * 1e3:.1f} ms/block, {t_head * 1e3:.1f} ms/head, extrapolated to {L} blocks"}
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    L, D = SHAPES[args.shape]
+    base = cpu_reference(args.shape, args.steps, args.warmup)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / base["value"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 weights, f32 matmul, f64 vectors",
+            "data": "synthetic", "config": {"workload": f"RWKV-4 {args.shape} shape L={L} D={D} V={VOCAB}, batch-1 decode",
+                                            "note": "CPU path of the reference; GPUs unused"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------- our arm
+def time_isolated_kernels(model, reps=3):
+    """Per matrix shape: GB/s of single GEMV launches timed alone with CUDA events.  Successive
+    launches walk over the layers, so every launch reads bytes that are not in L2."""
+    from rwkvstic_b200 import ops
+    dev = model.device
+    out = {}
+    D, F = model.n_embd, model.n_ffn
+    xs = {D: torch.randn(D, device=dev), F: torch.randn(F, device=dev)}
+    groups = {"att_kvr 3x[D,D]": [[ly.mat[k] for k in ("att.key", "att.value", "att.receptance")] for ly in model.w.layers],
+              "att_out [D,D]": [[ly.mat["att.output"]] for ly in model.w.layers],
+              "ffn_key+rec [4D,D]+[D,D]": [[ly.mat["ffn.key"], ly.mat["ffn.receptance"]] for ly in model.w.layers],
+              "ffn_value [D,4D]": [[ly.mat["ffn.value"]] for ly in model.w.layers],
+              "head [V,D]": [[model.w.head]]}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for name, launches in groups.items():
+        ys = [torch.empty(m.n_out, device=dev) for m in launches[0]]
+        nbytes = sum(m.qt.numel() for m in launches[0])
+        times = []
+        for r in range(reps + 1):
+            for mats in launches:
+                if len(launches) == 1:
+                    flush.fill_(r)                      # evict the single matrix from L2
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                ops.gemv_u8(mats, [xs[m.k_in] for m in mats], ys)
+                e1.record()
+                e1.synchronize()
+                if r > 0:
+                    times.append(e0.elapsed_time(e1))
+        t = statistics.median(times)
+        out[name] = {"bytes": nbytes, "us": round(t * 1e3, 2), "gbs": round(nbytes / t / 1e6, 1)}
+    return out
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from rwkvstic_b200.model import B200RWKV
+
+    L, D = SHAPES[args.shape]
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    model = B200RWKV.synthetic(L, D, seed=1234, device=dev, copy_logits=False)
+    K, W = args.steps, max(args.warmup, 3)
+    gen = torch.Generator().manual_seed(100 + rank)
+    host_tokens = torch.randint(0, VOCAB, (K + W,), generator=gen, dtype=torch.int64).pin_memory()
+    dev_tokens = host_tokens.to(dev)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-resident loop: tokens already in HBM, logits stay in HBM
+    state = model.emptyState.clone()
+    for i in range(W):
+        model.forward(dev_tokens[i:i + 1], state)
+    barrier()
+    sampler = ClockSampler()
+    if rank == 0:
+        sampler.start()
+    launches0 = model.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(W, W + K):
+        model.forward(dev_tokens[i:i + 1], state)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = model.launch_count - launches0
+    clocks = sampler.stop(set(range(world))) if rank == 0 else None
+    model.check_status()
+
+    # ---- end to end through the public API with host buffers
+    state = model.emptyState.clone()
+    pinned_logits = torch.empty(VOCAB, dtype=torch.float32).pin_memory()
+    tok = host_tokens[:1].clone().pin_memory()
+    for i in range(W):
+        lg, state = model.forward(tok, state)
+        pinned_logits.copy_(lg, non_blocking=True)
+        torch.cuda.synchronize(dev)
+        tok[0] = int(torch.argmax(pinned_logits))
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(K):
+        lg, state = model.forward(tok, state)            # H2D of the token inside
+        pinned_logits.copy_(lg, non_blocking=True)       # D2H of the step's result
+        torch.cuda.synchronize(dev)
+        tok[0] = int(torch.argmax(pinned_logits))        # greedy feedback on the host
+    torch.cuda.synchronize(dev)
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    model.check_status()
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+        cnt = torch.tensor([launches], device=dev, dtype=torch.int64)
+        dist.all_reduce(cnt)
+        launches = int(cnt[0])
+
+    if rank == 0:
+        w8, total_bytes = decode_bytes_per_token(L, D)
+        peak, peak_src = measured_peaks()
+        step_ms = ms / K
+        achieved = total_bytes / (step_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": world * K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+            "data": "synthetic",
+            "config": {"workload": f"RWKV-4 {args.shape} shape L={L} D={D} F={4 * D} V={VOCAB}, uint8 FASTQUANT weights, "
+                                   f"batch-1 decode, one stream per GPU (data-parallel replicas)",
+                       "l2": f"no flush needed: every step streams {w8 / 1e9:.2f} GB of weights, far larger than the 126 MB L2",
+                       "timing": "CUDA events on the launching stream, max over ranks"},
+            "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 8,
+                    "d2h_bytes_per_step": VOCAB * 4},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": peak_src,
+                         "kernel": "stream_gemv_kernel", "launches_per_step": model.launches_per_step - 1,
+                         "algorithmic_bytes_per_launch": total_bytes / (model.launches_per_step - 1),
+                         "avg_launch_us": step_ms * 1e3 / (model.launches_per_step - 1),
+                         "frac_of_nominal_8TBs": achieved / 8000.0},
+        }
+        if world == 1:
+            line["kernels"] = time_isolated_kernels(model)
+            if not args.no_cpu_baseline:
+                del model
+                torch.cuda.empty_cache()
+                line["cpu_baseline"] = cpu_reference(args.shape, 4, 1)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shape", default="7b", choices=list(SHAPES))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        sys.exit("--gpus N > 1 must be launched with torchrun (one rank per GPU)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,140 @@
+/*
+ * b200rwkv - C ABI of the sm_100a RWKV-4 uint8 inference kernels.
+ *
+ * Plain C: pointers and sizes only, no torch types.  Every pointer named "device"
+ * is a CUDA device pointer on the current device; `stream` is a cudaStream_t passed as
+ * void*.  Functions return 0 or a negative B200RWKV_E* code and never abort; the text
+ * of the last error on the calling thread is available from b200rwkv_last_error().
+ * Unless a comment says otherwise a function allocates nothing, launches
+ * asynchronously on `stream`, and the caller owns every buffer.
+ *
+ * "Reference" below is rwkvstic 3.0.0; paths are relative to its
+ * src/rwkvstic/agnostic/backends/ folder.
+ */
+#ifndef B200RWKV_H
+#define B200RWKV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200RWKV_OK 0
+#define B200RWKV_EINVAL (-1)   /* null/misaligned pointer, unsupported shape */
+#define B200RWKV_ECUDA (-2)    /* a CUDA runtime call failed */
+#define B200RWKV_ETIMEOUT (-3) /* a bounded device-side wait expired (see b200rwkv_status_*) */
+
+/* Bits a kernel may set in the caller's device status word (an int the caller zeroes). */
+#define B200RWKV_STATUS_WAIT_FULL 1    /* consumer gave up waiting for a weight stage   */
+#define B200RWKV_STATUS_WAIT_EMPTY 2   /* producer gave up waiting for a free ring slot */
+#define B200RWKV_STATUS_WAIT_PEER 4    /* layer-split handoff flag never arrived        */
+
+/*
+ * One quantised matrix, used as y = x @ W with W[k_in, n_out].  Bytes are stored
+ * output-major, `qt[n_out][k_in]` with k contiguous (the transpose of the reference's
+ * MM8.weight u8[in,out], modules/matmul.py:15-21), 16-byte aligned, k_in % 16 == 0.
+ *
+ *   y[n] = rx[n] * ( sum_k (x[k]*ry[k]) * qt[n][k] + half * sum_k x[k]*ry[k] )
+ *          + sum_k x[k]*my[k] + mx[n] * sum_k x[k]
+ *
+ * FASTQUANT (modules/matmul.py:26-40): ry = range, my = offset, rx = mx = NULL, half = 0.
+ * Two-axis scheme "(q+0.5)*ry*rx+my+mx": all four vectors, half = 0.5.
+ */
+typedef struct b200rwkv_matrix {
+  const uint8_t* qt; /* device u8 [n_out][k_in] */
+  const float* ry;   /* device f32 [k_in] */
+  const float* my;   /* device f32 [k_in] */
+  const float* rx;   /* device f32 [n_out] or NULL (= 1) */
+  const float* mx;   /* device f32 [n_out] or NULL (= 0) */
+  float half;
+  int32_t n_out;
+  int32_t k_in;
+} b200rwkv_matrix;
+
+/* Parameters of one RWKV-4 block (modules/block.py:7-50). All device f32 [n_embd]. */
+typedef struct b200rwkv_layer {
+  const float *ln1_w, *ln1_b, *ln2_w, *ln2_b;
+  const float *att_mix_k, *att_mix_v, *att_mix_r; /* time_mix_* (block.py:35-37) */
+  const float *ffn_mix_k, *ffn_mix_r;             /* block.py:46-47 */
+  const float* time_decay;                        /* w = -exp(raw time_decay) (block.py:41) */
+  const float* time_first;                        /* u, raw (block.py:39) */
+  b200rwkv_matrix att_key, att_value, att_receptance, att_output;
+  b200rwkv_matrix ffn_key, ffn_receptance, ffn_value;
+} b200rwkv_layer;
+
+/* A whole model (opt.py:25-58).  `layers` is a HOST array of n_layer entries. */
+typedef struct b200rwkv_model {
+  int32_t n_layer, n_embd, n_ffn, n_vocab;
+  const float* emb; /* device f32 [n_vocab][n_embd] */
+  const float *ln0_w, *ln0_b, *ln_out_w, *ln_out_b;
+  b200rwkv_matrix head;
+  const b200rwkv_layer* layers;
+} b200rwkv_model;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int b200rwkv_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* b200rwkv_last_error(void);
+
+/*
+ * uint8 GEMV, 1 to 3 matrices of equal k_in in one launch:  y_i = contract(mats[i], x[i]).
+ * Replaces rwkv::mm8_one / rwkv::mm8_three (cuda/wrapper.cpp:52-129, kernels
+ * cuda/operators32.cu:18-115) together with the offset term the reference adds on the
+ * host side (modules/matmul.py:58-62, :95-102).  x[i]: device f32 [k_in]; y[i]: device
+ * f32 [n_out_i], overwritten, or added to when `accumulate` is non-zero (the reference
+ * op accumulates onto a zero-filled y).  `status`: device int, may be NULL.
+ */
+int b200rwkv_gemv_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y,
+                     int accumulate, int* status, void* stream);
+
+/*
+ * WKV-4 recurrence, B independent streams x C channels, sequential over T
+ * (replaces rwkv::wkv_forward, cuda/wrapper.cpp:45-50 / cuda/operators.cu:6-44, and
+ * TorchWKV, modules/wkv.py:23-40).  k, v, y: device f32 [B][T][C]; w (= -exp(decay)),
+ * u: device f32 [C]; aa, bb, pp: device f32 [B][C] updated in place.
+ * convention 0: max-trick state (agnosticRwkv.py:68-103): sums are scaled by exp(-pp),
+ *               decay applied at the start of the next step; empty state (0, 0, -1e30).
+ * convention 1: the reference FASTQUANT state (modules/wkv.py:31-39): aa, bb already
+ *               multiplied by exp(w), pp untouched.  Computed with the same max-trick
+ *               arithmetic internally and converted on entry and exit.
+ */
+int b200rwkv_wkv_scan(int B, int T, int C, const float* w, const float* u, const float* k, const float* v,
+                      float* y, float* aa, float* bb, float* pp, int convention, void* stream);
+
+/*
+ * Host-only introspection of the GEMV launch geometry for reduction length k_in, `nmat`
+ * matrices, the largest n_out, and a GPU with `num_sms` SMs.  Fills
+ * out[0..9] = {chunks_per_thread, threads_per_row, rows_side_by_side, rows_per_thread_per_stage,
+ * ring_stages, stage_bytes, max_rows_per_cta, grid, shared_memory_bytes, consumer_threads}.
+ * Returns B200RWKV_EINVAL for an unsupported shape.  No counterpart in the reference (its
+ * launch shape is fixed: cuda/operators32.cu:86-115); used by tests and the roofline report.
+ */
+int b200rwkv_gemv_plan(int k_in, int nmat, int max_n_out, int num_sms, int64_t* out);
+
+/* Bytes of device scratch that b200rwkv_decode_step needs for this model. */
+size_t b200rwkv_decode_workspace_bytes(const b200rwkv_model* m);
+
+/*
+ * One decode step (T = 1) of the whole network for one stream: the fused replacement for
+ * myRWKV.forward (opt.py:61-76) with Block.forward (modules/block.py:56-102) at T == 1.
+ *   token     device int64[1]
+ *   state     device f32 [n_layer][5][n_embd], updated in place: rows 0/1 the att/ffn
+ *             token-shift carries (block.py:61-64, :85-88), rows 2..4 aa, bb, pp in the
+ *             max-trick convention; the empty state is (0,0,0,0,-1e30) as opt.py:31-32.
+ *   logits    device f32 [n_vocab], or NULL to skip ln_out + head (prompt tokens whose
+ *             logits nobody reads)
+ *   workspace device scratch of b200rwkv_decode_workspace_bytes(m), 256-byte aligned; its
+ *             first int is the status word the kernels OR error bits into.
+ * Launches 4*n_layer + 2 kernels chained by programmatic dependent launch; safe to
+ * capture in a CUDA graph.
+ */
+int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200RWKV_H */

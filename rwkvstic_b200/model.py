@@ -1,0 +1,293 @@
+"""Host-side mirror of the reference's FASTQUANT model object.
+
+``B200RWKV`` has the interface ``rwkvstic.rwkvMaster.RWKVMaster`` consumes
+(rwkvMaster.py:32-38, :71): ``forward(tokens, state) -> (logits, state)`` and an
+``emptyState`` attribute, with the same meaning as ``OptRWKV(...)`` from
+agnostic/backends/opt.py:15-119:
+
+* ``tokens``  int64 ``[T]`` (list, CPU or CUDA tensor).  T > 1 is sequence mode; the
+  logits are those of the last token (opt.py:71-73).
+* ``state``   ``[L,5,D]``; rows 0/1 are the att/ffn token-shift carries, rows 2..4 the
+  WKV accumulators, empty state ``(0,0,0,0,-1e30)`` exactly as opt.py:31-32.  It is
+  updated IN PLACE and returned, like the reference does (opt.py:68-69).  Runtime dtype
+  is fp32 (the reference uses fp64); the WKV rows use the max-trick convention of
+  agnosticRwkv.py:68-103 - ``state_to_reference`` / ``state_from_reference`` convert.
+
+All arithmetic happens in the CUDA library (``_lib``); this file only owns device
+memory, CUDA-graph capture and the call sequence.  There is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _lib
+from .quant import QuantMatrix, quantize_fastquant, quantize_two_axis
+from .synth import VOCAB, iter_synth_tensors
+
+MATRIX_KEYS = ("att.key", "att.value", "att.receptance", "att.output", "ffn.key", "ffn.receptance", "ffn.value")
+
+
+@dataclass
+class LayerWeights:
+    vec: Dict[str, torch.Tensor] = field(default_factory=dict)   # f32 [D] each
+    mat: Dict[str, QuantMatrix] = field(default_factory=dict)    # keyed by MATRIX_KEYS
+
+
+@dataclass
+class QuantizedWeights:
+    """Everything the kernels read, resident on one device."""
+    n_layer: int
+    n_embd: int
+    n_ffn: int
+    n_vocab: int
+    emb: torch.Tensor
+    ln0: Tuple[torch.Tensor, torch.Tensor]
+    ln_out: Tuple[torch.Tensor, torch.Tensor]
+    head: QuantMatrix
+    layers: List[LayerWeights]
+
+    def weight_bytes(self) -> int:
+        """uint8 matrix bytes one decode step streams (13*L*D^2 + V*D for F = 4D)."""
+        n = self.head.qt.numel()
+        for ly in self.layers:
+            n += sum(m.qt.numel() for m in ly.mat.values())
+        return n
+
+
+def _quantizer(scheme: str):
+    if scheme == "fastquant":
+        return quantize_fastquant
+    if scheme == "two_axis":
+        return quantize_two_axis
+    raise ValueError(f"unknown quantisation scheme {scheme!r}")
+
+
+def quantize_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], device, scheme: str = "fastquant",
+                     quant_device=None) -> QuantizedWeights:
+    """Build ``QuantizedWeights`` from (name, tensor) pairs with the reference checkpoint key
+    names (helpers/loadWeights.py:19-26, modules/block.py:13-47).  Consumes the iterable one
+    tensor at a time, so large shapes never need the fp32 checkpoint in memory."""
+    q = _quantizer(scheme)
+    dev = torch.device(device)
+    qdev = torch.device(quant_device) if quant_device is not None else None
+    layers: Dict[int, LayerWeights] = {}
+    top: Dict[str, torch.Tensor] = {}
+    head = None
+    f32 = lambda t: t.detach().reshape(-1).to(torch.float32).to(dev).contiguous()
+    for name, t in tensors:
+        if name.startswith("blocks."):
+            _, idx, rest = name.split(".", 2)
+            ly = layers.setdefault(int(idx), LayerWeights())
+            if rest.endswith(".weight") and rest[:-7] in MATRIX_KEYS:
+                w = t.detach().float()
+                ly.mat[rest[:-7]] = q(w.to(qdev) if qdev is not None else w).to(dev)
+            elif rest == "att.time_decay":
+                ly.vec[rest] = (-torch.exp(t.detach().double().reshape(-1))).to(torch.float32).to(dev).contiguous()
+            elif rest.startswith("ln0."):
+                top[rest] = f32(t)
+            else:
+                ly.vec[rest] = f32(t)
+        elif name == "head.weight":
+            w = t.detach().float()
+            head = q(w.to(qdev) if qdev is not None else w).to(dev)
+        elif name == "emb.weight":
+            top["emb"] = t.detach().to(torch.float32).to(dev).contiguous()
+        else:
+            top[name] = f32(t)
+    n_layer = len(layers)
+    ordered = [layers[i] for i in range(n_layer)]
+    D = ordered[0].mat["att.key"].k_in
+    F = ordered[0].mat["ffn.key"].n_out
+    return QuantizedWeights(n_layer=n_layer, n_embd=D, n_ffn=F, n_vocab=top["emb"].shape[0], emb=top["emb"],
+                            ln0=(top["ln0.weight"], top["ln0.bias"]),
+                            ln_out=(top["ln_out.weight"], top["ln_out.bias"]), head=head, layers=ordered)
+
+
+def state_to_reference(state: torch.Tensor, time_decay: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Convert a max-trick state to the reference FASTQUANT meaning (modules/wkv.py:31-39):
+    ``aa_ref = exp(w + pp) * aa``, same for bb; pp reported as the reference leaves it (-1e30)."""
+    out = state.detach().double().clone()
+    for i, w in enumerate(time_decay):
+        e = torch.exp(w.double().to(out.device) + out[..., i, 4, :])
+        out[..., i, 2, :] *= e
+        out[..., i, 3, :] *= e
+    out[..., 4, :] = float(torch.tensor(-1e30, dtype=torch.float32))
+    return out
+
+
+def state_from_reference(state: torch.Tensor, time_decay: Sequence[torch.Tensor]) -> torch.Tensor:
+    """Inverse of ``state_to_reference``: ``aa = aa_ref, pp = -w`` (empty rows stay empty)."""
+    out = state.detach().to(torch.float32).clone()
+    for i, w in enumerate(time_decay):
+        empty = (out[..., i, 2, :] == 0) & (out[..., i, 3, :] == 0)
+        out[..., i, 4, :] = torch.where(empty, torch.full_like(out[..., i, 4, :], -1e30), -w.float().to(out.device))
+    return out
+
+
+class B200RWKV:
+    """RWKV-4 with uint8 weights on one B200.  See the module docstring for the contract."""
+
+    RnnOnly = False  # sequence mode is supported (rwkvMaster.py:97 looks this up)
+
+    def __init__(self, weights: QuantizedWeights, use_graph: bool = True, copy_logits: bool = True):
+        self.w = weights
+        self.device = weights.emb.device
+        if self.device.type != "cuda":
+            raise RuntimeError("B200RWKV needs a CUDA device: the kernels are sm_100a only and there is no CPU path")
+        self._L = _lib.lib()
+        self.n_layer, self.n_embd, self.n_ffn, self.n_vocab = weights.n_layer, weights.n_embd, weights.n_ffn, weights.n_vocab
+        self.use_graph = use_graph
+        self.copy_logits = copy_logits
+        self.launches_per_step = 4 * self.n_layer + 2
+        self.time_decay = [ly.vec["att.time_decay"] for ly in weights.layers]
+        self.emptyState = torch.zeros(self.n_layer, 5, self.n_embd, dtype=torch.float32, device=self.device)
+        self.emptyState[:, 4] = -1e30
+        self._build_descriptor()
+        nbytes = int(self._L.b200rwkv_decode_workspace_bytes(C.byref(self._cmodel)))
+        self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._tok = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self._logits = torch.zeros(self.n_vocab, dtype=torch.float32, device=self.device)
+        self._graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self._seen: Dict[int, int] = {}
+        self.launch_count = 0  # kernels launched so far (for the benchmark's gpu_launches)
+
+    # ------------------------------------------------------------------ construction helpers
+    @classmethod
+    def from_checkpoint(cls, ck: Union[str, Dict[str, torch.Tensor]], device="cuda:0", scheme: str = "fastquant",
+                        **kw) -> "B200RWKV":
+        """From a ``.pth`` path or an in-memory dict with the reference key names.  Quantisation
+        runs on the CPU so the bytes are identical to the reference's (modules/matmul.py:26-40)."""
+        if isinstance(ck, str):
+            ck = torch.load(ck, map_location="cpu")
+        return cls(quantize_tensors(ck.items(), device, scheme), **kw)
+
+    @classmethod
+    def synthetic(cls, layers: int, embed: int, vocab: int = VOCAB, seed: int = 1234, device="cuda:0",
+                  scheme: str = "fastquant", **kw) -> "B200RWKV":
+        """Seeded random-init model generated and quantised on the device, matrix by matrix."""
+        gen = iter_synth_tensors(layers, embed, vocab, seed, device=str(device))
+        return cls(quantize_tensors(gen, device, scheme), **kw)
+
+    def _matrix(self, m: QuantMatrix) -> _lib.Matrix:
+        for t in (m.qt, m.ry, m.my):
+            assert t.is_contiguous() and t.device == self.device
+        assert m.qt.dtype == torch.uint8 and m.ry.dtype == torch.float32 and m.my.dtype == torch.float32
+        return _lib.Matrix(_lib.ptr(m.qt), _lib.ptr(m.ry), _lib.ptr(m.my), _lib.ptr(m.rx), _lib.ptr(m.mx),
+                           float(m.half), m.n_out, m.k_in)
+
+    def _build_descriptor(self) -> None:
+        w = self.w
+        self._clayers = (_lib.Layer * self.n_layer)()
+        for i, ly in enumerate(w.layers):
+            c = self._clayers[i]
+            v = ly.vec
+            c.ln1_w, c.ln1_b, c.ln2_w, c.ln2_b = (_lib.ptr(v[k]) for k in ("ln1.weight", "ln1.bias", "ln2.weight", "ln2.bias"))
+            c.att_mix_k, c.att_mix_v, c.att_mix_r = (_lib.ptr(v[k]) for k in ("att.time_mix_k", "att.time_mix_v", "att.time_mix_r"))
+            c.ffn_mix_k, c.ffn_mix_r = _lib.ptr(v["ffn.time_mix_k"]), _lib.ptr(v["ffn.time_mix_r"])
+            c.time_decay, c.time_first = _lib.ptr(v["att.time_decay"]), _lib.ptr(v["att.time_first"])
+            c.att_key, c.att_value, c.att_receptance, c.att_output = (self._matrix(ly.mat[k]) for k in MATRIX_KEYS[:4])
+            c.ffn_key, c.ffn_receptance, c.ffn_value = (self._matrix(ly.mat[k]) for k in MATRIX_KEYS[4:])
+        self._cmodel = _lib.Model(self.n_layer, self.n_embd, self.n_ffn, self.n_vocab, _lib.ptr(w.emb),
+                                  _lib.ptr(w.ln0[0]), _lib.ptr(w.ln0[1]), _lib.ptr(w.ln_out[0]), _lib.ptr(w.ln_out[1]),
+                                  self._matrix(w.head), C.cast(self._clayers, C.POINTER(_lib.Layer)))
+
+    # ------------------------------------------------------------------ one decode step
+    def _step_raw(self, tok_ptr: int, state_ptr: int, logits_ptr: Optional[int]) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(self._L.b200rwkv_decode_step(C.byref(self._cmodel), tok_ptr, state_ptr, logits_ptr,
+                                                self._ws.data_ptr(), self._ws.numel(), stream))
+
+    def _step(self, state: torch.Tensor, want_logits: bool) -> None:
+        """Run one step on the token in ``self._tok``; logits (if any) land in ``self._logits``."""
+        self.launch_count += self.launches_per_step - (0 if want_logits else 1)
+        lp = self._logits.data_ptr() if want_logits else None
+        if not self.use_graph:
+            self._step_raw(self._tok.data_ptr(), state.data_ptr(), lp)
+            return
+        key = (state.data_ptr(), want_logits)
+        g = self._graphs.get(key)
+        if g is None:
+            # Capture once a state buffer shows up for the second time (RWKVMaster.forward reuses
+            # one buffer for every token; loadContext clones per chunk and just runs eagerly).
+            n = self._seen.get(key, 0) + 1
+            self._seen[key] = n
+            if n < 2:
+                self._step_raw(self._tok.data_ptr(), state.data_ptr(), lp)
+                return
+            if len(self._graphs) >= 16:
+                self._graphs.clear()
+                self._seen.clear()
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(g):
+                self._step_raw(self._tok.data_ptr(), state.data_ptr(), lp)
+            self._graphs[key] = g
+        g.replay()
+
+    def check_status(self) -> None:
+        """Raise if any kernel reported an expired device-side wait (synchronises)."""
+        self._status_host.copy_(self._ws[:4].view(torch.int32))
+        bits = int(self._status_host[0])
+        if bits:
+            self._ws[:4].zero_()
+            raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+
+    # ------------------------------------------------------------------ public interface
+    def _own_state(self, state: torch.Tensor) -> torch.Tensor:
+        if (state.dtype == torch.float32 and state.device == self.device and state.is_contiguous()
+                and tuple(state.shape) == (self.n_layer, 5, self.n_embd)):
+            return state
+        if tuple(state.shape) != (self.n_layer, 5, self.n_embd):
+            raise ValueError(f"state must be [{self.n_layer},5,{self.n_embd}], got {tuple(state.shape)}")
+        return state.to(device=self.device, dtype=torch.float32).contiguous()
+
+    def forward(self, tokens, state: torch.Tensor):
+        """``(logits f32[V] on the device, state)`` - see the module docstring."""
+        if not torch.is_tensor(tokens):
+            tokens = torch.tensor(tokens if isinstance(tokens, (list, tuple)) else [tokens], dtype=torch.int64)
+        tokens = tokens.reshape(-1).to(torch.int64)
+        if tokens.numel() == 0:
+            raise ValueError("forward needs at least one token")
+        state = self._own_state(state)
+        with torch.cuda.device(self.device):
+            toks = tokens.to(self.device, non_blocking=True)
+            T = toks.numel()
+            for i in range(T):
+                self._tok.copy_(toks[i:i + 1], non_blocking=True)
+                self._step(state, want_logits=(i == T - 1))
+        return (self._logits.clone() if self.copy_logits else self._logits), state
+
+    __call__ = forward
+
+    def forward_batch(self, tokens: torch.Tensor, state: torch.Tensor):
+        """B independent streams: ``tokens [B]`` or ``[B,T]``, ``state [B,L,5,D]`` (in place).
+        Returns ``(logits [B,V], state)``.  Each stream's arithmetic is the single-stream path,
+        so results are bit-identical to B separate ``forward`` calls."""
+        tokens = tokens.reshape(tokens.shape[0], -1)
+        B = tokens.shape[0]
+        if state.dtype != torch.float32 or state.device != self.device or not state.is_contiguous():
+            raise ValueError("forward_batch needs a contiguous fp32 state on the model's device")
+        out = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device)
+        keep = self.copy_logits
+        self.copy_logits = False
+        try:
+            for b in range(B):
+                lg, _ = self.forward(tokens[b], state[b])
+                out[b].copy_(lg)
+        finally:
+            self.copy_logits = keep
+        return out, state
+
+    def empty_batch_state(self, B: int) -> torch.Tensor:
+        return self.emptyState.unsqueeze(0).repeat(B, 1, 1, 1).contiguous()
+
+    def to_reference_state(self, state: torch.Tensor) -> torch.Tensor:
+        return state_to_reference(state, self.time_decay)
+
+    def from_reference_state(self, state: torch.Tensor) -> torch.Tensor:
+        return state_from_reference(state.to(self.device), self.time_decay)

@@ -1,0 +1,75 @@
+"""Operator-level entry points over the C ABI, taking torch CUDA tensors.
+
+These mirror the reference's three custom ops (cuda/wrapper.cpp:45-129, called from
+modules/matmul.py:42-49, :70-80 and modules/wkv.py:18): a one- or three-matrix uint8
+GEMV and the WKV recurrence.  They validate, pass raw device pointers to the library and
+launch on torch's current stream.  No CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib
+from .quant import QuantMatrix
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _cmatrix(m: QuantMatrix) -> _lib.Matrix:
+    return _lib.Matrix(_lib.ptr(m.qt), _lib.ptr(m.ry), _lib.ptr(m.my), _lib.ptr(m.rx), _lib.ptr(m.mx),
+                       float(m.half), m.n_out, m.k_in)
+
+
+def gemv_u8(mats: Sequence[QuantMatrix], xs: Sequence[torch.Tensor], ys: Optional[Sequence[torch.Tensor]] = None,
+            accumulate: bool = False, status: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+    """``ys[i] = xs[i] @ W_i`` for 1..3 quantised matrices of equal k_in, one launch.
+
+    ``xs[i]`` fp32 ``[k_in]`` on the matrices' CUDA device; ``ys[i]`` fp32 ``[n_out_i]``
+    (allocated when omitted; with ``accumulate`` the result is added onto them, which is
+    what the reference ops do with their zero-filled ``y``)."""
+    n = len(mats)
+    if n < 1 or n > 3 or len(xs) != n:
+        raise ValueError("gemv_u8 takes 1..3 matrices and as many input vectors")
+    dev = mats[0].qt.device
+    if dev.type != "cuda":
+        raise RuntimeError("gemv_u8 needs CUDA tensors (no CPU path)")
+    if ys is None:
+        if accumulate:
+            raise ValueError("accumulate needs caller-provided outputs")
+        ys = [torch.empty(m.n_out, dtype=torch.float32, device=dev) for m in mats]
+    for m, x, y in zip(mats, xs, ys):
+        if x.dtype != torch.float32 or y.dtype != torch.float32 or not x.is_contiguous() or not y.is_contiguous():
+            raise ValueError("gemv_u8 needs contiguous fp32 vectors")
+        if x.numel() != m.k_in or y.numel() != m.n_out or x.device != dev or y.device != dev:
+            raise ValueError("gemv_u8 vector shape/device does not match its matrix")
+    cm = (_lib.Matrix * n)(*[_cmatrix(m) for m in mats])
+    cx = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+    cy = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200rwkv_gemv_u8(n, cm, cx, cy, int(accumulate), _lib.ptr(status), _stream(dev)))
+    return list(ys)
+
+
+def wkv_scan(w: torch.Tensor, u: torch.Tensor, k: torch.Tensor, v: torch.Tensor, aa: torch.Tensor,
+             bb: torch.Tensor, pp: torch.Tensor, convention: int = 0) -> torch.Tensor:
+    """WKV-4 over ``k, v [B,T,C]`` (or ``[T,C]``); ``aa, bb, pp [B,C]`` (or ``[C]``) updated in
+    place.  ``convention`` 0 = max-trick state, 1 = the reference FASTQUANT state."""
+    if k.dim() == 2:
+        k, v = k.unsqueeze(0), v.unsqueeze(0)
+    B, T, Cc = k.shape
+    for t in (w, u, k, v, aa, bb, pp):
+        if t.dtype != torch.float32 or not t.is_contiguous() or t.device.type != "cuda":
+            raise ValueError("wkv_scan needs contiguous fp32 CUDA tensors")
+    if aa.numel() != B * Cc or bb.numel() != B * Cc or pp.numel() != B * Cc or w.numel() != Cc or u.numel() != Cc:
+        raise ValueError("wkv_scan state/parameter shapes do not match k")
+    y = torch.empty_like(k)
+    with torch.cuda.device(k.device):
+        _lib.check(_lib.lib().b200rwkv_wkv_scan(B, T, Cc, w.data_ptr(), u.data_ptr(), k.data_ptr(), v.data_ptr(),
+                                                y.data_ptr(), aa.data_ptr(), bb.data_ptr(), pp.data_ptr(),
+                                                convention, _stream(k.device)))
+    return y

@@ -34,7 +34,7 @@ extern "C" {
 /*
  * One quantised matrix, used as y = x @ W with W[k_in, n_out].  Bytes are stored
  * output-major, `qt[n_out][k_in]` with k contiguous (the transpose of the reference's
- * MM8.weight u8[in,out], modules/matmul.py:15-21), 16-byte aligned, k_in % 16 == 0.
+ * MM8.weight u8[in,out], modules/matmul.py:15-21), 16-byte aligned, k_in % 128 == 0.
  *
  *   y[n] = rx[n] * ( sum_k (x[k]*ry[k]) * qt[n][k] + half * sum_k x[k]*ry[k] )
  *          + sum_k x[k]*my[k] + mx[n] * sum_k x[k]
@@ -79,16 +79,36 @@ int b200rwkv_version(void);
 /* Text of the last error raised on the calling thread ("" if none). */
 const char* b200rwkv_last_error(void);
 
+/* Bytes of device scratch b200rwkv_gemv_u8 needs for `nmat` matrices of reduction length k_in. */
+size_t b200rwkv_gemv_workspace_bytes(int k_in, int nmat);
+
 /*
- * uint8 GEMV, 1 to 3 matrices of equal k_in in one launch:  y_i = contract(mats[i], x[i]).
+ * uint8 GEMV, 1 to 3 matrices of equal k_in:  y_i = contract(mats[i], x[i]).
  * Replaces rwkv::mm8_one / rwkv::mm8_three (cuda/wrapper.cpp:52-129, kernels
  * cuda/operators32.cu:18-115) together with the offset term the reference adds on the
  * host side (modules/matmul.py:58-62, :95-102).  x[i]: device f32 [k_in]; y[i]: device
  * f32 [n_out_i], overwritten, or added to when `accumulate` is non-zero (the reference
- * op accumulates onto a zero-filled y).  `status`: device int, may be NULL.
+ * op accumulates onto a zero-filled y).  Two launches: a one-CTA kernel turns the x[i] into
+ * fixed-point digit planes, then the streaming kernel reads every weight byte once.
+ * `workspace`: device scratch of b200rwkv_gemv_workspace_bytes(k_in, nmat), 256-byte
+ * aligned; its first int is a status word the kernels OR B200RWKV_STATUS_* bits into (zero
+ * it once).  Calls that share a workspace must be ordered on one stream.
  */
 int b200rwkv_gemv_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y,
-                     int accumulate, int* status, void* stream);
+                     int accumulate, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * b200rwkv_gemv_u8 with a per-CTA phase timeline for profiling.  `trace`: device u64
+ * [1024][8], filled with %globaltimer nanoseconds.  Row c < grid (grid from
+ * b200rwkv_gemv_plan) belongs to CTA c of the streaming kernel: 0 kernel entry, 1 launch
+ * dependency resolved, 4 digit planes in shared memory (first weight stage may be consumed),
+ * 5 all rows done, 6 epilogue done, 7 producer issued its last bulk copy.  Row 1023 belongs to
+ * the preparation kernel: 0 entry, 1 dependency resolved, 2 layer-norm statistics done, 3 done.
+ * No counterpart in the reference.
+ */
+int b200rwkv_gemv_u8_traced(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y,
+                            int accumulate, void* workspace, size_t workspace_bytes, uint64_t* trace,
+                            void* stream);
 
 /*
  * WKV-4 recurrence, B independent streams x C channels, sequential over T
@@ -107,8 +127,9 @@ int b200rwkv_wkv_scan(int B, int T, int C, const float* w, const float* u, const
 /*
  * Host-only introspection of the GEMV launch geometry for reduction length k_in, `nmat`
  * matrices, the largest n_out, and a GPU with `num_sms` SMs.  Fills
- * out[0..9] = {chunks_per_thread, threads_per_row, rows_side_by_side, rows_per_thread_per_stage,
- * ring_stages, stage_bytes, max_rows_per_cta, grid, shared_memory_bytes, consumer_threads}.
+ * out[0..9] = {chunk_bytes (bytes of one row per ring stage), chunks_per_row, swizzle_bytes,
+ * rows_per_stage, ring_stages, stage_bytes, max_rows_per_cta (rounded up to 16), grid,
+ * shared_memory_bytes, consumer_threads}.
  * Returns B200RWKV_EINVAL for an unsupported shape.  No counterpart in the reference (its
  * launch shape is fixed: cuda/operators32.cu:86-115); used by tests and the roofline report.
  */
@@ -127,12 +148,21 @@ size_t b200rwkv_decode_workspace_bytes(const b200rwkv_model* m);
  *   logits    device f32 [n_vocab], or NULL to skip ln_out + head (prompt tokens whose
  *             logits nobody reads)
  *   workspace device scratch of b200rwkv_decode_workspace_bytes(m), 256-byte aligned; its
- *             first int is the status word the kernels OR error bits into.
- * Launches 4*n_layer + 2 kernels chained by programmatic dependent launch; safe to
- * capture in a CUDA graph.
+ *             first int is the status word the kernels OR error bits into (zero it once).
+ * Launches 8*n_layer + 3 kernels (per matrix group one activation-preparation CTA and one
+ * streaming GEMV grid) chained by programmatic dependent launch; safe to capture in a CUDA graph.
  */
 int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * b200rwkv_decode_step with the per-CTA phase timeline of every GEMV launch (profiling).
+ * `trace`: device u64 [4*n_layer + 1][1024][8]; GEMV launch i (in issue order: per layer key/value/
+ * receptance, attention output, ffn key+receptance, ffn value; then the head) and the preparation
+ * kernel in front of it fill trace[i] as described at b200rwkv_gemv_u8_traced.  No counterpart in the reference.
+ */
+int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
+                                void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream);
 
 #ifdef __cplusplus
 }

@@ -18,7 +18,8 @@ STATUS_WAIT_FULL, STATUS_WAIT_EMPTY, STATUS_WAIT_PEER = 1, 2, 4
 # Every symbol include/b200rwkv.h declares; tests check that the library exports all of them.
 EXPORTS = (
     "b200rwkv_version", "b200rwkv_last_error", "b200rwkv_gemv_u8", "b200rwkv_wkv_scan", "b200rwkv_gemv_plan",
-    "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step",
+    "b200rwkv_gemv_u8_traced", "b200rwkv_gemv_workspace_bytes",
+    "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step", "b200rwkv_decode_step_traced",
 )
 
 
@@ -63,7 +64,12 @@ def lib() -> C.CDLL:
     L.b200rwkv_last_error.restype = C.c_char_p
     L.b200rwkv_gemv_u8.restype = C.c_int
     L.b200rwkv_gemv_u8.argtypes = [C.c_int, C.POINTER(Matrix), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
-                                   C.c_int, C.c_void_p, C.c_void_p]
+                                   C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.b200rwkv_gemv_workspace_bytes.restype = C.c_size_t
+    L.b200rwkv_gemv_workspace_bytes.argtypes = [C.c_int, C.c_int]
+    L.b200rwkv_gemv_u8_traced.restype = C.c_int
+    L.b200rwkv_gemv_u8_traced.argtypes = [C.c_int, C.POINTER(Matrix), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                          C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
     L.b200rwkv_wkv_scan.restype = C.c_int
     L.b200rwkv_wkv_scan.argtypes = [C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 8 + [C.c_int, C.c_void_p]
     L.b200rwkv_gemv_plan.restype = C.c_int
@@ -73,6 +79,9 @@ def lib() -> C.CDLL:
     L.b200rwkv_decode_step.restype = C.c_int
     L.b200rwkv_decode_step.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_size_t, C.c_void_p]
+    L.b200rwkv_decode_step_traced.restype = C.c_int
+    L.b200rwkv_decode_step_traced.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_size_t, C.c_void_p, C.c_void_p]
     _lib = L
     return L
 
@@ -87,7 +96,7 @@ def ptr(t) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
-PLAN_FIELDS = ("chunks_per_thread", "threads_per_row", "rows_side_by_side", "rows_per_thread_per_stage",
+PLAN_FIELDS = ("chunk_bytes", "chunks_per_row", "swizzle_bytes", "rows_per_stage",
                "ring_stages", "stage_bytes", "max_rows_per_cta", "grid", "shared_memory_bytes", "consumer_threads")
 
 

@@ -34,14 +34,13 @@ static int device_sms() {
 }
 
 // ---------------------------------------------------------------------------------------- GEMV launch
-template <int KCH>
-static cudaError_t launch_kch(const GemvParams& P, const GemvPlan& plan, bool pdl, cudaStream_t stream) {
+static cudaError_t launch_planned(const GemvParams& P, const GemvPlan& plan, bool pdl, cudaStream_t stream) {
   static bool configured[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(stream_gemv_kernel<KCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    e = cudaFuncSetAttribute(stream_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
@@ -56,31 +55,92 @@ static cudaError_t launch_kch(const GemvParams& P, const GemvPlan& plan, bool pd
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, stream_gemv_kernel<KCH>, P);
+  return cudaLaunchKernelEx(&cfg, stream_gemv_kernel, P);
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Describe qt[N][K] to TMA as [K/128][N][128 bytes]; one box = [kc/128][16 rows][128 bytes], 128-byte swizzle.
+static bool encode_weight_map(CUtensorMap* map, const uint8_t* qt, int N, int K, int kc) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  const cuuint64_t gdim[3] = {128, cuuint64_t(N), cuuint64_t(K / 128)};
+  const cuuint64_t gstr[2] = {cuuint64_t(K), 128};
+  const cuuint32_t box[3] = {128, cuuint32_t(kTileRows), cuuint32_t(kc / 128)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(qt), gdim, gstr, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 cudaError_t launch_stream_gemv(GemvParams& P, int max_n, bool pdl, cudaStream_t stream, const char** why) {
   const int sms = device_sms();
   GemvPlan plan;
   if (sms <= 0 || !plan_gemv(P.K, P.nseg, max_n, sms, &plan)) {
-    *why = "unsupported GEMV shape (k_in must be a multiple of 16 and at most 40960; 1..3 matrices)";
+    *why = "unsupported GEMV shape (k_in must be a multiple of 128 and at most 65536; 1..3 matrices)";
     return cudaErrorInvalidValue;
   }
-  P.tpr = plan.tpr; P.rl = plan.rl; P.m = plan.m; P.log_m = plan.log_m;
-  P.stages = plan.stages; P.stage_bytes = plan.stage_bytes; P.rpc = plan.rpc;
-  *why = "kernel launch failed";
-  switch (plan.kch) {
-    case 1: return launch_kch<1>(P, plan, pdl, stream);
-    case 2: return launch_kch<2>(P, plan, pdl, stream);
-    case 3: return launch_kch<3>(P, plan, pdl, stream);
-    default: return launch_kch<4>(P, plan, pdl, stream);
+  P.kc = plan.kc; P.nchunks = plan.nchunks;
+  P.stages = plan.stages; P.stage_bytes = plan.stage_bytes; P.rpc16 = plan.rpc16;
+  for (int s = 0; s < P.nseg; ++s) {
+    if (!encode_weight_map(&P.tmap[s], P.seg[s].qt, P.seg[s].N, P.K, plan.kc)) {
+      *why = "cuTensorMapEncodeTiled failed for a weight matrix";
+      return cudaErrorInvalidValue;
+    }
   }
+  *why = "kernel launch failed";
+  return launch_planned(P, plan, pdl, stream);
+}
+
+cudaError_t launch_vector_prep(const PrepParams& P, bool pdl, cudaStream_t stream, const char** why) {
+  static bool configured[64];
+  *why = "vector_prep launch failed";
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(vector_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const size_t smem = prep_smem_bytes(P.K, P.nseg);
+  if (smem > 200 * 1024) {
+    *why = "unsupported shape: activation planes do not fit the preparation kernel's shared memory";
+    return cudaErrorInvalidValue;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(kPrepThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, vector_prep_kernel, P);
 }
 
 static int check_matrix(const b200rwkv_matrix& m, const char* name) {
   if (!m.qt || !m.ry || !m.my) return fail(B200RWKV_EINVAL, "%s: null qt/ry/my", name);
-  if (m.n_out <= 0 || m.k_in <= 0 || (m.k_in % 16) != 0)
-    return fail(B200RWKV_EINVAL, "%s: n_out=%d k_in=%d (k_in must be a positive multiple of 16)", name, m.n_out, m.k_in);
+  if (m.n_out <= 0 || m.k_in <= 0 || (m.k_in % 128) != 0)
+    return fail(B200RWKV_EINVAL, "%s: n_out=%d k_in=%d (k_in must be a positive multiple of 128)", name, m.n_out, m.k_in);
   if (!aligned16(m.qt) || !aligned16(m.ry) || !aligned16(m.my))
     return fail(B200RWKV_EINVAL, "%s: qt/ry/my must be 16-byte aligned", name);
   return B200RWKV_OK;
@@ -88,8 +148,22 @@ static int check_matrix(const b200rwkv_matrix& m, const char* name) {
 
 static void fill_seg(GemvSeg& s, const b200rwkv_matrix& m) {
   memset(&s, 0, sizeof(s));
-  s.qt = m.qt; s.ry = m.ry; s.my = m.my; s.rx = m.rx; s.mx = m.mx;
+  s.qt = m.qt; s.rx = m.rx; s.mx = m.mx;
   s.half = m.half; s.N = m.n_out; s.act = ACT_NONE;
+}
+
+constexpr int kNextPrefetchBytes = 256 * 1024;  // per CTA; x147 CTAs = 37 MB of the 126 MB L2
+
+// Tell launch P which matrices the following launch streams (same k_in for all of them).
+static void set_next(GemvParams& P, const b200rwkv_matrix* const* next, int n) {
+  int pf = kNextPrefetchBytes;
+  if (const char* e = getenv("B200RWKV_PREFETCH_KB")) pf = atoi(e) * 1024;  // TEMP experiment
+  P.next_nseg = n; P.next_k = n > 0 ? next[0]->k_in : 0; P.next_prefetch = n > 0 ? pf : 0;
+  for (int i = 0; i < n; ++i) { P.next_qt[i] = next[i]->qt; P.next_n[i] = next[i]->n_out; }
+}
+
+static void fill_prep_seg(PrepSeg& s, const b200rwkv_matrix& m, const float* mix, const float* xin) {
+  s.ry = m.ry; s.my = m.my; s.mix = mix; s.xin = xin;
 }
 
 // ---------------------------------------------------------------------------------------- small kernels
@@ -161,9 +235,13 @@ wkv_scan_kernel(int B, int T, int C, const float* __restrict__ w, const float* _
   }
 }
 
+constexpr size_t kTraceStride = 1024 * 8;  // u64 slots per GEMV launch in a decode-step trace
+
 struct Workspace {
   int* status;
-  float *xa, *xb, *rwkv, *s_att, *s_ffn, *rf, *kk;
+  float *xa, *xb, *rwkv, *rf, *kk;
+  unsigned char* planes;
+  SegScalars* scal;
   size_t bytes;
 };
 
@@ -179,12 +257,17 @@ static Workspace carve(const b200rwkv_model* m, void* base) {
   w.xa = reinterpret_cast<float*>(take(D));
   w.xb = reinterpret_cast<float*>(take(D));
   w.rwkv = reinterpret_cast<float*>(take(D));
-  w.s_att = reinterpret_cast<float*>(take(D));
-  w.s_ffn = reinterpret_cast<float*>(take(D));
   w.rf = reinterpret_cast<float*>(take(D));
   w.kk = reinterpret_cast<float*>(take(F));
+  w.planes = reinterpret_cast<unsigned char*>(take(3 * D > F ? 3 * D : F));  // 4*K bytes per matrix
+  w.scal = reinterpret_cast<SegScalars*>(take(sizeof(SegScalars) * kMaxSeg));
   w.bytes = off;
   return w;
+}
+
+// Scratch of the stand-alone GEMV entry point: [status 256 B][planes nmat*4*K][scalars].
+static size_t gemv_workspace_bytes(int k_in, int nmat) {
+  return 256 + align256(size_t(nmat) * 4 * k_in) + align256(sizeof(SegScalars) * kMaxSeg);
 }
 
 }  // namespace b200
@@ -197,27 +280,59 @@ int b200rwkv_version(void) { return 100; }
 
 const char* b200rwkv_last_error(void) { return g_err; }
 
-int b200rwkv_gemv_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y, int accumulate,
-                     int* status, void* stream) {
-  if (nmat < 1 || nmat > kMaxSeg || !mats || !x || !y) return fail(B200RWKV_EINVAL, "gemv_u8: nmat=%d or null argument", nmat);
+static int gemv_u8_impl(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y, int accumulate,
+                        void* workspace, size_t workspace_bytes, unsigned long long* trace, void* stream) {
+  if (nmat < 1 || nmat > kMaxSeg || !mats || !x || !y || !workspace)
+    return fail(B200RWKV_EINVAL, "gemv_u8: nmat=%d or null argument", nmat);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(B200RWKV_EINVAL, "gemv_u8: workspace must be 256-byte aligned");
   GemvParams P;
+  PrepParams Q;
   memset(&P, 0, sizeof(P));
+  memset(&Q, 0, sizeof(Q));
   int max_n = 0;
   for (int i = 0; i < nmat; ++i) {
     if (int rc = check_matrix(mats[i], "gemv_u8 matrix")) return rc;
     if (mats[i].k_in != mats[0].k_in) return fail(B200RWKV_EINVAL, "gemv_u8: matrices must share k_in");
     if (!x[i] || !y[i] || !aligned16(x[i])) return fail(B200RWKV_EINVAL, "gemv_u8: x/y null or x not 16-byte aligned");
     fill_seg(P.seg[i], mats[i]);
-    P.seg[i].xin = x[i];
     P.seg[i].out = y[i];
+    fill_prep_seg(Q.seg[i], mats[i], nullptr, x[i]);
     if (mats[i].n_out > max_n) max_n = mats[i].n_out;
   }
-  P.nseg = nmat; P.K = mats[0].k_in; P.pro = PRO_VEC; P.epi = EPI_GENERIC; P.accumulate = accumulate ? 1 : 0;
-  P.status = status;
+  const int K = mats[0].k_in;
+  if (workspace_bytes < gemv_workspace_bytes(K, nmat))
+    return fail(B200RWKV_EINVAL, "gemv_u8: workspace %zu < %zu bytes", workspace_bytes, gemv_workspace_bytes(K, nmat));
+  char* wsb = static_cast<char*>(workspace);
+  int* status = reinterpret_cast<int*>(wsb);
+  unsigned char* planes = reinterpret_cast<unsigned char*>(wsb + 256);
+  SegScalars* scal = reinterpret_cast<SegScalars*>(wsb + 256 + align256(size_t(nmat) * 4 * K));
+  Q.nseg = nmat; Q.K = K; Q.ln = 0; Q.planes = planes; Q.scal = scal;
+  Q.trace = trace ? trace + 1023 * 8 : nullptr;
+  P.nseg = nmat; P.K = K; P.epi = EPI_GENERIC; P.accumulate = accumulate ? 1 : 0;
+  P.planes = planes; P.scal = scal; P.status = status; P.trace = trace;
   const char* why = "";
-  cudaError_t e = launch_stream_gemv(P, max_n, false, static_cast<cudaStream_t>(stream), &why);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_vector_prep(Q, false, s, &why);
+  if (e == cudaSuccess) e = launch_stream_gemv(P, max_n, true, s, &why);
   if (e != cudaSuccess) return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "gemv_u8: %s (%s)", why, cudaGetErrorString(e));
   return B200RWKV_OK;
+}
+
+size_t b200rwkv_gemv_workspace_bytes(int k_in, int nmat) {
+  if (k_in <= 0 || nmat < 1 || nmat > kMaxSeg) return 0;
+  return gemv_workspace_bytes(k_in, nmat);
+}
+
+int b200rwkv_gemv_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y, int accumulate,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  return gemv_u8_impl(nmat, mats, x, y, accumulate, workspace, workspace_bytes, nullptr, stream);
+}
+
+int b200rwkv_gemv_u8_traced(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y,
+                            int accumulate, void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream) {
+  if (!trace) return fail(B200RWKV_EINVAL, "gemv_u8_traced: null trace buffer");
+  return gemv_u8_impl(nmat, mats, x, y, accumulate, workspace, workspace_bytes,
+                      reinterpret_cast<unsigned long long*>(trace), stream);
 }
 
 int b200rwkv_wkv_scan(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,
@@ -239,7 +354,7 @@ int b200rwkv_gemv_plan(int k_in, int nmat, int max_n_out, int num_sms, int64_t* 
   GemvPlan p;
   if (!out || num_sms <= 0 || !plan_gemv(k_in, nmat, max_n_out, num_sms, &p))
     return fail(B200RWKV_EINVAL, "gemv_plan: unsupported shape k_in=%d nmat=%d n_out=%d sms=%d", k_in, nmat, max_n_out, num_sms);
-  const int64_t v[10] = {p.kch, p.tpr, p.rl, p.m, p.stages, p.stage_bytes, p.rpc, p.grid, (int64_t)p.smem, kConsumers};
+  const int64_t v[10] = {p.kc, p.nchunks, 128, kTileRows, p.stages, p.stage_bytes, p.rpc16, p.grid, (int64_t)p.smem, kConsumers};
   for (int i = 0; i < 10; ++i) out[i] = v[i];
   return B200RWKV_OK;
 }
@@ -249,13 +364,13 @@ size_t b200rwkv_decode_workspace_bytes(const b200rwkv_model* m) {
   return carve(m, nullptr).bytes;
 }
 
-int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* state, float* logits, void* workspace,
-                         size_t workspace_bytes, void* stream) {
+static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float* state, float* logits, void* workspace,
+                            size_t workspace_bytes, unsigned long long* trace, void* stream) {
   if (!m || !token || !state || !workspace || !m->layers || !m->emb)
     return fail(B200RWKV_EINVAL, "decode_step: null argument");
   const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab, L = m->n_layer;
-  if (D <= 0 || (D % 16) != 0 || F <= 0 || (F % 16) != 0 || V <= 0 || L <= 0)
-    return fail(B200RWKV_EINVAL, "decode_step: n_embd=%d n_ffn=%d must be positive multiples of 16", D, F);
+  if (D <= 0 || (D % 128) != 0 || F <= 0 || (F % 128) != 0 || V <= 0 || L <= 0)
+    return fail(B200RWKV_EINVAL, "decode_step: n_embd=%d n_ffn=%d must be positive multiples of 128", D, F);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || !aligned16(state))
     return fail(B200RWKV_EINVAL, "decode_step: workspace must be 256-byte and state 16-byte aligned");
   Workspace ws = carve(m, workspace);
@@ -263,6 +378,8 @@ int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* s
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const char* why = "";
   cudaError_t e;
+  int li = 0;  // GEMV launch index, selects the slice of the optional trace buffer
+  auto trace_slice = [&]() -> unsigned long long* { return trace ? trace + size_t(li++) * kTraceStride : nullptr; };
 
   {  // embedding gather + ln0, chained like every other launch
     cudaLaunchConfig_t cfg;
@@ -290,50 +407,103 @@ int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* s
                     chk[i]->k_in, want_n[i], want_k[i]);
     }
     GemvParams P;
-    // 1. ln1 + token-shift mix -> key/value/receptance -> WKV state update -> sigmoid(r)*wkv
+    PrepParams Q;
+    // 1. ln1 + token-shift mix (carry = state row 0) -> key/value/receptance -> WKV update -> sigmoid(r)*wkv
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.att_key, ly.att_mix_k, nullptr);
+    fill_prep_seg(Q.seg[1], ly.att_value, ly.att_mix_v, nullptr);
+    fill_prep_seg(Q.seg[2], ly.att_receptance, ly.att_mix_r, nullptr);
+    Q.nseg = 3; Q.K = D; Q.ln = 1; Q.ln_x = ws.xa; Q.ln_w = ly.ln1_w; Q.ln_b = ly.ln1_b; Q.shift = st;
+    Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
+    if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
-    fill_seg(P.seg[0], ly.att_key);        P.seg[0].mix = ly.att_mix_k;
-    fill_seg(P.seg[1], ly.att_value);      P.seg[1].mix = ly.att_mix_v;
-    fill_seg(P.seg[2], ly.att_receptance); P.seg[2].mix = ly.att_mix_r;
-    P.nseg = 3; P.K = D; P.pro = PRO_LNMIX; P.ln_x = ws.xa; P.ln_w = ly.ln1_w; P.ln_b = ly.ln1_b;
-    P.shift_in = st; P.shift_out = ws.s_att;
+    fill_seg(P.seg[0], ly.att_key); fill_seg(P.seg[1], ly.att_value); fill_seg(P.seg[2], ly.att_receptance);
+    P.nseg = 3; P.K = D; P.planes = ws.planes; P.scal = ws.scal;
     P.epi = EPI_WKV; P.wkv_w = ly.time_decay; P.wkv_u = ly.time_first;
     P.aa = st + 2 * size_t(D); P.bb = st + 3 * size_t(D); P.pp = st + 4 * size_t(D); P.wkv_out = ws.rwkv;
-    P.status = ws.status;
+    { const b200rwkv_matrix* nx[1] = {&ly.att_output}; set_next(P, nx, 1); }
+    P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, D, true, s, &why)) != cudaSuccess) goto launch_failed;
-    // 2. attention output projection + residual; commits the att token-shift carry
+    // 2. attention output projection + residual
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.att_output, nullptr, ws.rwkv);
+    Q.nseg = 1; Q.K = D; Q.planes = ws.planes; Q.scal = ws.scal;
+    Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
+    if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
-    fill_seg(P.seg[0], ly.att_output); P.seg[0].xin = ws.rwkv; P.seg[0].out = ws.xb; P.seg[0].res = ws.xa;
-    P.nseg = 1; P.K = D; P.pro = PRO_VEC; P.epi = EPI_GENERIC;
-    P.commit_src = ws.s_att; P.commit_dst = st; P.commit_n = D; P.status = ws.status;
+    fill_seg(P.seg[0], ly.att_output); P.seg[0].out = ws.xb; P.seg[0].res = ws.xa;
+    P.nseg = 1; P.K = D; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
+    { const b200rwkv_matrix* nx[2] = {&ly.ffn_key, &ly.ffn_receptance}; set_next(P, nx, 2); }
+    P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, D, true, s, &why)) != cudaSuccess) goto launch_failed;
-    // 3. ln2 + token-shift mix -> ffn key (relu^2) and ffn receptance (sigmoid)
+    // 3. ln2 + token-shift mix (carry = state row 1) -> ffn key (relu^2) and ffn receptance (sigmoid)
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.ffn_key, ly.ffn_mix_k, nullptr);
+    fill_prep_seg(Q.seg[1], ly.ffn_receptance, ly.ffn_mix_r, nullptr);
+    Q.nseg = 2; Q.K = D; Q.ln = 1; Q.ln_x = ws.xb; Q.ln_w = ly.ln2_w; Q.ln_b = ly.ln2_b; Q.shift = st + size_t(D);
+    Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
+    if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
-    fill_seg(P.seg[0], ly.ffn_key);        P.seg[0].mix = ly.ffn_mix_k; P.seg[0].act = ACT_RELUSQ;  P.seg[0].out = ws.kk;
-    fill_seg(P.seg[1], ly.ffn_receptance); P.seg[1].mix = ly.ffn_mix_r; P.seg[1].act = ACT_SIGMOID; P.seg[1].out = ws.rf;
-    P.nseg = 2; P.K = D; P.pro = PRO_LNMIX; P.ln_x = ws.xb; P.ln_w = ly.ln2_w; P.ln_b = ly.ln2_b;
-    P.shift_in = st + size_t(D); P.shift_out = ws.s_ffn; P.epi = EPI_GENERIC; P.status = ws.status;
+    fill_seg(P.seg[0], ly.ffn_key);        P.seg[0].act = ACT_RELUSQ;  P.seg[0].out = ws.kk;
+    fill_seg(P.seg[1], ly.ffn_receptance); P.seg[1].act = ACT_SIGMOID; P.seg[1].out = ws.rf;
+    P.nseg = 2; P.K = D; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
+    { const b200rwkv_matrix* nx[1] = {&ly.ffn_value}; set_next(P, nx, 1); }
+    P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, F > D ? F : D, true, s, &why)) != cudaSuccess) goto launch_failed;
-    // 4. ffn value projection, gated by the receptance, + residual; commits the ffn carry
+    // 4. ffn value projection, gated by the receptance, + residual
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.ffn_value, nullptr, ws.kk);
+    Q.nseg = 1; Q.K = F; Q.planes = ws.planes; Q.scal = ws.scal;
+    Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
+    if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
-    fill_seg(P.seg[0], ly.ffn_value); P.seg[0].xin = ws.kk; P.seg[0].out = ws.xa; P.seg[0].res = ws.xb; P.seg[0].gate = ws.rf;
-    P.nseg = 1; P.K = F; P.pro = PRO_VEC; P.epi = EPI_GENERIC;
-    P.commit_src = ws.s_ffn; P.commit_dst = st + size_t(D); P.commit_n = D; P.status = ws.status;
+    fill_seg(P.seg[0], ly.ffn_value); P.seg[0].out = ws.xa; P.seg[0].res = ws.xb; P.seg[0].gate = ws.rf;
+    P.nseg = 1; P.K = F; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
+    if (l + 1 < L) {
+      const b200rwkv_layer& nl = m->layers[l + 1];
+      const b200rwkv_matrix* nx[3] = {&nl.att_key, &nl.att_value, &nl.att_receptance};
+      set_next(P, nx, 3);
+    } else if (logits) {
+      const b200rwkv_matrix* nx[1] = {&m->head};
+      set_next(P, nx, 1);
+    }
+    P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, D, true, s, &why)) != cudaSuccess) goto launch_failed;
   }
   if (logits) {
     if (int rc = check_matrix(m->head, "decode_step head")) return rc;
     if (m->head.n_out != V || m->head.k_in != D) return fail(B200RWKV_EINVAL, "decode_step: head is %dx%d", m->head.n_out, m->head.k_in);
     GemvParams P;
+    PrepParams Q;
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], m->head, nullptr, nullptr);
+    Q.nseg = 1; Q.K = D; Q.ln = 1; Q.ln_x = ws.xa; Q.ln_w = m->ln_out_w; Q.ln_b = m->ln_out_b;
+    Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
+    if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_seg(P.seg[0], m->head); P.seg[0].out = logits;
-    P.nseg = 1; P.K = D; P.pro = PRO_LNMIX; P.ln_x = ws.xa; P.ln_w = m->ln_out_w; P.ln_b = m->ln_out_b;
-    P.epi = EPI_GENERIC; P.status = ws.status;
+    P.nseg = 1; P.K = D; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
+    {  // the next decode step starts with layer 0's key/value/receptance
+      const b200rwkv_matrix* nx[3] = {&m->layers[0].att_key, &m->layers[0].att_value, &m->layers[0].att_receptance};
+      set_next(P, nx, 3);
+    }
+    P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, V, true, s, &why)) != cudaSuccess) goto launch_failed;
   }
   return B200RWKV_OK;
 launch_failed:
   return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "decode_step: %s (%s)", why, cudaGetErrorString(e));
+}
+
+int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* state, float* logits, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  return decode_step_impl(m, token, state, logits, workspace, workspace_bytes, nullptr, stream);
+}
+
+int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
+                                void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream) {
+  if (!trace) return fail(B200RWKV_EINVAL, "decode_step_traced: null trace buffer");
+  return decode_step_impl(m, token, state, logits, workspace, workspace_bytes, reinterpret_cast<unsigned long long*>(trace), stream);
 }
 
 }  // extern "C"

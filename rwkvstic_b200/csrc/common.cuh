@@ -94,6 +94,21 @@ __device__ __forceinline__ uint32_t dp4a_uu(uint32_t q, uint32_t x, uint32_t acc
   return r;
 }
 
+// Loads whose ISSUE POINT matters (they are placed early so that their latency hides behind other
+// work).  volatile asm keeps them where they are written relative to the barrier / dependency
+// instructions; a plain or __ldg load may legally be sunk to its first use.
+// ld_param_v4: read-only data no kernel writes.  ld_act_v4: data an earlier kernel produced (L2 only).
+__device__ __forceinline__ float4 ld_param_v4(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.nc.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float4 ld_act_v4(const float4* p) {
+  float4 v;
+  asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -142,7 +142,7 @@ class B200RWKV:
         self.n_layer, self.n_embd, self.n_ffn, self.n_vocab = weights.n_layer, weights.n_embd, weights.n_ffn, weights.n_vocab
         self.use_graph = use_graph
         self.copy_logits = copy_logits
-        self.launches_per_step = 4 * self.n_layer + 2
+        self.launches_per_step = 8 * self.n_layer + 3
         self.time_decay = [ly.vec["att.time_decay"] for ly in weights.layers]
         self.emptyState = torch.zeros(self.n_layer, 5, self.n_embd, dtype=torch.float32, device=self.device)
         self.emptyState[:, 4] = -1e30
@@ -204,7 +204,7 @@ class B200RWKV:
 
     def _step(self, state: torch.Tensor, want_logits: bool) -> None:
         """Run one step on the token in ``self._tok``; logits (if any) land in ``self._logits``."""
-        self.launch_count += self.launches_per_step - (0 if want_logits else 1)
+        self.launch_count += self.launches_per_step - (0 if want_logits else 2)
         lp = self._logits.data_ptr() if want_logits else None
         if not self.use_graph:
             self._step_raw(self._tok.data_ptr(), state.data_ptr(), lp)
@@ -228,6 +228,20 @@ class B200RWKV:
                 self._step_raw(self._tok.data_ptr(), state.data_ptr(), lp)
             self._graphs[key] = g
         g.replay()
+
+    def trace_step(self, token: int, state: torch.Tensor) -> torch.Tensor:
+        """Profiling: run one eager decode step and return the phase timeline, an int64 CPU tensor
+        ``[4L+1 launches, 1024, 8]`` of %globaltimer nanoseconds: rows < grid are the GEMV CTAs, row 1023
+        the preparation kernel (see b200rwkv_gemv_u8_traced)."""
+        n = 4 * self.n_layer + 1
+        trace = torch.zeros(n, 1024, 8, dtype=torch.int64, device=self.device)
+        self._tok.fill_(int(token))
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(self._L.b200rwkv_decode_step_traced(C.byref(self._cmodel), self._tok.data_ptr(), state.data_ptr(),
+                                                       self._logits.data_ptr(), self._ws.data_ptr(), self._ws.numel(),
+                                                       trace.data_ptr(), stream))
+        torch.cuda.synchronize(self.device)
+        return trace.cpu()
 
     def check_status(self) -> None:
         """Raise if any kernel reported an expired device-side wait (synchronises)."""

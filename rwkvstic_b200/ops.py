@@ -25,13 +25,29 @@ def _cmatrix(m: QuantMatrix) -> _lib.Matrix:
                        float(m.half), m.n_out, m.k_in)
 
 
+_workspaces = {}
+
+
+def gemv_workspace(device, k_in: int, nmat: int) -> torch.Tensor:
+    """Zeroed scratch for ``gemv_u8`` (cached per device and size; calls sharing it must be ordered
+    on one stream).  Its first int32 is the kernels' status word."""
+    n = int(_lib.lib().b200rwkv_gemv_workspace_bytes(k_in, nmat))
+    key = (str(device), n)
+    if key not in _workspaces:
+        _workspaces[key] = torch.zeros(n, dtype=torch.uint8, device=device)
+    return _workspaces[key]
+
+
 def gemv_u8(mats: Sequence[QuantMatrix], xs: Sequence[torch.Tensor], ys: Optional[Sequence[torch.Tensor]] = None,
-            accumulate: bool = False, status: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+            accumulate: bool = False, workspace: Optional[torch.Tensor] = None,
+            trace: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
     """``ys[i] = xs[i] @ W_i`` for 1..3 quantised matrices of equal k_in, one launch.
 
     ``xs[i]`` fp32 ``[k_in]`` on the matrices' CUDA device; ``ys[i]`` fp32 ``[n_out_i]``
     (allocated when omitted; with ``accumulate`` the result is added onto them, which is
-    what the reference ops do with their zero-filled ``y``)."""
+    what the reference ops do with their zero-filled ``y``).  ``trace``: optional int64
+    ``[1024, 8]`` CUDA tensor that receives the per-CTA phase timeline (profiling).
+    ``workspace``: scratch from ``gemv_workspace`` (a cached one is used when omitted)."""
     n = len(mats)
     if n < 1 or n > 3 or len(xs) != n:
         raise ValueError("gemv_u8 takes 1..3 matrices and as many input vectors")
@@ -50,8 +66,15 @@ def gemv_u8(mats: Sequence[QuantMatrix], xs: Sequence[torch.Tensor], ys: Optiona
     cm = (_lib.Matrix * n)(*[_cmatrix(m) for m in mats])
     cx = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
     cy = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    if workspace is None:
+        workspace = gemv_workspace(dev, mats[0].k_in, n)
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().b200rwkv_gemv_u8(n, cm, cx, cy, int(accumulate), _lib.ptr(status), _stream(dev)))
+        if trace is None:
+            _lib.check(_lib.lib().b200rwkv_gemv_u8(n, cm, cx, cy, int(accumulate), workspace.data_ptr(),
+                                                   workspace.numel(), _stream(dev)))
+        else:
+            _lib.check(_lib.lib().b200rwkv_gemv_u8_traced(n, cm, cx, cy, int(accumulate), workspace.data_ptr(),
+                                                          workspace.numel(), trace.data_ptr(), _stream(dev)))
     return list(ys)
 
 

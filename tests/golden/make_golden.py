@@ -17,7 +17,7 @@ building blocks on small seeded inputs.
 
 Outputs:
   ops_small.npz     per-op vectors (quantiser, mm8, layernorm, wkv, one Block)
-  model_tiny.npz    L=2 D=64 V=257 model: sequence mode and token-by-token
+  model_tiny.npz    L=2 D=128 V=257 model: sequence mode and token-by-token
   model_169m.npz    BASELINE config 0: L=12 D=768 V=50277, 32 prompt + 64 greedy tokens
 """
 from __future__ import annotations
@@ -120,7 +120,7 @@ def ops_small():
 
 
 def model_tiny():
-    ck = synth_checkpoint(2, 64, vocab=257, seed=31)
+    ck = synth_checkpoint(2, 128, vocab=257, seed=31)
     model = load_reference_model(ck)
     toks = synth_tokens(9, seed=5, vocab=257)
     # sequence mode in one call

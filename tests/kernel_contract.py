@@ -4,7 +4,7 @@ Not the oracle (that is ``oracle/fastquant_oracle.py``, the reference's algorith
 fallback (the product never imports this).  It predicts what the kernels compute so that
 
 * the integer part of the GEMV can be checked bit-for-bit on the GPU (``fixed_point_gemv``
-  reproduces the 24-bit fixed-point planes and the exact integer dot product), and
+  reproduces the 24-bit fixed-point digits and the exact integer dot product), and
 * the accuracy of the fp32 / fixed-point design against the reference (fp64 vectors, fp32
   matmul) can be measured on the CPU, where the GPU is not available.
 """
@@ -15,7 +15,7 @@ import torch
 
 from rwkvstic_b200.quant import QuantMatrix
 
-QMAX = np.float32(8388352.0)
+QMAX = np.float32(8355000.0)
 
 
 def fixed_point_gemv(x: torch.Tensor, m: QuantMatrix, with_affine: bool = True) -> torch.Tensor:

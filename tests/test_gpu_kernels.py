@@ -31,17 +31,17 @@ def run_gemv(mats, xs, accumulate=False, ys=None):
             b[32:32 + m.n_out] = ys[i].to(DEV)
         bufs.append(b)
         views.append(b[32:32 + m.n_out])
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ops.gemv_u8([m.to(DEV) for m in mats], [x.to(DEV) for x in xs], views, accumulate=accumulate, status=status)
+    ws = ops.gemv_workspace(DEV, mats[0].k_in, len(mats))
+    ops.gemv_u8([m.to(DEV) for m in mats], [x.to(DEV) for x in xs], views, accumulate=accumulate, workspace=ws)
     torch.cuda.synchronize()
-    assert int(status.item()) == 0
+    assert int(ws[:4].view(torch.int32).item()) == 0        # no device-side wait expired
     for b in bufs:
         assert bool((b[:32] == CANARY).all()) and bool((b[-32:] == CANARY).all())
     return [v.cpu() for v in views]
 
 
 # (n_out, k_in): ragged small shapes, every RWKV-4 family shape incl. the 7B/14B full sizes
-SHAPES = [(80, 48), (1, 16), (257, 768), (3072, 768), (768, 3072), (2048, 2048), (2560, 2560), (521, 10240),
+SHAPES = [(80, 128), (1, 128), (19, 384), (257, 768), (3072, 768), (768, 3072), (2048, 2048), (2560, 2560), (521, 10240),
           (4096, 4096), (16384, 4096), (4096, 16384), (5120, 5120), (1031, 20480), (50277, 4096)]
 
 
@@ -54,7 +54,7 @@ def test_gemv_integer_part_is_bit_exact(n, k):
     assert torch.equal(got, want)
 
 
-@pytest.mark.parametrize("n,k", [(80, 48), (3072, 768), (4096, 4096), (4096, 16384), (50277, 768)])
+@pytest.mark.parametrize("n,k", [(80, 128), (3072, 768), (4096, 4096), (4096, 16384), (50277, 768)])
 def test_gemv_fastquant_vs_oracle(n, k):
     g = torch.Generator().manual_seed(n * 7 + k)
     w = torch.randn(n, k, generator=g) * 0.02
@@ -116,11 +116,11 @@ def test_gemv_deterministic():
 
 
 def test_gemv_rejects_bad_shapes():
-    m = random_matrix(8, 16, seed=1).to(DEV)
-    bad = QuantMatrix(qt=torch.zeros(8, 24, dtype=torch.uint8, device=DEV), ry=torch.zeros(24, device=DEV),
-                      my=torch.zeros(24, device=DEV))
+    m = random_matrix(8, 128, seed=1).to(DEV)
+    bad = QuantMatrix(qt=torch.zeros(8, 96, dtype=torch.uint8, device=DEV), ry=torch.zeros(96, device=DEV),
+                      my=torch.zeros(96, device=DEV))
     with pytest.raises(Exception):
-        ops.gemv_u8([bad], [torch.zeros(24, device=DEV)])
+        ops.gemv_u8([bad], [torch.zeros(96, device=DEV)])
     with pytest.raises(ValueError):
         ops.gemv_u8([m], [torch.zeros(8, device=DEV)])
 

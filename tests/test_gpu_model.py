@@ -17,7 +17,7 @@ def t64(a):
 
 @pytest.fixture(scope="module")
 def tiny():
-    return B200RWKV.from_checkpoint(synth_checkpoint(2, 64, vocab=257, seed=31), device=DEV)
+    return B200RWKV.from_checkpoint(synth_checkpoint(2, 128, vocab=257, seed=31), device=DEV)
 
 
 @pytest.fixture(scope="module")
@@ -50,7 +50,7 @@ def test_tiny_sequence_chunk_and_token_modes(tiny, golden):
 
 def test_empty_state_matches_reference_layout(tiny):
     e = tiny.emptyState.cpu()
-    assert tuple(e.shape) == (2, 5, 64) and bool((e[:, :4] == 0).all())
+    assert tuple(e.shape) == (2, 5, 128) and bool((e[:, :4] == 0).all())
     assert bool((e[:, 4] == torch.tensor(-1e30, dtype=torch.float32)).all())
 
 
@@ -110,4 +110,4 @@ def test_169m_prompt_then_64_greedy_tokens(m169, golden):
 
 def test_rejects_wrong_state_shape(tiny):
     with pytest.raises(ValueError):
-        tiny.forward([1], torch.zeros(3, 5, 64))
+        tiny.forward([1], torch.zeros(3, 5, 128))

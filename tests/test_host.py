@@ -31,14 +31,14 @@ def test_library_exports_every_declared_symbol():
 
 def test_bad_arguments_return_codes_not_aborts():
     L = _lib.lib()
-    assert L.b200rwkv_gemv_u8(0, None, None, None, 0, None, None) == _lib.EINVAL
+    assert L.b200rwkv_gemv_u8(0, None, None, None, 0, None, 0, None) == _lib.EINVAL
     assert b"gemv_u8" in L.b200rwkv_last_error()
     assert L.b200rwkv_wkv_scan(1, 1, 0, *([None] * 8), 0, None) == _lib.EINVAL
     assert L.b200rwkv_decode_step(None, None, None, None, None, 0, None) == _lib.EINVAL
     with pytest.raises(_lib.B200RWKVError):
-        _lib.gemv_plan(24, 1, 8)          # k_in not a multiple of 16
+        _lib.gemv_plan(96, 1, 8)            # k_in not a multiple of 128
     with pytest.raises(_lib.B200RWKVError):
-        _lib.gemv_plan(64 * 1024, 1, 8)   # row does not fit a ring stage
+        _lib.gemv_plan(128 * 1024, 1, 8)    # beyond the supported reduction length
 
 
 def test_quantiser_is_bit_identical_to_reference(golden):
@@ -72,14 +72,14 @@ def test_gemv_geometry_invariants(name):
     F = 4 * D
     for K, nmat, N in ((D, 3, D), (D, 1, D), (D, 2, F), (F, 1, D), (D, 1, VOCAB)):
         p = _lib.gemv_plan(K, nmat, N)
-        tpr, rl, m = p["threads_per_row"], p["rows_side_by_side"], p["rows_per_thread_per_stage"]
-        assert tpr % 32 == 0 and tpr * rl <= p["consumer_threads"]
-        assert p["chunks_per_thread"] * tpr * 16 >= K          # every byte of a row has an owner
-        assert m in (1, 2, 4, 8) and rl * m * K <= p["stage_bytes"] <= 40 * 1024
-        assert p["ring_stages"] >= 2 and p["shared_memory_bytes"] <= 227 * 1024
-        assert p["grid"] * p["max_rows_per_cta"] >= N
-        # lane utilisation of the chosen geometry
-        assert (K // 16) * rl / (p["chunks_per_thread"] * p["consumer_threads"]) >= 0.7
+        kc, n = p["chunk_bytes"], p["chunks_per_row"]
+        assert kc % 128 == 0 and kc <= 2048 and kc * n >= K > kc * (n - 1)  # chunks tile a row, last one non-empty
+        assert p["swizzle_bytes"] == 128 and p["rows_per_stage"] == 16
+        assert p["stage_bytes"] == 16 * kc and p["stage_bytes"] % 1024 == 0
+        assert p["ring_stages"] >= 3 and p["shared_memory_bytes"] <= 227 * 1024
+        assert p["grid"] * p["max_rows_per_cta"] >= N and p["max_rows_per_cta"] % 16 == 0
+        # at least 2.5 us of weight stream fits the ring at 6.5 TB/s over 148 SMs (44 KB/us per SM)
+        assert p["ring_stages"] * 16 * kc >= 2.5 * 44e3
 
 
 def test_fixed_point_contract_accuracy_single_matrix():
@@ -113,7 +113,7 @@ def test_state_convention_round_trip():
 
 def test_contract_model_meets_tolerance_on_tiny_golden(golden):
     g = golden("model_tiny.npz")
-    wts = quantize_tensors(synth_checkpoint(2, 64, vocab=257, seed=31).items(), "cpu")
+    wts = quantize_tensors(synth_checkpoint(2, 128, vocab=257, seed=31).items(), "cpu")
     m = ContractModel(wts)
     lg, st = m.forward(g["tokens"], m.emptyState.clone())
     assert float((lg.double() - torch.from_numpy(g["logits_seq"])).abs().max()) < 2e-3

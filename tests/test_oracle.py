@@ -63,7 +63,7 @@ def test_block(golden):
 
 def test_tiny_model_sequence_chunk_token(golden):
     g = golden("model_tiny.npz")
-    m = O.OracleRWKV(synth_checkpoint(2, 64, vocab=257, seed=31))
+    m = O.OracleRWKV(synth_checkpoint(2, 128, vocab=257, seed=31))
     toks = t(g["tokens"])
     lg, s = m.forward(toks, m.emptyState.clone())
     assert torch.equal(lg, t(g["logits_seq"])) and torch.equal(s, t(g["state_seq"]))

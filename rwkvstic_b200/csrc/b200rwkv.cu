@@ -152,13 +152,11 @@ static void fill_seg(GemvSeg& s, const b200rwkv_matrix& m) {
   s.half = m.half; s.N = m.n_out; s.act = ACT_NONE;
 }
 
-constexpr int kNextPrefetchBytes = 256 * 1024;  // per CTA; x147 CTAs = 37 MB of the 126 MB L2
+constexpr int kNextPrefetchBytes = 384 * 1024;  // per CTA; x147 CTAs = 56 MB of the 126 MB L2
 
 // Tell launch P which matrices the following launch streams (same k_in for all of them).
 static void set_next(GemvParams& P, const b200rwkv_matrix* const* next, int n) {
-  int pf = kNextPrefetchBytes;
-  if (const char* e = getenv("B200RWKV_PREFETCH_KB")) pf = atoi(e) * 1024;  // TEMP experiment
-  P.next_nseg = n; P.next_k = n > 0 ? next[0]->k_in : 0; P.next_prefetch = n > 0 ? pf : 0;
+  P.next_nseg = n; P.next_k = n > 0 ? next[0]->k_in : 0; P.next_prefetch = n > 0 ? kNextPrefetchBytes : 0;
   for (int i = 0; i < n; ++i) { P.next_qt[i] = next[i]->qt; P.next_n[i] = next[i]->n_out; }
 }
 

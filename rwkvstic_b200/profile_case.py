@@ -1,0 +1,58 @@
+"""A small, self-contained GEMV workload for profilers: ``python -m rwkvstic_b200.profile_case``.
+
+Launches the streaming uint8 GEMV (one activation-preparation CTA + one streaming grid per
+launch) on a few DISTINCT random matrices of one RWKV-4 shape, so that every launch reads
+bytes that are not in L2 while the whole run holds well under 1 GB on the device.  Meant for
+``ncu -k regex:stream_gemv -c 3`` style captures; prints the CUDA-event time per launch.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import ops
+from .quant import QuantMatrix
+from .synth import SHAPES, VOCAB
+
+
+def matrices(kind: str, D: int, device, copies: int):
+    F = 4 * D
+    shapes = {"att_kvr": [(D, D)] * 3, "att_out": [(D, D)], "ffn_kr": [(F, D), (D, D)], "ffn_value": [(D, F)],
+              "head": [(VOCAB, D)]}[kind]
+    g = torch.Generator(device=device).manual_seed(1)
+    out = []
+    for _ in range(copies):
+        out.append([QuantMatrix(qt=torch.randint(0, 256, (n, k), generator=g, dtype=torch.uint8, device=device),
+                                ry=torch.rand(k, generator=g, device=device) * 1e-3 + 1e-4,
+                                my=torch.randn(k, generator=g, device=device) * 0.05) for n, k in shapes])
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="7b", choices=list(SHAPES))
+    ap.add_argument("--matrix", default="ffn_kr", choices=["att_kvr", "att_out", "ffn_kr", "ffn_value", "head"])
+    ap.add_argument("--copies", type=int, default=4, help="distinct matrix sets (4 x 84 MB > the 126 MB L2)")
+    ap.add_argument("--launches", type=int, default=8)
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    _, D = SHAPES[args.shape]
+    sets = matrices(args.matrix, D, dev, args.copies)
+    xs = {D: torch.randn(D, device=dev), 4 * D: torch.randn(4 * D, device=dev)}
+    nbytes = sum(m.qt.numel() for m in sets[0])
+    times = []
+    for i in range(args.launches):
+        mats = sets[i % len(sets)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.gemv_u8(mats, [xs[m.k_in] for m in mats])
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    print(f"{args.matrix} {args.shape}: {nbytes / 1e6:.1f} MB per launch, event time per launch (us): "
+          + " ".join(f"{t:.1f}" for t in times))
+
+
+if __name__ == "__main__":
+    main()

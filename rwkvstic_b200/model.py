@@ -87,6 +87,8 @@ def quantize_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], device, scheme
                 ly.mat[rest[:-7]] = q(w.to(qdev) if qdev is not None else w).to(dev)
             elif rest == "att.time_decay":
                 ly.vec[rest] = (-torch.exp(t.detach().double().reshape(-1))).to(torch.float32).to(dev).contiguous()
+            elif rest == "att.time_decay_final":       # already w = -exp(raw) (helpers/loadWeights.py:63-64)
+                ly.vec["att.time_decay"] = f32(t)
             elif rest.startswith("ln0."):
                 top[rest] = f32(t)
             else:

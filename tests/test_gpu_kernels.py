@@ -167,3 +167,42 @@ def test_wkv_scan_batched_streams_and_large_k():
         a1, b1, p1 = dev(aa[s]), dev(bb[s]), dev(pp[s])
         y1 = ops.wkv_scan(dev(w), dev(u), dev(k[s]), dev(v[s]), a1, b1, p1).cpu()
         assert torch.equal(y1[0], y[s]) and torch.equal(a1.cpu(), a[s].cpu())
+
+
+def test_reference_op_library_names_and_semantics(golden):
+    """torch.ops.rwkv.{mm8_one,mm8_three,wkv_forward} as the reference modules call them
+    (modules/matmul.py:42-49, :70-80; modules/wkv.py:8-19), including from TorchScript."""
+    from rwkvstic_b200 import torch_ops
+    torch_ops.register()
+    g = torch.Generator().manual_seed(12)
+    N, M = 256, 320                                        # in, out
+    wq = [torch.randint(0, 256, (N, M), generator=g, dtype=torch.uint8).to(DEV) for _ in range(3)]
+    r = [(torch.rand(N, generator=g) * 1e-3 + 1e-4).to(DEV) for _ in range(3)]
+    x = [torch.randn(N, generator=g).to(DEV) for _ in range(3)]
+    want = [(xi.double() * ri.double()) @ wi.double() for xi, ri, wi in zip(x, r, wq)]
+    y = torch.zeros(M, device=DEV)
+    torch.ops.rwkv.mm8_one(N, M, x[0], wq[0], y, r[0])
+    assert torch.allclose(y.double(), want[0], rtol=1e-5, atol=1e-5)
+    torch.ops.rwkv.mm8_one(N, M, x[0], wq[0], y, r[0])     # accumulates onto y, like the atomicAdd kernels
+    assert torch.allclose(y.double(), 2 * want[0], rtol=1e-5, atol=1e-5)
+    ys = [torch.zeros(M, device=DEV) for _ in range(3)]
+    torch.ops.rwkv.mm8_three(N, M, *x, *wq, *ys, *r)
+    for a, b in zip(ys, want):
+        assert torch.allclose(a.double(), b, rtol=1e-5, atol=1e-5)
+
+    @torch.jit.script
+    def scripted(N: int, M: int, x, w, y, r):
+        torch.ops.rwkv.mm8_one(N, M, x, w, y, r)
+        return y
+    y2 = scripted(N, M, x[1], wq[1], torch.zeros(M, device=DEV), r[1])
+    assert torch.allclose(y2.double(), want[1], rtol=1e-5, atol=1e-5)
+
+    gg = golden("ops_small.npz")
+    d = lambda n: torch.from_numpy(gg[n]).to(DEV)
+    yk = torch.empty(7, 32, dtype=torch.float64, device=DEV)
+    aa, bb, pp = d("wkv_aa").clone(), d("wkv_bb").clone(), d("wkv_pp").clone()
+    torch.ops.rwkv.wkv_forward(1, 7, 32, d("wkv_w"), d("wkv_u"), d("wkv_k"), d("wkv_v"), yk, aa, bb, pp)
+    assert torch.allclose(yk.cpu(), torch.from_numpy(gg["wkv_y"]), rtol=1e-5, atol=1e-5)
+    assert torch.allclose(aa.cpu(), torch.from_numpy(gg["wkv_aa2"]), rtol=1e-5, atol=1e-5)
+    assert torch.allclose(bb.cpu(), torch.from_numpy(gg["wkv_bb2"]), rtol=1e-5, atol=1e-5)
+    assert torch.equal(pp.cpu(), torch.from_numpy(gg["wkv_pp"]))

@@ -90,11 +90,14 @@ def register() -> None:
     if _lib_handle is not None:
         return
     lib = torch.library.Library("rwkv", "DEF")
-    lib.define("wkv_forward(int B, int T, int C, Tensor w, Tensor u, Tensor k, Tensor v, Tensor y, Tensor aa, "
-               "Tensor bb, Tensor pp) -> ()")
-    lib.define("mm8_one(int N, int M, Tensor x, Tensor w, Tensor y, Tensor r) -> ()")
-    lib.define("mm8_three(int N, int M, Tensor x, Tensor x1, Tensor x2, Tensor w, Tensor w1, Tensor w2, Tensor y, "
-               "Tensor y1, Tensor y2, Tensor r, Tensor r1, Tensor r2) -> ()")
+    # The written-to tensors carry alias annotations: a schema parsed from text is otherwise taken
+    # to be pure, and TorchScript would drop a call that returns nothing.  (The reference's ops get
+    # their schema inferred from C++ and are treated as side-effecting wholesale.)
+    lib.define("wkv_forward(int B, int T, int C, Tensor w, Tensor u, Tensor k, Tensor v, Tensor(a!) y, "
+               "Tensor(b!) aa, Tensor(c!) bb, Tensor(d!) pp) -> ()")
+    lib.define("mm8_one(int N, int M, Tensor x, Tensor w, Tensor(a!) y, Tensor r) -> ()")
+    lib.define("mm8_three(int N, int M, Tensor x, Tensor x1, Tensor x2, Tensor w, Tensor w1, Tensor w2, "
+               "Tensor(a!) y, Tensor(b!) y1, Tensor(c!) y2, Tensor r, Tensor r1, Tensor r2) -> ()")
     lib.impl("wkv_forward", wkv_forward, "CUDA")
     lib.impl("mm8_one", mm8_one, "CUDA")
     lib.impl("mm8_three", mm8_three, "CUDA")

@@ -111,6 +111,27 @@ int b200rwkv_gemv_u8_traced(int nmat, const b200rwkv_matrix* mats, const float* 
                             void* stream);
 
 /*
+ * b200rwkv_gemv_u8 for callers that cannot allocate device memory: plugin hosts whose memory
+ * pool is closed to extensions, code running while a stream capture is in progress, or a
+ * C program that never touches cudaMalloc at all.  Same arithmetic and same two launches as
+ * b200rwkv_gemv_u8 (results are bit-identical), but the scratch for the activation digits lives
+ * in a 192.25 KB array compiled into the library, which every GPU that loads the library
+ * holds until the process exits.  The call itself never allocates or frees anything.
+ *   limit     nmat * 4 * k_in <= 196608 bytes (three matrices up to k_in = 16384, one up to
+ *             49152); larger requests return B200RWKV_EINVAL and a message naming the limit.
+ *   status    optional caller-owned device int for the B200RWKV_STATUS_* bits, or NULL.
+ *   set-up    the first call on each device looks up the array's device address; make that
+ *             call before starting any stream capture.
+ *   sharing   all calls on a device use the same array and find the previous call's contents
+ *             in it (nothing in it needs clearing: each call overwrites what it reads).  Two
+ *             calls that can overlap on the GPU (different streams, no event between them) race
+ *             on it - order them.
+ * No counterpart in the reference.
+ */
+int b200rwkv_gemv_u8_static(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y,
+                            int accumulate, int* status, void* stream);
+
+/*
  * WKV-4 recurrence, B independent streams x C channels, sequential over T
  * (replaces rwkv::wkv_forward, cuda/wrapper.cpp:45-50 / cuda/operators.cu:6-44, and
  * TorchWKV, modules/wkv.py:23-40).  k, v, y: device f32 [B][T][C]; w (= -exp(decay)),

@@ -18,7 +18,7 @@ STATUS_WAIT_FULL, STATUS_WAIT_EMPTY, STATUS_WAIT_PEER = 1, 2, 4
 # Every symbol include/b200rwkv.h declares; tests check that the library exports all of them.
 EXPORTS = (
     "b200rwkv_version", "b200rwkv_last_error", "b200rwkv_gemv_u8", "b200rwkv_wkv_scan", "b200rwkv_gemv_plan",
-    "b200rwkv_gemv_u8_traced", "b200rwkv_gemv_workspace_bytes",
+    "b200rwkv_gemv_u8_traced", "b200rwkv_gemv_workspace_bytes", "b200rwkv_gemv_u8_static",
     "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step", "b200rwkv_decode_step_traced",
 )
 
@@ -70,6 +70,9 @@ def lib() -> C.CDLL:
     L.b200rwkv_gemv_u8_traced.restype = C.c_int
     L.b200rwkv_gemv_u8_traced.argtypes = [C.c_int, C.POINTER(Matrix), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                           C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
+    L.b200rwkv_gemv_u8_static.restype = C.c_int
+    L.b200rwkv_gemv_u8_static.argtypes = [C.c_int, C.POINTER(Matrix), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                          C.c_int, C.c_void_p, C.c_void_p]
     L.b200rwkv_wkv_scan.restype = C.c_int
     L.b200rwkv_wkv_scan.argtypes = [C.c_int, C.c_int, C.c_int] + [C.c_void_p] * 8 + [C.c_int, C.c_void_p]
     L.b200rwkv_gemv_plan.restype = C.c_int

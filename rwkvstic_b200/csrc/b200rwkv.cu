@@ -268,6 +268,13 @@ static size_t gemv_workspace_bytes(int k_in, int nmat) {
   return 256 + align256(size_t(nmat) * 4 * k_in) + align256(sizeof(SegScalars) * kMaxSeg);
 }
 
+// ---------------------------------------------------------------------------------------- static scratch
+// Scratch of b200rwkv_gemv_u8_static: digit planes (up to kStaticPlaneBytes) followed by the
+// per-matrix scalars.  Lives in every GPU's memory from the moment the library is loaded there.
+constexpr size_t kStaticPlaneBytes = 192 * 1024;   // = 3 matrices x 4 x k_in(16384), or 1 x 4 x 49152
+constexpr size_t kStaticScratchBytes = kStaticPlaneBytes + 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 }  // namespace b200
 
 using namespace b200;
@@ -331,6 +338,53 @@ int b200rwkv_gemv_u8_traced(int nmat, const b200rwkv_matrix* mats, const float* 
   if (!trace) return fail(B200RWKV_EINVAL, "gemv_u8_traced: null trace buffer");
   return gemv_u8_impl(nmat, mats, x, y, accumulate, workspace, workspace_bytes,
                       reinterpret_cast<unsigned long long*>(trace), stream);
+}
+
+int b200rwkv_gemv_u8_static(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y,
+                            int accumulate, int* status, void* stream) {
+  if (nmat < 1 || nmat > kMaxSeg || !mats || !x || !y) return fail(B200RWKV_EINVAL, "gemv_u8_static: nmat=%d or null argument", nmat);
+  // In host code the name of a __device__ array is only a handle.  Its device address is looked up
+  // once per device, with that device current, and cached; the kernels are given the address.
+  static unsigned char* scratch_of_device[64];
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) return fail(B200RWKV_ECUDA, "gemv_u8_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (!scratch_of_device[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return fail(B200RWKV_ECUDA, "gemv_u8_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    scratch_of_device[dev] = static_cast<unsigned char*>(p);
+  }
+  GemvParams P;
+  PrepParams Q;
+  memset(&P, 0, sizeof(P));
+  memset(&Q, 0, sizeof(Q));
+  int max_n = 0;
+  for (int i = 0; i < nmat; ++i) {
+    if (int rc = check_matrix(mats[i], "gemv_u8_static matrix")) return rc;
+    if (mats[i].k_in != mats[0].k_in) return fail(B200RWKV_EINVAL, "gemv_u8_static: matrices must share k_in");
+    if (!x[i] || !y[i] || !aligned16(x[i])) return fail(B200RWKV_EINVAL, "gemv_u8_static: x/y null or x not 16-byte aligned");
+    fill_seg(P.seg[i], mats[i]);
+    P.seg[i].out = y[i];
+    fill_prep_seg(Q.seg[i], mats[i], nullptr, x[i]);
+    if (mats[i].n_out > max_n) max_n = mats[i].n_out;
+  }
+  const int K = mats[0].k_in;
+  const size_t need = size_t(nmat) * 4 * K;
+  if (need > kStaticPlaneBytes)
+    return fail(B200RWKV_EINVAL, "gemv_u8_static: nmat * 4 * k_in = %zu bytes exceeds the built-in scratch of %zu bytes "
+                "(use b200rwkv_gemv_u8 with a caller-provided workspace)", need, kStaticPlaneBytes);
+  unsigned char* planes = scratch_of_device[dev];
+  SegScalars* scal = reinterpret_cast<SegScalars*>(planes + kStaticPlaneBytes);
+  Q.nseg = nmat; Q.K = K; Q.ln = 0; Q.planes = planes; Q.scal = scal;
+  P.nseg = nmat; P.K = K; P.epi = EPI_GENERIC; P.accumulate = accumulate ? 1 : 0;
+  P.planes = planes; P.scal = scal; P.status = status;
+  const char* why = "";
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  e = launch_vector_prep(Q, false, s, &why);
+  if (e == cudaSuccess) e = launch_stream_gemv(P, max_n, true, s, &why);
+  if (e != cudaSuccess) return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "gemv_u8_static: %s (%s)", why, cudaGetErrorString(e));
+  return B200RWKV_OK;
 }
 
 int b200rwkv_wkv_scan(int B, int T, int C, const float* w, const float* u, const float* k, const float* v, float* y,

@@ -118,7 +118,7 @@ cudaError_t launch_vector_prep(const PrepParams& P, bool pdl, cudaStream_t strea
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const size_t smem = prep_smem_bytes(P.K, P.nseg);
+  const size_t smem = prep_smem_bytes(P.K, P.nseg, P.mode);
   if (smem > 200 * 1024) {
     *why = "unsupported shape: activation planes do not fit the preparation kernel's shared memory";
     return cudaErrorInvalidValue;
@@ -166,17 +166,22 @@ static void fill_prep_seg(PrepSeg& s, const b200rwkv_matrix& m, const float* mix
 
 // ---------------------------------------------------------------------------------------- small kernels
 // x = LayerNorm(emb[token]) (the reference's emb.py:8-9 gather followed by ln_in, opt.py:63-64).
+// First kernel of a decode step: it also clears the step's publication slots and publishes the sum
+// and sum of squares of x for the first block's layer norm (slot 0).
 __global__ void __launch_bounds__(512, 1)
 embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ token, int D, int V,
-                 const float* __restrict__ w, const float* __restrict__ b, float* __restrict__ out) {
+                 const float* __restrict__ w, const float* __restrict__ b, float* __restrict__ out,
+                 PubSlot* __restrict__ pub, int npub) {
   __shared__ float red[16];
+  __shared__ long long redl[32];
   __shared__ float bc;
   griddep_launch_dependents();
   griddep_wait();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < npub * 16; i += 512) reinterpret_cast<long long*>(pub)[i] = 0;
   long long tok = *token;
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
   const float* row = emb + size_t(tok) * D;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   auto block_sum = [&](float v) -> float {
     v = warp_sum(v);
     if (lane == 0) red[warp] = v;
@@ -197,7 +202,22 @@ embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ to
   s = 0.f;
   for (int i = tid; i < D; i += 512) { const float c = row[i] - mean; s += c * c; }
   const float sdev = sqrtf(block_sum(s) / float(D) + 1e-5f);
-  for (int i = tid; i < D; i += 512) out[i] = w[i] * ((row[i] - mean) / sdev) + b[i];
+  long long p_sum = 0, p_sq = 0;
+  for (int i = tid; i < D; i += 512) {
+    const float y = w[i] * ((row[i] - mean) / sdev) + b[i];
+    out[i] = y;
+    p_sum += __double2ll_rn(double(y) * kPubSumScale);
+    p_sq += __double2ll_rn(double(y) * double(y) * kPubSqScale);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { p_sum += __shfl_xor_sync(0xffffffffu, p_sum, o); p_sq += __shfl_xor_sync(0xffffffffu, p_sq, o); }
+  if (lane == 0) { redl[warp * 2] = p_sum; redl[warp * 2 + 1] = p_sq; }
+  __syncthreads();                      // also orders the zeroing of slot 0 before the store below
+  if (tid < 2) {
+    long long a = 0;
+    for (int i = 0; i < 16; ++i) a += redl[i * 2 + tid];
+    if (tid == 0) pub[0].sum = a; else pub[0].sq = a;
+  }
 }
 
 // WKV-4 recurrence, one thread per (stream, channel), sequential over T; k/v/y are [B][T][C] so a
@@ -237,9 +257,10 @@ constexpr size_t kTraceStride = 1024 * 8;  // u64 slots per GEMV launch in a dec
 
 struct Workspace {
   int* status;
-  float *xa, *xb, *rwkv, *rf, *kk;
+  float *xa, *xb, *xs_att, *rf, *xs_ffn;
   unsigned char* planes;
   SegScalars* scal;
+  PubSlot* pub;      // one slot per GEMV launch of a step
   size_t bytes;
 };
 
@@ -254,11 +275,12 @@ static Workspace carve(const b200rwkv_model* m, void* base) {
   w.status = reinterpret_cast<int*>(take(256));
   w.xa = reinterpret_cast<float*>(take(D));
   w.xb = reinterpret_cast<float*>(take(D));
-  w.rwkv = reinterpret_cast<float*>(take(D));
+  w.xs_att = reinterpret_cast<float*>(take(D));    // sigmoid(r)*wkv, already times the output matrix's ry
   w.rf = reinterpret_cast<float*>(take(D));
-  w.kk = reinterpret_cast<float*>(take(F));
+  w.xs_ffn = reinterpret_cast<float*>(take(F));    // relu(k)^2, already times the value matrix's ry
   w.planes = reinterpret_cast<unsigned char*>(take(3 * D > F ? 3 * D : F));  // 4*K bytes per matrix
   w.scal = reinterpret_cast<SegScalars*>(take(sizeof(SegScalars) * kMaxSeg));
+  w.pub = reinterpret_cast<PubSlot*>(take(sizeof(PubSlot) * (4 * size_t(m->n_layer) + 1)));
   w.bytes = off;
   return w;
 }
@@ -311,7 +333,7 @@ static int gemv_u8_impl(int nmat, const b200rwkv_matrix* mats, const float* cons
   int* status = reinterpret_cast<int*>(wsb);
   unsigned char* planes = reinterpret_cast<unsigned char*>(wsb + 256);
   SegScalars* scal = reinterpret_cast<SegScalars*>(wsb + 256 + align256(size_t(nmat) * 4 * K));
-  Q.nseg = nmat; Q.K = K; Q.ln = 0; Q.planes = planes; Q.scal = scal;
+  Q.nseg = nmat; Q.K = K; Q.mode = PREP_PLAIN; Q.planes = planes; Q.scal = scal;
   Q.trace = trace ? trace + 1023 * 8 : nullptr;
   P.nseg = nmat; P.K = K; P.epi = EPI_GENERIC; P.accumulate = accumulate ? 1 : 0;
   P.planes = planes; P.scal = scal; P.status = status; P.trace = trace;
@@ -376,7 +398,7 @@ int b200rwkv_gemv_u8_static(int nmat, const b200rwkv_matrix* mats, const float* 
                 "(use b200rwkv_gemv_u8 with a caller-provided workspace)", need, kStaticPlaneBytes);
   unsigned char* planes = scratch_of_device[dev];
   SegScalars* scal = reinterpret_cast<SegScalars*>(planes + kStaticPlaneBytes);
-  Q.nseg = nmat; Q.K = K; Q.ln = 0; Q.planes = planes; Q.scal = scal;
+  Q.nseg = nmat; Q.K = K; Q.mode = PREP_PLAIN; Q.planes = planes; Q.scal = scal;
   P.nseg = nmat; P.K = K; P.epi = EPI_GENERIC; P.accumulate = accumulate ? 1 : 0;
   P.planes = planes; P.scal = scal; P.status = status;
   const char* why = "";
@@ -442,7 +464,7 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, embed_ln0_kernel, m->emb, reinterpret_cast<const long long*>(token), D, V, m->ln0_w,
-                           m->ln0_b, ws.xa);
+                           m->ln0_b, ws.xa, ws.pub, 4 * L + 1);
     if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "decode_step: embed launch: %s", cudaGetErrorString(e));
   }
 
@@ -460,57 +482,64 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     }
     GemvParams P;
     PrepParams Q;
-    // 1. ln1 + token-shift mix (carry = state row 0) -> key/value/receptance -> WKV update -> sigmoid(r)*wkv
+    PubSlot* pub = ws.pub + 4 * size_t(l);   // slot j feeds the preparation of GEMV launch j of the step
+    // 1. ln1 + token-shift mix (carry = state row 0) -> key/value/receptance -> WKV update ->
+    //    sigmoid(r)*wkv, written already scaled for the output projection
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], ly.att_key, ly.att_mix_k, nullptr);
     fill_prep_seg(Q.seg[1], ly.att_value, ly.att_mix_v, nullptr);
     fill_prep_seg(Q.seg[2], ly.att_receptance, ly.att_mix_r, nullptr);
-    Q.nseg = 3; Q.K = D; Q.ln = 1; Q.ln_x = ws.xa; Q.ln_w = ly.ln1_w; Q.ln_b = ly.ln1_b; Q.shift = st;
+    Q.nseg = 3; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xa; Q.ln_w = ly.ln1_w; Q.ln_b = ly.ln1_b; Q.shift = st;
+    Q.pub = pub + 0;
     Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_seg(P.seg[0], ly.att_key); fill_seg(P.seg[1], ly.att_value); fill_seg(P.seg[2], ly.att_receptance);
     P.nseg = 3; P.K = D; P.planes = ws.planes; P.scal = ws.scal;
     P.epi = EPI_WKV; P.wkv_w = ly.time_decay; P.wkv_u = ly.time_first;
-    P.aa = st + 2 * size_t(D); P.bb = st + 3 * size_t(D); P.pp = st + 4 * size_t(D); P.wkv_out = ws.rwkv;
+    P.aa = st + 2 * size_t(D); P.bb = st + 3 * size_t(D); P.pp = st + 4 * size_t(D);
+    P.seg[0].xs_out = ws.xs_att; P.seg[0].xs_ry = ly.att_output.ry; P.seg[0].xs_my = ly.att_output.my; P.seg[0].pub_xs = pub + 1;
     { const b200rwkv_matrix* nx[1] = {&ly.att_output}; set_next(P, nx, 1); }
     P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, D, true, s, &why)) != cudaSuccess) goto launch_failed;
-    // 2. attention output projection + residual
+    // 2. attention output projection + residual; publishes the layer-norm sums of the new residual
     memset(&Q, 0, sizeof(Q));
-    fill_prep_seg(Q.seg[0], ly.att_output, nullptr, ws.rwkv);
-    Q.nseg = 1; Q.K = D; Q.planes = ws.planes; Q.scal = ws.scal;
+    fill_prep_seg(Q.seg[0], ly.att_output, nullptr, ws.xs_att);
+    Q.nseg = 1; Q.K = D; Q.mode = PREP_XS; Q.pub = pub + 1; Q.planes = ws.planes; Q.scal = ws.scal;
     Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_seg(P.seg[0], ly.att_output); P.seg[0].out = ws.xb; P.seg[0].res = ws.xa;
-    P.nseg = 1; P.K = D; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
+    P.nseg = 1; P.K = D; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC; P.pub_ln = pub + 2;
     { const b200rwkv_matrix* nx[2] = {&ly.ffn_key, &ly.ffn_receptance}; set_next(P, nx, 2); }
     P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, D, true, s, &why)) != cudaSuccess) goto launch_failed;
-    // 3. ln2 + token-shift mix (carry = state row 1) -> ffn key (relu^2) and ffn receptance (sigmoid)
+    // 3. ln2 + token-shift mix (carry = state row 1) -> ffn key (relu^2, written already scaled for
+    //    the value projection) and ffn receptance (sigmoid)
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], ly.ffn_key, ly.ffn_mix_k, nullptr);
     fill_prep_seg(Q.seg[1], ly.ffn_receptance, ly.ffn_mix_r, nullptr);
-    Q.nseg = 2; Q.K = D; Q.ln = 1; Q.ln_x = ws.xb; Q.ln_w = ly.ln2_w; Q.ln_b = ly.ln2_b; Q.shift = st + size_t(D);
+    Q.nseg = 2; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xb; Q.ln_w = ly.ln2_w; Q.ln_b = ly.ln2_b; Q.shift = st + size_t(D);
+    Q.pub = pub + 2;
     Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
-    fill_seg(P.seg[0], ly.ffn_key);        P.seg[0].act = ACT_RELUSQ;  P.seg[0].out = ws.kk;
+    fill_seg(P.seg[0], ly.ffn_key);        P.seg[0].act = ACT_RELUSQ;
+    P.seg[0].xs_out = ws.xs_ffn; P.seg[0].xs_ry = ly.ffn_value.ry; P.seg[0].xs_my = ly.ffn_value.my; P.seg[0].pub_xs = pub + 3;
     fill_seg(P.seg[1], ly.ffn_receptance); P.seg[1].act = ACT_SIGMOID; P.seg[1].out = ws.rf;
     P.nseg = 2; P.K = D; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
     { const b200rwkv_matrix* nx[1] = {&ly.ffn_value}; set_next(P, nx, 1); }
     P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, F > D ? F : D, true, s, &why)) != cudaSuccess) goto launch_failed;
-    // 4. ffn value projection, gated by the receptance, + residual
+    // 4. ffn value projection, gated by the receptance, + residual; publishes the layer-norm sums
     memset(&Q, 0, sizeof(Q));
-    fill_prep_seg(Q.seg[0], ly.ffn_value, nullptr, ws.kk);
-    Q.nseg = 1; Q.K = F; Q.planes = ws.planes; Q.scal = ws.scal;
+    fill_prep_seg(Q.seg[0], ly.ffn_value, nullptr, ws.xs_ffn);
+    Q.nseg = 1; Q.K = F; Q.mode = PREP_XS; Q.pub = pub + 3; Q.planes = ws.planes; Q.scal = ws.scal;
     Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_seg(P.seg[0], ly.ffn_value); P.seg[0].out = ws.xa; P.seg[0].res = ws.xb; P.seg[0].gate = ws.rf;
-    P.nseg = 1; P.K = F; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
+    P.nseg = 1; P.K = F; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC; P.pub_ln = pub + 4;
     if (l + 1 < L) {
       const b200rwkv_layer& nl = m->layers[l + 1];
       const b200rwkv_matrix* nx[3] = {&nl.att_key, &nl.att_value, &nl.att_receptance};
@@ -529,7 +558,8 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     PrepParams Q;
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], m->head, nullptr, nullptr);
-    Q.nseg = 1; Q.K = D; Q.ln = 1; Q.ln_x = ws.xa; Q.ln_w = m->ln_out_w; Q.ln_b = m->ln_out_b;
+    Q.nseg = 1; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xa; Q.ln_w = m->ln_out_w; Q.ln_b = m->ln_out_b;
+    Q.pub = ws.pub + 4 * size_t(L);
     Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));

@@ -50,6 +50,13 @@ struct GemvSeg {
   float* out;          // EPI_GENERIC: destination [N]
   const float* res;    // EPI_GENERIC: residual added to the output, or null
   const float* gate;   // EPI_GENERIC: multiplies act(y), or null
+  // When the next launch's input is an element-wise function of this segment's outputs, the
+  // epilogue writes it already scaled, xs_out[n] = out_value * xs_ry[n], and publishes max|xs| and
+  // the sums of xs, value and value * xs_my[n] (EPI_WKV uses segment 0's fields for sigmoid(r)*wkv).
+  float* xs_out;
+  const float* xs_ry;
+  const float* xs_my;
+  PubSlot* pub_xs;
   float half;
   int N;
   int act;
@@ -76,7 +83,8 @@ struct GemvParams {
   float* aa;               // state rows, updated in place [N]
   float* bb;
   float* pp;
-  float* wkv_out;          // sigmoid(r) * wkv [N]
+  float* wkv_out;          // sigmoid(r) * wkv [N], or null when only seg[0].xs_out is wanted
+  PubSlot* pub_ln;         // EPI_GENERIC: publish sum and sum of squares of segment 0's outputs, or null
   int* status;             // device status word or null
   unsigned long long* trace;  // diagnostics: 8 globaltimer stamps per CTA, or null
   // The launch that follows on the stream (same grid): once this CTA's own copies are all issued,
@@ -94,7 +102,8 @@ constexpr int kOffEmpty = 128;     // 16 x u64
 constexpr int kOffAbort = 256;     // int abort flag, int stages issued
 constexpr int kOffPlaneBar = 264;  // u64 mbarrier: digit planes have landed
 constexpr int kOffScale = 384;     // SegScalars[3]
-constexpr int kOffRows = 512;      // int32 rowsum[nseg*rpc16][4], then digit planes, then ring
+constexpr int kOffEpi = 512;       // epilogue reduction scratch: long long [16 warps][6] + float [16]
+constexpr int kOffRows = 1536;     // int32 rowsum[nseg*rpc16][4], then digit planes, then ring
 
 struct GemvPlan {
   int kc, nchunks, stages, stage_bytes, rpc16, grid;
@@ -328,19 +337,34 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
       if (P.seg[s].mx) y += P.seg[s].mx[n] * scal[s].sumx;
       return y;
     };
+    // per-thread partials of what this launch publishes for the next one
+    long long p_sum = 0, p_sq = 0, p_zp = 0, p_sxs = 0, p_sx = 0;
+    float p_amax = 0.f;
+    PubSlot* pub_xs = nullptr;
+    auto publish_xs = [&](const GemvSeg& sg, int n, float v) {
+      const float xs = v * sg.xs_ry[n];
+      sg.xs_out[n] = xs;
+      p_amax = fmaxf(p_amax, fabsf(xs));
+      p_zp += __double2ll_rn(double(v * sg.xs_my[n]) * kPubSumScale);
+      p_sxs += __double2ll_rn(double(xs) * kPubXsScale);
+      p_sx += __double2ll_rn(double(v) * kPubSumScale);
+    };
     if (P.epi == EPI_WKV) {
+      pub_xs = P.seg[0].pub_xs;
       for (int row = tid; row < nr[0]; row += kConsumers) {
         const int n = r0[0] + row;
         const float k = value(0, row, n), v = value(1, row, n), r = sigmoidf_(value(2, row, n));
         float aa = P.aa[n], bb = P.bb[n], pp = P.pp[n];
         const float y = wkv_step(k, v, P.wkv_w[n], P.wkv_u[n], aa, bb, pp);
         P.aa[n] = aa; P.bb[n] = bb; P.pp[n] = pp;
-        P.wkv_out[n] = r * y;
+        if (P.wkv_out) P.wkv_out[n] = r * y;
+        if (pub_xs) publish_xs(P.seg[0], n, r * y);
       }
     } else {
 #pragma unroll
       for (int s = 0; s < kMaxSeg; ++s) {
         if (s < P.nseg) {
+          if (P.seg[s].pub_xs) pub_xs = P.seg[s].pub_xs;
           for (int row = tid; row < nr[s]; row += kConsumers) {
             const int n = r0[s] + row;
             float y = value(s, row, n);
@@ -349,9 +373,46 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
             if (P.seg[s].gate) y *= P.seg[s].gate[n];
             if (P.seg[s].res) y += P.seg[s].res[n];
             if (P.accumulate) y += P.seg[s].out[n];
-            P.seg[s].out[n] = y;
+            if (P.seg[s].out) P.seg[s].out[n] = y;
+            if (P.seg[s].pub_xs) publish_xs(P.seg[s], n, y);
+            if (s == 0 && P.pub_ln) {
+              p_sum += __double2ll_rn(double(y) * kPubSumScale);
+              p_sq += __double2ll_rn(double(y) * double(y) * kPubSqScale);
+            }
           }
         }
+      }
+    }
+    if (pub_xs || P.pub_ln) {
+      // exact block totals (integers; the max is order-independent too), one atomic per quantity and CTA
+      long long* esum = reinterpret_cast<long long*>(smem + kOffEpi);
+      float* emax = reinterpret_cast<float*>(smem + kOffEpi + kConsumerWarps * 6 * 8);
+      long long v5[5] = {p_sum, p_sq, p_zp, p_sxs, p_sx};
+#pragma unroll
+      for (int i = 0; i < 5; ++i)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v5[i] += __shfl_xor_sync(0xffffffffu, v5[i], o);
+      p_amax = warp_max(p_amax);
+      if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < 5; ++i) esum[warp * 6 + i] = v5[i];
+        emax[warp] = p_amax;
+      }
+      named_bar_sync(1, kConsumers);
+      if (tid < 5) {
+        long long a = 0;
+        for (int w = 0; w < kConsumerWarps; ++w) a += esum[w * 6 + tid];
+        if (tid < 2) {
+          if (P.pub_ln) atomicAdd(reinterpret_cast<unsigned long long*>(tid == 0 ? &P.pub_ln->sum : &P.pub_ln->sq),
+                                  (unsigned long long)a);
+        } else if (pub_xs) {
+          long long* dst = tid == 2 ? &pub_xs->zp : (tid == 3 ? &pub_xs->sumxs : &pub_xs->sumx);
+          atomicAdd(reinterpret_cast<unsigned long long*>(dst), (unsigned long long)a);
+        }
+      } else if (tid == 5 && pub_xs) {
+        float m = 0.f;
+        for (int w = 0; w < kConsumerWarps; ++w) m = fmaxf(m, emax[w]);
+        atomicMax(&pub_xs->amax_bits, __float_as_uint(m));   // non-negative floats order like their bits
       }
     }
   }

@@ -9,6 +9,11 @@
 //   xs_s[k] = v_s[k] * ry_s[k];   inv_s = QMAX / max_k |xs_s[k]|;   X_s[k] = rint(xs_s[k] * inv_s)
 //   planes  : signed base-256 digits of X_s, 128 bytes per 32 inputs: [a:32][b:32][c:32][0:32]
 //   scalars : 1/inv_s (fp64), zp_s = sum_k v_s[k]*my_s[k], sum_k xs_s[k], sum_k v_s[k]
+//
+// To keep the chain between two GEMV launches short, whatever needs a reduction over ALL outputs of
+// the previous launch is published by that launch's epilogue with order-independent integer
+// atomics (PubSlot): the layer-norm sums, or - when the next matrix input is an element-wise
+// function of the previous outputs - the already scaled xs with its max and sums.
 #pragma once
 
 #include "common.cuh"
@@ -21,52 +26,116 @@ constexpr int kPrepRedBytes = (kPrepWarps + 1) * 16 * 4 + 64;  // reduction scra
 constexpr int kMaxSeg = 3;
 constexpr float kQMax = 8355000.0f;  // |X| <= QMAX keeps all three signed digits inside int8
 
+// Fixed-point units of the published sums (int64 accumulators: exact, order-independent).  The
+// ranges they leave: |sum x|, sum x^2, |sum v*my|, |sum v| < 2.1e9 and |sum xs| < 8.3e6.
+constexpr double kPubSumScale = 4294967296.0;        // 2^32
+constexpr double kPubSqScale = 4294967296.0;         // 2^32
+constexpr double kPubXsScale = 1099511627776.0;      // 2^40 (xs = v * ry is small: ry ~ 1e-3)
+
+// What the epilogue of one launch publishes for the preparation of the next (zeroed once per step).
+struct PubSlot {
+  long long sum;              // sum_n x[n]   * 2^32   (x = the residual stream the launch wrote)
+  long long sq;               // sum_n x[n]^2 * 2^32
+  unsigned amax_bits;         // float bits of max_n |xs[n]|  (xs = next input, already times ry)
+  unsigned pad;
+  long long zp, sumxs, sumx;  // sum v*my * 2^32, sum xs * 2^40, sum v * 2^32
+  long long reserved[10];
+};
+static_assert(sizeof(PubSlot) == 128, "PubSlot is one 128-byte line");
+
 struct SegScalars {   // 32 bytes per segment, written by the prep kernel, read by every GEMV CTA
   double sd;          // 1 / inv
   float zp, sumxs, sumx, pad;
 };
 
+enum PrepMode : int {
+  PREP_PLAIN = 0,   // v_s = xin_s; statistics by block reduction
+  PREP_LN = 1,      // v_s = mix(LayerNorm(ln_x), shift); mean/variance from pub->sum, pub->sq
+  PREP_XS = 2,      // one segment; xin_0 already holds xs; max and sums from pub
+};
+
 struct PrepSeg {
   const float* ry;    // [K] per-input scale
   const float* my;    // [K] per-input offset
-  const float* mix;   // [K] time-mix coefficient, or null (layer-norm mode only)
-  const float* xin;   // [K] input vector (plain mode only)
+  const float* mix;   // [K] time-mix coefficient, or null (PREP_LN only)
+  const float* xin;   // [K] input vector (PREP_PLAIN) or prepared xs (PREP_XS)
 };
 
 struct PrepParams {
   PrepSeg seg[kMaxSeg];
   int nseg, K;
-  int ln;                 // 1: layer norm (+ mix) of ln_x; 0: plain inputs
+  int mode;
   const float* ln_x;      // [K]
   const float* ln_w;
   const float* ln_b;
   float* shift;           // [K] carried previous-token vector: read, then overwritten with the
                           // layer-norm output (the state row of modules/block.py:61-64); may be null
+  const PubSlot* pub;     // published statistics (PREP_LN, PREP_XS)
   unsigned char* planes;  // out: nseg * 4*K bytes
   SegScalars* scal;       // out: nseg entries
   unsigned long long* trace;  // optional: 4 stamps (entry, dependency resolved, statistics, done)
 };
 
-// Sum of `v` over the whole CTA, result in every thread.  Two barriers; `red` row layout [warp][16],
-// column `col` is used for the partials and red[256 + col] for the total.
-__device__ __forceinline__ float prep_block_sum(float v, float* red, int col) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  v = warp_sum(v);
-  if (lane == 0) red[warp * 16 + col] = v;
-  __syncthreads();
-  if (warp == 0) {
-    float a = lane < kPrepWarps ? red[lane * 16 + col] : 0.f;
-    a = warp_sum(a);
-    if (lane == 0) red[kPrepWarps * 16 + col] = a;
+// rint(v) for 0 <= v < 2^23 without the conversion pipe: the sum with 2^23 holds it in the mantissa.
+__device__ __forceinline__ int rint_nonneg(float v) { return __float_as_int(__fadd_rn(v, 8388608.0f)) - 0x4B000000; }
+
+// Digits of four inputs -> one word per plane, stored to the block layout.  X = a*65536 + b*256 + c
+// with b, c in [-128,127]: the bytes of X + 0x8080 are (a, b+128, c+128), so flipping bit 7 of the
+// two low bytes gives the signed digits.
+__device__ __forceinline__ void store_digits(unsigned char* planes, int g, float4 xs, float inv) {
+  const float v[4] = {xs.x, xs.y, xs.z, xs.w};
+  uint32_t y[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int mag = rint_nonneg(__fmul_rn(fabsf(v[i]), inv));  // same value as cvt.rni of the fp32 product
+    const int X = v[i] < 0.f ? -mag : mag;
+    y[i] = uint32_t(X + 0x8080) ^ 0x8080u;
   }
-  __syncthreads();
-  return red[kPrepWarps * 16 + col];
+  const uint32_t c01 = __byte_perm(y[0], y[1], 0x0040), c23 = __byte_perm(y[2], y[3], 0x0040);
+  const uint32_t b01 = __byte_perm(y[0], y[1], 0x0051), b23 = __byte_perm(y[2], y[3], 0x0051);
+  const uint32_t a01 = __byte_perm(y[0], y[1], 0x0062), a23 = __byte_perm(y[2], y[3], 0x0062);
+  uint32_t* blk = reinterpret_cast<uint32_t*>(planes + size_t(g >> 3) * 128);
+  const int j = g & 7;
+  blk[j] = __byte_perm(a01, a23, 0x5410);
+  blk[8 + j] = __byte_perm(b01, b23, 0x5410);
+  blk[16 + j] = __byte_perm(c01, c23, 0x5410);
+  blk[24 + j] = 0u;
 }
 
-// GB = groups of four inputs a thread keeps in registers per batch; NS = segments compiled in.
+// Block reduction of the 4*nseg statistics: warp partials -> shared memory -> warp 0 folds the rows
+// (one lane per statistic) -> everyone reads the totals.
+template <int NS>
+__device__ __forceinline__ void prep_reduce_stats(float (&amax)[NS], float (&szp)[NS], float (&sxs)[NS], float (&sx)[NS],
+                                                  float* red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#pragma unroll
+  for (int s = 0; s < NS; ++s) {
+    amax[s] = warp_max(amax[s]); szp[s] = warp_sum(szp[s]); sxs[s] = warp_sum(sxs[s]); sx[s] = warp_sum(sx[s]);
+    if (lane == 0) {
+      red[warp * 16 + 2 + s] = amax[s]; red[warp * 16 + 5 + s] = szp[s];
+      red[warp * 16 + 8 + s] = sxs[s];  red[warp * 16 + 11 + s] = sx[s];
+    }
+  }
+  __syncthreads();
+  if (warp == 0 && lane >= 2 && lane < 14) {
+    float a = red[lane];
+    for (int w = 1; w < kPrepWarps; ++w) a = lane < 5 ? fmaxf(a, red[w * 16 + lane]) : a + red[w * 16 + lane];
+    red[kPrepWarps * 16 + lane] = a;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int s = 0; s < NS; ++s) {
+    amax[s] = red[kPrepWarps * 16 + 2 + s]; szp[s] = red[kPrepWarps * 16 + 5 + s];
+    sxs[s] = red[kPrepWarps * 16 + 8 + s];  sx[s] = red[kPrepWarps * 16 + 11 + s];
+  }
+}
+
+// PREP_PLAIN and PREP_LN.  GB = groups of four inputs a thread keeps in registers per batch; NS =
+// segments compiled in.  xs is parked in shared memory (`stage`, 16 bytes per group and segment)
+// between the statistics pass and the digit pass.
 template <int GB, int NS, bool LN>
 __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* stage, float* red) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int tid = threadIdx.x;
   const int K = P.K, NG = K / 4;
 
   // ---- parameter vectors of the first batch: loaded before the dependency wait
@@ -96,15 +165,31 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
   griddep_wait();  // everything below reads what earlier kernels wrote
   if (tid == 0 && P.trace) P.trace[1] = globaltimer_ns();
 
-  // Activation loads of the first batch go out together, right after the dependency resolves:
-  // one memory round trip on the critical path.
-  float4 dep0[GB][LN ? 1 : NS];  // LN: carried previous-token vector; else the input vectors
-  auto load_deps = [&](float4 (&dep)[GB][LN ? 1 : NS], int g0) {
+  float mean = 0.f, rstd = 1.f;
+  if (LN) {
+    // the launch that wrote ln_x also published its sum and sum of squares (exact integer atomics)
+    const double m = double(__ldcg(&P.pub->sum)) / (kPubSumScale * double(K));
+    const double ex2 = double(__ldcg(&P.pub->sq)) / (kPubSqScale * double(K));
+    const double var = ex2 - m * m;
+    mean = float(m);
+    rstd = 1.0f / sqrtf(float(var > 0.0 ? var : 0.0) + 1e-5f);
+  }
+  if (tid == 0 && P.trace) P.trace[2] = globaltimer_ns();
+
+  // ---- xs per segment and its statistics
+  float amax[NS], szp[NS], sxs[NS], sx[NS];
+#pragma unroll
+  for (int s = 0; s < NS; ++s) { amax[s] = 0.f; szp[s] = 0.f; sxs[s] = 0.f; sx[s] = 0.f; }
+  for (int g0 = tid, batch = 0; g0 < NG; g0 += GB * kPrepThreads, ++batch) {
+    if (batch > 0) load_consts(g0);
+    // activation loads of the batch go out together: one memory round trip
+    float4 xv[LN ? GB : 1], dep[GB][LN ? 1 : NS];
 #pragma unroll
     for (int i = 0; i < GB; ++i) {
       const int g = g0 + i * kPrepThreads;
       if (g < NG) {
         if (LN) {
+          xv[i] = ld_act_v4(reinterpret_cast<const float4*>(P.ln_x) + g);
           dep[i][0] = P.shift ? ld_act_v4(reinterpret_cast<const float4*>(P.shift) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
 #pragma unroll
@@ -113,68 +198,13 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
         }
       }
     }
-  };
-  // Until the digits are written, group g keeps its fp32 values at byte 16*g of its segment's
-  // staging region; segment 0's region first holds the raw ln_x.
-  float4* tmp0 = reinterpret_cast<float4*>(stage);
-  float mean = 0.f, sdev = 1.f;
-  if (LN) {
-    float sum = 0.f;
-    {
-      float4 xv[GB];
-#pragma unroll
-      for (int i = 0; i < GB; ++i) {
-        const int g = tid + i * kPrepThreads;
-        if (g < NG) xv[i] = ld_act_v4(reinterpret_cast<const float4*>(P.ln_x) + g);
-      }
-      load_deps(dep0, tid);
-#pragma unroll
-      for (int i = 0; i < GB; ++i) {
-        const int g = tid + i * kPrepThreads;
-        if (g < NG) { tmp0[g] = xv[i]; sum += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w); }
-      }
-    }
-    for (int g = tid + GB * kPrepThreads; g < NG; g += kPrepThreads) {  // inputs beyond the first batch
-      const float4 x = ld_act_v4(reinterpret_cast<const float4*>(P.ln_x) + g);
-      tmp0[g] = x;
-      sum += (x.x + x.y) + (x.z + x.w);
-    }
-    mean = prep_block_sum(sum, red, 0) / float(K);
-    float m2 = 0.f;
-    for (int g = tid; g < NG; g += kPrepThreads) {
-      const float4 x = tmp0[g];
-      const float a = x.x - mean, b = x.y - mean, c = x.z - mean, d = x.w - mean;
-      m2 += (a * a + b * b) + (c * c + d * d);
-    }
-    sdev = sqrtf(prep_block_sum(m2, red, 1) / float(K) + 1e-5f);
-  } else {
-    load_deps(dep0, tid);
-  }
-  if (tid == 0 && P.trace) P.trace[2] = globaltimer_ns();
-
-  // ---- xs per segment and its statistics
-  const float rstd = 1.0f / sdev;
-  float amax[NS], szp[NS], sxs[NS], sx[NS];
-#pragma unroll
-  for (int s = 0; s < NS; ++s) { amax[s] = 0.f; szp[s] = 0.f; sxs[s] = 0.f; sx[s] = 0.f; }
-  for (int g0 = tid, batch = 0; g0 < NG; g0 += GB * kPrepThreads, ++batch) {
-    float4 dep[GB][LN ? 1 : NS];
-    if (batch > 0) {
-      load_consts(g0);
-      load_deps(dep, g0);
-    } else {
-#pragma unroll
-      for (int i = 0; i < GB; ++i)
-#pragma unroll
-        for (int j = 0; j < (LN ? 1 : NS); ++j) dep[i][j] = dep0[i][j];
-    }
 #pragma unroll
     for (int i = 0; i < GB; ++i) {
       const int g = g0 + i * kPrepThreads;
       if (g < NG) {
         float4 xy = make_float4(0.f, 0.f, 0.f, 0.f);
         if (LN) {
-          const float4 x = tmp0[g];
+          const float4 x = xv[i];
           xy.x = cw[i].x * ((x.x - mean) * rstd) + cb[i].x;
           xy.y = cw[i].y * ((x.y - mean) * rstd) + cb[i].y;
           xy.z = cw[i].z * ((x.z - mean) * rstd) + cb[i].z;
@@ -203,36 +233,15 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
             szp[s] += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
             sxs[s] += (xs.x + xs.y) + (xs.z + xs.w);
             sx[s] += (v.x + v.y) + (v.z + v.w);
-            reinterpret_cast<float4*>(stage + size_t(s) * 4 * K)[g] = xs;  // own slot
+            reinterpret_cast<float4*>(stage + size_t(s) * 4 * K)[g] = xs;  // own slot, read back below
           }
         }
       }
     }
   }
-  // block reduction of the 4*nseg statistics: warp partials -> shared memory -> warp 0 folds the
-  // 16 rows (one lane per statistic) -> everyone reads the totals.  Columns 2.. of the scratch rows.
-#pragma unroll
-  for (int s = 0; s < NS; ++s) {
-    amax[s] = warp_max(amax[s]); szp[s] = warp_sum(szp[s]); sxs[s] = warp_sum(sxs[s]); sx[s] = warp_sum(sx[s]);
-    if (lane == 0) {
-      red[warp * 16 + 2 + s] = amax[s]; red[warp * 16 + 5 + s] = szp[s];
-      red[warp * 16 + 8 + s] = sxs[s];  red[warp * 16 + 11 + s] = sx[s];
-    }
-  }
-  __syncthreads();
-  if (warp == 0 && lane >= 2 && lane < 14) {
-    float a = red[lane];
-    for (int w = 1; w < kPrepWarps; ++w) a = lane < 5 ? fmaxf(a, red[w * 16 + lane]) : a + red[w * 16 + lane];
-    red[kPrepWarps * 16 + lane] = a;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int s = 0; s < NS; ++s) {
-    amax[s] = red[kPrepWarps * 16 + 2 + s]; szp[s] = red[kPrepWarps * 16 + 5 + s];
-    sxs[s] = red[kPrepWarps * 16 + 8 + s];  sx[s] = red[kPrepWarps * 16 + 11 + s];
-  }
+  prep_reduce_stats<NS>(amax, szp, sxs, sx, red);
 
-  // ---- digits.  The eight groups of one 32-input block are owned by eight neighbouring lanes.
+  // ---- digits, straight to global memory
 #pragma unroll
   for (int s = 0; s < NS; ++s) {
     if (s < P.nseg) {
@@ -243,53 +252,62 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
         sc.zp = szp[s]; sc.sumxs = sxs[s]; sc.sumx = sx[s]; sc.pad = 0.f;
         P.scal[s] = sc;
       }
-      unsigned char* pl = stage + size_t(s) * 4 * K;
-      for (int gb = tid - lane; gb < NG; gb += kPrepThreads) {
-        const int g = gb + lane;
-        const bool act = g < NG;
-        float4 xs = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (act) xs = reinterpret_cast<const float4*>(pl)[g];
-        __syncwarp();
-        if (act) {
-          const int X[4] = {__float2int_rn(xs.x * inv), __float2int_rn(xs.y * inv), __float2int_rn(xs.z * inv),
-                            __float2int_rn(xs.w * inv)};
-          uint32_t wa = 0u, wb = 0u, wc = 0u;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int x1 = (X[i] + 128) >> 8;   // X = x1*256 + c, c in [-128,127]
-            const int x2 = (x1 + 128) >> 8;     // x1 = x2*256 + b
-            wc |= (uint32_t(X[i]) & 0xffu) << (8 * i);
-            wb |= (uint32_t(x1) & 0xffu) << (8 * i);
-            wa |= (uint32_t(x2) & 0xffu) << (8 * i);
-          }
-          uint32_t* blk = reinterpret_cast<uint32_t*>(pl + size_t(g >> 3) * 128);
-          const int j = g & 7;
-          blk[j] = wa; blk[8 + j] = wb; blk[16 + j] = wc; blk[24 + j] = 0u;
-        }
-      }
+      const float4* src = reinterpret_cast<const float4*>(stage + size_t(s) * 4 * K);
+      unsigned char* dst = P.planes + size_t(s) * 4 * K;
+#pragma unroll 2
+      for (int g = tid; g < NG; g += kPrepThreads) store_digits(dst, g, src[g], inv);
     }
   }
-  __syncthreads();
-  // ---- staging -> global, 16 bytes per thread per step
-  const int n16 = P.nseg * K / 4;
-  for (int i = tid; i < n16; i += kPrepThreads)
-    reinterpret_cast<uint4*>(P.planes)[i] = reinterpret_cast<const uint4*>(stage)[i];
+}
+
+// PREP_XS: the previous epilogue already wrote xs and published max / sums; only digits remain.
+__device__ __forceinline__ void prep_xs(const PrepParams& P) {
+  const int tid = threadIdx.x;
+  const int NG = P.K / 4;
+  griddep_wait();
+  if (tid == 0 && P.trace) P.trace[1] = globaltimer_ns();
+  const float amax = __uint_as_float(__ldcg(&P.pub->amax_bits));
+  const float inv = amax > 0.f ? kQMax / amax : 0.f;
+  if (tid == 0) {
+    SegScalars sc;
+    sc.sd = amax > 0.f ? 1.0 / double(inv) : 0.0;
+    sc.zp = float(double(__ldcg(&P.pub->zp)) / kPubSumScale);
+    sc.sumxs = float(double(__ldcg(&P.pub->sumxs)) / kPubXsScale);
+    sc.sumx = float(double(__ldcg(&P.pub->sumx)) / kPubSumScale);
+    sc.pad = 0.f;
+    P.scal[0] = sc;
+    if (P.trace) P.trace[2] = globaltimer_ns();
+  }
+  for (int g0 = tid; g0 < NG; g0 += 4 * kPrepThreads) {
+    float4 xs[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int g = g0 + i * kPrepThreads;
+      if (g < NG) xs[i] = ld_act_v4(reinterpret_cast<const float4*>(P.seg[0].xin) + g);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int g = g0 + i * kPrepThreads;
+      if (g < NG) store_digits(P.planes, g, xs[i], inv);
+    }
+  }
 }
 
 __global__ void __launch_bounds__(kPrepThreads, 1) vector_prep_kernel(const __grid_constant__ PrepParams P) {
   extern __shared__ __align__(128) unsigned char prep_smem[];
   float* red = reinterpret_cast<float*>(prep_smem);          // [16 warps + 1][16]
-  unsigned char* stage = prep_smem + kPrepRedBytes;          // nseg * 4*K bytes
+  unsigned char* stage = prep_smem + kPrepRedBytes;          // nseg * 4*K bytes of fp32 xs
   if (threadIdx.x == 0 && P.trace) P.trace[0] = globaltimer_ns();
   griddep_launch_dependents();
-  // Three specialisations (registers per thread differ): layer norm + mix for up to three matrices;
-  // one plain matrix (long K); up to three plain matrices.
-  if (P.ln) prep_body<2, kMaxSeg, true>(P, stage, red);
+  if (P.mode == PREP_XS) prep_xs(P);
+  else if (P.mode == PREP_LN) prep_body<2, kMaxSeg, true>(P, stage, red);
   else if (P.nseg == 1) prep_body<8, 1, false>(P, stage, red);
   else prep_body<2, kMaxSeg, false>(P, stage, red);
   if (threadIdx.x == 0 && P.trace) P.trace[3] = globaltimer_ns();
 }
 
-inline size_t prep_smem_bytes(int K, int nseg) { return size_t(kPrepRedBytes) + size_t(nseg) * 4 * K; }
+inline size_t prep_smem_bytes(int K, int nseg, int mode) {
+  return size_t(kPrepRedBytes) + (mode == PREP_XS ? 0 : size_t(nseg) * 4 * K);
+}
 
 }  // namespace b200

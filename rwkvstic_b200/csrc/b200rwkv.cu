@@ -118,14 +118,14 @@ cudaError_t launch_vector_prep(const PrepParams& P, bool pdl, cudaStream_t strea
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const size_t smem = prep_smem_bytes(P.K, P.nseg, P.mode);
+  const size_t smem = prep_smem_bytes(P.K, P.mode);
   if (smem > 200 * 1024) {
     *why = "unsupported shape: activation planes do not fit the preparation kernel's shared memory";
     return cudaErrorInvalidValue;
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(1);
+  cfg.gridDim = dim3(prep_grid(P.nseg, P.mode));
   cfg.blockDim = dim3(kPrepThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -163,6 +163,8 @@ static void set_next(GemvParams& P, const b200rwkv_matrix* const* next, int n) {
 static void fill_prep_seg(PrepSeg& s, const b200rwkv_matrix& m, const float* mix, const float* xin) {
   s.ry = m.ry; s.my = m.my; s.mix = mix; s.xin = xin;
 }
+
+static bool wants_sums(const b200rwkv_matrix& m) { return m.rx || m.mx || m.half != 0.f; }
 
 // ---------------------------------------------------------------------------------------- small kernels
 // x = LayerNorm(emb[token]) (the reference's emb.py:8-9 gather followed by ln_in, opt.py:63-64).
@@ -206,8 +208,8 @@ embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ to
   for (int i = tid; i < D; i += 512) {
     const float y = w[i] * ((row[i] - mean) / sdev) + b[i];
     out[i] = y;
-    p_sum += __double2ll_rn(double(y) * kPubSumScale);
-    p_sq += __double2ll_rn(double(y) * double(y) * kPubSqScale);
+    p_sum += __float2ll_rn(y * kPubSumScale);
+    p_sq += __float2ll_rn(__fmul_rn(y, y) * kPubSqScale);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) { p_sum += __shfl_xor_sync(0xffffffffu, p_sum, o); p_sq += __shfl_xor_sync(0xffffffffu, p_sq, o); }
@@ -257,7 +259,7 @@ constexpr size_t kTraceStride = 1024 * 8;  // u64 slots per GEMV launch in a dec
 
 struct Workspace {
   int* status;
-  float *xa, *xb, *xs_att, *rf, *xs_ffn;
+  float *xa, *xb, *xs_att, *rf, *xs_ffn, *shift_new;
   unsigned char* planes;
   SegScalars* scal;
   PubSlot* pub;      // one slot per GEMV launch of a step
@@ -277,6 +279,7 @@ static Workspace carve(const b200rwkv_model* m, void* base) {
   w.xb = reinterpret_cast<float*>(take(D));
   w.xs_att = reinterpret_cast<float*>(take(D));    // sigmoid(r)*wkv, already times the output matrix's ry
   w.rf = reinterpret_cast<float*>(take(D));
+  w.shift_new = reinterpret_cast<float*>(take(D));  // next token-shift carry, committed by the following GEMV launch
   w.xs_ffn = reinterpret_cast<float*>(take(F));    // relu(k)^2, already times the value matrix's ry
   w.planes = reinterpret_cast<unsigned char*>(take(3 * D > F ? 3 * D : F));  // 4*K bytes per matrix
   w.scal = reinterpret_cast<SegScalars*>(take(sizeof(SegScalars) * kMaxSeg));
@@ -333,7 +336,7 @@ static int gemv_u8_impl(int nmat, const b200rwkv_matrix* mats, const float* cons
   int* status = reinterpret_cast<int*>(wsb);
   unsigned char* planes = reinterpret_cast<unsigned char*>(wsb + 256);
   SegScalars* scal = reinterpret_cast<SegScalars*>(wsb + 256 + align256(size_t(nmat) * 4 * K));
-  Q.nseg = nmat; Q.K = K; Q.mode = PREP_PLAIN; Q.planes = planes; Q.scal = scal;
+  Q.nseg = nmat; Q.K = K; Q.mode = PREP_PLAIN; Q.planes = planes; Q.scal = scal; Q.need_sums = 1;
   Q.trace = trace ? trace + 1023 * 8 : nullptr;
   P.nseg = nmat; P.K = K; P.epi = EPI_GENERIC; P.accumulate = accumulate ? 1 : 0;
   P.planes = planes; P.scal = scal; P.status = status; P.trace = trace;
@@ -398,7 +401,7 @@ int b200rwkv_gemv_u8_static(int nmat, const b200rwkv_matrix* mats, const float* 
                 "(use b200rwkv_gemv_u8 with a caller-provided workspace)", need, kStaticPlaneBytes);
   unsigned char* planes = scratch_of_device[dev];
   SegScalars* scal = reinterpret_cast<SegScalars*>(planes + kStaticPlaneBytes);
-  Q.nseg = nmat; Q.K = K; Q.mode = PREP_PLAIN; Q.planes = planes; Q.scal = scal;
+  Q.nseg = nmat; Q.K = K; Q.mode = PREP_PLAIN; Q.planes = planes; Q.scal = scal; Q.need_sums = 1;
   P.nseg = nmat; P.K = K; P.epi = EPI_GENERIC; P.accumulate = accumulate ? 1 : 0;
   P.planes = planes; P.scal = scal; P.status = status;
   const char* why = "";
@@ -489,7 +492,8 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     fill_prep_seg(Q.seg[0], ly.att_key, ly.att_mix_k, nullptr);
     fill_prep_seg(Q.seg[1], ly.att_value, ly.att_mix_v, nullptr);
     fill_prep_seg(Q.seg[2], ly.att_receptance, ly.att_mix_r, nullptr);
-    Q.nseg = 3; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xa; Q.ln_w = ly.ln1_w; Q.ln_b = ly.ln1_b; Q.shift = st;
+    Q.nseg = 3; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xa; Q.ln_w = ly.ln1_w; Q.ln_b = ly.ln1_b; Q.shift = st; Q.shift_out = ws.shift_new;
+    Q.need_sums = wants_sums(ly.att_key) || wants_sums(ly.att_value) || wants_sums(ly.att_receptance);
     Q.pub = pub + 0;
     Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
@@ -498,6 +502,7 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     P.nseg = 3; P.K = D; P.planes = ws.planes; P.scal = ws.scal;
     P.epi = EPI_WKV; P.wkv_w = ly.time_decay; P.wkv_u = ly.time_first;
     P.aa = st + 2 * size_t(D); P.bb = st + 3 * size_t(D); P.pp = st + 4 * size_t(D);
+    P.commit_src = ws.shift_new; P.commit_dst = st; P.commit_n = D;
     P.seg[0].xs_out = ws.xs_att; P.seg[0].xs_ry = ly.att_output.ry; P.seg[0].xs_my = ly.att_output.my; P.seg[0].pub_xs = pub + 1;
     { const b200rwkv_matrix* nx[1] = {&ly.att_output}; set_next(P, nx, 1); }
     P.status = ws.status; P.trace = trace_slice();
@@ -519,7 +524,8 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], ly.ffn_key, ly.ffn_mix_k, nullptr);
     fill_prep_seg(Q.seg[1], ly.ffn_receptance, ly.ffn_mix_r, nullptr);
-    Q.nseg = 2; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xb; Q.ln_w = ly.ln2_w; Q.ln_b = ly.ln2_b; Q.shift = st + size_t(D);
+    Q.nseg = 2; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xb; Q.ln_w = ly.ln2_w; Q.ln_b = ly.ln2_b; Q.shift = st + size_t(D); Q.shift_out = ws.shift_new;
+    Q.need_sums = wants_sums(ly.ffn_key) || wants_sums(ly.ffn_receptance);
     Q.pub = pub + 2;
     Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;
@@ -528,6 +534,7 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     P.seg[0].xs_out = ws.xs_ffn; P.seg[0].xs_ry = ly.ffn_value.ry; P.seg[0].xs_my = ly.ffn_value.my; P.seg[0].pub_xs = pub + 3;
     fill_seg(P.seg[1], ly.ffn_receptance); P.seg[1].act = ACT_SIGMOID; P.seg[1].out = ws.rf;
     P.nseg = 2; P.K = D; P.planes = ws.planes; P.scal = ws.scal; P.epi = EPI_GENERIC;
+    P.commit_src = ws.shift_new; P.commit_dst = st + size_t(D); P.commit_n = D;
     { const b200rwkv_matrix* nx[1] = {&ly.ffn_value}; set_next(P, nx, 1); }
     P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, F > D ? F : D, true, s, &why)) != cudaSuccess) goto launch_failed;
@@ -559,6 +566,7 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], m->head, nullptr, nullptr);
     Q.nseg = 1; Q.K = D; Q.mode = PREP_LN; Q.ln_x = ws.xa; Q.ln_w = m->ln_out_w; Q.ln_b = m->ln_out_b;
+    Q.need_sums = wants_sums(m->head);
     Q.pub = ws.pub + 4 * size_t(L);
     Q.planes = ws.planes; Q.scal = ws.scal; Q.trace = trace ? trace + size_t(li) * kTraceStride + 1023 * 8 : nullptr;
     if ((e = launch_vector_prep(Q, true, s, &why)) != cudaSuccess) goto launch_failed;

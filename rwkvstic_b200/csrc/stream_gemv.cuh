@@ -9,8 +9,8 @@
 // as [K/128][N][128 bytes], a stage is one box of 16 rows x one K-chunk (<= 2048 bytes per row) and
 // lands as [K-chunk/128][16 rows][128 B] with the 128-byte swizzle, so one instruction moves 32 KB
 // and ldmatrix reads it bank-conflict free.  16 consumer warps split the K-chunk of every stage.  The grid
-// leaves one SM free: that is where the activation-preparation kernel (vector_prep.cuh) of the
-// NEXT launch runs while this one streams.
+// leaves three SMs free: that is where the activation-preparation kernel (vector_prep.cuh, one CTA
+// per matrix) of the NEXT launch runs while this one streams.
 //
 // Arithmetic: the activations arrive as 24-bit fixed point X[k] = rint(xs[k]*inv) in three signed
 // base-256 digit planes (X = a*65536 + b*256 + c), prepared once per launch by vector_prep_kernel.
@@ -38,6 +38,7 @@ constexpr int kGemvThreads = kConsumers + 32;   // + one producer warp
 constexpr int kMaxStages = 16;
 constexpr int kTileRows = 16;                   // rows per stage = MMA M
 constexpr int kChunkMax = 2048;                 // bytes of one row per stage
+constexpr int kInFlight = 2;                    // stages in flight while the ring is first filled (pacing)
 constexpr int kSmemLimit = 227 * 1024;          // dynamic shared memory per CTA on sm_100
 
 enum Act : int { ACT_NONE = 0, ACT_RELUSQ = 1, ACT_SIGMOID = 2 };
@@ -94,6 +95,11 @@ struct GemvParams {
   int next_n[kMaxSeg];
   int next_nseg, next_k;
   int next_prefetch;       // bytes per CTA, 0 = none
+  // deferred state commit done by CTA 0 once the dependency has resolved: dst[0..n) = src[0..n)
+  // (the token-shift carry the preparation kernel computed but could not write in place)
+  const float* commit_src;
+  float* commit_dst;
+  int commit_n;
 };
 
 // Shared-memory map (byte offsets)
@@ -116,7 +122,7 @@ inline bool plan_gemv(int K, int nseg, int max_n, int num_sms, GemvPlan* p) {
   p->nchunks = (K + kChunkMax - 1) / kChunkMax;
   p->kc = ((K + p->nchunks - 1) / p->nchunks + 127) / 128 * 128;
   p->stage_bytes = kTileRows * p->kc;
-  p->grid = num_sms - 1 < max_n ? num_sms - 1 : max_n;  // one SM stays free for vector_prep_kernel
+  p->grid = num_sms - kMaxSeg < max_n ? num_sms - kMaxSeg : max_n;  // three SMs stay free for vector_prep_kernel
   if (p->grid < 1) p->grid = 1;
   const int rpc = (max_n + p->grid - 1) / p->grid;
   p->rpc16 = (rpc + 15) / 16 * 16;
@@ -219,6 +225,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
               ok = false;
               break;
             }
+            // Pacing of the first ring fill: at most kInFlight stages requested but not yet landed.
+            // All CTAs start their stream at the moment the preparation kernel of this very launch
+            // does its one latency-critical round trip; without pacing that load would sit behind
+            // ~24 MB of queued weight requests (3+ us).  Once the ring has been filled, requests
+            // follow consumption and the full ring depth may be in flight.
+            if (issued >= kInFlight && issued < P.stages) {
+              const int j = issued - kInFlight;
+              if (!mbar_wait_bounded(full0 + 8 * (j % P.stages), uint32_t(j / P.stages) & 1u, abort_flag)) {
+                if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
+                ok = false;
+                break;
+              }
+            }
             mbar_arrive_expect_tx(full0 + 8 * slot, uint32_t(P.stage_bytes));
             tma_load_3d(smem_u32(ring + size_t(slot) * P.stage_bytes), &P.tmap[s], 0, r0[s] + row, ch * (P.kc / 128),
                         full0 + 8 * slot);
@@ -255,9 +274,35 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
       bulk_g2s(smem_u32(planes), P.planes, plane_bytes, plane_bar);
     }
     if (tid < P.nseg * 8) reinterpret_cast<float*>(scal)[tid] = __ldcg(reinterpret_cast<const float*>(P.scal) + tid);
+    if (cta == 0 && P.commit_n > 0) {
+      for (int i = tid; i < P.commit_n / 4; i += kConsumers)
+        reinterpret_cast<float4*>(P.commit_dst)[i] = ld_act_v4(reinterpret_cast<const float4*>(P.commit_src) + i);
+    }
     bool dead = !__all_sync(0xffffffffu, mbar_wait_bounded(plane_bar, 0, abort_flag));
     named_bar_sync(1, kConsumers);  // scalars and zeroed row sums visible to every consumer warp
     if (tid == 0) B200_TRACE(4);
+
+    // ---- operands of the epilogue for this thread's first row of every segment: requested now,
+    // used after the main loop, so their latency hides behind the weight stream
+    float e_res[kMaxSeg], e_gate[kMaxSeg], e_ry[kMaxSeg], e_my[kMaxSeg], e_rx[kMaxSeg], e_mx[kMaxSeg];
+    float e_aa = 0.f, e_bb = 0.f, e_pp = 0.f, e_w = 0.f, e_u = 0.f;
+#pragma unroll
+    for (int s = 0; s < kMaxSeg; ++s) {
+      e_res[s] = 0.f; e_gate[s] = 1.f; e_ry[s] = 0.f; e_my[s] = 0.f; e_rx[s] = 1.f; e_mx[s] = 0.f;
+      if (s < P.nseg && tid < nr[s]) {
+        const int n = r0[s] + tid;
+        if (P.seg[s].res) e_res[s] = ld_act_f32(P.seg[s].res + n);
+        if (P.seg[s].gate) e_gate[s] = ld_act_f32(P.seg[s].gate + n);
+        if (P.seg[s].rx) e_rx[s] = ld_param_f32(P.seg[s].rx + n);
+        if (P.seg[s].mx) e_mx[s] = ld_param_f32(P.seg[s].mx + n);
+        if (P.seg[s].pub_xs) { e_ry[s] = ld_param_f32(P.seg[s].xs_ry + n); e_my[s] = ld_param_f32(P.seg[s].xs_my + n); }
+      }
+    }
+    if (P.epi == EPI_WKV && tid < nr[0]) {
+      const int n = r0[0] + tid;
+      e_aa = ld_act_f32(P.aa + n); e_bb = ld_act_f32(P.bb + n); e_pp = ld_act_f32(P.pp + n);
+      e_w = ld_param_f32(P.wkv_w + n); e_u = ld_param_f32(P.wkv_u + n);
+    }
 
     // ---- main loop: integer tensor-core dot products over the streamed 16-row tiles
     {
@@ -326,39 +371,40 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
     named_bar_sync(1, kConsumers);
     if (tid == 0) B200_TRACE(5);
 
-    // ---- epilogue: affine terms + the element-wise op that follows this matrix in the block
-    auto value = [&](int s, int row, int n) -> float {
+    // ---- epilogue: affine terms + the element-wise op that follows this matrix in the block.
+    // `first` = this is the thread's first row of the segment, whose operands were preloaded.
+    auto value = [&](int s, int row, int n, bool first) -> float {
       const int* rs = rowsum + (size_t(s) * P.rpc16 + row) * 4;
       const long long I = (long long)rs[0] * 65536 + (long long)rs[1] * 256 + (long long)rs[2];
-      const double main = double(I) * scal[s].sd;
-      float y = float(main) + P.seg[s].half * scal[s].sumxs;
-      if (P.seg[s].rx) y *= P.seg[s].rx[n];
+      float y = __fmul_rn(__ll2float_rn(I), scal[s].sd) + P.seg[s].half * scal[s].sumxs;
+      if (P.seg[s].rx) y *= first ? e_rx[s] : P.seg[s].rx[n];
       y += scal[s].zp;
-      if (P.seg[s].mx) y += P.seg[s].mx[n] * scal[s].sumx;
+      if (P.seg[s].mx) y += (first ? e_mx[s] : P.seg[s].mx[n]) * scal[s].sumx;
       return y;
     };
     // per-thread partials of what this launch publishes for the next one
     long long p_sum = 0, p_sq = 0, p_zp = 0, p_sxs = 0, p_sx = 0;
     float p_amax = 0.f;
     PubSlot* pub_xs = nullptr;
-    auto publish_xs = [&](const GemvSeg& sg, int n, float v) {
-      const float xs = v * sg.xs_ry[n];
+    auto publish_xs = [&](const GemvSeg& sg, int n, float v, float ry, float my) {
+      const float xs = v * ry;
       sg.xs_out[n] = xs;
       p_amax = fmaxf(p_amax, fabsf(xs));
-      p_zp += __double2ll_rn(double(v * sg.xs_my[n]) * kPubSumScale);
-      p_sxs += __double2ll_rn(double(xs) * kPubXsScale);
-      p_sx += __double2ll_rn(double(v) * kPubSumScale);
+      p_zp += __float2ll_rn(v * my * kPubSumScale);   // scaling by a power of two is exact
+      p_sxs += __float2ll_rn(xs * kPubXsScale);
+      p_sx += __float2ll_rn(v * kPubSumScale);
     };
     if (P.epi == EPI_WKV) {
       pub_xs = P.seg[0].pub_xs;
       for (int row = tid; row < nr[0]; row += kConsumers) {
         const int n = r0[0] + row;
-        const float k = value(0, row, n), v = value(1, row, n), r = sigmoidf_(value(2, row, n));
-        float aa = P.aa[n], bb = P.bb[n], pp = P.pp[n];
-        const float y = wkv_step(k, v, P.wkv_w[n], P.wkv_u[n], aa, bb, pp);
+        const bool first = row == tid;
+        const float k = value(0, row, n, first), v = value(1, row, n, first), r = sigmoidf_(value(2, row, n, first));
+        float aa = first ? e_aa : P.aa[n], bb = first ? e_bb : P.bb[n], pp = first ? e_pp : P.pp[n];
+        const float y = wkv_step(k, v, first ? e_w : P.wkv_w[n], first ? e_u : P.wkv_u[n], aa, bb, pp);
         P.aa[n] = aa; P.bb[n] = bb; P.pp[n] = pp;
         if (P.wkv_out) P.wkv_out[n] = r * y;
-        if (pub_xs) publish_xs(P.seg[0], n, r * y);
+        if (pub_xs) publish_xs(P.seg[0], n, r * y, first ? e_ry[0] : P.seg[0].xs_ry[n], first ? e_my[0] : P.seg[0].xs_my[n]);
       }
     } else {
 #pragma unroll
@@ -367,17 +413,19 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
           if (P.seg[s].pub_xs) pub_xs = P.seg[s].pub_xs;
           for (int row = tid; row < nr[s]; row += kConsumers) {
             const int n = r0[s] + row;
-            float y = value(s, row, n);
+            const bool first = row == tid;
+            float y = value(s, row, n, first);
             if (P.seg[s].act == ACT_RELUSQ) { y = fmaxf(y, 0.f); y *= y; }
             else if (P.seg[s].act == ACT_SIGMOID) y = sigmoidf_(y);
-            if (P.seg[s].gate) y *= P.seg[s].gate[n];
-            if (P.seg[s].res) y += P.seg[s].res[n];
+            if (P.seg[s].gate) y *= first ? e_gate[s] : P.seg[s].gate[n];
+            if (P.seg[s].res) y += first ? e_res[s] : P.seg[s].res[n];
             if (P.accumulate) y += P.seg[s].out[n];
             if (P.seg[s].out) P.seg[s].out[n] = y;
-            if (P.seg[s].pub_xs) publish_xs(P.seg[s], n, y);
+            if (P.seg[s].pub_xs)
+              publish_xs(P.seg[s], n, y, first ? e_ry[s] : P.seg[s].xs_ry[n], first ? e_my[s] : P.seg[s].xs_my[n]);
             if (s == 0 && P.pub_ln) {
-              p_sum += __double2ll_rn(double(y) * kPubSumScale);
-              p_sq += __double2ll_rn(double(y) * double(y) * kPubSqScale);
+              p_sum += __float2ll_rn(y * kPubSumScale);
+              p_sq += __float2ll_rn(__fmul_rn(y, y) * kPubSqScale);
             }
           }
         }

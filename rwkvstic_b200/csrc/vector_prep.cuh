@@ -1,7 +1,8 @@
-// Activation preparation for the streaming GEMV: one CTA turns the raw activation vector(s) into
-// the fixed-point digit planes and scalar terms that every GEMV CTA needs, ONCE, instead of every
-// CTA recomputing them.  It runs on the SM the GEMV grid leaves free, so it can be resident while
-// the previous GEMV still streams and load its parameter vectors before its dependency resolves.
+// Activation preparation for the streaming GEMV: one CTA per matrix turns the raw activation
+// vector into the fixed-point digit planes and scalar terms that every GEMV CTA needs, ONCE,
+// instead of every CTA recomputing them.  The CTAs run on the SMs the GEMV grid leaves free, so they
+// can be resident while the previous GEMV still streams and load their parameter vectors before
+// their dependency resolves.
 //
 // Per segment s (up to three matrices share one launch):
 //   v_s[k]  = input of matrix s: either xin_s[k], or LayerNorm(ln_x)[k] mixed with the carried
@@ -28,9 +29,9 @@ constexpr float kQMax = 8355000.0f;  // |X| <= QMAX keeps all three signed digit
 
 // Fixed-point units of the published sums (int64 accumulators: exact, order-independent).  The
 // ranges they leave: |sum x|, sum x^2, |sum v*my|, |sum v| < 2.1e9 and |sum xs| < 8.3e6.
-constexpr double kPubSumScale = 4294967296.0;        // 2^32
-constexpr double kPubSqScale = 4294967296.0;         // 2^32
-constexpr double kPubXsScale = 1099511627776.0;      // 2^40 (xs = v * ry is small: ry ~ 1e-3)
+constexpr float kPubSumScale = 4294967296.0f;        // 2^32
+constexpr float kPubSqScale = 4294967296.0f;         // 2^32
+constexpr float kPubXsScale = 1099511627776.0f;      // 2^40 (xs = v * ry is small: ry ~ 1e-3)
 
 // What the epilogue of one launch publishes for the preparation of the next (zeroed once per step).
 struct PubSlot {
@@ -44,8 +45,9 @@ struct PubSlot {
 static_assert(sizeof(PubSlot) == 128, "PubSlot is one 128-byte line");
 
 struct SegScalars {   // 32 bytes per segment, written by the prep kernel, read by every GEMV CTA
-  double sd;          // 1 / inv
-  float zp, sumxs, sumx, pad;
+  float sd;           // fp32(1 / inv): value of one fixed-point unit
+  float zp, sumxs, sumx;
+  float pad[4];
 };
 
 enum PrepMode : int {
@@ -68,8 +70,10 @@ struct PrepParams {
   const float* ln_x;      // [K]
   const float* ln_w;
   const float* ln_b;
-  float* shift;           // [K] carried previous-token vector: read, then overwritten with the
-                          // layer-norm output (the state row of modules/block.py:61-64); may be null
+  const float* shift;     // [K] carried previous-token vector (the state row of modules/block.py:61-64)
+  float* shift_out;       // [K] scratch that receives the layer-norm output = the next carry; the GEMV
+                          // launch that follows copies it into the state row (may be null)
+  int need_sums;          // also produce sum xs and sum v (only matrices with rx / mx / half need them)
   const PubSlot* pub;     // published statistics (PREP_LN, PREP_XS)
   unsigned char* planes;  // out: nseg * 4*K bytes
   SegScalars* scal;       // out: nseg entries
@@ -102,44 +106,36 @@ __device__ __forceinline__ void store_digits(unsigned char* planes, int g, float
   blk[24 + j] = 0u;
 }
 
-// Block reduction of the 4*nseg statistics: warp partials -> shared memory -> warp 0 folds the rows
-// (one lane per statistic) -> everyone reads the totals.
-template <int NS>
-__device__ __forceinline__ void prep_reduce_stats(float (&amax)[NS], float (&szp)[NS], float (&sxs)[NS], float (&sx)[NS],
-                                                  float* red) {
+// Block reduction of one segment's statistics (max|xs|, sum v*my, sum xs, sum v): warp partials ->
+// shared memory -> warp 0 folds the rows (one lane per statistic) -> everyone reads the totals.
+__device__ __forceinline__ void prep_reduce_stats(float& amax, float& szp, float& sxs, float& sx, float* red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-#pragma unroll
-  for (int s = 0; s < NS; ++s) {
-    amax[s] = warp_max(amax[s]); szp[s] = warp_sum(szp[s]); sxs[s] = warp_sum(sxs[s]); sx[s] = warp_sum(sx[s]);
-    if (lane == 0) {
-      red[warp * 16 + 2 + s] = amax[s]; red[warp * 16 + 5 + s] = szp[s];
-      red[warp * 16 + 8 + s] = sxs[s];  red[warp * 16 + 11 + s] = sx[s];
-    }
-  }
+  amax = warp_max(amax); szp = warp_sum(szp); sxs = warp_sum(sxs); sx = warp_sum(sx);
+  if (lane == 0) { red[warp * 4 + 0] = amax; red[warp * 4 + 1] = szp; red[warp * 4 + 2] = sxs; red[warp * 4 + 3] = sx; }
   __syncthreads();
-  if (warp == 0 && lane >= 2 && lane < 14) {
+  if (warp == 0 && lane < 4) {
     float a = red[lane];
-    for (int w = 1; w < kPrepWarps; ++w) a = lane < 5 ? fmaxf(a, red[w * 16 + lane]) : a + red[w * 16 + lane];
-    red[kPrepWarps * 16 + lane] = a;
+    for (int w = 1; w < kPrepWarps; ++w) a = lane == 0 ? fmaxf(a, red[w * 4 + lane]) : a + red[w * 4 + lane];
+    red[kPrepWarps * 4 + lane] = a;
   }
   __syncthreads();
-#pragma unroll
-  for (int s = 0; s < NS; ++s) {
-    amax[s] = red[kPrepWarps * 16 + 2 + s]; szp[s] = red[kPrepWarps * 16 + 5 + s];
-    sxs[s] = red[kPrepWarps * 16 + 8 + s];  sx[s] = red[kPrepWarps * 16 + 11 + s];
-  }
+  amax = red[kPrepWarps * 4 + 0]; szp = red[kPrepWarps * 4 + 1]; sxs = red[kPrepWarps * 4 + 2]; sx = red[kPrepWarps * 4 + 3];
 }
 
-// PREP_PLAIN and PREP_LN.  GB = groups of four inputs a thread keeps in registers per batch; NS =
-// segments compiled in.  xs is parked in shared memory (`stage`, 16 bytes per group and segment)
+// PREP_PLAIN and PREP_LN: CTA s prepares segment s (the segments share nothing but the layer norm,
+// which every CTA evaluates for itself from the published sums).  GB = groups of four inputs a
+// thread keeps in registers per batch.  xs is parked in shared memory (`stage`, 16 bytes per group)
 // between the statistics pass and the digit pass.
-template <int GB, int NS, bool LN>
+template <int GB, bool LN>
 __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* stage, float* red) {
   const int tid = threadIdx.x;
   const int K = P.K, NG = K / 4;
+  const int sidx = blockIdx.x;
+  const PrepSeg& S = P.seg[sidx];
+  const bool mixing = LN && S.mix != nullptr;
 
   // ---- parameter vectors of the first batch: loaded before the dependency wait
-  float4 cw[LN ? GB : 1], cb[LN ? GB : 1], cmu[GB][NS], cry[GB][NS], cmy[GB][NS];
+  float4 cw[LN ? GB : 1], cb[LN ? GB : 1], cmu[LN ? GB : 1], cry[GB], cmy[GB];
   auto load_consts = [&](int g0) {
 #pragma unroll
     for (int i = 0; i < GB; ++i) {
@@ -148,166 +144,145 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
         if (LN) {
           cw[i] = ld_param_v4(reinterpret_cast<const float4*>(P.ln_w) + g);
           cb[i] = ld_param_v4(reinterpret_cast<const float4*>(P.ln_b) + g);
+          if (mixing) cmu[i] = ld_param_v4(reinterpret_cast<const float4*>(S.mix) + g);
         }
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-          if (s < P.nseg) {
-            cry[i][s] = ld_param_v4(reinterpret_cast<const float4*>(P.seg[s].ry) + g);
-            cmy[i][s] = ld_param_v4(reinterpret_cast<const float4*>(P.seg[s].my) + g);
-            if (LN && P.seg[s].mix) cmu[i][s] = ld_param_v4(reinterpret_cast<const float4*>(P.seg[s].mix) + g);
-          }
-        }
+        cry[i] = ld_param_v4(reinterpret_cast<const float4*>(S.ry) + g);
+        cmy[i] = ld_param_v4(reinterpret_cast<const float4*>(S.my) + g);
       }
     }
   };
   load_consts(tid);
 
   griddep_wait();  // everything below reads what earlier kernels wrote
-  if (tid == 0 && P.trace) P.trace[1] = globaltimer_ns();
+  if (tid == 0 && P.trace && sidx == 0) P.trace[1] = globaltimer_ns();
 
   float mean = 0.f, rstd = 1.f;
-  if (LN) {
-    // the launch that wrote ln_x also published its sum and sum of squares (exact integer atomics)
-    const double m = double(__ldcg(&P.pub->sum)) / (kPubSumScale * double(K));
-    const double ex2 = double(__ldcg(&P.pub->sq)) / (kPubSqScale * double(K));
-    const double var = ex2 - m * m;
-    mean = float(m);
-    rstd = 1.0f / sqrtf(float(var > 0.0 ? var : 0.0) + 1e-5f);
-  }
-  if (tid == 0 && P.trace) P.trace[2] = globaltimer_ns();
-
-  // ---- xs per segment and its statistics
-  float amax[NS], szp[NS], sxs[NS], sx[NS];
-#pragma unroll
-  for (int s = 0; s < NS; ++s) { amax[s] = 0.f; szp[s] = 0.f; sxs[s] = 0.f; sx[s] = 0.f; }
+  float amax = 0.f, szp = 0.f, sxs = 0.f, sx = 0.f;
+  float4* park = reinterpret_cast<float4*>(stage);
   for (int g0 = tid, batch = 0; g0 < NG; g0 += GB * kPrepThreads, ++batch) {
     if (batch > 0) load_consts(g0);
     // activation loads of the batch go out together: one memory round trip
-    float4 xv[LN ? GB : 1], dep[GB][LN ? 1 : NS];
+    float4 xv[GB], tc[LN ? GB : 1];
 #pragma unroll
     for (int i = 0; i < GB; ++i) {
       const int g = g0 + i * kPrepThreads;
       if (g < NG) {
         if (LN) {
           xv[i] = ld_act_v4(reinterpret_cast<const float4*>(P.ln_x) + g);
-          dep[i][0] = P.shift ? ld_act_v4(reinterpret_cast<const float4*>(P.shift) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+          tc[i] = mixing && P.shift ? ld_act_v4(reinterpret_cast<const float4*>(P.shift) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
-#pragma unroll
-          for (int s = 0; s < NS; ++s)
-            if (s < P.nseg) dep[i][s] = ld_act_v4(reinterpret_cast<const float4*>(P.seg[s].xin) + g);
+          xv[i] = ld_act_v4(reinterpret_cast<const float4*>(S.xin) + g);
         }
       }
+    }
+    if (LN && batch == 0) {
+      // same round trip: the launch that wrote ln_x published its sum and sum of squares (exact
+      // integer atomics).  fp32 from here on: the fp64 pipe of this GPU is slow.
+      mean = __ll2float_rn(__ldcg(&P.pub->sum)) * (1.0f / (kPubSumScale * float(K)));
+      const float ex2 = __ll2float_rn(__ldcg(&P.pub->sq)) * (1.0f / (kPubSqScale * float(K)));
+      rstd = 1.0f / sqrtf(fmaxf(ex2 - mean * mean, 0.f) + 1e-5f);
+      if (tid == 0 && P.trace && sidx == 0) P.trace[2] = globaltimer_ns();
     }
 #pragma unroll
     for (int i = 0; i < GB; ++i) {
       const int g = g0 + i * kPrepThreads;
       if (g < NG) {
-        float4 xy = make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 v = xv[i];
         if (LN) {
           const float4 x = xv[i];
+          float4 xy;
           xy.x = cw[i].x * ((x.x - mean) * rstd) + cb[i].x;
           xy.y = cw[i].y * ((x.y - mean) * rstd) + cb[i].y;
           xy.z = cw[i].z * ((x.z - mean) * rstd) + cb[i].z;
           xy.w = cw[i].w * ((x.w - mean) * rstd) + cb[i].w;
-          if (P.shift) reinterpret_cast<float4*>(P.shift)[g] = xy;  // this thread read it just above
-        }
-#pragma unroll
-        for (int s = 0; s < NS; ++s) {
-          if (s < P.nseg) {
-            float4 v;
-            if (LN) {
-              v = xy;
-              if (P.seg[s].mix) {
-                const float4 mu = cmu[i][s], tc = dep[i][0];
-                v.x = xy.x * mu.x + tc.x * (1.f - mu.x);
-                v.y = xy.y * mu.y + tc.y * (1.f - mu.y);
-                v.z = xy.z * mu.z + tc.z * (1.f - mu.z);
-                v.w = xy.w * mu.w + tc.w * (1.f - mu.w);
-              }
-            } else {
-              v = dep[i][s];
-            }
-            const float4 ry = cry[i][s], my = cmy[i][s];
-            const float4 xs = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
-            amax[s] = fmaxf(amax[s], fmaxf(fmaxf(fabsf(xs.x), fabsf(xs.y)), fmaxf(fabsf(xs.z), fabsf(xs.w))));
-            szp[s] += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
-            sxs[s] += (xs.x + xs.y) + (xs.z + xs.w);
-            sx[s] += (v.x + v.y) + (v.z + v.w);
-            reinterpret_cast<float4*>(stage + size_t(s) * 4 * K)[g] = xs;  // own slot, read back below
+          // the new carry cannot go to the state row in place (the other CTAs are reading it): CTA 0
+          // parks it in shift_out and the GEMV launch that follows commits it
+          if (sidx == 0 && P.shift_out) reinterpret_cast<float4*>(P.shift_out)[g] = xy;
+          v = xy;
+          if (mixing) {
+            const float4 mu = cmu[i], t = tc[i];
+            v.x = xy.x * mu.x + t.x * (1.f - mu.x);
+            v.y = xy.y * mu.y + t.y * (1.f - mu.y);
+            v.z = xy.z * mu.z + t.z * (1.f - mu.z);
+            v.w = xy.w * mu.w + t.w * (1.f - mu.w);
           }
         }
+        const float4 ry = cry[i], my = cmy[i];
+        const float4 xs = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xs.x), fabsf(xs.y)), fmaxf(fabsf(xs.z), fabsf(xs.w))));
+        szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
+        if (P.need_sums) {
+          sxs += (xs.x + xs.y) + (xs.z + xs.w);
+          sx += (v.x + v.y) + (v.z + v.w);
+        }
+        park[g] = xs;  // own slot, read back below
       }
     }
   }
-  prep_reduce_stats<NS>(amax, szp, sxs, sx, red);
+  prep_reduce_stats(amax, szp, sxs, sx, red);
 
   // ---- digits, straight to global memory
-#pragma unroll
-  for (int s = 0; s < NS; ++s) {
-    if (s < P.nseg) {
-      const float inv = amax[s] > 0.f ? kQMax / amax[s] : 0.f;
-      if (tid == 0) {
-        SegScalars sc;
-        sc.sd = amax[s] > 0.f ? 1.0 / double(inv) : 0.0;
-        sc.zp = szp[s]; sc.sumxs = sxs[s]; sc.sumx = sx[s]; sc.pad = 0.f;
-        P.scal[s] = sc;
-      }
-      const float4* src = reinterpret_cast<const float4*>(stage + size_t(s) * 4 * K);
-      unsigned char* dst = P.planes + size_t(s) * 4 * K;
-#pragma unroll 2
-      for (int g = tid; g < NG; g += kPrepThreads) store_digits(dst, g, src[g], inv);
-    }
+  const float inv = amax > 0.f ? kQMax / amax : 0.f;
+  if (tid == 0) {
+    SegScalars sc;
+    sc.sd = amax > 0.f ? float(1.0 / double(inv)) : 0.f;
+    sc.zp = szp; sc.sumxs = sxs; sc.sumx = sx;
+    sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
+    P.scal[sidx] = sc;
   }
+  unsigned char* dst = P.planes + size_t(sidx) * 4 * K;
+#pragma unroll 2
+  for (int g = tid; g < NG; g += kPrepThreads) store_digits(dst, g, park[g], inv);
 }
 
 // PREP_XS: the previous epilogue already wrote xs and published max / sums; only digits remain.
+// The xs loads of the first batch and the loads of the published scalars go out together.
 __device__ __forceinline__ void prep_xs(const PrepParams& P) {
+  constexpr int GB = 8;
   const int tid = threadIdx.x;
   const int NG = P.K / 4;
   griddep_wait();
   if (tid == 0 && P.trace) P.trace[1] = globaltimer_ns();
+  float4 xs[GB];
+#pragma unroll
+  for (int i = 0; i < GB; ++i) {
+    const int g = tid + i * kPrepThreads;
+    if (g < NG) xs[i] = ld_act_v4(reinterpret_cast<const float4*>(P.seg[0].xin) + g);
+  }
   const float amax = __uint_as_float(__ldcg(&P.pub->amax_bits));
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
   if (tid == 0) {
     SegScalars sc;
-    sc.sd = amax > 0.f ? 1.0 / double(inv) : 0.0;
-    sc.zp = float(double(__ldcg(&P.pub->zp)) / kPubSumScale);
-    sc.sumxs = float(double(__ldcg(&P.pub->sumxs)) / kPubXsScale);
-    sc.sumx = float(double(__ldcg(&P.pub->sumx)) / kPubSumScale);
-    sc.pad = 0.f;
+    sc.sd = amax > 0.f ? float(1.0 / double(inv)) : 0.f;
+    sc.zp = __ll2float_rn(__ldcg(&P.pub->zp)) * (1.0f / kPubSumScale);
+    sc.sumxs = __ll2float_rn(__ldcg(&P.pub->sumxs)) * (1.0f / kPubXsScale);
+    sc.sumx = __ll2float_rn(__ldcg(&P.pub->sumx)) * (1.0f / kPubSumScale);
+    sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
     P.scal[0] = sc;
     if (P.trace) P.trace[2] = globaltimer_ns();
   }
-  for (int g0 = tid; g0 < NG; g0 += 4 * kPrepThreads) {
-    float4 xs[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int g = g0 + i * kPrepThreads;
-      if (g < NG) xs[i] = ld_act_v4(reinterpret_cast<const float4*>(P.seg[0].xin) + g);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int g = g0 + i * kPrepThreads;
-      if (g < NG) store_digits(P.planes, g, xs[i], inv);
-    }
+  for (int i = 0; i < GB; ++i) {
+    const int g = tid + i * kPrepThreads;
+    if (g < NG) store_digits(P.planes, g, xs[i], inv);
   }
+  for (int g = tid + GB * kPrepThreads; g < NG; g += kPrepThreads)   // inputs beyond the first batch
+    store_digits(P.planes, g, ld_act_v4(reinterpret_cast<const float4*>(P.seg[0].xin) + g), inv);
 }
 
 __global__ void __launch_bounds__(kPrepThreads, 1) vector_prep_kernel(const __grid_constant__ PrepParams P) {
   extern __shared__ __align__(128) unsigned char prep_smem[];
-  float* red = reinterpret_cast<float*>(prep_smem);          // [16 warps + 1][16]
-  unsigned char* stage = prep_smem + kPrepRedBytes;          // nseg * 4*K bytes of fp32 xs
-  if (threadIdx.x == 0 && P.trace) P.trace[0] = globaltimer_ns();
+  float* red = reinterpret_cast<float*>(prep_smem);          // [16 warps + 1][4]
+  unsigned char* stage = prep_smem + kPrepRedBytes;          // 4*K bytes: this CTA's fp32 xs
+  if (threadIdx.x == 0 && P.trace && blockIdx.x == 0) P.trace[0] = globaltimer_ns();
   griddep_launch_dependents();
   if (P.mode == PREP_XS) prep_xs(P);
-  else if (P.mode == PREP_LN) prep_body<2, kMaxSeg, true>(P, stage, red);
-  else if (P.nseg == 1) prep_body<8, 1, false>(P, stage, red);
-  else prep_body<2, kMaxSeg, false>(P, stage, red);
-  if (threadIdx.x == 0 && P.trace) P.trace[3] = globaltimer_ns();
+  else if (P.mode == PREP_LN) prep_body<4, true>(P, stage, red);
+  else prep_body<8, false>(P, stage, red);
+  if (threadIdx.x == 0 && P.trace && blockIdx.x == 0) P.trace[3] = globaltimer_ns();
 }
 
-inline size_t prep_smem_bytes(int K, int nseg, int mode) {
-  return size_t(kPrepRedBytes) + (mode == PREP_XS ? 0 : size_t(nseg) * 4 * K);
-}
+inline size_t prep_smem_bytes(int K, int mode) { return size_t(kPrepRedBytes) + (mode == PREP_XS ? 0 : size_t(4) * K); }
+inline int prep_grid(int nseg, int mode) { return mode == PREP_XS ? 1 : nseg; }
 
 }  // namespace b200

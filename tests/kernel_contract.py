@@ -28,8 +28,9 @@ def fixed_point_gemv(x: torch.Tensor, m: QuantMatrix, with_affine: bool = True) 
     else:
         inv = (torch.tensor(QMAX) / amax).to(torch.float32)  # fp32 division
         X = torch.round(xs * inv).to(torch.float64)          # cvt.rni of the fp32 product (half to even)
-        I = m.qt.to(torch.float64) @ X                       # exact: |I| < 2^46
-        main = (I * (1.0 / inv.double())).to(torch.float32)
+        I = (m.qt.to(torch.float64) @ X).to(torch.int64)     # exact: |I| < 2^46
+        sd = (1.0 / inv.double()).to(torch.float32)          # value of one fixed-point unit, fp32
+        main = I.to(torch.float32) * sd                      # int64 -> fp32 (nearest even), fp32 product
     if not with_affine:
         return main
     y = main + np.float32(m.half) * xs.sum()

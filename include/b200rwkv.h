@@ -185,6 +185,43 @@ int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* s
 int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
                                 void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream);
 
+/* Bytes of device scratch b200rwkv_gemm_u8 needs (digit rows: 3 bytes per input per row, rows
+ * rounded up to 64; plus 32 bytes per row and matrix). */
+size_t b200rwkv_gemm_workspace_bytes(int k_in, int nmat, int rows);
+
+/*
+ * uint8 GEMM, 1 to 3 matrices of equal k_in applied to `rows` activation rows each:
+ *   y_i[r][:] = contract(mats[i], x_i[r][:])        x_i: device f32 [rows][k_in], y_i: [rows][n_out_i]
+ * The many-rows form of b200rwkv_gemv_u8: replaces the reference's sequence-mode matmul, which
+ * dequantises the whole matrix and calls a float GEMM (modules/matmul.py:64-68, :103-114), and its
+ * batched decode.  Same arithmetic per row as the one-row kernel (24-bit fixed-point activations,
+ * exact integer dot products, the same affine terms), so a row's result does not depend on
+ * which of the two entry points computed it beyond the fp32 summation order of sum_k x*my.
+ * Two launches: a row-wise preparation kernel, then a tcgen05 (kind::i8) tensor-core kernel with
+ * TMA-fed operands and TMEM accumulators, one CTA per 128 outputs x 64 rows.  rows <= 65535.
+ * `workspace`: b200rwkv_gemm_workspace_bytes(k_in, nmat, rows), 256-byte aligned, first int = status.
+ */
+int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y, int rows,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of device scratch b200rwkv_forward_rows needs (0 if streams * tokens_per_stream > 65535). */
+size_t b200rwkv_rows_workspace_bytes(const b200rwkv_model* m, int streams, int tokens_per_stream);
+
+/*
+ * The whole network over `streams` independent streams of `tokens_per_stream` tokens each, every
+ * matrix applied to all streams * tokens rows at once (b200rwkv_gemm_u8's kernels): prompt
+ * ingestion (one stream, many tokens; myRWKV.forward with T > 1, opt.py:61-76, Block.forward
+ * modules/block.py:56-102) and batched decode (many streams, one token).
+ *   tokens   device int64 [streams][tokens_per_stream]
+ *   state    device f32: stream s at state + s * state_stride, each [n_layer][5][n_embd] as in
+ *            b200rwkv_decode_step, updated in place
+ *   logits   device f32 [streams][n_vocab]: logits after the LAST token of every stream, or NULL
+ * Rows = streams * tokens_per_stream <= 65535; longer prompts are fed in pieces (the state carries).
+ */
+int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int streams, int tokens_per_stream,
+                          float* state, int64_t state_stride, float* logits, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

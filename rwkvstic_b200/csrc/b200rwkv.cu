@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "stream_gemv.cuh"
+#include "tile_gemm.cuh"
 
 namespace b200 {
 
@@ -75,17 +76,22 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// Describe qt[N][K] to TMA as [K/128][N][128 bytes]; one box = [kc/128][16 rows][128 bytes], 128-byte swizzle.
-static bool encode_weight_map(CUtensorMap* map, const uint8_t* qt, int N, int K, int kc) {
+// Describe a byte matrix p[rows][K] to TMA as [K/128][rows][128 bytes]; one box =
+// [box_chunks][box_rows][128 bytes], 128-byte swizzle.
+static bool encode_byte_map(CUtensorMap* map, const void* p, unsigned long long rows, int K, int box_rows, int box_chunks) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return false;
-  const cuuint64_t gdim[3] = {128, cuuint64_t(N), cuuint64_t(K / 128)};
+  const cuuint64_t gdim[3] = {128, cuuint64_t(rows), cuuint64_t(K / 128)};
   const cuuint64_t gstr[2] = {cuuint64_t(K), 128};
-  const cuuint32_t box[3] = {128, cuuint32_t(kTileRows), cuuint32_t(kc / 128)};
+  const cuuint32_t box[3] = {128, cuuint32_t(box_rows), cuuint32_t(box_chunks)};
   const cuuint32_t estr[3] = {1, 1, 1};
-  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(qt), gdim, gstr, box, estr,
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(p), gdim, gstr, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool encode_weight_map(CUtensorMap* map, const uint8_t* qt, int N, int K, int kc) {
+  return encode_byte_map(map, qt, (unsigned long long)N, K, kTileRows, kc / 128);
 }
 
 cudaError_t launch_stream_gemv(GemvParams& P, int max_n, bool pdl, cudaStream_t stream, const char** why) {
@@ -291,6 +297,154 @@ static Workspace carve(const b200rwkv_model* m, void* base) {
 // Scratch of the stand-alone GEMV entry point: [status 256 B][planes nmat*4*K][scalars].
 static size_t gemv_workspace_bytes(int k_in, int nmat) {
   return 256 + align256(size_t(nmat) * 4 * k_in) + align256(sizeof(SegScalars) * kMaxSeg);
+}
+
+
+// ---------------------------------------------------------------------------------------- many-rows path
+// x[r] = LayerNorm(emb[token[r]]) for R rows (emb.py:8-9 + ln_in, opt.py:63-64); one CTA per row.
+__global__ void __launch_bounds__(256)
+embed_ln0_rows_kernel(const float* __restrict__ emb, const long long* __restrict__ tokens, int D, int V,
+                      const float* __restrict__ w, const float* __restrict__ b, float* __restrict__ out) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  long long tok = tokens[blockIdx.x];
+  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+  const float* row = emb + size_t(tok) * D;
+  float* o = out + size_t(blockIdx.x) * D;
+  auto block_sum = [&](float v) -> float {
+    v = warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (tid == 0) {
+      float a = 0.f;
+      for (int i = 0; i < 8; ++i) a += red[i];
+      bc = a;
+    }
+    __syncthreads();
+    const float r = bc;
+    __syncthreads();
+    return r;
+  };
+  float s = 0.f;
+  for (int i = tid; i < D; i += 256) s += row[i];
+  const float mean = block_sum(s) / float(D);
+  s = 0.f;
+  for (int i = tid; i < D; i += 256) { const float c = row[i] - mean; s += c * c; }
+  const float sdev = sqrtf(block_sum(s) / float(D) + 1e-5f);
+  for (int i = tid; i < D; i += 256) o[i] = w[i] * ((row[i] - mean) / sdev) + b[i];
+}
+
+// WKV-4 over rows laid out [stream][T][C]: one thread per (stream, channel), sequential over T,
+// max-trick state rows of stream s at aa/bb/pp + s * state_stride; y = gate * wkv written over k.
+__global__ void __launch_bounds__(128)
+wkv_rows_kernel(int B, int T, int C, const float* __restrict__ w, const float* __restrict__ u, float* __restrict__ k,
+                const float* __restrict__ v, const float* __restrict__ gate, float* __restrict__ aa,
+                float* __restrict__ bb, float* __restrict__ pp, long long state_stride) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * C) return;
+  const int s = idx / C, c = idx - s * C;
+  const float wv = w[c], uv = u[c];
+  const size_t so = size_t(s) * state_stride + c;
+  float a = aa[so], q = bb[so], p = pp[so];
+  const size_t base = size_t(s) * T * C + c;
+  for (int t = 0; t < T; ++t) {
+    const size_t o = base + size_t(t) * C;
+    k[o] = gate[o] * wkv_step(k[o], v[o], wv, uv, a, q, p);
+  }
+  aa[so] = a; bb[so] = q; pp[so] = p;
+}
+
+struct RowsWorkspace {
+  int* status;
+  float *xa, *xb, *kb, *vb, *rb, *kk, *shift_new;
+  signed char* digits;
+  SegScalars* scal;
+  size_t bytes;
+};
+
+static int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+static RowsWorkspace carve_rows(const b200rwkv_model* m, int B, int T, void* base) {
+  RowsWorkspace w;
+  char* p = static_cast<char*>(base);
+  size_t off = 0;
+  auto take = [&](size_t n) { char* r = p ? p + off : nullptr; off += align256(n); return r; };
+  const size_t R = size_t(B) * T, Rpad = size_t(round_up(int(R), kGemmRows));
+  const size_t D = size_t(m->n_embd), F = size_t(m->n_ffn);
+  w.status = reinterpret_cast<int*>(take(256));
+  w.xa = reinterpret_cast<float*>(take(R * D * 4));
+  w.xb = reinterpret_cast<float*>(take(R * D * 4));
+  w.kb = reinterpret_cast<float*>(take(R * D * 4));
+  w.vb = reinterpret_cast<float*>(take(R * D * 4));
+  w.rb = reinterpret_cast<float*>(take(R * D * 4));
+  w.kk = reinterpret_cast<float*>(take(R * F * 4));
+  w.shift_new = reinterpret_cast<float*>(take(size_t(B) * D * 4));
+  w.digits = reinterpret_cast<signed char*>(take(kDigits * Rpad * (3 * D > F ? 3 * D : F)));
+  w.scal = reinterpret_cast<SegScalars*>(take(sizeof(SegScalars) * kMaxSeg * R));
+  w.bytes = off;
+  return w;
+}
+
+static size_t gemm_workspace_bytes(int k_in, int nmat, int rows) {
+  const size_t Rpad = size_t(round_up(rows, kGemmRows));
+  return 256 + align256(size_t(nmat) * kDigits * Rpad * k_in) + align256(sizeof(SegScalars) * size_t(nmat) * rows);
+}
+
+static cudaError_t launch_rows_prep(const RowsPrepParams& P, cudaStream_t stream, const char** why) {
+  static bool configured[64];
+  *why = "rows_prep launch failed";
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(rows_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const size_t smem = rows_prep_smem(P.K);
+  if (smem > 200 * 1024 || P.R > 65535) {
+    *why = "unsupported shape: k_in too large for the row preparation kernel, or more than 65535 rows";
+    return cudaErrorInvalidValue;
+  }
+  rows_prep_kernel<<<dim3(P.nseg, P.R), kPrepThreads, smem, stream>>>(P);
+  return cudaGetLastError();
+}
+
+// Fills the tensor maps of P (weights and digit rows) and launches the tile GEMM.  digits: [nseg][3][Rpad][K].
+static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const* mats, const signed char* digits,
+                                    cudaStream_t stream, const char** why) {
+  static bool configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  *why = "tile_gemm launch failed";
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(tile_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  int max_n = 0;
+  for (int s = 0; s < P.nseg; ++s) {
+    GemmSeg& S = P.seg[s];
+    if (!encode_byte_map(&S.wmap, mats[s]->qt, (unsigned long long)S.N, P.K, kGemmM, 1) ||
+        !encode_byte_map(&S.xmap, digits + size_t(s) * kDigits * P.Rpad * P.K, (unsigned long long)kDigits * P.Rpad, P.K,
+                         kGemmRows, 1)) {
+      *why = "cuTensorMapEncodeTiled failed";
+      return cudaErrorInvalidValue;
+    }
+    if (S.N > max_n) max_n = S.N;
+  }
+  const dim3 grid(P.Rpad / kGemmRows, (max_n + kGemmM - 1) / kGemmM, P.nseg);
+  if (grid.y > 65535) { *why = "n_out too large"; return cudaErrorInvalidValue; }
+  tile_gemm_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(P);
+  return cudaGetLastError();
+}
+
+static void fill_gemm_seg(GemmSeg& s, const b200rwkv_matrix& m, const SegScalars* scal, float* out, long long ldo) {
+  memset(&s, 0, sizeof(s));
+  s.rx = m.rx; s.mx = m.mx; s.half = m.half; s.N = m.n_out; s.act = ACT_NONE;
+  s.scal = scal; s.out = out; s.ldo = ldo;
 }
 
 // ---------------------------------------------------------------------------------------- static scratch
@@ -594,6 +748,187 @@ int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, f
                                 void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream) {
   if (!trace) return fail(B200RWKV_EINVAL, "decode_step_traced: null trace buffer");
   return decode_step_impl(m, token, state, logits, workspace, workspace_bytes, reinterpret_cast<unsigned long long*>(trace), stream);
+}
+
+size_t b200rwkv_gemm_workspace_bytes(int k_in, int nmat, int rows) {
+  if (k_in <= 0 || nmat < 1 || nmat > kMaxSeg || rows < 1) return 0;
+  return gemm_workspace_bytes(k_in, nmat, rows);
+}
+
+int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y, int rows,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  if (nmat < 1 || nmat > kMaxSeg || !mats || !x || !y || !workspace || rows < 1 || rows > 65535)
+    return fail(B200RWKV_EINVAL, "gemm_u8: nmat=%d rows=%d (1..3 matrices, 1..65535 rows) or null argument", nmat, rows);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(B200RWKV_EINVAL, "gemm_u8: workspace must be 256-byte aligned");
+  const int K = mats[0].k_in;
+  for (int i = 0; i < nmat; ++i) {
+    if (int rc = check_matrix(mats[i], "gemm_u8 matrix")) return rc;
+    if (mats[i].k_in != K) return fail(B200RWKV_EINVAL, "gemm_u8: matrices must share k_in");
+    if (!x[i] || !y[i] || !aligned16(x[i])) return fail(B200RWKV_EINVAL, "gemm_u8: x/y null or x not 16-byte aligned");
+  }
+  if (workspace_bytes < gemm_workspace_bytes(K, nmat, rows))
+    return fail(B200RWKV_EINVAL, "gemm_u8: workspace %zu < %zu bytes", workspace_bytes, gemm_workspace_bytes(K, nmat, rows));
+  const int Rpad = round_up(rows, kGemmRows);
+  char* wsb = static_cast<char*>(workspace);
+  signed char* digits = reinterpret_cast<signed char*>(wsb + 256);
+  SegScalars* scal = reinterpret_cast<SegScalars*>(wsb + 256 + align256(size_t(nmat) * kDigits * Rpad * K));
+  RowsPrepParams Q;
+  GemmParams P;
+  memset(&Q, 0, sizeof(Q));
+  memset(&P, 0, sizeof(P));
+  const b200rwkv_matrix* mp[kMaxSeg];
+  for (int i = 0; i < nmat; ++i) {
+    fill_prep_seg(Q.seg[i], mats[i], nullptr, x[i]);
+    fill_gemm_seg(P.seg[i], mats[i], scal + size_t(i) * rows, y[i], mats[i].n_out);
+    mp[i] = &mats[i];
+  }
+  Q.nseg = nmat; Q.K = K; Q.R = rows; Q.T = 1; Q.Rpad = Rpad; Q.mode = ROWS_PLAIN; Q.need_sums = 1; Q.ldx = K;
+  Q.digits = digits; Q.scal = scal;
+  P.nseg = nmat; P.K = K; P.R = rows; P.Rpad = Rpad; P.status = reinterpret_cast<int*>(wsb);
+  const char* why = "";
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = launch_rows_prep(Q, s, &why);
+  if (e == cudaSuccess) e = launch_tile_gemm(P, mp, digits, s, &why);
+  if (e != cudaSuccess) return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "gemm_u8: %s (%s)", why, cudaGetErrorString(e));
+  return B200RWKV_OK;
+}
+
+size_t b200rwkv_rows_workspace_bytes(const b200rwkv_model* m, int streams, int tokens_per_stream) {
+  if (!m || m->n_embd <= 0 || m->n_ffn <= 0 || streams < 1 || tokens_per_stream < 1) return 0;
+  if ((long long)streams * tokens_per_stream > 65535) return 0;
+  return carve_rows(m, streams, tokens_per_stream, nullptr).bytes;
+}
+
+int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int streams, int tokens_per_stream, float* state,
+                          int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!m || !tokens || !state || !workspace || !m->layers || !m->emb) return fail(B200RWKV_EINVAL, "forward_rows: null argument");
+  const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab, L = m->n_layer, B = streams, T = tokens_per_stream;
+  if (D <= 0 || (D % 128) != 0 || F <= 0 || (F % 128) != 0 || V <= 0 || L <= 0)
+    return fail(B200RWKV_EINVAL, "forward_rows: n_embd=%d n_ffn=%d must be positive multiples of 128", D, F);
+  if (B < 1 || T < 1 || (long long)B * T > 65535) return fail(B200RWKV_EINVAL, "forward_rows: streams=%d x tokens=%d must be 1..65535 rows", B, T);
+  if (state_stride < (int64_t)L * 5 * D || (state_stride % 4) != 0)
+    return fail(B200RWKV_EINVAL, "forward_rows: state_stride %lld < n_layer*5*n_embd or not a multiple of 4", (long long)state_stride);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || !aligned16(state))
+    return fail(B200RWKV_EINVAL, "forward_rows: workspace must be 256-byte and state 16-byte aligned");
+  RowsWorkspace ws = carve_rows(m, B, T, workspace);
+  if (workspace_bytes < ws.bytes) return fail(B200RWKV_EINVAL, "forward_rows: workspace %zu < %zu bytes", workspace_bytes, ws.bytes);
+  const int R = B * T, Rpad = round_up(R, kGemmRows);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const char* why = "";
+  cudaError_t e;
+
+  embed_ln0_rows_kernel<<<R, 256, 0, s>>>(m->emb, reinterpret_cast<const long long*>(tokens), D, V, m->ln0_w, m->ln0_b, ws.xa);
+  if ((e = cudaGetLastError()) != cudaSuccess) return fail(B200RWKV_ECUDA, "forward_rows: embed launch: %s", cudaGetErrorString(e));
+
+  RowsPrepParams Q;
+  GemmParams P;
+  auto prep_common = [&](int nseg, int K, int mode, const float* ln_x, const float* ln_w, const float* ln_b,
+                         const float* shift, bool need_sums) {
+    Q.nseg = nseg; Q.K = K; Q.R = R; Q.T = T; Q.Rpad = Rpad; Q.mode = mode; Q.need_sums = need_sums ? 1 : 0; Q.ldx = K;
+    Q.ln_x = ln_x; Q.ln_w = ln_w; Q.ln_b = ln_b; Q.shift = shift; Q.shift_stride = state_stride;
+    Q.shift_out = mode == ROWS_LN ? ws.shift_new : nullptr; Q.digits = ws.digits; Q.scal = ws.scal;
+  };
+  auto gemm_common = [&](int nseg, int K) { P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.status = ws.status; };
+  // new token-shift carry of every stream -> its state row (after the kernel that read the old one)
+  auto commit_carry = [&](float* dst_row) -> cudaError_t {
+    return cudaMemcpy2DAsync(dst_row, size_t(state_stride) * 4, ws.shift_new, size_t(D) * 4, size_t(D) * 4, B,
+                             cudaMemcpyDeviceToDevice, s);
+  };
+
+  for (int l = 0; l < L; ++l) {
+    const b200rwkv_layer& ly = m->layers[l];
+    float* st = state + size_t(l) * 5 * D;
+    const b200rwkv_matrix* chk[7] = {&ly.att_key, &ly.att_value, &ly.att_receptance, &ly.att_output,
+                                     &ly.ffn_key, &ly.ffn_receptance, &ly.ffn_value};
+    const int want_n[7] = {D, D, D, D, F, D, D}, want_k[7] = {D, D, D, D, D, D, F};
+    for (int i = 0; i < 7; ++i) {
+      if (int rc = check_matrix(*chk[i], "forward_rows layer matrix")) return rc;
+      if (chk[i]->n_out != want_n[i] || chk[i]->k_in != want_k[i])
+        return fail(B200RWKV_EINVAL, "forward_rows: layer %d matrix %d is %dx%d, expected %dx%d", l, i, chk[i]->n_out,
+                    chk[i]->k_in, want_n[i], want_k[i]);
+    }
+    // 1. ln1 + token-shift mix -> key, value, sigmoid(receptance)
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.att_key, ly.att_mix_k, nullptr);
+    fill_prep_seg(Q.seg[1], ly.att_value, ly.att_mix_v, nullptr);
+    fill_prep_seg(Q.seg[2], ly.att_receptance, ly.att_mix_r, nullptr);
+    prep_common(3, D, ROWS_LN, ws.xa, ly.ln1_w, ly.ln1_b, st,
+                wants_sums(ly.att_key) || wants_sums(ly.att_value) || wants_sums(ly.att_receptance));
+    if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
+    why = "carry copy failed";
+    if ((e = commit_carry(st)) != cudaSuccess) goto launch_failed;
+    memset(&P, 0, sizeof(P));
+    fill_gemm_seg(P.seg[0], ly.att_key, ws.scal, ws.kb, D);
+    fill_gemm_seg(P.seg[1], ly.att_value, ws.scal + size_t(R), ws.vb, D);
+    fill_gemm_seg(P.seg[2], ly.att_receptance, ws.scal + 2 * size_t(R), ws.rb, D);
+    P.seg[2].act = ACT_SIGMOID;
+    gemm_common(3, D);
+    { const b200rwkv_matrix* mp[3] = {&ly.att_key, &ly.att_value, &ly.att_receptance};
+      if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
+    // 2. WKV recurrence over each stream's rows; kb <- sigmoid(r) * wkv
+    wkv_rows_kernel<<<(B * D + 127) / 128, 128, 0, s>>>(B, T, D, ly.time_decay, ly.time_first, ws.kb, ws.vb, ws.rb,
+                                                         st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D), state_stride);
+    why = "wkv_rows launch failed";
+    if ((e = cudaGetLastError()) != cudaSuccess) goto launch_failed;
+    // 3. attention output projection + residual -> xb
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.att_output, nullptr, ws.kb);
+    prep_common(1, D, ROWS_PLAIN, nullptr, nullptr, nullptr, nullptr, wants_sums(ly.att_output));
+    if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
+    memset(&P, 0, sizeof(P));
+    fill_gemm_seg(P.seg[0], ly.att_output, ws.scal, ws.xb, D);
+    P.seg[0].res = ws.xa; P.seg[0].ldres = D;
+    gemm_common(1, D);
+    { const b200rwkv_matrix* mp[1] = {&ly.att_output};
+      if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
+    // 4. ln2 + token-shift mix -> relu(key)^2, sigmoid(receptance)
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.ffn_key, ly.ffn_mix_k, nullptr);
+    fill_prep_seg(Q.seg[1], ly.ffn_receptance, ly.ffn_mix_r, nullptr);
+    prep_common(2, D, ROWS_LN, ws.xb, ly.ln2_w, ly.ln2_b, st + size_t(D), wants_sums(ly.ffn_key) || wants_sums(ly.ffn_receptance));
+    if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
+    why = "carry copy failed";
+    if ((e = commit_carry(st + size_t(D))) != cudaSuccess) goto launch_failed;
+    memset(&P, 0, sizeof(P));
+    fill_gemm_seg(P.seg[0], ly.ffn_key, ws.scal, ws.kk, F);
+    P.seg[0].act = ACT_RELUSQ;
+    fill_gemm_seg(P.seg[1], ly.ffn_receptance, ws.scal + size_t(R), ws.rb, D);
+    P.seg[1].act = ACT_SIGMOID;
+    gemm_common(2, D);
+    { const b200rwkv_matrix* mp[2] = {&ly.ffn_key, &ly.ffn_receptance};
+      if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
+    // 5. ffn value projection, gated, + residual -> xa
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], ly.ffn_value, nullptr, ws.kk);
+    prep_common(1, F, ROWS_PLAIN, nullptr, nullptr, nullptr, nullptr, wants_sums(ly.ffn_value));
+    if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
+    memset(&P, 0, sizeof(P));
+    fill_gemm_seg(P.seg[0], ly.ffn_value, ws.scal, ws.xa, D);
+    P.seg[0].res = ws.xb; P.seg[0].ldres = D; P.seg[0].gate = ws.rb; P.seg[0].ldgate = D;
+    gemm_common(1, F);
+    { const b200rwkv_matrix* mp[1] = {&ly.ffn_value};
+      if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
+  }
+  if (logits) {
+    // ln_out + head on the last row of every stream (opt.py:73-75)
+    if (int rc = check_matrix(m->head, "forward_rows head")) return rc;
+    if (m->head.n_out != V || m->head.k_in != D) return fail(B200RWKV_EINVAL, "forward_rows: head is %dx%d", m->head.n_out, m->head.k_in);
+    const int Bpad = round_up(B, kGemmRows);
+    memset(&Q, 0, sizeof(Q));
+    fill_prep_seg(Q.seg[0], m->head, nullptr, nullptr);
+    Q.nseg = 1; Q.K = D; Q.R = B; Q.T = 1; Q.Rpad = Bpad; Q.mode = ROWS_LN; Q.need_sums = wants_sums(m->head) ? 1 : 0;
+    Q.ldx = (long long)T * D; Q.ln_x = ws.xa + size_t(T - 1) * D; Q.ln_w = m->ln_out_w; Q.ln_b = m->ln_out_b;
+    Q.digits = ws.digits; Q.scal = ws.scal;
+    if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
+    memset(&P, 0, sizeof(P));
+    fill_gemm_seg(P.seg[0], m->head, ws.scal, logits, V);
+    P.nseg = 1; P.K = D; P.R = B; P.Rpad = Bpad; P.status = ws.status;
+    { const b200rwkv_matrix* mp[1] = {&m->head};
+      if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
+  }
+  return B200RWKV_OK;
+launch_failed:
+  return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "forward_rows: %s (%s)", why, cudaGetErrorString(e));
 }
 
 }  // extern "C"

@@ -1,0 +1,423 @@
+// uint8 weight x fixed-point activation GEMM for sm_100a: the many-rows path (prompt ingestion with
+// T tokens per stream, decode with B streams) of the same arithmetic contract as stream_gemv.cuh.
+//
+//   out[r][n] = epilogue( contract(matrix, x[r])[n] )      r = 0..R-1 activation rows
+//
+// Arithmetic is identical to the one-row kernel: every activation row is turned into 24-bit fixed
+// point X = rint(xs * QMAX / max|xs|), split into three signed base-256 digits, and the dot products
+// with the uint8 weights are exact integer sums recombined in int64.  Here the digit rows are the
+// B operand of 5th-generation tensor-core MMAs (tcgen05.mma kind::i8, u8 x s8 -> s32):
+//
+//   A  = 128 weight rows x 128 bytes of K   (TMA box of qt[N][K], 128-byte swizzle, K-major)
+//   B  = 192 digit rows  x 128 bytes of K   (three TMA boxes, [digit][64 activation rows])
+//   D  = 128 lanes x 192 columns of int32 in tensor memory (TMEM), column = digit*64 + row
+//
+// One CTA owns one (128 weight rows) x (64 activation rows) output tile and walks K in 128-byte steps through a
+// ring of shared-memory stages: warp 0 issues the TMA copies, warp 1 issues the MMAs (one elected
+// thread; completion is signalled to the ring by tcgen05.commit on the stage's mbarrier), warps
+// 4-7 read the accumulator with tcgen05.ld and apply the affine terms and the fused element-wise
+// op.  CTAs that share a weight tile are adjacent in launch order so the tile is read from HBM once
+// and from L2 afterwards.
+//
+// Every wait is bounded (common.cuh): on expiry the CTA raises its abort flag, sets a status bit,
+// skips its remaining work, and still frees its tensor memory before it retires.
+#pragma once
+
+#include "stream_gemv.cuh"
+
+namespace b200 {
+
+constexpr int kGemmM = 128;                              // weight rows per tile = MMA M
+constexpr int kGemmRows = 64;                            // activation rows per tile
+constexpr int kDigits = 3;
+constexpr int kGemmN = kGemmRows * kDigits;              // MMA N: 192 columns
+constexpr int kGemmStages = 5;
+constexpr int kGemmABytes = kGemmM * 128;                // 16 KB
+constexpr int kGemmBDigitBytes = kGemmRows * 128;        // 8 KB per digit
+constexpr int kGemmStageBytes = kGemmABytes + kDigits * kGemmBDigitBytes;   // 40 KB
+constexpr int kGemmTmemCols = 256;                       // allocation granularity: power of two >= 192
+constexpr int kGemmThreads = 256;
+constexpr int kGemmOffScal = 1024;                       // SegScalars[64]
+constexpr int kGemmOffRing = 3072;
+constexpr int kGemmSmem = kGemmOffRing + kGemmStages * kGemmStageBytes;
+
+struct GemmSeg {
+  CUtensorMap wmap;    // u8 qt as [K/128][N][128 B], box [1][128][128], 128-byte swizzle
+  CUtensorMap xmap;    // s8 digits as [K/128][3*Rpad][128 B], box [1][64][128], 128-byte swizzle
+  const float* rx;     // [N] or null
+  const float* mx;     // [N] or null
+  const SegScalars* scal;  // [R] per activation row: sd, zp, sumxs, sumx
+  float* out;          // [R][ldo]
+  const float* res;    // [R][ldres] added to the output, or null
+  const float* gate;   // [R][ldgate] multiplies act(y), or null
+  long long ldo, ldres, ldgate;
+  float half;
+  int N;
+  int act;
+};
+
+struct GemmParams {
+  GemmSeg seg[kMaxSeg];
+  int nseg, K, R, Rpad;
+  int* status;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major tile of 128-byte rows, 128-byte swizzle; groups of 8
+// rows are 1024 bytes apart.  `addr` is the shared-memory byte address of the tile (1024-aligned)
+// plus the byte offset of the K slice inside the 128-byte row.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= uint64_t((addr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+  d |= uint64_t(1024 >> 4) << 32;          // stride between 8-row groups
+  d |= uint64_t(1) << 46;                  // descriptor version of this architecture
+  d |= uint64_t(2) << 61;                  // 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: D s32, A u8, B s8, both K-major, M x N.
+__host__ __device__ constexpr uint32_t umma_idesc_u8s8(int M, int N) {
+  return (2u << 4) | (0u << 7) | (1u << 10) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The mbarrier receives one arrival when every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 16 consecutive int32 columns of this warp's 32 lanes.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid_constant__ GemmParams P) {
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const GemmSeg& S = P.seg[blockIdx.z];
+  const int n0 = blockIdx.y * kGemmM;
+  const int row0 = blockIdx.x * kGemmRows;
+  if (n0 >= S.N) return;   // segments of one launch may have different N (whole CTA leaves: no barrier yet)
+  const int nk = P.K / 128;
+
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 8), acc_bar = smem_u32(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 256);
+  volatile int* issued_ptr = reinterpret_cast<volatile int*>(smem + 260);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 264);
+  SegScalars* scal = reinterpret_cast<SegScalars*>(smem + kGemmOffScal);
+  unsigned char* ring = smem + kGemmOffRing;
+
+  if (tid == 0) {
+    for (int i = 0; i < kGemmStages; ++i) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    *issued_ptr = 0;
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kGemmTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  griddep_launch_dependents();
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      griddep_wait();   // the digit rows come from the preparation kernel in front of this launch
+      int issued = 0;
+      for (int kc = 0; kc < nk; ++kc) {
+        const int slot = kc % kGemmStages;
+        const uint32_t phase = uint32_t(kc / kGemmStages) & 1u;
+        if (!mbar_wait_bounded(empty0 + 8 * slot, phase ^ 1u, abort_flag)) {
+          if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_EMPTY);
+          break;
+        }
+        const uint32_t bar = full0 + 8 * slot;
+        const uint32_t dst = smem_u32(ring + size_t(slot) * kGemmStageBytes);
+        mbar_arrive_expect_tx(bar, kGemmStageBytes);
+        tma_load_3d(dst, &S.wmap, 0, n0, kc, bar);
+#pragma unroll
+        for (int d = 0; d < kDigits; ++d)
+          tma_load_3d(dst + kGemmABytes + d * kGemmBDigitBytes, &S.xmap, 0, d * P.Rpad + row0, kc, bar);
+        ++issued;
+      }
+      *issued_ptr = issued;
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_u8s8(kGemmM, kGemmN);
+      bool ok = true;
+      for (int kc = 0; kc < nk && ok; ++kc) {
+        const int slot = kc % kGemmStages;
+        const uint32_t phase = uint32_t(kc / kGemmStages) & 1u;
+        if (!mbar_wait_bounded(full0 + 8 * slot, phase, abort_flag)) {
+          if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a = smem_u32(ring + size_t(slot) * kGemmStageBytes);
+        const uint64_t ad = umma_desc(a), bd = umma_desc(a + kGemmABytes);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)   // 32 bytes of K per instruction: +2 in the descriptors' 16-byte address units
+          umma_i8(tmem, ad + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (kc | k) != 0 ? 1u : 0u);
+        umma_commit(empty0 + 8 * slot);   // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(acc_bar);       // accumulator complete
+    }
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------------- epilogue (TMEM lanes 32*(warp%4)..+31)
+    const int q = warp - 4;
+    const int et = tid - 128;
+    griddep_wait();
+    for (int i = et; i < kGemmRows * 8; i += 128) {
+      const int r = row0 + (i >> 3);
+      reinterpret_cast<float*>(scal)[i] = r < P.R ? __ldcg(reinterpret_cast<const float*>(S.scal + r) + (i & 7)) : 0.f;
+    }
+    named_bar_sync(1, 128);
+    const int n = n0 + q * 32 + lane;
+    const bool nvalid = n < S.N;
+    const float rx = (nvalid && S.rx) ? S.rx[n] : 1.f, mx = (nvalid && S.mx) ? S.mx[n] : 0.f;
+    const bool ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
+    if (__all_sync(0xffffffffu, ok)) {
+      tc_fence_after();
+      const uint32_t tbase = tmem + (uint32_t(q * 32) << 16);
+#pragma unroll 1
+      for (int j0 = 0; j0 < kGemmRows; j0 += 16) {
+        if (row0 + j0 >= P.R) break;   // warp-uniform
+        int da[16], db[16], dc[16];
+        tmem_ld16(tbase + uint32_t(j0), da);
+        tmem_ld16(tbase + uint32_t(kGemmRows + j0), db);
+        tmem_ld16(tbase + uint32_t(2 * kGemmRows + j0), dc);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int r = row0 + j0 + j;
+          if (r < P.R && nvalid) {
+            const SegScalars& sc = scal[j0 + j];
+            const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
+            float y = __fmul_rn(__ll2float_rn(I), sc.sd) + S.half * sc.sumxs;
+            if (S.rx) y *= rx;
+            y += sc.zp;
+            if (S.mx) y += mx * sc.sumx;
+            if (S.act == ACT_RELUSQ) { y = fmaxf(y, 0.f); y *= y; }
+            else if (S.act == ACT_SIGMOID) y = sigmoidf_(y);
+            if (S.gate) y *= __ldcg(S.gate + size_t(r) * S.ldgate + n);
+            if (S.res) y += __ldcg(S.res + size_t(r) * S.ldres + n);
+            S.out[size_t(r) * S.ldo + n] = y;
+          }
+        }
+      }
+    } else if (lane == 0 && P.status) {
+      atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  // After an aborted wait copies may still be in flight into this CTA's shared memory: give each
+  // issued copy a bounded chance to land before the CTA retires.
+  if (tid == 0 && *abort_flag) {
+    const int issued = *issued_ptr;
+    const unsigned long long t0 = globaltimer_ns();
+    for (int i = issued > kGemmStages ? issued - kGemmStages : 0; i < issued; ++i) {
+      const uint32_t bar = full0 + 8 * (i % kGemmStages), parity = uint32_t(i / kGemmStages) & 1u;
+      while (!mbar_try_wait(bar, parity) && globaltimer_ns() - t0 < kWaitLimitNs / 10) {
+      }
+    }
+  }
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kGemmTmemCols) : "memory");
+  }
+}
+
+// ======================================================================================================
+// Row-wise activation preparation: CTA (s, r) turns activation row r into the digit rows and scalars
+// of matrix s.  Same arithmetic per row as vector_prep.cuh; the statistics are block reductions
+// (nothing is published between launches on this path).
+//   ROWS_PLAIN  v = xin_s[r]
+//   ROWS_LN     v = mix_s * LN(ln_x[r]) + (1 - mix_s) * carry, where the carry of a stream's first row
+//               is its state row and that of every later row is LN(ln_x[r-1]) (modules/block.py:58-67)
+// Row r belongs to stream r / T at position r % T.
+enum RowsMode : int { ROWS_PLAIN = 0, ROWS_LN = 1 };
+
+struct RowsPrepParams {
+  PrepSeg seg[kMaxSeg];
+  int nseg, K, R, T, Rpad;
+  int mode, need_sums;
+  long long ldx;              // floats between consecutive rows of xin / ln_x
+  const float* ln_x;
+  const float* ln_w;
+  const float* ln_b;
+  const float* shift;         // carry of stream b at shift + b * shift_stride, or null (zeros)
+  long long shift_stride;
+  float* shift_out;           // [R/T][K]: LN of every stream's last row = its next carry (or null)
+  signed char* digits;        // [nseg][3][Rpad][K]
+  SegScalars* scal;           // [nseg][R]
+};
+
+// Sums of two per-thread values over the CTA; every thread gets both totals.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  a = warp_sum(a); b = warp_sum(b);
+  __syncthreads();   // red may still be read from an earlier use
+  if (lane == 0) { red[warp * 2] = a; red[warp * 2 + 1] = b; }
+  __syncthreads();
+  float sa = 0.f, sb = 0.f;
+  for (int w = 0; w < kPrepWarps; ++w) { sa += red[w * 2]; sb += red[w * 2 + 1]; }
+  a = sa; b = sb;
+}
+
+__global__ void __launch_bounds__(kPrepThreads, 2) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
+  extern __shared__ __align__(128) unsigned char prep_smem[];
+  float* red = reinterpret_cast<float*>(prep_smem);
+  float4* park = reinterpret_cast<float4*>(prep_smem + kPrepRedBytes);
+  const int tid = threadIdx.x;
+  const int K = P.K, NG = K / 4;
+  const int sidx = blockIdx.x, r = blockIdx.y;
+  const int b = r / P.T, t = r - b * P.T;
+  const PrepSeg& S = P.seg[sidx];
+  griddep_launch_dependents();
+  griddep_wait();
+
+  float mean = 0.f, rstd = 1.f, meanp = 0.f, rstdp = 1.f;
+  const float4* xr = nullptr;
+  const float4* xp = nullptr;     // previous row (t > 0)
+  const float4* carry = nullptr;  // state row (t == 0)
+  const bool ln = P.mode == ROWS_LN;
+  const bool mixing = ln && S.mix != nullptr;
+  if (ln) {
+    xr = reinterpret_cast<const float4*>(P.ln_x + size_t(r) * P.ldx);
+    if (mixing) {
+      if (t > 0) xp = reinterpret_cast<const float4*>(P.ln_x + size_t(r - 1) * P.ldx);
+      else if (P.shift) carry = reinterpret_cast<const float4*>(P.shift + size_t(b) * P.shift_stride);
+    }
+    float s0 = 0.f, s1 = 0.f;
+    for (int g = tid; g < NG; g += kPrepThreads) {
+      const float4 x = __ldcg(xr + g);
+      s0 += (x.x + x.y) + (x.z + x.w);
+      if (xp) { const float4 y = __ldcg(xp + g); s1 += (y.x + y.y) + (y.z + y.w); }
+    }
+    block_sum2(s0, s1, red);
+    mean = s0 / float(K); meanp = s1 / float(K);
+    s0 = 0.f; s1 = 0.f;
+    for (int g = tid; g < NG; g += kPrepThreads) {
+      const float4 x = __ldcg(xr + g);
+      const float a0 = x.x - mean, a1 = x.y - mean, a2 = x.z - mean, a3 = x.w - mean;
+      s0 += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+      if (xp) {
+        const float4 y = __ldcg(xp + g);
+        const float c0 = y.x - meanp, c1 = y.y - meanp, c2 = y.z - meanp, c3 = y.w - meanp;
+        s1 += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+      }
+    }
+    block_sum2(s0, s1, red);
+    rstd = 1.0f / sqrtf(s0 / float(K) + 1e-5f);
+    rstdp = 1.0f / sqrtf(s1 / float(K) + 1e-5f);
+    __syncthreads();   // red is reused by the statistics reduction below
+  }
+
+  float amax = 0.f, szp = 0.f, sxs = 0.f, sx = 0.f;
+  const float4* xin = ln ? nullptr : reinterpret_cast<const float4*>(S.xin + size_t(r) * P.ldx);
+  const bool last_of_stream = ln && sidx == 0 && P.shift_out && t == P.T - 1;
+  for (int g = tid; g < NG; g += kPrepThreads) {
+    float4 v;
+    if (ln) {
+      const float4 x = __ldcg(xr + g);
+      const float4 w = __ldg(reinterpret_cast<const float4*>(P.ln_w) + g), bb = __ldg(reinterpret_cast<const float4*>(P.ln_b) + g);
+      float4 xy;
+      xy.x = w.x * ((x.x - mean) * rstd) + bb.x;
+      xy.y = w.y * ((x.y - mean) * rstd) + bb.y;
+      xy.z = w.z * ((x.z - mean) * rstd) + bb.z;
+      xy.w = w.w * ((x.w - mean) * rstd) + bb.w;
+      if (last_of_stream) reinterpret_cast<float4*>(P.shift_out + size_t(b) * K)[g] = xy;
+      v = xy;
+      if (mixing) {
+        float4 tc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (xp) {
+          const float4 y = __ldcg(xp + g);
+          tc.x = w.x * ((y.x - meanp) * rstdp) + bb.x;
+          tc.y = w.y * ((y.y - meanp) * rstdp) + bb.y;
+          tc.z = w.z * ((y.z - meanp) * rstdp) + bb.z;
+          tc.w = w.w * ((y.w - meanp) * rstdp) + bb.w;
+        } else if (carry) {
+          tc = __ldcg(carry + g);
+        }
+        const float4 mu = __ldg(reinterpret_cast<const float4*>(S.mix) + g);
+        v.x = xy.x * mu.x + tc.x * (1.f - mu.x);
+        v.y = xy.y * mu.y + tc.y * (1.f - mu.y);
+        v.z = xy.z * mu.z + tc.z * (1.f - mu.z);
+        v.w = xy.w * mu.w + tc.w * (1.f - mu.w);
+      }
+    } else {
+      v = __ldcg(xin + g);
+    }
+    const float4 ry = __ldg(reinterpret_cast<const float4*>(S.ry) + g), my = __ldg(reinterpret_cast<const float4*>(S.my) + g);
+    const float4 xs = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xs.x), fabsf(xs.y)), fmaxf(fabsf(xs.z), fabsf(xs.w))));
+    szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
+    if (P.need_sums) {
+      sxs += (xs.x + xs.y) + (xs.z + xs.w);
+      sx += (v.x + v.y) + (v.z + v.w);
+    }
+    park[g] = xs;
+  }
+  prep_reduce_stats(amax, szp, sxs, sx, red);
+
+  const float inv = amax > 0.f ? kQMax / amax : 0.f;
+  if (tid == 0) {
+    SegScalars sc;
+    sc.sd = amax > 0.f ? float(1.0 / double(inv)) : 0.f;
+    sc.zp = szp; sc.sumxs = sxs; sc.sumx = sx;
+    sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
+    P.scal[size_t(sidx) * P.R + r] = sc;
+  }
+  // digit d of row r of matrix s: digits[((s*3 + d) * Rpad + r) * K ...], four inputs per word
+  uint32_t* da = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 0) * P.Rpad + r) * K);
+  uint32_t* db = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 1) * P.Rpad + r) * K);
+  uint32_t* dc = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 2) * P.Rpad + r) * K);
+  for (int g = tid; g < NG; g += kPrepThreads) {
+    const float4 xs = park[g];
+    const float v[4] = {xs.x, xs.y, xs.z, xs.w};
+    uint32_t y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int mag = rint_nonneg(__fmul_rn(fabsf(v[i]), inv));
+      const int X = v[i] < 0.f ? -mag : mag;
+      y[i] = uint32_t(X + 0x8080) ^ 0x8080u;   // bytes: (c, b, a, sign extension)
+    }
+    const uint32_t c01 = __byte_perm(y[0], y[1], 0x0040), c23 = __byte_perm(y[2], y[3], 0x0040);
+    const uint32_t b01 = __byte_perm(y[0], y[1], 0x0051), b23 = __byte_perm(y[2], y[3], 0x0051);
+    const uint32_t a01 = __byte_perm(y[0], y[1], 0x0062), a23 = __byte_perm(y[2], y[3], 0x0062);
+    da[g] = __byte_perm(a01, a23, 0x5410);
+    db[g] = __byte_perm(b01, b23, 0x5410);
+    dc[g] = __byte_perm(c01, c23, 0x5410);
+  }
+}
+
+inline size_t rows_prep_smem(int K) { return size_t(kPrepRedBytes) + size_t(4) * K; }
+
+}  // namespace b200

@@ -154,6 +154,9 @@ class B200RWKV:
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._tok = torch.zeros(1, dtype=torch.int64, device=self.device)
         self._logits = torch.zeros(self.n_vocab, dtype=torch.float32, device=self.device)
+        self._rows_ws: Dict[Tuple[int, int], torch.Tensor] = {}
+        self.rows_threshold = 16      # forward / forward_batch use the tensor-core rows path from this many rows
+        self.rows_per_call = 4096     # upper bound on rows (streams x tokens) of one rows-path call
         self._graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self._seen: Dict[int, int] = {}
         self.launch_count = 0  # kernels launched so far (for the benchmark's gpu_launches)
@@ -262,6 +265,45 @@ class B200RWKV:
             raise ValueError(f"state must be [{self.n_layer},5,{self.n_embd}], got {tuple(state.shape)}")
         return state.to(device=self.device, dtype=torch.float32).contiguous()
 
+    def forward_rows(self, tokens: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        """Tensor-core path: ``tokens [B,T]`` int64, ``state [B,L,5,D]`` fp32 contiguous on the
+        device (updated in place).  Every matrix is applied to all B*T rows at once
+        (b200rwkv_forward_rows); prompts longer than ``rows_per_call // B`` tokens are fed in
+        pieces.  Returns the logits ``[B,V]`` after each stream's last token."""
+        if tokens.dim() != 2 or tokens.numel() == 0:
+            raise ValueError("forward_rows needs tokens [B,T] with at least one token")
+        B, T = tokens.shape
+        if (state.dtype != torch.float32 or state.device != self.device or not state.is_contiguous()
+                or tuple(state.shape) != (B, self.n_layer, 5, self.n_embd)):
+            raise ValueError(f"forward_rows needs a contiguous fp32 state [{B},{self.n_layer},5,{self.n_embd}] on the model's device")
+        if B > 65535:
+            raise ValueError("forward_rows: at most 65535 streams per call")
+        out = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device)
+        step = max(1, min(self.rows_per_call, 65535) // B)
+        with torch.cuda.device(self.device):
+            toks = tokens.to(device=self.device, dtype=torch.int64)
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            for t0 in range(0, T, step):
+                piece = toks[:, t0:t0 + step].contiguous()
+                tp = piece.shape[1]
+                ws = self._rows_ws.get((B, tp))
+                if ws is None:
+                    n = int(self._L.b200rwkv_rows_workspace_bytes(C.byref(self._cmodel), B, tp))
+                    if len(self._rows_ws) >= 4:
+                        self._rows_ws.clear()
+                    ws = self._rows_ws[(B, tp)] = torch.zeros(n, dtype=torch.uint8, device=self.device)
+                last = t0 + step >= T
+                _lib.check(self._L.b200rwkv_forward_rows(C.byref(self._cmodel), piece.data_ptr(), B, tp, state.data_ptr(),
+                                                         state.stride(0), out.data_ptr() if last else None,
+                                                         ws.data_ptr(), ws.numel(), stream))
+                self.launch_count += 10 * self.n_layer + 1 + (2 if last else 0)
+                self._status_host.copy_(ws[:4].view(torch.int32))
+                bits = int(self._status_host[0])
+                if bits:
+                    ws[:4].zero_()
+                    raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+        return out
+
     def forward(self, tokens, state: torch.Tensor):
         """``(logits f32[V] on the device, state)`` - see the module docstring."""
         if not torch.is_tensor(tokens):
@@ -270,6 +312,9 @@ class B200RWKV:
         if tokens.numel() == 0:
             raise ValueError("forward needs at least one token")
         state = self._own_state(state)
+        if tokens.numel() >= self.rows_threshold:
+            self._logits.copy_(self.forward_rows(tokens.reshape(1, -1), state.unsqueeze(0))[0])
+            return (self._logits.clone() if self.copy_logits else self._logits), state
         with torch.cuda.device(self.device):
             toks = tokens.to(self.device, non_blocking=True)
             T = toks.numel()
@@ -280,14 +325,20 @@ class B200RWKV:
 
     __call__ = forward
 
-    def forward_batch(self, tokens: torch.Tensor, state: torch.Tensor):
+    def forward_batch(self, tokens: torch.Tensor, state: torch.Tensor, rows: Optional[bool] = None):
         """B independent streams: ``tokens [B]`` or ``[B,T]``, ``state [B,L,5,D]`` (in place).
-        Returns ``(logits [B,V], state)``.  Each stream's arithmetic is the single-stream path,
-        so results are bit-identical to B separate ``forward`` calls."""
+        Returns ``(logits [B,V], state)``.  From ``rows_threshold`` rows (B*T) on, or when
+        ``rows`` is True, every matrix is applied to all rows at once on the tensor cores
+        (``forward_rows``); below it each stream runs the one-row streaming path, bit-identical
+        to B separate ``forward`` calls."""
         tokens = tokens.reshape(tokens.shape[0], -1)
         B = tokens.shape[0]
         if state.dtype != torch.float32 or state.device != self.device or not state.is_contiguous():
             raise ValueError("forward_batch needs a contiguous fp32 state on the model's device")
+        if rows is None:
+            rows = tokens.numel() >= self.rows_threshold
+        if rows:
+            return self.forward_rows(tokens, state), state
         out = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device)
         keep = self.copy_logits
         self.copy_logits = False

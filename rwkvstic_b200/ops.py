@@ -78,6 +78,42 @@ def gemv_u8(mats: Sequence[QuantMatrix], xs: Sequence[torch.Tensor], ys: Optiona
     return list(ys)
 
 
+def gemm_u8(mats: Sequence[QuantMatrix], xs: Sequence[torch.Tensor],
+            ys: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
+    """``ys[i] = xs[i] @ W_i`` for 1..3 quantised matrices of equal k_in and ``xs[i]`` fp32
+    ``[rows, k_in]``: the many-rows (tensor-core) form of ``gemv_u8``, which the reference serves by
+    dequantising the matrix (modules/matmul.py:64-68).  Returns fp32 ``[rows, n_out_i]``."""
+    n = len(mats)
+    if n < 1 or n > 3 or len(xs) != n:
+        raise ValueError("gemm_u8 takes 1..3 matrices and as many input matrices")
+    dev = mats[0].qt.device
+    if dev.type != "cuda":
+        raise RuntimeError("gemm_u8 needs CUDA tensors (no CPU path)")
+    rows = xs[0].shape[0]
+    if ys is None:
+        ys = [torch.empty(rows, m.n_out, dtype=torch.float32, device=dev) for m in mats]
+    for m, x, y in zip(mats, xs, ys):
+        if x.dtype != torch.float32 or y.dtype != torch.float32 or not x.is_contiguous() or not y.is_contiguous():
+            raise ValueError("gemm_u8 needs contiguous fp32 matrices")
+        if tuple(x.shape) != (rows, m.k_in) or tuple(y.shape) != (rows, m.n_out) or x.device != dev or y.device != dev:
+            raise ValueError("gemm_u8 operand shape/device does not match its matrix")
+    cm = (_lib.Matrix * n)(*[_cmatrix(m) for m in mats])
+    cx = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
+    cy = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
+    nbytes = int(_lib.lib().b200rwkv_gemm_workspace_bytes(mats[0].k_in, n, rows))
+    key = (str(dev), "gemm", nbytes)
+    if key not in _workspaces:
+        _workspaces[key] = torch.zeros(nbytes, dtype=torch.uint8, device=dev)
+    ws = _workspaces[key]
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200rwkv_gemm_u8(n, cm, cx, cy, rows, ws.data_ptr(), ws.numel(), _stream(dev)))
+    status = int(ws[:4].view(torch.int32).item())
+    if status:
+        ws[:4].zero_()
+        raise _lib.B200RWKVError(_lib.ETIMEOUT, f"gemm_u8: a bounded device-side wait expired (status bits {status})")
+    return list(ys)
+
+
 def wkv_scan(w: torch.Tensor, u: torch.Tensor, k: torch.Tensor, v: torch.Tensor, aa: torch.Tensor,
              bb: torch.Tensor, pp: torch.Tensor, convention: int = 0) -> torch.Tensor:
     """WKV-4 over ``k, v [B,T,C]`` (or ``[T,C]``); ``aa, bb, pp [B,C]`` (or ``[C]``) updated in

@@ -198,6 +198,45 @@ def time_isolated_kernels(model, reps=5):
     return out
 
 
+def measured_tensor_peak():
+    """Dense bf16 TFLOP/s measured on this pool (burst figure), or the stated fallback."""
+    try:
+        with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except Exception:
+        return 1590.0
+
+
+def matrix_params(L, D, V=VOCAB):
+    """Matrix elements every activation row is multiplied with (7 matrices per block + head)."""
+    F = 4 * D
+    return L * (4 * D * D + 2 * D * F + D * D) + V * D
+
+
+def time_prefill(dev, tf_peak, B=8, T=1024):
+    """Prompt ingestion at the 3B shape: B streams x T tokens in sequence mode through forward_rows."""
+    from rwkvstic_b200.model import B200RWKV
+    L, D = SHAPES["3b"]
+    model = B200RWKV.synthetic(L, D, seed=1234, device=dev, copy_logits=False)
+    toks = torch.randint(0, VOCAB, (B, T), generator=torch.Generator().manual_seed(7), dtype=torch.int64).to(dev)
+    times = []
+    for i in range(4):
+        state = model.empty_batch_state(B)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        model.forward_rows(toks, state)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if i:
+            times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    alg = 2.0 * (matrix_params(L, D) - VOCAB * D) * B * T / (ms * 1e-3) / 1e12   # the head runs on B rows only
+    return {"workload": f"RWKV-4 3b shape L={L} D={D}, {B} streams x {T} tokens, sequence mode", "ms": ms,
+            "value": B * T / (ms * 1e-3), "unit": UNIT, "rows_per_call": model.rows_per_call,
+            "tensor": {"algorithmic_tflops": alg, "peak_bf16_tflops": tf_peak, "frac_of_measured_bf16": alg / tf_peak}}
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from rwkvstic_b200.model import B200RWKV
@@ -259,10 +298,29 @@ def run_ours(args, rank, world, local_rank):
     e2e_ms = (time.perf_counter() - t0) * 1e3
     model.check_status()
 
+    # ---- batched decode: B independent streams per GPU through the tensor-core rows path, greedy
+    # feedback on the device (tokens and logits never leave HBM)
+    Bs, Kb = args.streams, max(4, min(K, 32))
+    bstate = model.empty_batch_state(Bs)
+    btok = torch.randint(0, VOCAB, (Bs, 1), generator=gen, dtype=torch.int64).to(dev)
+    for i in range(3):
+        btok = model.forward_rows(btok, bstate).argmax(dim=1, keepdim=True)
+    barrier()
+    b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_b0 = model.launch_count
+    b0.record()
+    for i in range(Kb):
+        btok = model.forward_rows(btok, bstate).argmax(dim=1, keepdim=True)
+    b1.record()
+    barrier()
+    batched_ms = b0.elapsed_time(b1)
+    launches_b = model.launch_count - launches_b0
+    del bstate
+
     if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, e2e_ms, batched_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
+        ms, e2e_ms, batched_ms = float(t[0]), float(t[1]), float(t[2])
         cnt = torch.tensor([launches], device=dev, dtype=torch.int64)
         dist.all_reduce(cnt)
         launches = int(cnt[0])
@@ -294,10 +352,24 @@ def run_ours(args, rank, world, local_rank):
                          "avg_launch_us": step_ms * 1e3 / n_gemv,
                          "frac_of_nominal_8TBs": achieved / 8000.0},
         }
+        tf_peak = measured_tensor_peak()
+        macs = matrix_params(L, D)   # multiply-adds per activation row
+        alg_tflops = 2.0 * macs * Bs * Kb / (batched_ms * 1e-3) / 1e12
+        line["batched_decode"] = {
+            "streams_per_gpu": Bs, "steps": Kb, "ms_per_step": batched_ms / Kb,
+            "value": world * Bs * Kb / (batched_ms * 1e-3), "unit": UNIT, "gpu_launches_per_rank": launches_b,
+            "kernel": "tile_gemm_kernel (tcgen05 kind::i8, three 8-bit activation digits per row)",
+            "tensor": {"algorithmic_tflops": alg_tflops, "peak_bf16_tflops": tf_peak,
+                       "frac_of_measured_bf16": alg_tflops / tf_peak if tf_peak else None}}
         if world == 1:
             line["kernels"] = time_isolated_kernels(model)
-            if not args.no_cpu_baseline:
+            if not args.no_prefill:
                 del model
+                torch.cuda.empty_cache()
+                model = None
+                line["prefill"] = time_prefill(dev, tf_peak)
+            if not args.no_cpu_baseline:
+                model = None
                 torch.cuda.empty_cache()
                 line["cpu_baseline"] = cpu_reference(args.shape, 4, 1)
         print(json.dumps(line), flush=True)
@@ -313,6 +385,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--shape", default="7b", choices=list(SHAPES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 3B-shape prompt-ingestion measurement (N=1 only)")
+    ap.add_argument("--streams", type=int, default=256, help="streams per GPU of the batched-decode measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

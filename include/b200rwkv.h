@@ -222,6 +222,25 @@ int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int st
                           float* state, int64_t state_stride, float* logits, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/*
+ * One pipeline stage of b200rwkv_forward_rows for a model whose blocks are partitioned
+ * contiguously over several GPUs (the layer split: each GPU holds the blocks of its stage, as the
+ * reference's TORCH_SPLIT strategy places whole layers on devices).  `m` describes THIS stage:
+ * n_layer and `layers` are the stage's blocks; emb/ln0 are needed only by the first stage, ln_out/head
+ * only by the last.
+ *   tokens   first stage: device int64 [streams][tokens_per_stream]; later stages: NULL
+ *   x        device f32 [streams*tokens_per_stream][n_embd], 16-byte aligned: the residual stream.
+ *            Later stages read it (as received from the previous stage); every stage leaves its
+ *            output in it for the caller to hand to the next GPU (peer copy / NCCL send).
+ *   state    the stage's own blocks only: stream s at state + s*state_stride, [n_layer][5][n_embd]
+ *   logits   last stage: device f32 [streams][n_vocab] (or NULL); other stages: NULL
+ * Workspace size: b200rwkv_rows_workspace_bytes of the stage's model.
+ * The handoff itself is the caller's (rwkvstic_b200/layer_split.py uses torch.distributed P2P).
+ */
+int b200rwkv_forward_rows_stage(const b200rwkv_model* m, const int64_t* tokens, float* x, int streams,
+                                int tokens_per_stream, float* state, int64_t state_stride, float* logits,
+                                void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -348,7 +348,21 @@ wkv_rows_kernel(int B, int T, int C, const float* __restrict__ w, const float* _
   const size_t so = size_t(s) * state_stride + c;
   float a = aa[so], q = bb[so], p = pp[so];
   const size_t base = size_t(s) * T * C + c;
-  for (int t = 0; t < T; ++t) {
+  // The recurrence is sequential in t but its inputs are not: fetch eight steps at a time so the
+  // chain waits for memory once per eight steps instead of once per step.
+  constexpr int U = 8;
+  int t = 0;
+  for (; t + U <= T; t += U) {
+    float kv[U], vv[U], gv[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const size_t o = base + size_t(t + i) * C;
+      kv[i] = __ldcg(k + o); vv[i] = __ldcg(v + o); gv[i] = __ldcg(gate + o);
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) k[base + size_t(t + i) * C] = gv[i] * wkv_step(kv[i], vv[i], wv, uv, a, q, p);
+  }
+  for (; t < T; ++t) {
     const size_t o = base + size_t(t) * C;
     k[o] = gate[o] * wkv_step(k[o], v[o], wv, uv, a, q, p);
   }
@@ -363,14 +377,13 @@ struct RowsWorkspace {
   size_t bytes;
 };
 
-static int round_up(int v, int m) { return (v + m - 1) / m * m; }
 
 static RowsWorkspace carve_rows(const b200rwkv_model* m, int B, int T, void* base) {
   RowsWorkspace w;
   char* p = static_cast<char*>(base);
   size_t off = 0;
   auto take = [&](size_t n) { char* r = p ? p + off : nullptr; off += align256(n); return r; };
-  const size_t R = size_t(B) * T, Rpad = size_t(round_up(int(R), kGemmRows));
+  const size_t R = size_t(B) * T, Rpad = size_t(gemm_padded_rows(int(R)));
   const size_t D = size_t(m->n_embd), F = size_t(m->n_ffn);
   w.status = reinterpret_cast<int*>(take(256));
   w.xa = reinterpret_cast<float*>(take(R * D * 4));
@@ -387,7 +400,7 @@ static RowsWorkspace carve_rows(const b200rwkv_model* m, int B, int T, void* bas
 }
 
 static size_t gemm_workspace_bytes(int k_in, int nmat, int rows) {
-  const size_t Rpad = size_t(round_up(rows, kGemmRows));
+  const size_t Rpad = size_t(gemm_padded_rows(rows));
   return 256 + align256(size_t(nmat) * kDigits * Rpad * k_in) + align256(sizeof(SegScalars) * size_t(nmat) * rows);
 }
 
@@ -402,7 +415,7 @@ static cudaError_t launch_rows_prep(const RowsPrepParams& P, cudaStream_t stream
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const size_t smem = rows_prep_smem(P.K);
+  const size_t smem = rows_prep_smem(P.K, P.mode);
   if (smem > 200 * 1024 || P.R > 65535) {
     *why = "unsupported shape: k_in too large for the row preparation kernel, or more than 65535 rows";
     return cudaErrorInvalidValue;
@@ -424,18 +437,27 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
+  // Tiles of 256 weight rows move the fewest operand bytes per MAC; when they would not fill the GPU
+  // twice over, tiles of 128 rows give twice the CTAs.
   int max_n = 0;
+  long long tiles256 = 0;
+  for (int s = 0; s < P.nseg; ++s) {
+    if (P.seg[s].N > max_n) max_n = P.seg[s].N;
+    tiles256 += (long long)(P.Rpad / P.Rt) * ((P.seg[s].N + kGemmM - 1) / kGemmM);
+  }
+  P.mt = tiles256 >= 2ll * device_sms() ? kGemmM : 128;
   for (int s = 0; s < P.nseg; ++s) {
     GemmSeg& S = P.seg[s];
-    if (!encode_byte_map(&S.wmap, mats[s]->qt, (unsigned long long)S.N, P.K, kGemmM, 1) ||
+    if (!encode_byte_map(&S.wmap, mats[s]->qt, (unsigned long long)S.N, P.K, P.mt, 1) ||
         !encode_byte_map(&S.xmap, digits + size_t(s) * kDigits * P.Rpad * P.K, (unsigned long long)kDigits * P.Rpad, P.K,
-                         kGemmRows, 1)) {
+                         P.Rt, 1)) {
       *why = "cuTensorMapEncodeTiled failed";
       return cudaErrorInvalidValue;
     }
-    if (S.N > max_n) max_n = S.N;
   }
-  const dim3 grid(P.Rpad / kGemmRows, (max_n + kGemmM - 1) / kGemmM, P.nseg);
+  { const char* d = getenv("B200RWKV_GEMM_DEBUG"); P.dbg = d ? atoi(d) : 0; }
+  if (P.dbg == 3) return cudaSuccess;   // measurement only: preparation kernel alone
+  const dim3 grid(P.Rpad / P.Rt, (max_n + P.mt - 1) / P.mt, P.nseg);
   if (grid.y > 65535) { *why = "n_out too large"; return cudaErrorInvalidValue; }
   tile_gemm_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(P);
   return cudaGetLastError();
@@ -768,7 +790,7 @@ int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* 
   }
   if (workspace_bytes < gemm_workspace_bytes(K, nmat, rows))
     return fail(B200RWKV_EINVAL, "gemm_u8: workspace %zu < %zu bytes", workspace_bytes, gemm_workspace_bytes(K, nmat, rows));
-  const int Rpad = round_up(rows, kGemmRows);
+  const int Rpad = gemm_padded_rows(rows);
   char* wsb = static_cast<char*>(workspace);
   signed char* digits = reinterpret_cast<signed char*>(wsb + 256);
   SegScalars* scal = reinterpret_cast<SegScalars*>(wsb + 256 + align256(size_t(nmat) * kDigits * Rpad * K));
@@ -784,7 +806,7 @@ int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* 
   }
   Q.nseg = nmat; Q.K = K; Q.R = rows; Q.T = 1; Q.Rpad = Rpad; Q.mode = ROWS_PLAIN; Q.need_sums = 1; Q.ldx = K;
   Q.digits = digits; Q.scal = scal;
-  P.nseg = nmat; P.K = K; P.R = rows; P.Rpad = Rpad; P.status = reinterpret_cast<int*>(wsb);
+  P.nseg = nmat; P.K = K; P.R = rows; P.Rpad = Rpad; P.Rt = gemm_tile_rows(rows); P.status = reinterpret_cast<int*>(wsb);
   const char* why = "";
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = launch_rows_prep(Q, s, &why);
@@ -799,11 +821,16 @@ size_t b200rwkv_rows_workspace_bytes(const b200rwkv_model* m, int streams, int t
   return carve_rows(m, streams, tokens_per_stream, nullptr).bytes;
 }
 
-int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int streams, int tokens_per_stream, float* state,
-                          int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes, void* stream) {
-  if (!m || !tokens || !state || !workspace || !m->layers || !m->emb) return fail(B200RWKV_EINVAL, "forward_rows: null argument");
+// tokens != null: embedding + ln0 produce the rows; else the rows arrive in x_ext.  x_ext != null: the
+// residual stream lives there (and is left there for the next pipeline stage) instead of the workspace.
+static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, float* x_ext, int streams, int tokens_per_stream,
+                             float* state, int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  if (!m || !state || !workspace || !m->layers || (!tokens && !x_ext) || (tokens && !m->emb))
+    return fail(B200RWKV_EINVAL, "forward_rows: null argument");
+  if (x_ext && !aligned16(x_ext)) return fail(B200RWKV_EINVAL, "forward_rows: x must be 16-byte aligned");
   const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab, L = m->n_layer, B = streams, T = tokens_per_stream;
-  if (D <= 0 || (D % 128) != 0 || F <= 0 || (F % 128) != 0 || V <= 0 || L <= 0)
+  if (D <= 0 || (D % 128) != 0 || F <= 0 || (F % 128) != 0 || L <= 0 || ((tokens || logits) && V <= 0))
     return fail(B200RWKV_EINVAL, "forward_rows: n_embd=%d n_ffn=%d must be positive multiples of 128", D, F);
   if (B < 1 || T < 1 || (long long)B * T > 65535) return fail(B200RWKV_EINVAL, "forward_rows: streams=%d x tokens=%d must be 1..65535 rows", B, T);
   if (state_stride < (int64_t)L * 5 * D || (state_stride % 4) != 0)
@@ -812,13 +839,16 @@ int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int st
     return fail(B200RWKV_EINVAL, "forward_rows: workspace must be 256-byte and state 16-byte aligned");
   RowsWorkspace ws = carve_rows(m, B, T, workspace);
   if (workspace_bytes < ws.bytes) return fail(B200RWKV_EINVAL, "forward_rows: workspace %zu < %zu bytes", workspace_bytes, ws.bytes);
-  const int R = B * T, Rpad = round_up(R, kGemmRows);
+  const int R = B * T, Rpad = gemm_padded_rows(R);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const char* why = "";
   cudaError_t e;
 
-  embed_ln0_rows_kernel<<<R, 256, 0, s>>>(m->emb, reinterpret_cast<const long long*>(tokens), D, V, m->ln0_w, m->ln0_b, ws.xa);
-  if ((e = cudaGetLastError()) != cudaSuccess) return fail(B200RWKV_ECUDA, "forward_rows: embed launch: %s", cudaGetErrorString(e));
+  if (x_ext) ws.xa = x_ext;
+  if (tokens) {
+    embed_ln0_rows_kernel<<<R, 256, 0, s>>>(m->emb, reinterpret_cast<const long long*>(tokens), D, V, m->ln0_w, m->ln0_b, ws.xa);
+    if ((e = cudaGetLastError()) != cudaSuccess) return fail(B200RWKV_ECUDA, "forward_rows: embed launch: %s", cudaGetErrorString(e));
+  }
 
   RowsPrepParams Q;
   GemmParams P;
@@ -828,7 +858,7 @@ int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int st
     Q.ln_x = ln_x; Q.ln_w = ln_w; Q.ln_b = ln_b; Q.shift = shift; Q.shift_stride = state_stride;
     Q.shift_out = mode == ROWS_LN ? ws.shift_new : nullptr; Q.digits = ws.digits; Q.scal = ws.scal;
   };
-  auto gemm_common = [&](int nseg, int K) { P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.status = ws.status; };
+  auto gemm_common = [&](int nseg, int K) { P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.Rt = gemm_tile_rows(R); P.status = ws.status; };
   // new token-shift carry of every stream -> its state row (after the kernel that read the old one)
   auto commit_carry = [&](float* dst_row) -> cudaError_t {
     return cudaMemcpy2DAsync(dst_row, size_t(state_stride) * 4, ws.shift_new, size_t(D) * 4, size_t(D) * 4, B,
@@ -913,7 +943,7 @@ int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int st
     // ln_out + head on the last row of every stream (opt.py:73-75)
     if (int rc = check_matrix(m->head, "forward_rows head")) return rc;
     if (m->head.n_out != V || m->head.k_in != D) return fail(B200RWKV_EINVAL, "forward_rows: head is %dx%d", m->head.n_out, m->head.k_in);
-    const int Bpad = round_up(B, kGemmRows);
+    const int Bpad = gemm_padded_rows(B);
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], m->head, nullptr, nullptr);
     Q.nseg = 1; Q.K = D; Q.R = B; Q.T = 1; Q.Rpad = Bpad; Q.mode = ROWS_LN; Q.need_sums = wants_sums(m->head) ? 1 : 0;
@@ -922,13 +952,28 @@ int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int st
     if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_gemm_seg(P.seg[0], m->head, ws.scal, logits, V);
-    P.nseg = 1; P.K = D; P.R = B; P.Rpad = Bpad; P.status = ws.status;
+    P.nseg = 1; P.K = D; P.R = B; P.Rpad = Bpad; P.Rt = gemm_tile_rows(B); P.status = ws.status;
     { const b200rwkv_matrix* mp[1] = {&m->head};
       if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
   }
   return B200RWKV_OK;
 launch_failed:
   return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "forward_rows: %s (%s)", why, cudaGetErrorString(e));
+}
+
+int b200rwkv_forward_rows(const b200rwkv_model* m, const int64_t* tokens, int streams, int tokens_per_stream, float* state,
+                          int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!tokens) return fail(B200RWKV_EINVAL, "forward_rows: null tokens");
+  return forward_rows_impl(m, tokens, nullptr, streams, tokens_per_stream, state, state_stride, logits, workspace,
+                           workspace_bytes, stream);
+}
+
+int b200rwkv_forward_rows_stage(const b200rwkv_model* m, const int64_t* tokens, float* x, int streams, int tokens_per_stream,
+                                float* state, int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  if (!x) return fail(B200RWKV_EINVAL, "forward_rows_stage: null x");
+  return forward_rows_impl(m, tokens, x, streams, tokens_per_stream, state, state_stride, logits, workspace, workspace_bytes,
+                           stream);
 }
 
 }  // extern "C"

@@ -8,16 +8,19 @@
 // with the uint8 weights are exact integer sums recombined in int64.  Here the digit rows are the
 // B operand of 5th-generation tensor-core MMAs (tcgen05.mma kind::i8, u8 x s8 -> s32):
 //
-//   A  = 128 weight rows x 128 bytes of K   (TMA box of qt[N][K], 128-byte swizzle, K-major)
-//   B  = 192 digit rows  x 128 bytes of K   (three TMA boxes, [digit][64 activation rows])
-//   D  = 128 lanes x 192 columns of int32 in tensor memory (TMEM), column = digit*64 + row
+//   A  = 2 x 128 weight rows x 128 bytes of K   (one TMA box of qt[N][K], 128-byte swizzle, K-major)
+//   B  = 3*Rt digit rows     x 128 bytes of K   (three TMA boxes, [digit][Rt activation rows], Rt <= 80)
+//   D  = two accumulators of 128 lanes x 3*Rt int32 columns in tensor memory (TMEM),
+//        column = digit*Rt + row; the second accumulator starts at column 256
 //
-// One CTA owns one (128 weight rows) x (64 activation rows) output tile and walks K in 128-byte steps through a
-// ring of shared-memory stages: warp 0 issues the TMA copies, warp 1 issues the MMAs (one elected
-// thread; completion is signalled to the ring by tcgen05.commit on the stage's mbarrier), warps
-// 4-7 read the accumulator with tcgen05.ld and apply the affine terms and the fused element-wise
-// op.  CTAs that share a weight tile are adjacent in launch order so the tile is read from HBM once
-// and from L2 afterwards.
+// One CTA owns one (256 weight rows) x (Rt activation rows) output tile and walks K in 128-byte
+// steps through a ring of shared-memory stages: warp 0 issues the TMA copies, warp 1 issues the
+// MMAs (one elected thread; completion is signalled to the ring by tcgen05.commit on the stage's
+// mbarrier), warps 4-11 read the accumulators with tcgen05.ld and apply the affine terms and the
+// fused element-wise op.  The kernel is bound by operand traffic from L2 to shared memory (int8
+// MMAs need ~250 MACs per byte to saturate, a tile gives M*N/(M+N) = 124), which is why the tile
+// pairs two weight sub-tiles with one digit tile.  CTAs that share a weight tile are adjacent in
+// launch order so the tile is read from HBM once and from L2 afterwards.
 //
 // Every wait is bounded (common.cuh): on expiry the CTA raises its abort flag, sets a status bit,
 // skips its remaining work, and still frees its tensor memory before it retires.
@@ -27,23 +30,32 @@
 
 namespace b200 {
 
-constexpr int kGemmM = 128;                              // weight rows per tile = MMA M
-constexpr int kGemmRows = 64;                            // activation rows per tile
+constexpr int kGemmM = 256;                              // weight rows per tile = two MMA M=128 sub-tiles
+constexpr int kGemmRowsMax = 80;                         // activation rows per tile (multiple of 16)
 constexpr int kDigits = 3;
-constexpr int kGemmN = kGemmRows * kDigits;              // MMA N: 192 columns
-constexpr int kGemmStages = 5;
-constexpr int kGemmABytes = kGemmM * 128;                // 16 KB
-constexpr int kGemmBDigitBytes = kGemmRows * 128;        // 8 KB per digit
-constexpr int kGemmStageBytes = kGemmABytes + kDigits * kGemmBDigitBytes;   // 40 KB
-constexpr int kGemmTmemCols = 256;                       // allocation granularity: power of two >= 192
-constexpr int kGemmThreads = 256;
-constexpr int kGemmOffScal = 1024;                       // SegScalars[64]
-constexpr int kGemmOffRing = 3072;
+constexpr int kGemmStages = 3;
+constexpr int kGemmABytes = kGemmM * 128;                // 32 KB
+constexpr int kGemmStageBytes = kGemmABytes + kDigits * kGemmRowsMax * 128;   // 62 KB
+constexpr int kGemmTmemCols = 512;                       // both accumulators; one CTA per SM (shared memory)
+constexpr int kGemmAcc1Col = 256;                        // first column of the second accumulator
+constexpr int kGemmThreads = 384;                        // warp 0 TMA, 1 MMA, 2 TMEM allocation, 4-11 epilogue
+constexpr int kGemmOffScal = 1024;                       // SegScalars[80]
+constexpr int kGemmOffRing = 4096;
 constexpr int kGemmSmem = kGemmOffRing + kGemmStages * kGemmStageBytes;
 
+// Rows per tile for R activation rows: as few tiles as possible, then as small as possible.
+inline int gemm_tile_rows(int R) {
+  const int tiles = (R + kGemmRowsMax - 1) / kGemmRowsMax;
+  return ((R + tiles - 1) / tiles + 15) / 16 * 16;
+}
+inline int gemm_padded_rows(int R) {
+  const int rt = gemm_tile_rows(R);
+  return (R + rt - 1) / rt * rt;
+}
+
 struct GemmSeg {
-  CUtensorMap wmap;    // u8 qt as [K/128][N][128 B], box [1][128][128], 128-byte swizzle
-  CUtensorMap xmap;    // s8 digits as [K/128][3*Rpad][128 B], box [1][64][128], 128-byte swizzle
+  CUtensorMap wmap;    // u8 qt as [K/128][N][128 B], box [1][mt][128], 128-byte swizzle
+  CUtensorMap xmap;    // s8 digits as [K/128][3*Rpad][128 B], box [1][Rt][128], 128-byte swizzle
   const float* rx;     // [N] or null
   const float* mx;     // [N] or null
   const SegScalars* scal;  // [R] per activation row: sd, zp, sumxs, sumx
@@ -59,7 +71,10 @@ struct GemmSeg {
 struct GemmParams {
   GemmSeg seg[kMaxSeg];
   int nseg, K, R, Rpad;
+  int Rt;              // activation rows per tile (multiple of 16, <= 80); Rpad is a multiple of it
+  int mt;              // weight rows per tile: 256 (two accumulators) or 128 (small grids: more CTAs)
   int* status;
+  int dbg;             // measurement only: 1 = no operand copies (MMAs on stale shared memory), 2 = no MMAs, 4 = no epilogue
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------------
@@ -111,10 +126,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const GemmSeg& S = P.seg[blockIdx.z];
-  const int n0 = blockIdx.y * kGemmM;
-  const int row0 = blockIdx.x * kGemmRows;
+  const int n0 = blockIdx.y * P.mt;
+  const int Rt = P.Rt;
+  const int row0 = blockIdx.x * Rt;
   if (n0 >= S.N) return;   // segments of one launch may have different N (whole CTA leaves: no barrier yet)
   const int nk = P.K / 128;
+  const bool two = P.mt == kGemmM && n0 + 128 < S.N;   // the second 128-row sub-tile exists and holds real rows
+  const uint32_t a_bytes = uint32_t(P.mt) * 128u;
+  const uint32_t b_bytes = uint32_t(kDigits * Rt * 128);
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 8), acc_bar = smem_u32(bars + 16);
@@ -146,7 +165,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
     if (lane == 0) {
       griddep_wait();   // the digit rows come from the preparation kernel in front of this launch
       int issued = 0;
-      for (int kc = 0; kc < nk; ++kc) {
+      for (int kc = 0; kc < (P.dbg == 1 ? 0 : nk); ++kc) {
         const int slot = kc % kGemmStages;
         const uint32_t phase = uint32_t(kc / kGemmStages) & 1u;
         if (!mbar_wait_bounded(empty0 + 8 * slot, phase ^ 1u, abort_flag)) {
@@ -155,11 +174,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         }
         const uint32_t bar = full0 + 8 * slot;
         const uint32_t dst = smem_u32(ring + size_t(slot) * kGemmStageBytes);
-        mbar_arrive_expect_tx(bar, kGemmStageBytes);
-        tma_load_3d(dst, &S.wmap, 0, n0, kc, bar);
+        mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
+        tma_load_3d(dst, &S.wmap, 0, n0, kc, bar);   // rows past N are zero-filled
 #pragma unroll
         for (int d = 0; d < kDigits; ++d)
-          tma_load_3d(dst + kGemmABytes + d * kGemmBDigitBytes, &S.xmap, 0, d * P.Rpad + row0, kc, bar);
+          tma_load_3d(dst + kGemmABytes + uint32_t(d * Rt * 128), &S.xmap, 0, d * P.Rpad + row0, kc, bar);
         ++issued;
       }
       *issued_ptr = issued;
@@ -167,67 +186,99 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_u8s8(kGemmM, kGemmN);
+      const uint32_t idesc = umma_idesc_u8s8(128, kDigits * Rt);
       bool ok = true;
       for (int kc = 0; kc < nk && ok; ++kc) {
         const int slot = kc % kGemmStages;
         const uint32_t phase = uint32_t(kc / kGemmStages) & 1u;
-        if (!mbar_wait_bounded(full0 + 8 * slot, phase, abort_flag)) {
+        if (P.dbg != 1 && !mbar_wait_bounded(full0 + 8 * slot, phase, abort_flag)) {
           if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
           ok = false;
           break;
         }
         tc_fence_after();
+        if (P.dbg == 2) { mbar_arrive(empty0 + 8 * slot); continue; }
         const uint32_t a = smem_u32(ring + size_t(slot) * kGemmStageBytes);
-        const uint64_t ad = umma_desc(a), bd = umma_desc(a + kGemmABytes);
+        const uint64_t ad0 = umma_desc(a), ad1 = umma_desc(a + 128 * 128), bd = umma_desc(a + kGemmABytes);
 #pragma unroll
-        for (int k = 0; k < 4; ++k)   // 32 bytes of K per instruction: +2 in the descriptors' 16-byte address units
-          umma_i8(tmem, ad + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, (kc | k) != 0 ? 1u : 0u);
+        for (int k = 0; k < 4; ++k) {   // 32 bytes of K per instruction: +2 in the descriptors' 16-byte address units
+          const uint32_t acc = (kc | k) != 0 ? 1u : 0u;
+          umma_i8(tmem, ad0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+          if (two) umma_i8(tmem + kGemmAcc1Col, ad1 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+        }
         umma_commit(empty0 + 8 * slot);   // frees the stage once these MMAs have read it
       }
-      if (ok) umma_commit(acc_bar);       // accumulator complete
+      if (ok) umma_commit(acc_bar);       // accumulators complete
     }
   } else if (warp >= 4) {
-    // ---------------------------------------------------------------- epilogue (TMEM lanes 32*(warp%4)..+31)
-    const int q = warp - 4;
+    // ---------------------------------------------------------------- epilogue: 8 warps.  A warp can
+    // read TMEM lanes 32*(warp%4)..+31 only, so two warps share each lane quadrant and take
+    // alternate 16-row chunks of the accumulators.
+    const int q = warp & 3, eg = (warp - 4) >> 2;
     const int et = tid - 128;
     griddep_wait();
-    for (int i = et; i < kGemmRows * 8; i += 128) {
+    for (int i = et; i < Rt * 8; i += kGemmThreads - 128) {
       const int r = row0 + (i >> 3);
       reinterpret_cast<float*>(scal)[i] = r < P.R ? __ldcg(reinterpret_cast<const float*>(S.scal + r) + (i & 7)) : 0.f;
     }
-    named_bar_sync(1, 128);
-    const int n = n0 + q * 32 + lane;
-    const bool nvalid = n < S.N;
-    const float rx = (nvalid && S.rx) ? S.rx[n] : 1.f, mx = (nvalid && S.mx) ? S.mx[n] : 0.f;
+    named_bar_sync(1, kGemmThreads - 128);
     const bool ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
     if (__all_sync(0xffffffffu, ok)) {
       tc_fence_after();
-      const uint32_t tbase = tmem + (uint32_t(q * 32) << 16);
+      const int nchunks = Rt / 16, nitems = (two ? 2 : 1) * nchunks;
 #pragma unroll 1
-      for (int j0 = 0; j0 < kGemmRows; j0 += 16) {
-        if (row0 + j0 >= P.R) break;   // warp-uniform
+      for (int item = eg; item < (P.dbg == 4 ? 0 : nitems); item += 2) {
+        const int h = item / nchunks, j0 = (item - h * nchunks) * 16;
+        if (row0 + j0 >= P.R) continue;   // warp-uniform
+        const int n = n0 + h * 128 + q * 32 + lane;
+        const bool nvalid = n < S.N;
+        const int nc = nvalid ? n : S.N - 1;   // clamped: loads stay in bounds, the store is predicated
+        const float rx = S.rx ? S.rx[nc] : 1.f, mx = S.mx ? S.mx[nc] : 0.f;
+        const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t(h * kGemmAcc1Col + j0);
         int da[16], db[16], dc[16];
-        tmem_ld16(tbase + uint32_t(j0), da);
-        tmem_ld16(tbase + uint32_t(kGemmRows + j0), db);
-        tmem_ld16(tbase + uint32_t(2 * kGemmRows + j0), dc);
+        tmem_ld16(tbase, da);
+        tmem_ld16(tbase + uint32_t(Rt), db);
+        tmem_ld16(tbase + uint32_t(2 * Rt), dc);
         tmem_ld_wait();
+        // branch-free over the 16 rows so that their dependency chains interleave (one warp per
+        // scheduler: a row at a time would run at the latency of every instruction)
+        float yv[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const SegScalars& sc = scal[j0 + j];
+          const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
+          float y = __fmul_rn(__ll2float_rn(I), sc.sd) + S.half * sc.sumxs;
+          y *= rx;               // rx = 1, mx = 0 when the matrix has no per-output terms: exact no-ops
+          y += sc.zp;
+          y += mx * sc.sumx;
+          yv[j] = y;
+        }
+        if (S.act == ACT_RELUSQ) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { const float t = fmaxf(yv[j], 0.f); yv[j] = t * t; }
+        } else if (S.act == ACT_SIGMOID) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) yv[j] = sigmoidf_(yv[j]);
+        }
+        const int rlast = P.R - 1;
+        if (S.gate) {
+          float gv[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { const int r = min(row0 + j0 + j, rlast); gv[j] = __ldcg(S.gate + size_t(r) * S.ldgate + nc); }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) yv[j] *= gv[j];
+        }
+        if (S.res) {
+          float rv[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { const int r = min(row0 + j0 + j, rlast); rv[j] = __ldcg(S.res + size_t(r) * S.ldres + nc); }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) yv[j] += rv[j];
+        }
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int r = row0 + j0 + j;
-          if (r < P.R && nvalid) {
-            const SegScalars& sc = scal[j0 + j];
-            const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
-            float y = __fmul_rn(__ll2float_rn(I), sc.sd) + S.half * sc.sumxs;
-            if (S.rx) y *= rx;
-            y += sc.zp;
-            if (S.mx) y += mx * sc.sumx;
-            if (S.act == ACT_RELUSQ) { y = fmaxf(y, 0.f); y *= y; }
-            else if (S.act == ACT_SIGMOID) y = sigmoidf_(y);
-            if (S.gate) y *= __ldcg(S.gate + size_t(r) * S.ldgate + n);
-            if (S.res) y += __ldcg(S.res + size_t(r) * S.ldres + n);
-            S.out[size_t(r) * S.ldo + n] = y;
-          }
+          if (r <= rlast && nvalid) S.out[size_t(r) * S.ldo + n] = yv[j];
         }
       }
     } else if (lane == 0 && P.status) {
@@ -291,49 +342,87 @@ __device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
   a = sa; b = sb;
 }
 
-__global__ void __launch_bounds__(kPrepThreads, 2) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
-  extern __shared__ __align__(128) unsigned char prep_smem[];
-  float* red = reinterpret_cast<float*>(prep_smem);
-  float4* park = reinterpret_cast<float4*>(prep_smem + kPrepRedBytes);
+// Digit words of four inputs (same digit arithmetic as store_digits in vector_prep.cuh).
+__device__ __forceinline__ void rows_store_digits(uint32_t* da, uint32_t* db, uint32_t* dc, int g, float4 xs, float inv) {
+  const float v[4] = {xs.x, xs.y, xs.z, xs.w};
+  uint32_t y[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int mag = rint_nonneg(__fmul_rn(fabsf(v[i]), inv));
+    const int X = v[i] < 0.f ? -mag : mag;
+    y[i] = uint32_t(X + 0x8080) ^ 0x8080u;   // bytes: (c, b, a, sign extension)
+  }
+  const uint32_t c01 = __byte_perm(y[0], y[1], 0x0040), c23 = __byte_perm(y[2], y[3], 0x0040);
+  const uint32_t b01 = __byte_perm(y[0], y[1], 0x0051), b23 = __byte_perm(y[2], y[3], 0x0051);
+  const uint32_t a01 = __byte_perm(y[0], y[1], 0x0062), a23 = __byte_perm(y[2], y[3], 0x0062);
+  da[g] = __byte_perm(a01, a23, 0x5410);
+  db[g] = __byte_perm(b01, b23, 0x5410);
+  dc[g] = __byte_perm(c01, c23, 0x5410);
+}
+
+__device__ __forceinline__ float4 ln_apply(float4 x, float mean, float rstd, float4 w, float4 b) {
+  return make_float4(w.x * ((x.x - mean) * rstd) + b.x, w.y * ((x.y - mean) * rstd) + b.y,
+                     w.z * ((x.z - mean) * rstd) + b.z, w.w * ((x.w - mean) * rstd) + b.w);
+}
+
+// One activation row per CTA.  REG = true keeps the row in registers (up to G groups of four inputs
+// per thread: one round trip to memory, then the reductions, then the digit stores); REG = false
+// is the any-length variant that re-reads the row and parks xs in shared memory.
+template <int G, bool REG>
+__device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* red, float4* park) {
   const int tid = threadIdx.x;
   const int K = P.K, NG = K / 4;
   const int sidx = blockIdx.x, r = blockIdx.y;
   const int b = r / P.T, t = r - b * P.T;
   const PrepSeg& S = P.seg[sidx];
-  griddep_launch_dependents();
-  griddep_wait();
-
-  float mean = 0.f, rstd = 1.f, meanp = 0.f, rstdp = 1.f;
-  const float4* xr = nullptr;
-  const float4* xp = nullptr;     // previous row (t > 0)
-  const float4* carry = nullptr;  // state row (t == 0)
   const bool ln = P.mode == ROWS_LN;
   const bool mixing = ln && S.mix != nullptr;
+  const float4* xr = reinterpret_cast<const float4*>((ln ? P.ln_x : S.xin) + size_t(r) * P.ldx);
+  const float4* xp = nullptr;     // previous row (t > 0)
+  const float4* carry = nullptr;  // state row (t == 0)
+  if (mixing) {
+    if (t > 0) xp = reinterpret_cast<const float4*>(P.ln_x + size_t(r - 1) * P.ldx);
+    else if (P.shift) carry = reinterpret_cast<const float4*>(P.shift + size_t(b) * P.shift_stride);
+  }
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  float4 xv[REG ? G : 1], pv[REG ? G : 1];
+  if (REG) {
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      const int g = tid + i * kPrepThreads;
+      xv[i] = g < NG ? __ldcg(xr + g) : zero4;
+      pv[i] = (g < NG && xp) ? __ldcg(xp + g) : ((g < NG && carry) ? __ldcg(carry + g) : zero4);
+    }
+  }
+  auto x_at = [&](int i, int g) -> float4 { return REG ? xv[i] : __ldcg(xr + g); };
+  auto p_at = [&](int i, int g) -> float4 { return REG ? pv[i] : (xp ? __ldcg(xp + g) : (carry ? __ldcg(carry + g) : zero4)); };
+
+  float mean = 0.f, rstd = 1.f, meanp = 0.f, rstdp = 1.f;
   if (ln) {
-    xr = reinterpret_cast<const float4*>(P.ln_x + size_t(r) * P.ldx);
-    if (mixing) {
-      if (t > 0) xp = reinterpret_cast<const float4*>(P.ln_x + size_t(r - 1) * P.ldx);
-      else if (P.shift) carry = reinterpret_cast<const float4*>(P.shift + size_t(b) * P.shift_stride);
-    }
     float s0 = 0.f, s1 = 0.f;
-    for (int g = tid; g < NG; g += kPrepThreads) {
-      const float4 x = __ldcg(xr + g);
-      s0 += (x.x + x.y) + (x.z + x.w);
-      if (xp) { const float4 y = __ldcg(xp + g); s1 += (y.x + y.y) + (y.z + y.w); }
-    }
+#pragma unroll
+    for (int i = 0; i < (REG ? G : 1); ++i)
+      for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads) {
+        const float4 x = x_at(i, g);
+        s0 += (x.x + x.y) + (x.z + x.w);
+        if (xp) { const float4 y = p_at(i, g); s1 += (y.x + y.y) + (y.z + y.w); }
+      }
     block_sum2(s0, s1, red);
     mean = s0 / float(K); meanp = s1 / float(K);
     s0 = 0.f; s1 = 0.f;
-    for (int g = tid; g < NG; g += kPrepThreads) {
-      const float4 x = __ldcg(xr + g);
-      const float a0 = x.x - mean, a1 = x.y - mean, a2 = x.z - mean, a3 = x.w - mean;
-      s0 += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
-      if (xp) {
-        const float4 y = __ldcg(xp + g);
-        const float c0 = y.x - meanp, c1 = y.y - meanp, c2 = y.z - meanp, c3 = y.w - meanp;
-        s1 += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+#pragma unroll
+    for (int i = 0; i < (REG ? G : 1); ++i)
+      for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads) {
+        const float4 x = x_at(i, g);
+        const float a0 = x.x - mean, a1 = x.y - mean, a2 = x.z - mean, a3 = x.w - mean;
+        s0 += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+        if (xp) {
+          const float4 y = p_at(i, g);
+          const float c0 = y.x - meanp, c1 = y.y - meanp, c2 = y.z - meanp, c3 = y.w - meanp;
+          s1 += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+        }
       }
-    }
     block_sum2(s0, s1, red);
     rstd = 1.0f / sqrtf(s0 / float(K) + 1e-5f);
     rstdp = 1.0f / sqrtf(s1 / float(K) + 1e-5f);
@@ -341,50 +430,36 @@ __global__ void __launch_bounds__(kPrepThreads, 2) rows_prep_kernel(const __grid
   }
 
   float amax = 0.f, szp = 0.f, sxs = 0.f, sx = 0.f;
-  const float4* xin = ln ? nullptr : reinterpret_cast<const float4*>(S.xin + size_t(r) * P.ldx);
   const bool last_of_stream = ln && sidx == 0 && P.shift_out && t == P.T - 1;
-  for (int g = tid; g < NG; g += kPrepThreads) {
-    float4 v;
-    if (ln) {
-      const float4 x = __ldcg(xr + g);
-      const float4 w = __ldg(reinterpret_cast<const float4*>(P.ln_w) + g), bb = __ldg(reinterpret_cast<const float4*>(P.ln_b) + g);
-      float4 xy;
-      xy.x = w.x * ((x.x - mean) * rstd) + bb.x;
-      xy.y = w.y * ((x.y - mean) * rstd) + bb.y;
-      xy.z = w.z * ((x.z - mean) * rstd) + bb.z;
-      xy.w = w.w * ((x.w - mean) * rstd) + bb.w;
-      if (last_of_stream) reinterpret_cast<float4*>(P.shift_out + size_t(b) * K)[g] = xy;
-      v = xy;
-      if (mixing) {
-        float4 tc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (xp) {
-          const float4 y = __ldcg(xp + g);
-          tc.x = w.x * ((y.x - meanp) * rstdp) + bb.x;
-          tc.y = w.y * ((y.y - meanp) * rstdp) + bb.y;
-          tc.z = w.z * ((y.z - meanp) * rstdp) + bb.z;
-          tc.w = w.w * ((y.w - meanp) * rstdp) + bb.w;
-        } else if (carry) {
-          tc = __ldcg(carry + g);
+#pragma unroll
+  for (int i = 0; i < (REG ? G : 1); ++i)
+    for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads) {
+      float4 v = x_at(i, g);
+      if (ln) {
+        const float4 w = __ldg(reinterpret_cast<const float4*>(P.ln_w) + g), bb = __ldg(reinterpret_cast<const float4*>(P.ln_b) + g);
+        const float4 xy = ln_apply(v, mean, rstd, w, bb);
+        if (last_of_stream) reinterpret_cast<float4*>(P.shift_out + size_t(b) * K)[g] = xy;
+        v = xy;
+        if (mixing) {
+          float4 tc = p_at(i, g);
+          if (xp) tc = ln_apply(tc, meanp, rstdp, w, bb);
+          const float4 mu = __ldg(reinterpret_cast<const float4*>(S.mix) + g);
+          v.x = xy.x * mu.x + tc.x * (1.f - mu.x);
+          v.y = xy.y * mu.y + tc.y * (1.f - mu.y);
+          v.z = xy.z * mu.z + tc.z * (1.f - mu.z);
+          v.w = xy.w * mu.w + tc.w * (1.f - mu.w);
         }
-        const float4 mu = __ldg(reinterpret_cast<const float4*>(S.mix) + g);
-        v.x = xy.x * mu.x + tc.x * (1.f - mu.x);
-        v.y = xy.y * mu.y + tc.y * (1.f - mu.y);
-        v.z = xy.z * mu.z + tc.z * (1.f - mu.z);
-        v.w = xy.w * mu.w + tc.w * (1.f - mu.w);
       }
-    } else {
-      v = __ldcg(xin + g);
+      const float4 ry = __ldg(reinterpret_cast<const float4*>(S.ry) + g), my = __ldg(reinterpret_cast<const float4*>(S.my) + g);
+      const float4 xs = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
+      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xs.x), fabsf(xs.y)), fmaxf(fabsf(xs.z), fabsf(xs.w))));
+      szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
+      if (P.need_sums) {
+        sxs += (xs.x + xs.y) + (xs.z + xs.w);
+        sx += (v.x + v.y) + (v.z + v.w);
+      }
+      if (REG) xv[i] = xs; else park[g] = xs;
     }
-    const float4 ry = __ldg(reinterpret_cast<const float4*>(S.ry) + g), my = __ldg(reinterpret_cast<const float4*>(S.my) + g);
-    const float4 xs = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xs.x), fabsf(xs.y)), fmaxf(fabsf(xs.z), fabsf(xs.w))));
-    szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
-    if (P.need_sums) {
-      sxs += (xs.x + xs.y) + (xs.z + xs.w);
-      sx += (v.x + v.y) + (v.z + v.w);
-    }
-    park[g] = xs;
-  }
   prep_reduce_stats(amax, szp, sxs, sx, red);
 
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
@@ -399,25 +474,31 @@ __global__ void __launch_bounds__(kPrepThreads, 2) rows_prep_kernel(const __grid
   uint32_t* da = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 0) * P.Rpad + r) * K);
   uint32_t* db = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 1) * P.Rpad + r) * K);
   uint32_t* dc = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 2) * P.Rpad + r) * K);
-  for (int g = tid; g < NG; g += kPrepThreads) {
-    const float4 xs = park[g];
-    const float v[4] = {xs.x, xs.y, xs.z, xs.w};
-    uint32_t y[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int mag = rint_nonneg(__fmul_rn(fabsf(v[i]), inv));
-      const int X = v[i] < 0.f ? -mag : mag;
-      y[i] = uint32_t(X + 0x8080) ^ 0x8080u;   // bytes: (c, b, a, sign extension)
-    }
-    const uint32_t c01 = __byte_perm(y[0], y[1], 0x0040), c23 = __byte_perm(y[2], y[3], 0x0040);
-    const uint32_t b01 = __byte_perm(y[0], y[1], 0x0051), b23 = __byte_perm(y[2], y[3], 0x0051);
-    const uint32_t a01 = __byte_perm(y[0], y[1], 0x0062), a23 = __byte_perm(y[2], y[3], 0x0062);
-    da[g] = __byte_perm(a01, a23, 0x5410);
-    db[g] = __byte_perm(b01, b23, 0x5410);
-    dc[g] = __byte_perm(c01, c23, 0x5410);
+  for (int i = 0; i < (REG ? G : 1); ++i)
+    for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads)
+      rows_store_digits(da, db, dc, g, REG ? xv[i] : park[g], inv);
+}
+
+__global__ void __launch_bounds__(kPrepThreads, 2) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
+  extern __shared__ __align__(128) unsigned char prep_smem[];
+  float* red = reinterpret_cast<float*>(prep_smem);
+  float4* park = reinterpret_cast<float4*>(prep_smem + kPrepRedBytes);
+  griddep_launch_dependents();
+  griddep_wait();
+  const int NG = P.K / 4;
+  if (P.mode == ROWS_LN) {
+    if (NG <= 4 * kPrepThreads) rows_prep_body<4, true>(P, red, park);
+    else rows_prep_body<1, false>(P, red, park);
+  } else {
+    if (NG <= 8 * kPrepThreads) rows_prep_body<8, true>(P, red, park);
+    else rows_prep_body<1, false>(P, red, park);
   }
 }
 
-inline size_t rows_prep_smem(int K) { return size_t(kPrepRedBytes) + size_t(4) * K; }
-
+// Shared memory: the reduction scratch, plus 4*K bytes of parked xs when the row does not fit the registers.
+inline size_t rows_prep_smem(int K, int mode) {
+  const bool in_regs = K / 4 <= (mode == ROWS_LN ? 4 : 8) * kPrepThreads;
+  return size_t(kPrepRedBytes) + (in_regs ? 0 : size_t(4) * K);
+}
 }  // namespace b200

@@ -44,15 +44,16 @@ class QuantizedWeights:
     n_embd: int
     n_ffn: int
     n_vocab: int
-    emb: torch.Tensor
+    emb: Optional[torch.Tensor]              # None on a pipeline stage other than the first
     ln0: Tuple[torch.Tensor, torch.Tensor]
     ln_out: Tuple[torch.Tensor, torch.Tensor]
-    head: QuantMatrix
+    head: Optional[QuantMatrix]              # None on a pipeline stage other than the last
     layers: List[LayerWeights]
+    first_layer: int = 0                     # global index of layers[0] (layer split)
 
     def weight_bytes(self) -> int:
         """uint8 matrix bytes one decode step streams (13*L*D^2 + V*D for F = 4D)."""
-        n = self.head.qt.numel()
+        n = self.head.qt.numel() if self.head is not None else 0
         for ly in self.layers:
             n += sum(m.qt.numel() for m in ly.mat.values())
         return n
@@ -67,10 +68,15 @@ def _quantizer(scheme: str):
 
 
 def quantize_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], device, scheme: str = "fastquant",
-                     quant_device=None) -> QuantizedWeights:
+                     quant_device=None, layer_range: Optional[Tuple[int, int]] = None,
+                     keep_emb: bool = True, keep_head: bool = True) -> QuantizedWeights:
     """Build ``QuantizedWeights`` from (name, tensor) pairs with the reference checkpoint key
     names (helpers/loadWeights.py:19-26, modules/block.py:13-47).  Consumes the iterable one
-    tensor at a time, so large shapes never need the fp32 checkpoint in memory."""
+    tensor at a time, so large shapes never need the fp32 checkpoint in memory.
+
+    ``layer_range=(l0, l1)`` keeps only blocks l0..l1-1 (one stage of a layer split); a stage that
+    is not the first drops the embedding (``keep_emb=False``), one that is not the last drops the
+    head (``keep_head=False``)."""
     q = _quantizer(scheme)
     dev = torch.device(device)
     qdev = torch.device(quant_device) if quant_device is not None else None
@@ -78,9 +84,15 @@ def quantize_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], device, scheme
     top: Dict[str, torch.Tensor] = {}
     head = None
     f32 = lambda t: t.detach().reshape(-1).to(torch.float32).to(dev).contiguous()
+    n_vocab = 0
     for name, t in tensors:
         if name.startswith("blocks."):
             _, idx, rest = name.split(".", 2)
+            if rest.startswith("ln0."):
+                top[rest] = f32(t)
+                continue
+            if layer_range is not None and not (layer_range[0] <= int(idx) < layer_range[1]):
+                continue
             ly = layers.setdefault(int(idx), LayerWeights())
             if rest.endswith(".weight") and rest[:-7] in MATRIX_KEYS:
                 w = t.detach().float()
@@ -94,19 +106,24 @@ def quantize_tensors(tensors: Iterable[Tuple[str, torch.Tensor]], device, scheme
             else:
                 ly.vec[rest] = f32(t)
         elif name == "head.weight":
-            w = t.detach().float()
-            head = q(w.to(qdev) if qdev is not None else w).to(dev)
+            n_vocab = t.shape[0]
+            if keep_head:
+                w = t.detach().float()
+                head = q(w.to(qdev) if qdev is not None else w).to(dev)
         elif name == "emb.weight":
-            top["emb"] = t.detach().to(torch.float32).to(dev).contiguous()
+            n_vocab = t.shape[0]
+            if keep_emb:
+                top["emb"] = t.detach().to(torch.float32).to(dev).contiguous()
         else:
             top[name] = f32(t)
-    n_layer = len(layers)
-    ordered = [layers[i] for i in range(n_layer)]
+    first = min(layers)
+    ordered = [layers[i] for i in range(first, first + len(layers))]
     D = ordered[0].mat["att.key"].k_in
     F = ordered[0].mat["ffn.key"].n_out
-    return QuantizedWeights(n_layer=n_layer, n_embd=D, n_ffn=F, n_vocab=top["emb"].shape[0], emb=top["emb"],
+    return QuantizedWeights(n_layer=len(ordered), n_embd=D, n_ffn=F, n_vocab=n_vocab, emb=top.get("emb"),
                             ln0=(top["ln0.weight"], top["ln0.bias"]),
-                            ln_out=(top["ln_out.weight"], top["ln_out.bias"]), head=head, layers=ordered)
+                            ln_out=(top["ln_out.weight"], top["ln_out.bias"]), head=head, layers=ordered,
+                            first_layer=first)
 
 
 def state_to_reference(state: torch.Tensor, time_decay: Sequence[torch.Tensor]) -> torch.Tensor:
@@ -137,7 +154,7 @@ class B200RWKV:
 
     def __init__(self, weights: QuantizedWeights, use_graph: bool = True, copy_logits: bool = True):
         self.w = weights
-        self.device = weights.emb.device
+        self.device = weights.ln0[0].device
         if self.device.type != "cuda":
             raise RuntimeError("B200RWKV needs a CUDA device: the kernels are sm_100a only and there is no CPU path")
         self._L = _lib.lib()
@@ -199,7 +216,8 @@ class B200RWKV:
             c.ffn_key, c.ffn_receptance, c.ffn_value = (self._matrix(ly.mat[k]) for k in MATRIX_KEYS[4:])
         self._cmodel = _lib.Model(self.n_layer, self.n_embd, self.n_ffn, self.n_vocab, _lib.ptr(w.emb),
                                   _lib.ptr(w.ln0[0]), _lib.ptr(w.ln0[1]), _lib.ptr(w.ln_out[0]), _lib.ptr(w.ln_out[1]),
-                                  self._matrix(w.head), C.cast(self._clayers, C.POINTER(_lib.Layer)))
+                                  self._matrix(w.head) if w.head is not None else _lib.Matrix(),
+                                  C.cast(self._clayers, C.POINTER(_lib.Layer)))
 
     # ------------------------------------------------------------------ one decode step
     def _step_raw(self, tok_ptr: int, state_ptr: int, logits_ptr: Optional[int]) -> None:
@@ -303,6 +321,53 @@ class B200RWKV:
                     ws[:4].zero_()
                     raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
         return out
+
+    def forward_rows_stage(self, tokens: Optional[torch.Tensor], x: torch.Tensor, state: torch.Tensor,
+                           want_logits: bool) -> Optional[torch.Tensor]:
+        """One pipeline stage of ``forward_rows`` when this object holds only a contiguous range
+        of blocks (layer split).  ``tokens [B,T]`` on the first stage, else None and ``x`` fp32
+        ``[B*T, D]`` holds the residual stream received from the previous stage; ``x`` is updated
+        in place for the next stage.  ``state [B, L_stage, 5, D]``.  Returns logits ``[B,V]`` when
+        ``want_logits`` (last stage), else None.  Asynchronous on the current stream."""
+        B = state.shape[0]
+        if x.dim() != 2 or x.shape[1] != self.n_embd or x.shape[0] % B or not x.is_contiguous() or x.dtype != torch.float32:
+            raise ValueError("forward_rows_stage needs x fp32 [B*T, D], contiguous")
+        T = x.shape[0] // B
+        if tuple(state.shape) != (B, self.n_layer, 5, self.n_embd) or not state.is_contiguous() or state.dtype != torch.float32:
+            raise ValueError(f"forward_rows_stage needs a contiguous fp32 state [{B},{self.n_layer},5,{self.n_embd}]")
+        if tokens is not None:
+            if self.w.emb is None:
+                raise ValueError("this stage holds no embedding: pass tokens=None and the previous stage's x")
+            tokens = tokens.to(device=self.device, dtype=torch.int64).reshape(B, T).contiguous()
+        if want_logits and self.w.head is None:
+            raise ValueError("this stage holds no head")
+        out = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device) if want_logits else None
+        with torch.cuda.device(self.device):
+            ws = self._rows_ws.get((B, T))
+            if ws is None:
+                n = int(self._L.b200rwkv_rows_workspace_bytes(C.byref(self._cmodel), B, T))
+                if n == 0:
+                    raise ValueError("forward_rows_stage: at most 65535 rows per call")
+                if len(self._rows_ws) >= 4:
+                    self._rows_ws.clear()
+                ws = self._rows_ws[(B, T)] = torch.zeros(n, dtype=torch.uint8, device=self.device)
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            _lib.check(self._L.b200rwkv_forward_rows_stage(
+                C.byref(self._cmodel), None if tokens is None else tokens.data_ptr(), x.data_ptr(), B, T,
+                state.data_ptr(), state.stride(0), None if out is None else out.data_ptr(), ws.data_ptr(), ws.numel(), stream))
+            self.launch_count += 10 * self.n_layer + (1 if tokens is not None else 0) + (2 if want_logits else 0)
+            self._last_rows_ws = ws
+        return out
+
+    def check_rows_status(self) -> None:
+        """Raise if a kernel of the last ``forward_rows_stage`` call reported an expired wait (synchronises)."""
+        ws = getattr(self, "_last_rows_ws", None)
+        if ws is None:
+            return
+        bits = int(ws[:4].view(torch.int32).item())
+        if bits:
+            ws[:4].zero_()
+            raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
 
     def forward(self, tokens, state: torch.Tensor):
         """``(logits f32[V] on the device, state)`` - see the module docstring."""

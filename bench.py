@@ -237,6 +237,56 @@ def time_prefill(dev, tf_peak, B=8, T=1024):
             "tensor": {"algorithmic_tflops": alg, "peak_bf16_tflops": tf_peak, "frac_of_measured_bf16": alg / tf_peak}}
 
 
+def run_layer_split(args, rank, world, local_rank):
+    """14B shape with its blocks partitioned contiguously over the ranks (launch with torchrun):
+    64-stream decode and a 2048-token prompt; the residual stream hops GPUs over NCCL point-to-point."""
+    import torch.distributed as dist
+    from rwkvstic_b200 import layer_split as LS
+    from rwkvstic_b200.synth import iter_synth_tensors
+
+    L, D = SHAPES[args.shape]
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    model = LS.build_stage(iter_synth_tensors(L, D, VOCAB, 1234, device=str(dev)), rank, world, L, dev)
+    pipe = LS.make_pipeline(model, rank, world)
+    Bs, K, W, mb = args.streams, args.steps, max(args.warmup, 3), args.microbatches
+
+    def timed(fn):
+        torch.cuda.synchronize(dev); dist.barrier(); torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize(dev); dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    state = LS.empty_stage_state(model, Bs)
+    tok = torch.randint(0, VOCAB, (Bs, 1), generator=torch.Generator().manual_seed(5), dtype=torch.int64)
+    pipe.decode_greedy(tok, state, W, mb)
+    decode_ms = timed(lambda: pipe.decode_greedy(tok, state, K, mb))
+    pstate = LS.empty_stage_state(model, 1)
+    prompt = torch.randint(0, VOCAB, (1, 2048), generator=torch.Generator().manual_seed(6), dtype=torch.int64).to(dev)
+    pipe.rows_per_item = 512
+    pipe.forward_rows(prompt, pstate)
+    prefill_ms = timed(lambda: pipe.forward_rows(prompt, pstate))
+    model.check_rows_status()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "rwkv4_14b_layer_split_decode_tokens_per_s_b64", "value": Bs * K / (decode_ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": decode_ms / K, "higher_is_better": True,
+            "scaling": "strong", "dtype": "u8", "data": "synthetic",
+            "config": {"workload": f"RWKV-4 {args.shape} shape L={L} D={D}, blocks split contiguously over {world} GPUs, "
+                                   f"{Bs} streams in {mb} micro-batches, greedy decode",
+                       "handoff": "NCCL send/recv of the fp32 residual stream [rows, D] between consecutive ranks",
+                       "timing": "CUDA events, max over ranks"},
+            "prefill": {"tokens": 2048, "ms": prefill_ms, "value": 2048 / (prefill_ms * 1e-3), "unit": UNIT,
+                        "tokens_per_piece": 512}}), flush=True)
+    dist.destroy_process_group()
+
+
 def run_ours(args, rank, world, local_rank):
     import torch.distributed as dist
     from rwkvstic_b200.model import B200RWKV
@@ -386,6 +436,9 @@ def main():
     ap.add_argument("--shape", default="7b", choices=list(SHAPES))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 3B-shape prompt-ingestion measurement (N=1 only)")
+    ap.add_argument("--mode", default="replicas", choices=["replicas", "layer-split"],
+                    help="replicas: the headline data-parallel decode; layer-split: 14B blocks partitioned over the ranks")
+    ap.add_argument("--microbatches", type=int, default=4, help="stream groups in flight through the layer-split pipeline")
     ap.add_argument("--streams", type=int, default=256, help="streams per GPU of the batched-decode measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -393,6 +446,15 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.mode == "layer-split":
+        if world < 2:
+            sys.exit("--mode layer-split needs torchrun with at least two ranks")
+        if args.shape == "7b":
+            args.shape = "14b"
+        if args.streams == 256:
+            args.streams = 64
+        run_layer_split(args, rank, world, local_rank)
         return
     if world != args.gpus and world == 1 and args.gpus > 1:
         sys.exit("--gpus N > 1 must be launched with torchrun (one rank per GPU)")

@@ -74,20 +74,25 @@ class LayerSplitPipeline:
         piece = max(1, self.rows_per_item // per_group)
         items = work_items(B, T, mb, piece)
         logits = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device) if self.last else None
-        keep = []   # buffers of sends in flight stay referenced until the call returns
+        keep = []   # sends in flight: (request, buffer) stay referenced until the call returns
         for (b0, b1, t0, t1) in items:
             rows = (b1 - b0) * (t1 - t0)
             x = torch.empty(rows, self.n_embd, dtype=torch.float32, device=self.device)
             if not self.first:
-                dist.recv(x, src=self.rank - 1, group=self.group)
+                # batched point-to-point ops: NCCL runs them on their own channel instead of
+                # serialising them with the group's collectives; wait() orders the stream, not the host
+                for req in dist.batch_isend_irecv([dist.P2POp(dist.irecv, x, self.rank - 1, group=self.group)]):
+                    req.wait()
             toks = tokens[b0:b1, t0:t1] if self.first else None
             want = self.last and t1 == T
             out = self.stage_fn(toks, x, state[b0:b1], want)
             if want:
                 logits[b0:b1] = out
             if not self.last:
-                dist.send(x, dst=self.rank + 1, group=self.group)
-                keep.append(x)
+                keep.append((dist.batch_isend_irecv([dist.P2POp(dist.isend, x, self.rank + 1, group=self.group)]), x))
+        for reqs, _ in keep:
+            for req in reqs:
+                req.wait()
         return logits
 
     def decode_greedy(self, tokens: torch.Tensor, state: torch.Tensor, steps: int, microbatches: int = 1) -> torch.Tensor:

@@ -70,7 +70,14 @@ class ContractModel:
 
     def step(self, token: int, state: torch.Tensor, want_logits: bool = True):
         w = self.w
-        xa = layernorm32(w.emb[token], *w.ln0)
+        xa = self.blocks(layernorm32(w.emb[token], *w.ln0), state)
+        if not want_logits:
+            return None, state
+        return fixed_point_gemv(layernorm32(xa, *w.ln_out), w.head), state
+
+    def blocks(self, xa: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        """All blocks this object holds applied to one residual-stream row; ``state`` in place."""
+        w = self.w
         for i, ly in enumerate(w.layers):
             v, m, st = ly.vec, ly.mat, state[i]
             xy = layernorm32(xa, v["ln1.weight"], v["ln1.bias"])
@@ -90,9 +97,23 @@ class ContractModel:
             rf = torch.sigmoid(fixed_point_gemv(fr, m["ffn.receptance"]))
             st[1] = dd
             xa = xb + rf * fixed_point_gemv(kk, m["ffn.value"])
-        if not want_logits:
-            return None, state
-        return fixed_point_gemv(layernorm32(xa, *w.ln_out), w.head), state
+        return xa
+
+    def stage(self, tokens, x: torch.Tensor, state: torch.Tensor, want_logits: bool):
+        """CPU stand-in for B200RWKV.forward_rows_stage: ``tokens [B,T]`` or None, ``x [B*T, D]`` in
+        place, ``state [B, L_stage, 5, D]``; logits ``[B,V]`` of each stream's last row when asked."""
+        w = self.w
+        B = state.shape[0]
+        T = x.shape[0] // B
+        out = torch.empty(B, w.n_vocab) if want_logits else None
+        for b in range(B):
+            for t in range(T):
+                row = b * T + t
+                xin = layernorm32(w.emb[int(tokens[b, t])], *w.ln0) if tokens is not None else x[row]
+                x[row] = self.blocks(xin, state[b])
+            if want_logits:
+                out[b] = fixed_point_gemv(layernorm32(x[b * T + T - 1], *w.ln_out), w.head)
+        return out
 
     def forward(self, tokens, state):
         logits = None

@@ -1,9 +1,12 @@
-"""A small, self-contained GEMV workload for profilers: ``python -m rwkvstic_b200.profile_case``.
+"""Small, self-contained GEMV / GEMM workloads for profilers: ``python -m rwkvstic_b200.profile_case``.
 
 Launches the streaming uint8 GEMV (one activation-preparation CTA + one streaming grid per
 launch) on a few DISTINCT random matrices of one RWKV-4 shape, so that every launch reads
 bytes that are not in L2 while the whole run holds well under 1 GB on the device.  Meant for
 ``ncu -k regex:stream_gemv -c 3`` style captures; prints the CUDA-event time per launch.
+
+With ``--rows R`` (R > 1) the same matrices are applied to R activation rows through the
+tensor-core path instead (row preparation + ``tile_gemm_kernel``): ``ncu -k regex:tile_gemm``.
 """
 from __future__ import annotations
 
@@ -35,23 +38,33 @@ def main():
     ap.add_argument("--matrix", default="ffn_kr", choices=["att_kvr", "att_out", "ffn_kr", "ffn_value", "head"])
     ap.add_argument("--copies", type=int, default=4, help="distinct matrix sets (4 x 84 MB > the 126 MB L2)")
     ap.add_argument("--launches", type=int, default=8)
+    ap.add_argument("--rows", type=int, default=1, help="activation rows; > 1 selects the tile GEMM")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     _, D = SHAPES[args.shape]
     sets = matrices(args.matrix, D, dev, args.copies)
-    xs = {D: torch.randn(D, device=dev), 4 * D: torch.randn(4 * D, device=dev)}
+    R = args.rows
+    if R > 1:
+        xs = {D: torch.randn(R, D, device=dev), 4 * D: torch.randn(R, 4 * D, device=dev)}
+    else:
+        xs = {D: torch.randn(D, device=dev), 4 * D: torch.randn(4 * D, device=dev)}
     nbytes = sum(m.qt.numel() for m in sets[0])
     times = []
     for i in range(args.launches):
         mats = sets[i % len(sets)]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        ops.gemv_u8(mats, [xs[m.k_in] for m in mats])
+        if R > 1:
+            ops.gemm_u8(mats, [xs[m.k_in] for m in mats])
+        else:
+            ops.gemv_u8(mats, [xs[m.k_in] for m in mats])
         e1.record()
         e1.synchronize()
         times.append(e0.elapsed_time(e1) * 1e3)
-    print(f"{args.matrix} {args.shape}: {nbytes / 1e6:.1f} MB per launch, event time per launch (us): "
+    print(f"{args.matrix} {args.shape} rows={R}: {nbytes / 1e6:.1f} MB of weights per launch, event time per launch (us): "
           + " ".join(f"{t:.1f}" for t in times))
+    if R > 1:
+        print(f"multiply-adds per launch: {R * nbytes / 1e9:.2f} G (x3 activation digits on the tensor cores)")
 
 
 if __name__ == "__main__":

@@ -241,6 +241,17 @@ int b200rwkv_forward_rows_stage(const b200rwkv_model* m, const int64_t* tokens, 
                                 int tokens_per_stream, float* state, int64_t state_stride, float* logits,
                                 void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Greedy sampling on the device (replaces the host-side argmax of the reference's sampler for
+ * temperature 0, rwkvMaster.py:32-45, which reads the whole logits vector back per token).
+ * out[r] = index of the largest of x[r*ldx .. r*ldx+n), lowest index on ties.  `history`
+ * (optional, with its device counter and capacity): row 0's result is also appended at
+ * history[*history_count] and the counter incremented, so a decode loop can feed `out` straight
+ * back as the next token and read all generated ids once at the end.
+ */
+int b200rwkv_argmax(const float* x, int rows, int n, int64_t ldx, int64_t* out, int64_t* history,
+                    int* history_count, int history_capacity, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

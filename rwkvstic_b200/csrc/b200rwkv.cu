@@ -469,6 +469,51 @@ static void fill_gemm_seg(GemmSeg& s, const b200rwkv_matrix& m, const SegScalars
   s.scal = scal; s.out = out; s.ldo = ldo;
 }
 
+
+// Greedy sampling on the device: index of the largest of n values per row (ties: lowest index, as
+// torch.argmax on a CPU tensor gives); optionally appended to a history buffer so that a decode
+// loop can run without the host reading anything until it ends.
+__global__ void __launch_bounds__(1024)
+argmax_rows_kernel(const float* __restrict__ x, int n, long long ldx, long long* __restrict__ out,
+                   long long* __restrict__ hist, int* __restrict__ hist_count, int hist_cap) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float* row = x + size_t(blockIdx.x) * ldx;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = tid; i < n; i += 1024) {
+    const float v = __ldcg(row + i);
+    if (v > best || (v == best && i < bi) || bi == 0x7fffffff) { best = v; bi = i; }
+  }
+  auto better = [](float v, int i, float w, int j) { return j != 0x7fffffff && (i == 0x7fffffff || w > v || (w == v && j < i)); };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float w = __shfl_xor_sync(0xffffffffu, best, o);
+    const int j = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(best, bi, w, j)) { best = w; bi = j; }
+  }
+  if (lane == 0) { sv[warp] = best; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    best = sv[lane]; bi = si[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float w = __shfl_xor_sync(0xffffffffu, best, o);
+      const int j = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (better(best, bi, w, j)) { best = w; bi = j; }
+    }
+    if (lane == 0) {
+      out[blockIdx.x] = bi;
+      if (hist && hist_count && blockIdx.x == 0) {
+        const int c = *hist_count;
+        if (c < hist_cap) hist[c] = bi;
+        *hist_count = c + 1;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------- static scratch
 // Scratch of b200rwkv_gemv_u8_static: digit planes (up to kStaticPlaneBytes) followed by the
 // per-matrix scalars.  Lives in every GPU's memory from the moment the library is loaded there.
@@ -974,6 +1019,17 @@ int b200rwkv_forward_rows_stage(const b200rwkv_model* m, const int64_t* tokens, 
   if (!x) return fail(B200RWKV_EINVAL, "forward_rows_stage: null x");
   return forward_rows_impl(m, tokens, x, streams, tokens_per_stream, state, state_stride, logits, workspace, workspace_bytes,
                            stream);
+}
+
+int b200rwkv_argmax(const float* x, int rows, int n, int64_t ldx, int64_t* out, int64_t* history, int* history_count,
+                    int history_capacity, void* stream) {
+  if (!x || !out || rows < 1 || n < 1 || ldx < n || (history && (!history_count || history_capacity < 1)))
+    return fail(B200RWKV_EINVAL, "argmax: bad argument (rows=%d n=%d)", rows, n);
+  argmax_rows_kernel<<<rows, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, n, ldx, reinterpret_cast<long long*>(out), reinterpret_cast<long long*>(history), history_count, history_capacity);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "argmax: %s", cudaGetErrorString(e));
+  return B200RWKV_OK;
 }
 
 }  // extern "C"

@@ -369,6 +369,51 @@ class B200RWKV:
             ws[:4].zero_()
             raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
 
+    # ------------------------------------------------------------------ greedy sampling on the device
+    def argmax_token(self, logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Device int64[1]: index of the largest logit of the last ``forward`` (or of ``logits``),
+        computed on the device so that only 8 bytes need to travel to the host per token."""
+        lg = self._logits if logits is None else logits
+        out = torch.empty(1, dtype=torch.int64, device=self.device)
+        with torch.cuda.device(self.device):
+            _lib.check(self._L.b200rwkv_argmax(lg.data_ptr(), 1, lg.numel(), lg.numel(), out.data_ptr(), None, None, 0,
+                                               torch.cuda.current_stream(self.device).cuda_stream))
+        self.launch_count += 1
+        return out
+
+    def generate_greedy(self, token, state: torch.Tensor, n: int) -> torch.Tensor:
+        """``n`` greedy decode steps that never leave the device: feed ``token``, take the arg-max
+        of the logits, feed it back, ...  Each step is one CUDA-graph replay (the decode step
+        plus an arg-max kernel that writes the next token into the step's own input buffer and
+        appends it to a history buffer).  Returns the ``n`` generated ids (device int64);
+        ``state`` is updated in place.  Same tokens as calling ``forward`` + ``torch.argmax`` n times."""
+        state = self._own_state(state)
+        hist = torch.zeros(max(n, 1), dtype=torch.int64, device=self.device)
+        count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            self._tok.copy_(torch.as_tensor(token, dtype=torch.int64).reshape(1), non_blocking=True)
+            stream = lambda: torch.cuda.current_stream(self.device).cuda_stream
+
+            def one():
+                self._step_raw(self._tok.data_ptr(), state.data_ptr(), self._logits.data_ptr())
+                _lib.check(self._L.b200rwkv_argmax(self._logits.data_ptr(), 1, self.n_vocab, self.n_vocab,
+                                                   self._tok.data_ptr(), hist.data_ptr(), count.data_ptr(), hist.numel(),
+                                                   stream()))
+            if self.use_graph and n >= 3:
+                one()                                   # eager first step (also warms every lazy initialisation)
+                g = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize(self.device)
+                with torch.cuda.graph(g):
+                    one()
+                count.fill_(1)                          # the capture itself does not run the kernels
+                for _ in range(n - 1):
+                    g.replay()
+            else:
+                for _ in range(n):
+                    one()
+        self.launch_count += n * (self.launches_per_step + 1)
+        return hist[:n]
+
     def forward(self, tokens, state: torch.Tensor):
         """``(logits f32[V] on the device, state)`` - see the module docstring."""
         if not torch.is_tensor(tokens):

@@ -111,3 +111,21 @@ def test_169m_prompt_then_64_greedy_tokens(m169, golden):
 def test_rejects_wrong_state_shape(tiny):
     with pytest.raises(ValueError):
         tiny.forward([1], torch.zeros(3, 5, 128))
+
+
+def test_greedy_on_device_equals_host_argmax_loop(m169, golden):
+    """The device-side arg-max feedback loop generates the reference's greedy tokens."""
+    g = golden("model_169m.npz")
+    state = m169.emptyState.clone()
+    logits, state = m169.forward(torch.from_numpy(g["prompt"]), state)
+    first = m169.argmax_token()
+    assert int(first) == int(torch.argmax(logits)) == int(g["tokens"][0])
+    st_graph, st_eager = state.clone(), state.clone()
+    ids = m169.generate_greedy(int(first), st_graph, 63)
+    assert [int(first)] + ids.cpu().tolist() == g["tokens"].tolist()
+    eager = B200RWKV(m169.w, use_graph=False)
+    ids2 = eager.generate_greedy(int(first), st_eager, 63)
+    assert torch.equal(ids, ids2) and torch.equal(st_graph, st_eager)
+    ties = torch.tensor([1.0, 5.0, 5.0, -2.0, 5.0], device=DEV)
+    assert int(m169.argmax_token(ties)) == 1
+    m169.check_status()

@@ -437,15 +437,17 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  // Tiles of 256 weight rows move the fewest operand bytes per MAC; when they would not fill the GPU
-  // twice over, tiles of 128 rows give twice the CTAs.
-  int max_n = 0;
-  long long tiles256 = 0;
+  // Tiles of 256 weight rows move the fewest operand bytes per MAC (two sub-tiles share one digit
+  // tile); tiles of 128 rows spread more evenly over the CTAs when there are few of them.  Pick
+  // the smaller estimated makespan: rounds of tiles per CTA x relative cost of a tile.
+  long long tiles256 = 0, tiles128 = 0;
   for (int s = 0; s < P.nseg; ++s) {
-    if (P.seg[s].N > max_n) max_n = P.seg[s].N;
     tiles256 += (long long)(P.Rpad / P.Rt) * ((P.seg[s].N + kGemmM - 1) / kGemmM);
+    tiles128 += (long long)(P.Rpad / P.Rt) * ((P.seg[s].N + 127) / 128);
   }
-  P.mt = tiles256 >= 2ll * device_sms() ? kGemmM : 128;
+  const long long sms = device_sms() > 0 ? device_sms() : 1;
+  const double cost256 = double((tiles256 + sms - 1) / sms) * 2.0, cost128 = double((tiles128 + sms - 1) / sms) * 1.15;
+  P.mt = cost256 <= cost128 ? kGemmM : 128;
   for (int s = 0; s < P.nseg; ++s) {
     GemmSeg& S = P.seg[s];
     if (!encode_byte_map(&S.wmap, mats[s]->qt, (unsigned long long)S.N, P.K, P.mt, 1) ||
@@ -457,8 +459,13 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
   }
   { const char* d = getenv("B200RWKV_GEMM_DEBUG"); P.dbg = d ? atoi(d) : 0; }
   if (P.dbg == 3) return cudaSuccess;   // measurement only: preparation kernel alone
-  const dim3 grid(P.Rpad / P.Rt, (max_n + P.mt - 1) / P.mt, P.nseg);
-  if (grid.y > 65535) { *why = "n_out too large"; return cudaErrorInvalidValue; }
+  P.row_tiles = P.Rpad / P.Rt;
+  P.ntiles = 0;
+  for (int s = 0; s < P.nseg; ++s) {
+    P.tiles_seg[s] = P.row_tiles * ((P.seg[s].N + P.mt - 1) / P.mt);
+    P.ntiles += P.tiles_seg[s];
+  }
+  const dim3 grid(P.ntiles < device_sms() ? P.ntiles : device_sms());
   tile_gemm_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(P);
   return cudaGetLastError();
 }

@@ -13,7 +13,7 @@
 //   D  = two accumulators of 128 lanes x 3*Rt int32 columns in tensor memory (TMEM),
 //        column = digit*Rt + row; the second accumulator starts at column 256
 //
-// One CTA owns one (256 weight rows) x (Rt activation rows) output tile and walks K in 128-byte
+// One tile = (256 weight rows) x (Rt activation rows) of output; a CTA walks K in 128-byte
 // steps through a ring of shared-memory stages: warp 0 issues the TMA copies, warp 1 issues the
 // MMAs (one elected thread; completion is signalled to the ring by tcgen05.commit on the stage's
 // mbarrier), warps 4-11 read the accumulators with tcgen05.ld and apply the affine terms and the
@@ -39,6 +39,7 @@ constexpr int kGemmStageBytes = kGemmABytes + kDigits * kGemmRowsMax * 128;   //
 constexpr int kGemmTmemCols = 512;                       // both accumulators; one CTA per SM (shared memory)
 constexpr int kGemmAcc1Col = 256;                        // first column of the second accumulator
 constexpr int kGemmThreads = 384;                        // warp 0 TMA, 1 MMA, 2 TMEM allocation, 4-11 epilogue
+constexpr int kGemmEpiWarps = 8;
 constexpr int kGemmOffScal = 1024;                       // SegScalars[80]
 constexpr int kGemmOffRing = 4096;
 constexpr int kGemmSmem = kGemmOffRing + kGemmStages * kGemmStageBytes;
@@ -73,6 +74,9 @@ struct GemmParams {
   int nseg, K, R, Rpad;
   int Rt;              // activation rows per tile (multiple of 16, <= 80); Rpad is a multiple of it
   int mt;              // weight rows per tile: 256 (two accumulators) or 128 (small grids: more CTAs)
+  int row_tiles;       // Rpad / Rt
+  int tiles_seg[kMaxSeg];  // tiles per matrix = row_tiles * ceil(N / mt)
+  int ntiles;          // all tiles of the launch; the grid is min(ntiles, SMs), CTAs loop over tiles
   int* status;
   int dbg;             // measurement only: 1 = no operand copies (MMAs on stale shared memory), 2 = no MMAs, 4 = no epilogue
 };
@@ -122,21 +126,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Tile t of a launch -> (segment, first weight row, first activation row).  Tiles that share a weight
+// tile are consecutive, so CTAs working side by side read it from L2.
+struct GemmTile { int seg, n0, row0; };
+__device__ __forceinline__ GemmTile gemm_tile(const GemmParams& P, int t) {
+  int s = 0;
+  while (s < P.nseg - 1 && t >= P.tiles_seg[s]) { t -= P.tiles_seg[s]; ++s; }
+  const int wt = t / P.row_tiles;
+  return {s, wt * P.mt, (t - wt * P.row_tiles) * P.Rt};
+}
+
 __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid_constant__ GemmParams P) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const GemmSeg& S = P.seg[blockIdx.z];
-  const int n0 = blockIdx.y * P.mt;
   const int Rt = P.Rt;
-  const int row0 = blockIdx.x * Rt;
-  if (n0 >= S.N) return;   // segments of one launch may have different N (whole CTA leaves: no barrier yet)
   const int nk = P.K / 128;
-  const bool two = P.mt == kGemmM && n0 + 128 < S.N;   // the second 128-row sub-tile exists and holds real rows
   const uint32_t a_bytes = uint32_t(P.mt) * 128u;
   const uint32_t b_bytes = uint32_t(kDigits * Rt * 128);
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 8), acc_bar = smem_u32(bars + 16);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 8);
+  const uint32_t acc_full = smem_u32(bars + 16), acc_empty = smem_u32(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 256);
   volatile int* issued_ptr = reinterpret_cast<volatile int*>(smem + 260);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 264);
@@ -145,7 +155,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
 
   if (tid == 0) {
     for (int i = 0; i < kGemmStages; ++i) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
-    mbar_init(acc_bar, 1);
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, kGemmEpiWarps);
     *abort_flag = 0;
     *issued_ptr = 0;
     fence_mbar_init();
@@ -160,26 +171,33 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
   const uint32_t tmem = *tmem_slot;
   griddep_launch_dependents();
 
+  // Persistent: CTA c handles tiles c, c + grid, c + 2*grid, ...  The operand ring runs on across
+  // tiles (the producer is already fetching the next tile while the epilogue of this one runs).
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       griddep_wait();   // the digit rows come from the preparation kernel in front of this launch
       int issued = 0;
-      for (int kc = 0; kc < (P.dbg == 1 ? 0 : nk); ++kc) {
-        const int slot = kc % kGemmStages;
-        const uint32_t phase = uint32_t(kc / kGemmStages) & 1u;
-        if (!mbar_wait_bounded(empty0 + 8 * slot, phase ^ 1u, abort_flag)) {
-          if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_EMPTY);
-          break;
-        }
-        const uint32_t bar = full0 + 8 * slot;
-        const uint32_t dst = smem_u32(ring + size_t(slot) * kGemmStageBytes);
-        mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
-        tma_load_3d(dst, &S.wmap, 0, n0, kc, bar);   // rows past N are zero-filled
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < P.ntiles && ok; tile += gridDim.x) {
+        const GemmTile T = gemm_tile(P, tile);
+        const GemmSeg& S = P.seg[T.seg];
+        for (int kc = 0; kc < (P.dbg == 1 ? 0 : nk); ++kc, ++issued) {
+          const int slot = issued % kGemmStages;
+          const uint32_t phase = uint32_t(issued / kGemmStages) & 1u;
+          if (!mbar_wait_bounded(empty0 + 8 * slot, phase ^ 1u, abort_flag)) {
+            if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_EMPTY);
+            ok = false;
+            break;
+          }
+          const uint32_t bar = full0 + 8 * slot;
+          const uint32_t dst = smem_u32(ring + size_t(slot) * kGemmStageBytes);
+          mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
+          tma_load_3d(dst, &S.wmap, 0, T.n0, kc, bar);   // rows past N are zero-filled
 #pragma unroll
-        for (int d = 0; d < kDigits; ++d)
-          tma_load_3d(dst + kGemmABytes + uint32_t(d * Rt * 128), &S.xmap, 0, d * P.Rpad + row0, kc, bar);
-        ++issued;
+          for (int d = 0; d < kDigits; ++d)
+            tma_load_3d(dst + kGemmABytes + uint32_t(d * Rt * 128), &S.xmap, 0, d * P.Rpad + T.row0, kc, bar);
+        }
       }
       *issued_ptr = issued;
     }
@@ -188,27 +206,39 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_u8s8(128, kDigits * Rt);
       bool ok = true;
-      for (int kc = 0; kc < nk && ok; ++kc) {
-        const int slot = kc % kGemmStages;
-        const uint32_t phase = uint32_t(kc / kGemmStages) & 1u;
-        if (P.dbg != 1 && !mbar_wait_bounded(full0 + 8 * slot, phase, abort_flag)) {
-          if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
+      int step = 0, iter = 0;
+      for (int tile = blockIdx.x; tile < P.ntiles && ok; tile += gridDim.x, ++iter) {
+        const GemmTile T = gemm_tile(P, tile);
+        const bool two = P.mt == kGemmM && T.n0 + 128 < P.seg[T.seg].N;   // second 128-row sub-tile holds real rows
+        // the epilogue must have read the previous tile's accumulators out of TMEM
+        if (!mbar_wait_bounded(acc_empty, uint32_t(iter & 1) ^ 1u, abort_flag)) {
+          if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_EMPTY);
           ok = false;
           break;
         }
         tc_fence_after();
-        if (P.dbg == 2) { mbar_arrive(empty0 + 8 * slot); continue; }
-        const uint32_t a = smem_u32(ring + size_t(slot) * kGemmStageBytes);
-        const uint64_t ad0 = umma_desc(a), ad1 = umma_desc(a + 128 * 128), bd = umma_desc(a + kGemmABytes);
+        for (int kc = 0; kc < nk; ++kc, ++step) {
+          const int slot = step % kGemmStages;
+          const uint32_t phase = uint32_t(step / kGemmStages) & 1u;
+          if (P.dbg != 1 && !mbar_wait_bounded(full0 + 8 * slot, phase, abort_flag)) {
+            if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (P.dbg == 2) { mbar_arrive(empty0 + 8 * slot); continue; }
+          const uint32_t a = smem_u32(ring + size_t(slot) * kGemmStageBytes);
+          const uint64_t ad0 = umma_desc(a), ad1 = umma_desc(a + 128 * 128), bd = umma_desc(a + kGemmABytes);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {   // 32 bytes of K per instruction: +2 in the descriptors' 16-byte address units
-          const uint32_t acc = (kc | k) != 0 ? 1u : 0u;
-          umma_i8(tmem, ad0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
-          if (two) umma_i8(tmem + kGemmAcc1Col, ad1 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+          for (int k = 0; k < 4; ++k) {   // 32 bytes of K per instruction: +2 in the descriptors' 16-byte address units
+            const uint32_t acc = (kc | k) != 0 ? 1u : 0u;
+            umma_i8(tmem, ad0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+            if (two) umma_i8(tmem + kGemmAcc1Col, ad1 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+          }
+          umma_commit(empty0 + 8 * slot);   // frees the stage once these MMAs have read it
         }
-        umma_commit(empty0 + 8 * slot);   // frees the stage once these MMAs have read it
+        if (ok) umma_commit(acc_full);      // accumulators of this tile complete
       }
-      if (ok) umma_commit(acc_bar);       // accumulators complete
     }
   } else if (warp >= 4) {
     // ---------------------------------------------------------------- epilogue: 8 warps.  A warp can
@@ -217,17 +247,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
     const int q = warp & 3, eg = (warp - 4) >> 2;
     const int et = tid - 128;
     griddep_wait();
-    for (int i = et; i < Rt * 8; i += kGemmThreads - 128) {
-      const int r = row0 + (i >> 3);
-      reinterpret_cast<float*>(scal)[i] = r < P.R ? __ldcg(reinterpret_cast<const float*>(S.scal + r) + (i & 7)) : 0.f;
-    }
-    named_bar_sync(1, kGemmThreads - 128);
-    const bool ok = mbar_wait_bounded(acc_bar, 0, abort_flag);
-    if (__all_sync(0xffffffffu, ok)) {
+    bool ok = true;
+    int iter = 0;
+    for (int tile = blockIdx.x; tile < P.ntiles && ok; tile += gridDim.x, ++iter) {
+      const GemmTile T = gemm_tile(P, tile);
+      const GemmSeg& S = P.seg[T.seg];
+      const int n0 = T.n0, row0 = T.row0;
+      const bool two = P.mt == kGemmM && n0 + 128 < S.N;
+      named_bar_sync(1, kGemmEpiWarps * 32);   // every epilogue warp is done with the previous tile's scalars
+      for (int i = et; i < Rt * 8; i += kGemmEpiWarps * 32) {
+        const int r = row0 + (i >> 3);
+        reinterpret_cast<float*>(scal)[i] = r < P.R ? __ldcg(reinterpret_cast<const float*>(S.scal + r) + (i & 7)) : 0.f;
+      }
+      named_bar_sync(1, kGemmEpiWarps * 32);
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_full, uint32_t(iter & 1), abort_flag));
+      if (!ok) {
+        if (lane == 0 && P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
+        break;
+      }
       tc_fence_after();
-      const int nchunks = Rt / 16, nitems = (two ? 2 : 1) * nchunks;
+      const int nchunks = Rt / 16, nitems = P.dbg == 4 ? 0 : (two ? 2 : 1) * nchunks;
+      // this warp's last item that really reads TMEM: after it the accumulators may be overwritten
+      int last_item = -1;
+      for (int item = eg; item < nitems; item += 2)
+        if (row0 + (item % nchunks) * 16 < P.R) last_item = item;
+      if (last_item < 0) {
+        tc_fence_before();
+        if (lane == 0) mbar_arrive(acc_empty);
+      }
 #pragma unroll 1
-      for (int item = eg; item < (P.dbg == 4 ? 0 : nitems); item += 2) {
+      for (int item = eg; item < nitems; item += 2) {
         const int h = item / nchunks, j0 = (item - h * nchunks) * 16;
         if (row0 + j0 >= P.R) continue;   // warp-uniform
         const int n = n0 + h * 128 + q * 32 + lane;
@@ -240,17 +289,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         tmem_ld16(tbase + uint32_t(Rt), db);
         tmem_ld16(tbase + uint32_t(2 * Rt), dc);
         tmem_ld_wait();
+        if (item == last_item) {   // the rest of this item works from registers: let the next tile's MMAs start
+          tc_fence_before();
+          if (lane == 0) mbar_arrive(acc_empty);
+        }
         // branch-free over the 16 rows so that their dependency chains interleave (one warp per
         // scheduler: a row at a time would run at the latency of every instruction)
         float yv[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const SegScalars& sc = scal[j0 + j];
+          const float4 sc = *reinterpret_cast<const float4*>(&scal[j0 + j]);   // sd, zp, sumxs, sumx
           const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
-          float y = __fmul_rn(__ll2float_rn(I), sc.sd) + S.half * sc.sumxs;
+          float y = __fmul_rn(__ll2float_rn(I), sc.x) + S.half * sc.z;
           y *= rx;               // rx = 1, mx = 0 when the matrix has no per-output terms: exact no-ops
-          y += sc.zp;
-          y += mx * sc.sumx;
+          y += sc.y;
+          y += mx * sc.w;
           yv[j] = y;
         }
         if (S.act == ACT_RELUSQ) {
@@ -281,8 +334,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
           if (r <= rlast && nvalid) S.out[size_t(r) * S.ldo + n] = yv[j];
         }
       }
-    } else if (lane == 0 && P.status) {
-      atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
     }
   }
 

@@ -307,6 +307,8 @@ embed_ln0_rows_kernel(const float* __restrict__ emb, const long long* __restrict
                       const float* __restrict__ w, const float* __restrict__ b, float* __restrict__ out) {
   __shared__ float red[8];
   __shared__ float bc;
+  griddep_launch_dependents();
+  griddep_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   long long tok = tokens[blockIdx.x];
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
@@ -341,6 +343,8 @@ __global__ void __launch_bounds__(128)
 wkv_rows_kernel(int B, int T, int C, const float* __restrict__ w, const float* __restrict__ u, float* __restrict__ k,
                 const float* __restrict__ v, const float* __restrict__ gate, float* __restrict__ aa,
                 float* __restrict__ bb, float* __restrict__ pp, long long state_stride) {
+  griddep_launch_dependents();
+  griddep_wait();
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= B * C) return;
   const int s = idx / C, c = idx - s * C;
@@ -404,6 +408,21 @@ static size_t gemm_workspace_bytes(int k_in, int nmat, int rows) {
   return 256 + align256(size_t(nmat) * kDigits * Rpad * k_in) + align256(sizeof(SegScalars) * size_t(nmat) * rows);
 }
 
+// Launch with programmatic stream serialisation: the kernel may start while its predecessor on the
+// stream is still running; every kernel launched this way calls griddepcontrol.wait before it
+// touches global memory.
+template <typename Kernel, typename... Args>
+static cudaError_t launch_chained(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 static cudaError_t launch_rows_prep(const RowsPrepParams& P, cudaStream_t stream, const char** why) {
   static bool configured[64];
   *why = "rows_prep launch failed";
@@ -420,8 +439,7 @@ static cudaError_t launch_rows_prep(const RowsPrepParams& P, cudaStream_t stream
     *why = "unsupported shape: k_in too large for the row preparation kernel, or more than 65535 rows";
     return cudaErrorInvalidValue;
   }
-  rows_prep_kernel<<<dim3(P.nseg, P.R), kPrepThreads, smem, stream>>>(P);
-  return cudaGetLastError();
+  return launch_chained(rows_prep_kernel, dim3(P.nseg, P.R), dim3(kPrepThreads), smem, stream, P);
 }
 
 // Fills the tensor maps of P (weights and digit rows) and launches the tile GEMM.  digits: [nseg][3][Rpad][K].
@@ -466,8 +484,7 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
     P.ntiles += P.tiles_seg[s];
   }
   const dim3 grid(P.ntiles < device_sms() ? P.ntiles : device_sms());
-  tile_gemm_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(P);
-  return cudaGetLastError();
+  return launch_chained(tile_gemm_kernel, grid, dim3(kGemmThreads), size_t(kGemmSmem), stream, P);
 }
 
 static void fill_gemm_seg(GemmSeg& s, const b200rwkv_matrix& m, const SegScalars* scal, float* out, long long ldo) {
@@ -898,8 +915,9 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
 
   if (x_ext) ws.xa = x_ext;
   if (tokens) {
-    embed_ln0_rows_kernel<<<R, 256, 0, s>>>(m->emb, reinterpret_cast<const long long*>(tokens), D, V, m->ln0_w, m->ln0_b, ws.xa);
-    if ((e = cudaGetLastError()) != cudaSuccess) return fail(B200RWKV_ECUDA, "forward_rows: embed launch: %s", cudaGetErrorString(e));
+    e = launch_chained(embed_ln0_rows_kernel, dim3(R), dim3(256), 0, s, m->emb, reinterpret_cast<const long long*>(tokens), D, V,
+                       m->ln0_w, m->ln0_b, ws.xa);
+    if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "forward_rows: embed launch: %s", cudaGetErrorString(e));
   }
 
   RowsPrepParams Q;
@@ -911,10 +929,10 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     Q.shift_out = mode == ROWS_LN ? ws.shift_new : nullptr; Q.digits = ws.digits; Q.scal = ws.scal;
   };
   auto gemm_common = [&](int nseg, int K) { P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.Rt = gemm_tile_rows(R); P.status = ws.status; };
-  // new token-shift carry of every stream -> its state row (after the kernel that read the old one)
-  auto commit_carry = [&](float* dst_row) -> cudaError_t {
-    return cudaMemcpy2DAsync(dst_row, size_t(state_stride) * 4, ws.shift_new, size_t(D) * 4, size_t(D) * 4, B,
-                             cudaMemcpyDeviceToDevice, s);
+  // new token-shift carry of every stream -> its state row, done by the NEXT preparation launch
+  // (the launch that parked it had sibling CTAs still reading the old row)
+  auto commit_carry = [&](float* dst_row) {
+    Q.commit_src = ws.shift_new; Q.commit_dst = dst_row; Q.commit_stride = state_stride; Q.commit_n = D;
   };
 
   for (int l = 0; l < L; ++l) {
@@ -937,8 +955,6 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     prep_common(3, D, ROWS_LN, ws.xa, ly.ln1_w, ly.ln1_b, st,
                 wants_sums(ly.att_key) || wants_sums(ly.att_value) || wants_sums(ly.att_receptance));
     if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
-    why = "carry copy failed";
-    if ((e = commit_carry(st)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_gemm_seg(P.seg[0], ly.att_key, ws.scal, ws.kb, D);
     fill_gemm_seg(P.seg[1], ly.att_value, ws.scal + size_t(R), ws.vb, D);
@@ -948,14 +964,16 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     { const b200rwkv_matrix* mp[3] = {&ly.att_key, &ly.att_value, &ly.att_receptance};
       if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
     // 2. WKV recurrence over each stream's rows; kb <- sigmoid(r) * wkv
-    wkv_rows_kernel<<<(B * D + 127) / 128, 128, 0, s>>>(B, T, D, ly.time_decay, ly.time_first, ws.kb, ws.vb, ws.rb,
-                                                         st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D), state_stride);
     why = "wkv_rows launch failed";
-    if ((e = cudaGetLastError()) != cudaSuccess) goto launch_failed;
+    e = launch_chained(wkv_rows_kernel, dim3((B * D + 127) / 128), dim3(128), 0, s, B, T, D, ly.time_decay, ly.time_first, ws.kb,
+                       (const float*)ws.vb, (const float*)ws.rb, st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D),
+                       (long long)state_stride);
+    if (e != cudaSuccess) goto launch_failed;
     // 3. attention output projection + residual -> xb
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], ly.att_output, nullptr, ws.kb);
     prep_common(1, D, ROWS_PLAIN, nullptr, nullptr, nullptr, nullptr, wants_sums(ly.att_output));
+    commit_carry(st);                 // ln1 output of each stream's last row -> state row 0
     if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_gemm_seg(P.seg[0], ly.att_output, ws.scal, ws.xb, D);
@@ -969,8 +987,6 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     fill_prep_seg(Q.seg[1], ly.ffn_receptance, ly.ffn_mix_r, nullptr);
     prep_common(2, D, ROWS_LN, ws.xb, ly.ln2_w, ly.ln2_b, st + size_t(D), wants_sums(ly.ffn_key) || wants_sums(ly.ffn_receptance));
     if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
-    why = "carry copy failed";
-    if ((e = commit_carry(st + size_t(D))) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_gemm_seg(P.seg[0], ly.ffn_key, ws.scal, ws.kk, F);
     P.seg[0].act = ACT_RELUSQ;
@@ -983,6 +999,7 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     memset(&Q, 0, sizeof(Q));
     fill_prep_seg(Q.seg[0], ly.ffn_value, nullptr, ws.kk);
     prep_common(1, F, ROWS_PLAIN, nullptr, nullptr, nullptr, nullptr, wants_sums(ly.ffn_value));
+    commit_carry(st + size_t(D));     // ln2 output of each stream's last row -> state row 1
     if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_gemm_seg(P.seg[0], ly.ffn_value, ws.scal, ws.xa, D);

@@ -379,6 +379,14 @@ struct RowsPrepParams {
   float* shift_out;           // [R/T][K]: LN of every stream's last row = its next carry (or null)
   signed char* digits;        // [nseg][3][Rpad][K]
   SegScalars* scal;           // [nseg][R]
+  // Deferred commit of a token-shift carry that an EARLIER preparation launch parked (it could not
+  // write the state row its sibling CTAs were reading): stream b's commit_n floats go from
+  // commit_src + b*commit_n to commit_dst + b*commit_stride.  Done by the CTA of matrix 0 and the
+  // stream's last row.
+  const float* commit_src;
+  float* commit_dst;
+  long long commit_stride;
+  int commit_n;
 };
 
 // Sums of two per-thread values over the CTA; every thread gets both totals.
@@ -436,6 +444,11 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
     else if (P.shift) carry = reinterpret_cast<const float4*>(P.shift + size_t(b) * P.shift_stride);
   }
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (P.commit_n > 0 && sidx == 0 && t == P.T - 1) {
+    const float4* src = reinterpret_cast<const float4*>(P.commit_src + size_t(b) * P.commit_n);
+    float4* dst = reinterpret_cast<float4*>(P.commit_dst + size_t(b) * P.commit_stride);
+    for (int g = tid; g < P.commit_n / 4; g += kPrepThreads) dst[g] = __ldcg(src + g);
+  }
 
   float4 xv[REG ? G : 1], pv[REG ? G : 1];
   if (REG) {

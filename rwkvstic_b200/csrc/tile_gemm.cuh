@@ -146,7 +146,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 8);
-  const uint32_t acc_full = smem_u32(bars + 16), acc_empty = smem_u32(bars + 17);
+  const uint32_t acc_full0 = smem_u32(bars + 16), acc_empty0 = smem_u32(bars + 18);   // two of each (8 bytes apart)
+  // With 128-row tiles one accumulator needs 3*Rt <= 240 columns, so two fit in TMEM: tile i+1 is
+  // accumulated at column 256 while the epilogue still reads tile i at column 0.  With 256-row tiles
+  // the second accumulator of the SAME tile lives at column 256 and tiles alternate on one buffer.
+  const bool dbuf = P.mt != kGemmM;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 256);
   volatile int* issued_ptr = reinterpret_cast<volatile int*>(smem + 260);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + 264);
@@ -155,8 +159,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
 
   if (tid == 0) {
     for (int i = 0; i < kGemmStages; ++i) { mbar_init(full0 + 8 * i, 1); mbar_init(empty0 + 8 * i, 1); }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, kGemmEpiWarps);
+    for (int i = 0; i < 2; ++i) { mbar_init(acc_full0 + 8 * i, 1); mbar_init(acc_empty0 + 8 * i, kGemmEpiWarps); }
     *abort_flag = 0;
     *issued_ptr = 0;
     fence_mbar_init();
@@ -210,8 +213,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
       for (int tile = blockIdx.x; tile < P.ntiles && ok; tile += gridDim.x, ++iter) {
         const GemmTile T = gemm_tile(P, tile);
         const bool two = P.mt == kGemmM && T.n0 + 128 < P.seg[T.seg].N;   // second 128-row sub-tile holds real rows
-        // the epilogue must have read the previous tile's accumulators out of TMEM
-        if (!mbar_wait_bounded(acc_empty, uint32_t(iter & 1) ^ 1u, abort_flag)) {
+        // the epilogue must have read this buffer's previous tile out of TMEM
+        const int buf = dbuf ? (iter & 1) : 0, use = dbuf ? (iter >> 1) : iter;
+        const uint32_t tacc = tmem + uint32_t(buf * kGemmAcc1Col);
+        if (!mbar_wait_bounded(acc_empty0 + 8 * buf, uint32_t(use & 1) ^ 1u, abort_flag)) {
           if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_EMPTY);
           ok = false;
           break;
@@ -232,12 +237,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
 #pragma unroll
           for (int k = 0; k < 4; ++k) {   // 32 bytes of K per instruction: +2 in the descriptors' 16-byte address units
             const uint32_t acc = (kc | k) != 0 ? 1u : 0u;
-            umma_i8(tmem, ad0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
+            umma_i8(tacc, ad0 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
             if (two) umma_i8(tmem + kGemmAcc1Col, ad1 + uint64_t(2 * k), bd + uint64_t(2 * k), idesc, acc);
           }
           umma_commit(empty0 + 8 * slot);   // frees the stage once these MMAs have read it
         }
-        if (ok) umma_commit(acc_full);      // accumulators of this tile complete
+        if (ok) umma_commit(acc_full0 + 8 * buf);   // accumulators of this tile complete
       }
     }
   } else if (warp >= 4) {
@@ -260,7 +265,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         reinterpret_cast<float*>(scal)[i] = r < P.R ? __ldcg(reinterpret_cast<const float*>(S.scal + r) + (i & 7)) : 0.f;
       }
       named_bar_sync(1, kGemmEpiWarps * 32);
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_full, uint32_t(iter & 1), abort_flag));
+      const int buf = dbuf ? (iter & 1) : 0, use = dbuf ? (iter >> 1) : iter;
+      const uint32_t acc_empty = acc_empty0 + 8 * buf;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(acc_full0 + 8 * buf, uint32_t(use & 1), abort_flag));
       if (!ok) {
         if (lane == 0 && P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
         break;
@@ -283,7 +290,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         const bool nvalid = n < S.N;
         const int nc = nvalid ? n : S.N - 1;   // clamped: loads stay in bounds, the store is predicated
         const float rx = S.rx ? S.rx[nc] : 1.f, mx = S.mx ? S.mx[nc] : 0.f;
-        const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t(h * kGemmAcc1Col + j0);
+        const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t((h + buf) * kGemmAcc1Col + j0);
         int da[16], db[16], dc[16];
         tmem_ld16(tbase, da);
         tmem_ld16(tbase + uint32_t(Rt), db);

@@ -63,13 +63,17 @@ def decode_bytes_per_token(L, D, V=VOCAB, F=None):
 
 # ----------------------------------------------------------------------------------- clocks
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self):
         self.path = tempfile.mktemp(prefix="clocks_", suffix=".csv")
         self.proc = None
+        self.windows = []   # (start, end) wall-clock seconds of the timed regions
+
+    def window(self, start, end):
+        self.windows.append((start, end))
 
     def start(self):
         try:
@@ -86,23 +90,31 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        import datetime
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        rows = []
         with open(self.path) as f:
             for line in f:
                 p = [c.strip() for c in line.split(",")]
-                if len(p) < 9 or not p[0].isdigit() or int(p[0]) not in gpu_indices:
+                if len(p) < 10 or not p[1].isdigit() or int(p[1]) not in gpu_indices:
                     continue
                 try:
-                    sm.append(float(p[1])); mx.append(float(p[2]))
+                    ts = datetime.datetime.strptime(p[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    rows.append((ts, float(p[2]), float(p[3]), [n for n, v in zip(names, p[6:10]) if v.lower().startswith("active")]))
                 except ValueError:
                     continue
-                for name, val in zip(names, p[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
         os.unlink(self.path)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        inside = [r for r in rows if any(a <= r[0] <= b for a, b in self.windows)]
+        scope = "inside the timed regions"
+        if not inside and self.windows:   # regions shorter than the sampling period: take the span around them
+            lo, hi = min(a for a, _ in self.windows) - 0.3, max(b for _, b in self.windows) + 0.3
+            inside = [r for r in rows if lo <= r[0] <= hi]
+            scope = "within 0.3 s of the timed regions (regions shorter than the sampling period)"
+        if not inside:
+            inside, scope = rows, "whole run"
+        sm = [r[1] for r in inside]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max((r[2] for r in inside), default=None),
+                "samples": len(sm), "scope": scope, "reasons": sorted({n for r in inside for n in r[3]})}
 
 
 # ----------------------------------------------------------------------------------- CPU reference arm
@@ -309,14 +321,15 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize(dev)
 
     # ---- device-resident loop: tokens already in HBM, logits stay in HBM
+    sampler = ClockSampler()
+    if rank == 0:
+        sampler.start()
     state = model.emptyState.clone()
     for i in range(W):
         model.forward(dev_tokens[i:i + 1], state)
     barrier()
-    sampler = ClockSampler()
-    if rank == 0:
-        sampler.start()
     launches0 = model.launch_count
+    w0 = time.time()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(W, W + K):
@@ -324,8 +337,8 @@ def run_ours(args, rank, world, local_rank):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
+    sampler.window(w0, time.time())
     launches = model.launch_count - launches0
-    clocks = sampler.stop(set(range(world))) if rank == 0 else None
     model.check_status()
 
     # ---- end to end through the public API with host buffers: every step copies its input token
@@ -344,11 +357,13 @@ def run_ours(args, rank, world, local_rank):
     for i in range(W):
         e2e_step()
     barrier()
+    w0 = time.time()
     t0 = time.perf_counter()
     for i in range(K):
         e2e_step()
     torch.cuda.synchronize(dev)
     e2e_ms = (time.perf_counter() - t0) * 1e3
+    sampler.window(w0, time.time())
     model.check_status()
 
     # ---- batched decode: B independent streams per GPU through the tensor-core rows path, greedy
@@ -361,12 +376,15 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_b0 = model.launch_count
+    w0 = time.time()
     b0.record()
     for i in range(Kb):
         btok = model.forward_rows(btok, bstate).argmax(dim=1, keepdim=True)
     b1.record()
     barrier()
     batched_ms = b0.elapsed_time(b1)
+    sampler.window(w0, time.time())
+    clocks = sampler.stop(set(range(world))) if rank == 0 else None
     launches_b = model.launch_count - launches_b0
     del bstate
 

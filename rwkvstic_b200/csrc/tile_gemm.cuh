@@ -16,7 +16,7 @@
 // One tile = (256 weight rows) x (Rt activation rows) of output; a CTA walks K in 128-byte
 // steps through a ring of shared-memory stages: warp 0 issues the TMA copies, warp 1 issues the
 // MMAs (one elected thread; completion is signalled to the ring by tcgen05.commit on the stage's
-// mbarrier), warps 4-11 read the accumulators with tcgen05.ld and apply the affine terms and the
+// mbarrier), warps 4-19 read the accumulators with tcgen05.ld and apply the affine terms and the
 // fused element-wise op.  The kernel is bound by operand traffic from L2 to shared memory (int8
 // MMAs need ~250 MACs per byte to saturate, a tile gives M*N/(M+N) = 124), which is why the tile
 // pairs two weight sub-tiles with one digit tile.  CTAs that share a weight tile are adjacent in
@@ -38,8 +38,9 @@ constexpr int kGemmABytes = kGemmM * 128;                // 32 KB
 constexpr int kGemmStageBytes = kGemmABytes + kDigits * kGemmRowsMax * 128;   // 62 KB
 constexpr int kGemmTmemCols = 512;                       // both accumulators; one CTA per SM (shared memory)
 constexpr int kGemmAcc1Col = 256;                        // first column of the second accumulator
-constexpr int kGemmThreads = 384;                        // warp 0 TMA, 1 MMA, 2 TMEM allocation, 4-11 epilogue
-constexpr int kGemmEpiWarps = 8;
+constexpr int kGemmEpiWarps = 16;                        // four per TMEM lane quadrant
+constexpr int kGemmThreads = 128 + kGemmEpiWarps * 32;   // warp 0 TMA, 1 MMA, 2 TMEM allocation, 4.. epilogue
+constexpr int kGemmChunk = 8;                            // activation rows an epilogue warp handles per TMEM read
 constexpr int kGemmOffScal = 1024;                       // SegScalars[80]
 constexpr int kGemmOffRing = 4096;
 constexpr int kGemmSmem = kGemmOffRing + kGemmStages * kGemmStageBytes;
@@ -123,6 +124,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int (&v)[16]) {
         "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr)
       : "memory");
+}
+// 8 consecutive int32 columns of this warp's 32 lanes.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -246,10 +254,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
       }
     }
   } else if (warp >= 4) {
-    // ---------------------------------------------------------------- epilogue: 8 warps.  A warp can
-    // read TMEM lanes 32*(warp%4)..+31 only, so two warps share each lane quadrant and take
-    // alternate 16-row chunks of the accumulators.
+    // ---------------------------------------------------------------- epilogue: 16 warps.  A warp can
+    // read TMEM lanes 32*(warp%4)..+31 only, so four warps share each lane quadrant and take every
+    // fourth 8-row chunk of the accumulators (many warps with short chains: the epilogue is bound by
+    // instruction latency, not by issue slots).
     const int q = warp & 3, eg = (warp - 4) >> 2;
+    constexpr int EG = kGemmEpiWarps / 4, CH = kGemmChunk;
     const int et = tid - 128;
     griddep_wait();
     bool ok = true;
@@ -273,38 +283,37 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         break;
       }
       tc_fence_after();
-      const int nchunks = Rt / 16, nitems = P.dbg == 4 ? 0 : (two ? 2 : 1) * nchunks;
+      const int nchunks = Rt / CH, nitems = P.dbg == 4 ? 0 : (two ? 2 : 1) * nchunks;
       // this warp's last item that really reads TMEM: after it the accumulators may be overwritten
       int last_item = -1;
-      for (int item = eg; item < nitems; item += 2)
-        if (row0 + (item % nchunks) * 16 < P.R) last_item = item;
+      for (int item = eg; item < nitems; item += EG)
+        if (row0 + (item % nchunks) * CH < P.R) last_item = item;
       if (last_item < 0) {
         tc_fence_before();
         if (lane == 0) mbar_arrive(acc_empty);
       }
 #pragma unroll 1
-      for (int item = eg; item < nitems; item += 2) {
-        const int h = item / nchunks, j0 = (item - h * nchunks) * 16;
+      for (int item = eg; item < nitems; item += EG) {
+        const int h = item / nchunks, j0 = (item - h * nchunks) * CH;
         if (row0 + j0 >= P.R) continue;   // warp-uniform
         const int n = n0 + h * 128 + q * 32 + lane;
         const bool nvalid = n < S.N;
         const int nc = nvalid ? n : S.N - 1;   // clamped: loads stay in bounds, the store is predicated
         const float rx = S.rx ? S.rx[nc] : 1.f, mx = S.mx ? S.mx[nc] : 0.f;
         const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t((h + buf) * kGemmAcc1Col + j0);
-        int da[16], db[16], dc[16];
-        tmem_ld16(tbase, da);
-        tmem_ld16(tbase + uint32_t(Rt), db);
-        tmem_ld16(tbase + uint32_t(2 * Rt), dc);
+        int da[CH], db[CH], dc[CH];
+        tmem_ld8(tbase, da);
+        tmem_ld8(tbase + uint32_t(Rt), db);
+        tmem_ld8(tbase + uint32_t(2 * Rt), dc);
         tmem_ld_wait();
         if (item == last_item) {   // the rest of this item works from registers: let the next tile's MMAs start
           tc_fence_before();
           if (lane == 0) mbar_arrive(acc_empty);
         }
-        // branch-free over the 16 rows so that their dependency chains interleave (one warp per
-        // scheduler: a row at a time would run at the latency of every instruction)
-        float yv[16];
+        // branch-free over the rows so that their dependency chains interleave
+        float yv[CH];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < CH; ++j) {
           const float4 sc = *reinterpret_cast<const float4*>(&scal[j0 + j]);   // sd, zp, sumxs, sumx
           const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
           float y = __fmul_rn(__ll2float_rn(I), sc.x) + S.half * sc.z;
@@ -315,28 +324,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         }
         if (S.act == ACT_RELUSQ) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { const float t = fmaxf(yv[j], 0.f); yv[j] = t * t; }
+          for (int j = 0; j < CH; ++j) { const float t = fmaxf(yv[j], 0.f); yv[j] = t * t; }
         } else if (S.act == ACT_SIGMOID) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) yv[j] = sigmoidf_(yv[j]);
+          for (int j = 0; j < CH; ++j) yv[j] = sigmoidf_(yv[j]);
         }
         const int rlast = P.R - 1;
         if (S.gate) {
-          float gv[16];
+          float gv[CH];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { const int r = min(row0 + j0 + j, rlast); gv[j] = __ldcg(S.gate + size_t(r) * S.ldgate + nc); }
+          for (int j = 0; j < CH; ++j) { const int r = min(row0 + j0 + j, rlast); gv[j] = __ldcg(S.gate + size_t(r) * S.ldgate + nc); }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) yv[j] *= gv[j];
+          for (int j = 0; j < CH; ++j) yv[j] *= gv[j];
         }
         if (S.res) {
-          float rv[16];
+          float rv[CH];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) { const int r = min(row0 + j0 + j, rlast); rv[j] = __ldcg(S.res + size_t(r) * S.ldres + nc); }
+          for (int j = 0; j < CH; ++j) { const int r = min(row0 + j0 + j, rlast); rv[j] = __ldcg(S.res + size_t(r) * S.ldres + nc); }
 #pragma unroll
-          for (int j = 0; j < 16; ++j) yv[j] += rv[j];
+          for (int j = 0; j < CH; ++j) yv[j] += rv[j];
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
+        for (int j = 0; j < CH; ++j) {
           const int r = row0 + j0 + j;
           if (r <= rlast && nvalid) S.out[size_t(r) * S.ldo + n] = yv[j];
         }

@@ -436,7 +436,8 @@ static cudaError_t launch_rows_prep(const RowsPrepParams& P, cudaStream_t stream
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(rows_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    e = cudaFuncSetAttribute(rows_prep_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
@@ -445,7 +446,9 @@ static cudaError_t launch_rows_prep(const RowsPrepParams& P, cudaStream_t stream
     *why = "unsupported shape: k_in too large for the row preparation kernel, or more than 65535 rows";
     return cudaErrorInvalidValue;
   }
-  return launch_chained(rows_prep_kernel, dim3(P.nseg, P.R), dim3(kPrepThreads), smem, stream, P);
+  if (rows_prep_threads(P.K, P.mode) == 256)
+    return launch_chained(rows_prep_kernel<256>, dim3(P.nseg, P.R), dim3(256), smem, stream, P);
+  return launch_chained(rows_prep_kernel<512>, dim3(P.nseg, P.R), dim3(512), smem, stream, P);
 }
 
 // Fills the tensor maps of P (weights and digit rows) and launches the tile GEMM.  digits: [nseg][3][Rpad][K].

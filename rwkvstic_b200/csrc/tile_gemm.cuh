@@ -405,16 +405,38 @@ struct RowsPrepParams {
   int commit_n;
 };
 
-// Sums of two per-thread values over the CTA; every thread gets both totals.
-__device__ __forceinline__ void block_sum2(float& a, float& b, float* red) {
+// Sums of four per-thread values over a CTA of NT threads; every thread gets the totals.
+template <int NT>
+__device__ __forceinline__ void block_sum4(float (&v)[4], float* red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  a = warp_sum(a); b = warp_sum(b);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = warp_sum(v[i]);
   __syncthreads();   // red may still be read from an earlier use
-  if (lane == 0) { red[warp * 2] = a; red[warp * 2 + 1] = b; }
+  if (lane == 0) reinterpret_cast<float4*>(red)[warp] = make_float4(v[0], v[1], v[2], v[3]);
   __syncthreads();
-  float sa = 0.f, sb = 0.f;
-  for (int w = 0; w < kPrepWarps; ++w) { sa += red[w * 2]; sb += red[w * 2 + 1]; }
-  a = sa; b = sb;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int w = 0; w < NT / 32; ++w) {
+    const float4 t = reinterpret_cast<const float4*>(red)[w];
+    s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+  }
+  v[0] = s.x; v[1] = s.y; v[2] = s.z; v[3] = s.w;
+}
+
+// max of v[0] and sums of v[1..3] over a CTA of NT threads (statistics of one row: max|xs|, sum v*my,
+// sum xs, sum v); every thread gets the totals.
+template <int NT>
+__device__ __forceinline__ void block_stats(float (&v)[4], float* red) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  v[0] = warp_max(v[0]); v[1] = warp_sum(v[1]); v[2] = warp_sum(v[2]); v[3] = warp_sum(v[3]);
+  __syncthreads();
+  if (lane == 0) reinterpret_cast<float4*>(red)[warp] = make_float4(v[0], v[1], v[2], v[3]);
+  __syncthreads();
+  float4 s = reinterpret_cast<const float4*>(red)[0];
+  for (int w = 1; w < NT / 32; ++w) {
+    const float4 t = reinterpret_cast<const float4*>(red)[w];
+    s.x = fmaxf(s.x, t.x); s.y += t.y; s.z += t.z; s.w += t.w;
+  }
+  v[0] = s.x; v[1] = s.y; v[2] = s.z; v[3] = s.w;
 }
 
 // Digit words of four inputs (same digit arithmetic as store_digits in vector_prep.cuh).
@@ -443,7 +465,7 @@ __device__ __forceinline__ float4 ln_apply(float4 x, float mean, float rstd, flo
 // One activation row per CTA.  REG = true keeps the row in registers (up to G groups of four inputs
 // per thread: one round trip to memory, then the reductions, then the digit stores); REG = false
 // is the any-length variant that re-reads the row and parks xs in shared memory.
-template <int G, bool REG>
+template <int NT, int G, bool REG>
 __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* red, float4* park) {
   const int tid = threadIdx.x;
   const int K = P.K, NG = K / 4;
@@ -463,14 +485,14 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
   if (P.commit_n > 0 && sidx == 0 && t == P.T - 1) {
     const float4* src = reinterpret_cast<const float4*>(P.commit_src + size_t(b) * P.commit_n);
     float4* dst = reinterpret_cast<float4*>(P.commit_dst + size_t(b) * P.commit_stride);
-    for (int g = tid; g < P.commit_n / 4; g += kPrepThreads) dst[g] = __ldcg(src + g);
+    for (int g = tid; g < P.commit_n / 4; g += NT) dst[g] = __ldcg(src + g);
   }
 
   float4 xv[REG ? G : 1], pv[REG ? G : 1];
   if (REG) {
 #pragma unroll
     for (int i = 0; i < G; ++i) {
-      const int g = tid + i * kPrepThreads;
+      const int g = tid + i * NT;
       xv[i] = g < NG ? __ldcg(xr + g) : zero4;
       pv[i] = (g < NG && xp) ? __ldcg(xp + g) : ((g < NG && carry) ? __ldcg(carry + g) : zero4);
     }
@@ -480,32 +502,26 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
 
   float mean = 0.f, rstd = 1.f, meanp = 0.f, rstdp = 1.f;
   if (ln) {
-    float s0 = 0.f, s1 = 0.f;
+    // sum and sum of squares of this row and of the previous one in a single pass and a single
+    // block reduction; variance = E[x^2] - mean^2 (the residual stream's mean is small against its spread)
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < (REG ? G : 1); ++i)
-      for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads) {
+      for (int g = tid + i * NT; g < NG; g += REG ? NG : NT) {
         const float4 x = x_at(i, g);
-        s0 += (x.x + x.y) + (x.z + x.w);
-        if (xp) { const float4 y = p_at(i, g); s1 += (y.x + y.y) + (y.z + y.w); }
-      }
-    block_sum2(s0, s1, red);
-    mean = s0 / float(K); meanp = s1 / float(K);
-    s0 = 0.f; s1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < (REG ? G : 1); ++i)
-      for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads) {
-        const float4 x = x_at(i, g);
-        const float a0 = x.x - mean, a1 = x.y - mean, a2 = x.z - mean, a3 = x.w - mean;
-        s0 += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+        s[0] += (x.x + x.y) + (x.z + x.w);
+        s[1] += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
         if (xp) {
           const float4 y = p_at(i, g);
-          const float c0 = y.x - meanp, c1 = y.y - meanp, c2 = y.z - meanp, c3 = y.w - meanp;
-          s1 += (c0 * c0 + c1 * c1) + (c2 * c2 + c3 * c3);
+          s[2] += (y.x + y.y) + (y.z + y.w);
+          s[3] += (y.x * y.x + y.y * y.y) + (y.z * y.z + y.w * y.w);
         }
       }
-    block_sum2(s0, s1, red);
-    rstd = 1.0f / sqrtf(s0 / float(K) + 1e-5f);
-    rstdp = 1.0f / sqrtf(s1 / float(K) + 1e-5f);
+    block_sum4<NT>(s, red);
+    const float invk = 1.0f / float(K);
+    mean = s[0] * invk; meanp = s[2] * invk;
+    rstd = 1.0f / sqrtf(fmaxf(s[1] * invk - mean * mean, 0.f) + 1e-5f);
+    rstdp = 1.0f / sqrtf(fmaxf(s[3] * invk - meanp * meanp, 0.f) + 1e-5f);
     __syncthreads();   // red is reused by the statistics reduction below
   }
 
@@ -513,7 +529,7 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
   const bool last_of_stream = ln && sidx == 0 && P.shift_out && t == P.T - 1;
 #pragma unroll
   for (int i = 0; i < (REG ? G : 1); ++i)
-    for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads) {
+    for (int g = tid + i * NT; g < NG; g += REG ? NG : NT) {
       float4 v = x_at(i, g);
       if (ln) {
         const float4 w = __ldg(reinterpret_cast<const float4*>(P.ln_w) + g), bb = __ldg(reinterpret_cast<const float4*>(P.ln_b) + g);
@@ -540,7 +556,11 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
       }
       if (REG) xv[i] = xs; else park[g] = xs;
     }
-  prep_reduce_stats(amax, szp, sxs, sx, red);
+  {
+    float st[4] = {amax, szp, sxs, sx};
+    block_stats<NT>(st, red);
+    amax = st[0]; szp = st[1]; sxs = st[2]; sx = st[3];
+  }
 
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
   if (tid == 0) {
@@ -556,11 +576,14 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
   uint32_t* dc = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 2) * P.Rpad + r) * K);
 #pragma unroll
   for (int i = 0; i < (REG ? G : 1); ++i)
-    for (int g = tid + i * kPrepThreads; g < NG; g += REG ? NG : kPrepThreads)
+    for (int g = tid + i * NT; g < NG; g += REG ? NG : NT)
       rows_store_digits(da, db, dc, g, REG ? xv[i] : park[g], inv);
 }
 
-__global__ void __launch_bounds__(kPrepThreads, 2) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
+// 256 threads per row while the row fits their registers (more rows in flight per SM: the kernel is
+// a chain of load -> reduce -> reduce -> store per row), 512 threads for longer rows.
+template <int NT>
+__global__ void __launch_bounds__(NT, NT == 256 ? 4 : 2) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
   extern __shared__ __align__(128) unsigned char prep_smem[];
   float* red = reinterpret_cast<float*>(prep_smem);
   float4* park = reinterpret_cast<float4*>(prep_smem + kPrepRedBytes);
@@ -568,17 +591,19 @@ __global__ void __launch_bounds__(kPrepThreads, 2) rows_prep_kernel(const __grid
   griddep_wait();
   const int NG = P.K / 4;
   if (P.mode == ROWS_LN) {
-    if (NG <= 4 * kPrepThreads) rows_prep_body<4, true>(P, red, park);
-    else rows_prep_body<1, false>(P, red, park);
+    if (NG <= 4 * NT) rows_prep_body<NT, 4, true>(P, red, park);
+    else rows_prep_body<NT, 1, false>(P, red, park);
   } else {
-    if (NG <= 8 * kPrepThreads) rows_prep_body<8, true>(P, red, park);
-    else rows_prep_body<1, false>(P, red, park);
+    if (NG <= 8 * NT) rows_prep_body<NT, 8, true>(P, red, park);
+    else rows_prep_body<NT, 1, false>(P, red, park);
   }
 }
 
+inline int rows_prep_threads(int K, int mode) { return K / 4 <= (mode == ROWS_LN ? 4 : 8) * 256 ? 256 : 512; }
+
 // Shared memory: the reduction scratch, plus 4*K bytes of parked xs when the row does not fit the registers.
 inline size_t rows_prep_smem(int K, int mode) {
-  const bool in_regs = K / 4 <= (mode == ROWS_LN ? 4 : 8) * kPrepThreads;
+  const bool in_regs = K / 4 <= (mode == ROWS_LN ? 4 : 8) * rows_prep_threads(K, mode);
   return size_t(kPrepRedBytes) + (in_regs ? 0 : size_t(4) * K);
 }
 }  // namespace b200

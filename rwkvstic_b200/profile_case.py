@@ -39,7 +39,26 @@ def main():
     ap.add_argument("--copies", type=int, default=4, help="distinct matrix sets (4 x 84 MB > the 126 MB L2)")
     ap.add_argument("--launches", type=int, default=8)
     ap.add_argument("--rows", type=int, default=1, help="activation rows; > 1 selects the tile GEMM")
+    ap.add_argument("--network", type=int, default=0, metavar="LAYERS",
+                    help="instead of single matrices: a LAYERS-block model of --shape, one forward_rows call of "
+                         "--streams x --tokens rows (every kernel of the rows path, for a launch list)")
+    ap.add_argument("--streams", type=int, default=8)
+    ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
+    if args.network > 0:
+        from .model import B200RWKV
+        _, D = SHAPES[args.shape]
+        model = B200RWKV.synthetic(args.network, D, seed=1234, device="cuda:0")
+        toks = torch.randint(0, VOCAB, (args.streams, args.tokens), generator=torch.Generator().manual_seed(3))
+        for i in range(2):
+            state = model.empty_batch_state(args.streams)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            model.forward_rows(toks, state)
+            e1.record()
+            e1.synchronize()
+            print(f"{args.network} blocks of {args.shape}, {args.streams} x {args.tokens} rows: {e0.elapsed_time(e1):.2f} ms")
+        return
     dev = torch.device("cuda", 0)
     _, D = SHAPES[args.shape]
     sets = matrices(args.matrix, D, dev, args.copies)

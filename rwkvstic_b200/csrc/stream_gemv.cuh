@@ -38,7 +38,7 @@ constexpr int kGemvThreads = kConsumers + 32;   // + one producer warp
 constexpr int kMaxStages = 16;
 constexpr int kTileRows = 16;                   // rows per stage = MMA M
 constexpr int kChunkMax = 2048;                 // bytes of one row per stage
-constexpr int kInFlight = 2;                    // stages in flight while the ring is first filled (pacing)
+constexpr int kInFlight = 1;                    // stages in flight while the ring is first filled (pacing; 2: -2 %, 3+: -4 %)
 constexpr int kSmemLimit = 227 * 1024;          // dynamic shared memory per CTA on sm_100
 
 enum Act : int { ACT_NONE = 0, ACT_RELUSQ = 1, ACT_SIGMOID = 2 };
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
               ok = false;
               break;
             }
-            // Pacing of the first ring fill: at most kInFlight stages requested but not yet landed.
+            // Pacing of the first ring fill: at most kInFlight stage requested but not yet landed.
             // All CTAs start their stream at the moment the preparation kernel of this very launch
             // does its one latency-critical round trip; without pacing that load would sit behind
             // ~24 MB of queued weight requests (3+ us).  Once the ring has been filled, requests

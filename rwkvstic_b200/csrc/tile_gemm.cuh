@@ -565,7 +565,7 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
   if (tid == 0) {
     SegScalars sc;
-    sc.sd = amax > 0.f ? float(1.0 / double(inv)) : 0.f;
+    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;   // IEEE fp32 division, no fp64 on this path
     sc.zp = szp; sc.sumxs = sxs; sc.sumx = sx;
     sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
     P.scal[size_t(sidx) * P.R + r] = sc;

@@ -9,7 +9,7 @@
 //             previous-token vector (modules/block.py:58-67, :82-91; layernorm.py:11-20)
 //   xs_s[k] = v_s[k] * ry_s[k];   inv_s = QMAX / max_k |xs_s[k]|;   X_s[k] = rint(xs_s[k] * inv_s)
 //   planes  : signed base-256 digits of X_s, 128 bytes per 32 inputs: [a:32][b:32][c:32][0:32]
-//   scalars : 1/inv_s (fp64), zp_s = sum_k v_s[k]*my_s[k], sum_k xs_s[k], sum_k v_s[k]
+//   scalars : 1/inv_s (fp32), zp_s = sum_k v_s[k]*my_s[k], sum_k xs_s[k], sum_k v_s[k]
 //
 // To keep the chain between two GEMV launches short, whatever needs a reduction over ALL outputs of
 // the previous launch is published by that launch's epilogue with order-independent integer
@@ -107,19 +107,22 @@ __device__ __forceinline__ void store_digits(unsigned char* planes, int g, float
 }
 
 // Block reduction of one segment's statistics (max|xs|, sum v*my, sum xs, sum v): warp partials ->
-// shared memory -> warp 0 folds the rows (one lane per statistic) -> everyone reads the totals.
+// shared memory -> every warp folds the 16 partials itself with shuffles (one barrier, no serial loop).
 __device__ __forceinline__ void prep_reduce_stats(float& amax, float& szp, float& sxs, float& sx, float* red) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   amax = warp_max(amax); szp = warp_sum(szp); sxs = warp_sum(sxs); sx = warp_sum(sx);
-  if (lane == 0) { red[warp * 4 + 0] = amax; red[warp * 4 + 1] = szp; red[warp * 4 + 2] = sxs; red[warp * 4 + 3] = sx; }
+  if (lane == 0) reinterpret_cast<float4*>(red)[warp] = make_float4(amax, szp, sxs, sx);
   __syncthreads();
-  if (warp == 0 && lane < 4) {
-    float a = red[lane];
-    for (int w = 1; w < kPrepWarps; ++w) a = lane == 0 ? fmaxf(a, red[w * 4 + lane]) : a + red[w * 4 + lane];
-    red[kPrepWarps * 4 + lane] = a;
+  static_assert(kPrepWarps == 16, "the fold below covers 16 warp partials");
+  float4 t = reinterpret_cast<const float4*>(red)[lane & 15];
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {
+    t.x = fmaxf(t.x, __shfl_xor_sync(0xffffffffu, t.x, o));
+    t.y += __shfl_xor_sync(0xffffffffu, t.y, o);
+    t.z += __shfl_xor_sync(0xffffffffu, t.z, o);
+    t.w += __shfl_xor_sync(0xffffffffu, t.w, o);
   }
-  __syncthreads();
-  amax = red[kPrepWarps * 4 + 0]; szp = red[kPrepWarps * 4 + 1]; sxs = red[kPrepWarps * 4 + 2]; sx = red[kPrepWarps * 4 + 3];
+  amax = t.x; szp = t.y; sxs = t.z; sx = t.w;
 }
 
 // PREP_PLAIN and PREP_LN: CTA s prepares segment s (the segments share nothing but the layer norm,
@@ -225,7 +228,7 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
   if (tid == 0) {
     SegScalars sc;
-    sc.sd = amax > 0.f ? float(1.0 / double(inv)) : 0.f;
+    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;   // IEEE fp32 division, no fp64 on this path
     sc.zp = szp; sc.sumxs = sxs; sc.sumx = sx;
     sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
     P.scal[sidx] = sc;
@@ -253,7 +256,7 @@ __device__ __forceinline__ void prep_xs(const PrepParams& P) {
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
   if (tid == 0) {
     SegScalars sc;
-    sc.sd = amax > 0.f ? float(1.0 / double(inv)) : 0.f;
+    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;   // IEEE fp32 division, no fp64 on this path
     sc.zp = __ll2float_rn(__ldcg(&P.pub->zp)) * (1.0f / kPubSumScale);
     sc.sumxs = __ll2float_rn(__ldcg(&P.pub->sumxs)) * (1.0f / kPubXsScale);
     sc.sumx = __ll2float_rn(__ldcg(&P.pub->sumx)) * (1.0f / kPubSumScale);

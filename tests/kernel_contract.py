@@ -29,7 +29,7 @@ def fixed_point_gemv(x: torch.Tensor, m: QuantMatrix, with_affine: bool = True) 
         inv = (torch.tensor(QMAX) / amax).to(torch.float32)  # fp32 division
         X = torch.round(xs * inv).to(torch.float64)          # cvt.rni of the fp32 product (half to even)
         I = (m.qt.to(torch.float64) @ X).to(torch.int64)     # exact: |I| < 2^46
-        sd = (1.0 / inv.double()).to(torch.float32)          # value of one fixed-point unit, fp32
+        sd = torch.tensor(1.0, dtype=torch.float32) / inv    # value of one fixed-point unit: IEEE fp32 division
         main = I.to(torch.float32) * sd                      # int64 -> fp32 (nearest even), fp32 product
     if not with_affine:
         return main

@@ -252,17 +252,30 @@ class B200RWKV:
             self._graphs[key] = g
         g.replay()
 
-    def trace_step(self, token: int, state: torch.Tensor) -> torch.Tensor:
-        """Profiling: run one eager decode step and return the phase timeline, an int64 CPU tensor
+    def trace_step(self, token: int, state: torch.Tensor, graph: bool = False) -> torch.Tensor:
+        """Profiling: run one decode step and return the phase timeline, an int64 CPU tensor
         ``[4L+1 launches, 1024, 8]`` of %globaltimer nanoseconds: rows < grid are the GEMV CTAs, row 1023
-        the preparation kernel (see b200rwkv_gemv_u8_traced)."""
+        the preparation kernel (see b200rwkv_gemv_u8_traced).  ``graph=True`` captures the traced step
+        in a CUDA graph and returns the timeline of its second replay (launch latencies as in production)."""
         n = 4 * self.n_layer + 1
         trace = torch.zeros(n, 1024, 8, dtype=torch.int64, device=self.device)
         self._tok.fill_(int(token))
-        stream = torch.cuda.current_stream(self.device).cuda_stream
-        _lib.check(self._L.b200rwkv_decode_step_traced(C.byref(self._cmodel), self._tok.data_ptr(), state.data_ptr(),
-                                                       self._logits.data_ptr(), self._ws.data_ptr(), self._ws.numel(),
-                                                       trace.data_ptr(), stream))
+
+        def step():
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            _lib.check(self._L.b200rwkv_decode_step_traced(C.byref(self._cmodel), self._tok.data_ptr(), state.data_ptr(),
+                                                           self._logits.data_ptr(), self._ws.data_ptr(), self._ws.numel(),
+                                                           trace.data_ptr(), stream))
+        if not graph:
+            step()
+        else:
+            step()
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(g):
+                step()
+            g.replay()
+            g.replay()
         torch.cuda.synchronize(self.device)
         return trace.cpu()
 

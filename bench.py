@@ -459,7 +459,8 @@ def main():
     ap.add_argument("--no-prefill", action="store_true", help="skip the 3B-shape prompt-ingestion measurement (N=1 only)")
     ap.add_argument("--mode", default="replicas", choices=["replicas", "layer-split"],
                     help="replicas: the headline data-parallel decode; layer-split: 14B blocks partitioned over the ranks")
-    ap.add_argument("--microbatches", type=int, default=4, help="stream groups in flight through the layer-split pipeline")
+    ap.add_argument("--microbatches", type=int, default=1,
+                    help="stream groups of the layer-split pipeline (decode re-streams the stage weights per group: 1 is fastest)")
     ap.add_argument("--streams", type=int, default=256, help="streams per GPU of the batched-decode measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -464,17 +464,25 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  // Tiles of 256 weight rows move the fewest operand bytes per MAC (two sub-tiles share one digit
-  // tile); tiles of 128 rows spread more evenly over the CTAs when there are few of them.  Pick
-  // the smaller estimated makespan: rounds of tiles per CTA x relative cost of a tile.
-  long long tiles256 = 0, tiles128 = 0;
-  for (int s = 0; s < P.nseg; ++s) {
-    tiles256 += (long long)(P.Rpad / P.Rt) * ((P.seg[s].N + kGemmM - 1) / kGemmM);
-    tiles128 += (long long)(P.Rpad / P.Rt) * ((P.seg[s].N + 127) / 128);
+  // Tile shape.  The kernel is bound by operand bytes entering each SM (128 bytes of K per step for
+  // mt weight rows and 3*Rt digit rows) plus a fixed cost per tile; the launch takes as many rounds
+  // as the busiest CTA has tiles.  Few rows want small tiles (many CTAs, every weight byte still
+  // read once per row tile from L2); many rows want the 256 x 80 tile (most MACs per byte).
+  {
+    const long long sms = device_sms() > 0 ? device_sms() : 1;
+    const double fixed = 225.0 * 1024;   // ~3 us of a tile (start, accumulator hand-off, epilogue tail) in ingest bytes
+    double best = 0.0;
+    P.mt = 128; P.Rt = 16;
+    for (int mt = 128; mt <= kGemmM; mt += 128) {
+      for (int rt = 16; rt <= kGemmRowsMax; rt += 16) {
+        long long tiles = 0;
+        for (int s = 0; s < P.nseg; ++s) tiles += (long long)((P.R + rt - 1) / rt) * ((P.seg[s].N + mt - 1) / mt);
+        const double rounds = double((tiles + sms - 1) / sms);
+        const double cost = rounds * (double(P.K / 128) * 128.0 * (mt + kDigits * rt) + fixed);
+        if (best == 0.0 || cost < best) { best = cost; P.mt = mt; P.Rt = rt; }
+      }
+    }
   }
-  const long long sms = device_sms() > 0 ? device_sms() : 1;
-  const double cost256 = double((tiles256 + sms - 1) / sms) * 2.0, cost128 = double((tiles128 + sms - 1) / sms) * 1.15;
-  P.mt = cost256 <= cost128 ? kGemmM : 128;
   for (int s = 0; s < P.nseg; ++s) {
     GemmSeg& S = P.seg[s];
     if (!encode_byte_map(&S.wmap, mats[s]->qt, (unsigned long long)S.N, P.K, P.mt, 1) ||
@@ -486,7 +494,7 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
   }
   { const char* d = getenv("B200RWKV_GEMM_DEBUG"); P.dbg = d ? atoi(d) : 0; }
   if (P.dbg == 3) return cudaSuccess;   // measurement only: preparation kernel alone
-  P.row_tiles = P.Rpad / P.Rt;
+  P.row_tiles = (P.R + P.Rt - 1) / P.Rt;
   P.ntiles = 0;
   for (int s = 0; s < P.nseg; ++s) {
     P.tiles_seg[s] = P.row_tiles * ((P.seg[s].N + P.mt - 1) / P.mt);
@@ -884,7 +892,7 @@ int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* 
   }
   Q.nseg = nmat; Q.K = K; Q.R = rows; Q.T = 1; Q.Rpad = Rpad; Q.mode = ROWS_PLAIN; Q.need_sums = 1; Q.ldx = K;
   Q.digits = digits; Q.scal = scal;
-  P.nseg = nmat; P.K = K; P.R = rows; P.Rpad = Rpad; P.Rt = gemm_tile_rows(rows); P.status = reinterpret_cast<int*>(wsb);
+  P.nseg = nmat; P.K = K; P.R = rows; P.Rpad = Rpad; P.status = reinterpret_cast<int*>(wsb);
   const char* why = "";
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   g_chain_rows = rows <= 1024;
@@ -941,7 +949,7 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     Q.ln_x = ln_x; Q.ln_w = ln_w; Q.ln_b = ln_b; Q.shift = shift; Q.shift_stride = state_stride;
     Q.shift_out = mode == ROWS_LN ? ws.shift_new : nullptr; Q.digits = ws.digits; Q.scal = ws.scal;
   };
-  auto gemm_common = [&](int nseg, int K) { P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.Rt = gemm_tile_rows(R); P.status = ws.status; };
+  auto gemm_common = [&](int nseg, int K) { P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.status = ws.status; };
   // new token-shift carry of every stream -> its state row, done by the NEXT preparation launch
   // (the launch that parked it had sibling CTAs still reading the old row)
   auto commit_carry = [&](float* dst_row) {
@@ -1034,7 +1042,7 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_gemm_seg(P.seg[0], m->head, ws.scal, logits, V);
-    P.nseg = 1; P.K = D; P.R = B; P.Rpad = Bpad; P.Rt = gemm_tile_rows(B); P.status = ws.status;
+    P.nseg = 1; P.K = D; P.R = B; P.Rpad = Bpad; P.status = ws.status;
     { const b200rwkv_matrix* mp[1] = {&m->head};
       if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
   }

@@ -45,15 +45,10 @@ constexpr int kGemmOffScal = 1024;                       // SegScalars[80]
 constexpr int kGemmOffRing = 4096;
 constexpr int kGemmSmem = kGemmOffRing + kGemmStages * kGemmStageBytes;
 
-// Rows per tile for R activation rows: as few tiles as possible, then as small as possible.
-inline int gemm_tile_rows(int R) {
-  const int tiles = (R + kGemmRowsMax - 1) / kGemmRowsMax;
-  return ((R + tiles - 1) / tiles + 15) / 16 * 16;
-}
-inline int gemm_padded_rows(int R) {
-  const int rt = gemm_tile_rows(R);
-  return (R + rt - 1) / rt * rt;
-}
+// The digit rows of a launch are laid out [matrix][digit][Rpad][K] with Rpad = R rounded up to 16,
+// whatever tile height the GEMM then picks: a tile that reaches past row R reads the next digit
+// plane (or TMA's zero fill past the end) into accumulator columns that are never stored.
+inline int gemm_padded_rows(int R) { return (R + 15) / 16 * 16; }
 
 struct GemmSeg {
   CUtensorMap wmap;    // u8 qt as [K/128][N][128 B], box [1][mt][128], 128-byte swizzle
@@ -73,9 +68,9 @@ struct GemmSeg {
 struct GemmParams {
   GemmSeg seg[kMaxSeg];
   int nseg, K, R, Rpad;
-  int Rt;              // activation rows per tile (multiple of 16, <= 80); Rpad is a multiple of it
+  int Rt;              // activation rows per tile (multiple of 16, <= 80)
   int mt;              // weight rows per tile: 256 (two accumulators) or 128 (small grids: more CTAs)
-  int row_tiles;       // Rpad / Rt
+  int row_tiles;       // ceil(R / Rt)
   int tiles_seg[kMaxSeg];  // tiles per matrix = row_tiles * ceil(N / mt)
   int ntiles;          // all tiles of the launch; the grid is min(ntiles, SMs), CTAs loop over tiles
   int* status;

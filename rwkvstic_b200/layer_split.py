@@ -14,6 +14,11 @@ long prompts into token pieces.  Every stage handles the items in the same order
 (receive -> compute -> send); the sends and receives are asynchronous on the CUDA stream, so stage
 r works on item i+1 while stage r+1 works on item i.  Items of one stream group are dependent
 through the state and stay in order on every stage.
+
+Decode steps are bound by streaming the stage's weights, and every stream group streams them
+again, so ``microbatches=1`` is the fastest setting for decode (measured at the 14B shape, 64
+streams, 2 GPUs: 8.8 / 11.7 / 19.0 ms per step with 1 / 2 / 4 groups); prompts are compute-bound
+and their token pieces do overlap across the stages.
 """
 from __future__ import annotations
 

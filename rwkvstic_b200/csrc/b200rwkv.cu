@@ -373,9 +373,91 @@ wkv_rows_kernel(int B, int T, int C, const float* __restrict__ w, const float* _
   aa[so] = a; bb[so] = q; pp[so] = p;
 }
 
+
+// ---- WKV over long rows: T cut into chunks that run in parallel (the recurrence is a scan whose
+// state composes: after n steps without input the max-trick state (aa, bb, pp) is (aa, bb, pp + n*w),
+// and two states add after bringing them to a common exponent).
+constexpr int kWkvChunk = 64;
+
+// Pass 1: thread (stream, chunk j, channel) runs chunk j from the EMPTY state and stores the
+// resulting local state (no outputs); the last chunk is not needed.
+__global__ void __launch_bounds__(128)
+wkv_chunk_state_kernel(int B, int T, int C, int NC, const float* __restrict__ w, const float* __restrict__ k,
+                       const float* __restrict__ v, float* __restrict__ loc) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)B * (NC - 1) * C) return;
+  const int c = int(idx % C);
+  const int j = int((idx / C) % (NC - 1)), s = int(idx / ((long long)C * (NC - 1)));
+  const float wv = w[c];
+  float a = 0.f, q = 0.f, p = -1e30f;
+  const size_t base = (size_t(s) * T + size_t(j) * kWkvChunk) * C + c;
+  constexpr int U = 8;
+  for (int t = 0; t < kWkvChunk; t += U) {   // chunks before the last are full
+    float kv[U], vv[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) { kv[i] = __ldcg(k + base + size_t(t + i) * C); vv[i] = __ldcg(v + base + size_t(t + i) * C); }
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const float ww2 = p + wv, p2 = fmaxf(ww2, kv[i]);
+      const float f1 = expf(ww2 - p2), f2 = expf(kv[i] - p2);
+      a = f1 * a + f2 * vv[i]; q = f1 * q + f2; p = p2;
+    }
+  }
+  float* o = loc + (size_t(s) * (NC - 1) + j) * 3 * C + c;
+  o[0] = a; o[size_t(C)] = q; o[2 * size_t(C)] = p;
+}
+
+// Pass 2: thread (stream, chunk j, channel) rebuilds the state at the start of chunk j from the
+// stream's state and the local states of chunks 0..j-1, then runs chunk j with outputs
+// (y = gate * wkv written over k).  The thread of the last chunk stores the stream's new state.
+__global__ void __launch_bounds__(128)
+wkv_chunk_output_kernel(int B, int T, int C, int NC, const float* __restrict__ w, const float* __restrict__ u,
+                        float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ gate,
+                        const float* __restrict__ loc, float* __restrict__ aa, float* __restrict__ bb,
+                        float* __restrict__ pp, long long state_stride) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)B * NC * C) return;
+  const int c = int(idx % C);
+  const int j = int((idx / C) % NC), s = int(idx / ((long long)C * NC));
+  const float wv = w[c], uv = u[c];
+  const size_t so = size_t(s) * state_stride + c;
+  float a = aa[so], q = bb[so], p = pp[so];
+  const float wn = wv * float(kWkvChunk);
+  for (int i = 0; i < j; ++i) {
+    const float* l = loc + (size_t(s) * (NC - 1) + i) * 3 * C + c;
+    const float la = __ldcg(l), lq = __ldcg(l + size_t(C)), lp = __ldcg(l + 2 * size_t(C));
+    const float pd = p + wn, pm = fmaxf(pd, lp);
+    const float e1 = expf(pd - pm), e2 = expf(lp - pm);
+    a = e1 * a + e2 * la; q = e1 * q + e2 * lq; p = pm;
+  }
+  const int t0 = j * kWkvChunk, t1 = t0 + kWkvChunk < T ? t0 + kWkvChunk : T;
+  const size_t base = size_t(s) * T * C + c;
+  constexpr int U = 8;
+  int t = t0;
+  for (; t + U <= t1; t += U) {
+    float kv[U], vv[U], gv[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) {
+      const size_t o = base + size_t(t + i) * C;
+      kv[i] = __ldcg(k + o); vv[i] = __ldcg(v + o); gv[i] = __ldcg(gate + o);
+    }
+#pragma unroll
+    for (int i = 0; i < U; ++i) k[base + size_t(t + i) * C] = gv[i] * wkv_step(kv[i], vv[i], wv, uv, a, q, p);
+  }
+  for (; t < t1; ++t) {
+    const size_t o = base + size_t(t) * C;
+    k[o] = gate[o] * wkv_step(k[o], v[o], wv, uv, a, q, p);
+  }
+  if (j == NC - 1) { aa[so] = a; bb[so] = q; pp[so] = p; }
+}
+
 struct RowsWorkspace {
   int* status;
-  float *xa, *xb, *kb, *vb, *rb, *kk, *shift_new;
+  float *xa, *xb, *kb, *vb, *rb, *kk, *shift_new, *wkv_loc;
   signed char* digits;
   SegScalars* scal;
   size_t bytes;
@@ -397,6 +479,7 @@ static RowsWorkspace carve_rows(const b200rwkv_model* m, int B, int T, void* bas
   w.rb = reinterpret_cast<float*>(take(R * D * 4));
   w.kk = reinterpret_cast<float*>(take(R * F * 4));
   w.shift_new = reinterpret_cast<float*>(take(size_t(B) * D * 4));
+  w.wkv_loc = reinterpret_cast<float*>(take(size_t(B) * size_t((T + kWkvChunk - 1) / kWkvChunk) * 3 * D * 4));   // local chunk states
   w.digits = reinterpret_cast<signed char*>(take(kDigits * Rpad * (3 * D > F ? 3 * D : F)));
   w.scal = reinterpret_cast<SegScalars*>(take(sizeof(SegScalars) * kMaxSeg * R));
   w.bytes = off;
@@ -986,9 +1069,20 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
       if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
     // 2. WKV recurrence over each stream's rows; kb <- sigmoid(r) * wkv
     why = "wkv_rows launch failed";
-    e = launch_chained(wkv_rows_kernel, dim3((B * D + 127) / 128), dim3(128), 0, s, B, T, D, ly.time_decay, ly.time_first, ws.kb,
-                       (const float*)ws.vb, (const float*)ws.rb, st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D),
-                       (long long)state_stride);
+    if (T <= 2 * kWkvChunk) {
+      e = launch_chained(wkv_rows_kernel, dim3((B * D + 127) / 128), dim3(128), 0, s, B, T, D, ly.time_decay, ly.time_first, ws.kb,
+                         (const float*)ws.vb, (const float*)ws.rb, st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D),
+                         (long long)state_stride);
+    } else {   // long rows: chunks of 64 steps in parallel, two passes
+      const int NC = (T + kWkvChunk - 1) / kWkvChunk;
+      const long long n1 = (long long)B * (NC - 1) * D, n2 = (long long)B * NC * D;
+      e = launch_chained(wkv_chunk_state_kernel, dim3((unsigned)((n1 + 127) / 128)), dim3(128), 0, s, B, T, D, NC, ly.time_decay,
+                         (const float*)ws.kb, (const float*)ws.vb, ws.wkv_loc);
+      if (e == cudaSuccess)
+        e = launch_chained(wkv_chunk_output_kernel, dim3((unsigned)((n2 + 127) / 128)), dim3(128), 0, s, B, T, D, NC, ly.time_decay,
+                           ly.time_first, ws.kb, (const float*)ws.vb, (const float*)ws.rb, (const float*)ws.wkv_loc,
+                           st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D), (long long)state_stride);
+    }
     if (e != cudaSuccess) goto launch_failed;
     // 3. attention output projection + residual -> xb
     memset(&Q, 0, sizeof(Q));

@@ -150,6 +150,17 @@ def test_rows_path_agrees_with_one_row_path(tiny):
     assert torch.equal(lg_one[0], lg_all[3]) and torch.equal(st_one[0], st_all[3])
 
 
+def test_rows_long_rows_use_the_chunked_scan_and_agree_with_the_one_row_path(tiny):
+    B, T = 2, 200                                  # > 128 tokens per stream: WKV runs as parallel 64-step chunks
+    toks = synth_tokens(B * T, seed=13, vocab=257).reshape(B, T)
+    st_rows, st_seq = tiny.empty_batch_state(B), tiny.empty_batch_state(B)
+    lg_rows, _ = tiny.forward_batch(toks, st_rows, rows=True)
+    lg_seq, _ = tiny.forward_batch(toks, st_seq, rows=False)
+    assert float((lg_rows - lg_seq).abs().max()) < 5e-4
+    assert torch.allclose(st_rows[:, :, :4], st_seq[:, :, :4], rtol=1e-3, atol=1e-4)
+    assert torch.allclose(st_rows[:, :, 4], st_seq[:, :, 4], rtol=1e-5, atol=1e-4)
+
+
 def test_rows_long_prompt_in_pieces_and_via_forward(tiny):
     toks = synth_tokens(300, seed=11, vocab=257)
     keep = tiny.rows_per_call
@@ -190,3 +201,18 @@ def test_169m_prompt_rows_path_vs_reference_and_one_row_path(m169, golden):
     lg1, _ = m169.forward(torch.tensor([tok]), st_one)
     assert float((lg64[0] - lg1).abs().max()) < 5e-4
     assert int(torch.argmax(lg64[0])) == int(g["tokens"][1])
+
+
+def test_rows_entry_points_reject_bad_shapes(tiny):
+    st = tiny.empty_batch_state(2)
+    with pytest.raises(ValueError):
+        tiny.forward_rows(torch.zeros(3, 4, dtype=torch.int64), st)            # 3 streams, state for 2
+    with pytest.raises(ValueError):
+        tiny.forward_rows(torch.zeros(2, 0, dtype=torch.int64), st)
+    with pytest.raises(ValueError):
+        tiny.forward_rows(torch.zeros(2, 4, dtype=torch.int64), st.double())
+    with pytest.raises(ValueError):
+        tiny.forward_rows_stage(None, torch.zeros(7, 128, device=DEV), st, False)   # 7 rows do not split over 2 streams
+    # out-of-range token ids are clamped like the one-row path (never an out-of-bounds gather)
+    lg = tiny.forward_rows(torch.tensor([[5, 100000], [-3, 7]]), st)
+    assert torch.isfinite(lg).all()

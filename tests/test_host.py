@@ -35,6 +35,15 @@ def test_bad_arguments_return_codes_not_aborts():
     assert b"gemv_u8" in L.b200rwkv_last_error()
     assert L.b200rwkv_wkv_scan(1, 1, 0, *([None] * 8), 0, None) == _lib.EINVAL
     assert L.b200rwkv_decode_step(None, None, None, None, None, 0, None) == _lib.EINVAL
+    # the many-rows entry points validate before any CUDA call as well
+    assert L.b200rwkv_gemm_u8(1, None, None, None, 4, None, 0, None) == _lib.EINVAL
+    assert L.b200rwkv_gemm_u8(4, None, None, None, 4, None, 0, None) == _lib.EINVAL
+    assert b"gemm_u8" in L.b200rwkv_last_error()
+    assert L.b200rwkv_forward_rows(None, None, 1, 1, None, 0, None, None, 0, None) == _lib.EINVAL
+    assert L.b200rwkv_forward_rows_stage(None, None, None, 1, 1, None, 0, None, None, 0, None) == _lib.EINVAL
+    assert L.b200rwkv_argmax(None, 1, 8, 8, None, None, None, 0, None) == _lib.EINVAL
+    assert L.b200rwkv_gemm_workspace_bytes(4096, 3, 100) > 3 * 3 * 112 * 4096   # digit rows padded to 16
+    assert L.b200rwkv_gemm_workspace_bytes(4096, 4, 100) == 0 and L.b200rwkv_rows_workspace_bytes(None, 1, 1) == 0
     with pytest.raises(_lib.B200RWKVError):
         _lib.gemv_plan(96, 1, 8)            # k_in not a multiple of 128
     with pytest.raises(_lib.B200RWKVError):

@@ -12,7 +12,9 @@ import tempfile
 import pytest
 import torch
 
-REF = os.environ.get("RWKVSTIC_REFERENCE", "/root/reference")
+# the reference checkout: $RWKVSTIC_REFERENCE, else a folder named "reference" beside this repository
+REF = os.environ.get("RWKVSTIC_REFERENCE",
+                     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference"))
 pytestmark = pytest.mark.skipif(not os.path.isdir(os.path.join(REF, "src", "rwkvstic")),
                                 reason="reference checkout not available")
 

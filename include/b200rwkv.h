@@ -186,7 +186,7 @@ int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, f
                                 void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream);
 
 /* Bytes of device scratch b200rwkv_gemm_u8 needs (digit rows: 3 bytes per input per row, rows
- * rounded up to 64; plus 32 bytes per row and matrix). */
+ * rounded up to 16; plus 32 bytes per row and matrix). */
 size_t b200rwkv_gemm_workspace_bytes(int k_in, int nmat, int rows);
 
 /*
@@ -198,7 +198,8 @@ size_t b200rwkv_gemm_workspace_bytes(int k_in, int nmat, int rows);
  * exact integer dot products, the same affine terms), so a row's result does not depend on
  * which of the two entry points computed it beyond the fp32 summation order of sum_k x*my.
  * Two launches: a row-wise preparation kernel, then a tcgen05 (kind::i8) tensor-core kernel with
- * TMA-fed operands and TMEM accumulators, one CTA per 128 outputs x 64 rows.  rows <= 65535.
+ * TMA-fed operands and TMEM accumulators: persistent CTAs over tiles of 128 or 256 outputs x
+ * 16..80 rows, the shape picked per launch.  rows <= 65535.
  * `workspace`: b200rwkv_gemm_workspace_bytes(k_in, nmat, rows), 256-byte aligned, first int = status.
  */
 int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y, int rows,

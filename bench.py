@@ -349,8 +349,7 @@ def run_ours(args, rank, world, local_rank):
     nxt = torch.zeros(1, dtype=torch.int64).pin_memory()
 
     def e2e_step():
-        model.forward(tok, state)                        # H2D of the token inside
-        nxt.copy_(model.argmax_token(), non_blocking=True)   # D2H of the step's result
+        model.step_greedy(tok, state, nxt)               # H2D of the token, step + arg-max, D2H of the sampled id
         torch.cuda.synchronize(dev)
         tok[0] = int(nxt[0])                             # greedy feedback through the host
 
@@ -411,7 +410,7 @@ def run_ours(args, rank, world, local_rank):
                        "l2": f"no flush needed: every step streams {w8 / 1e9:.2f} GB of weights, far larger than the 126 MB L2",
                        "timing": "CUDA events on the launching stream, max over ranks"},
             "e2e": {"value": world * K / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": 8,
-                    "d2h_bytes_per_step": 8, "api": "B200RWKV.forward + argmax_token (greedy id read back per step)"},
+                    "d2h_bytes_per_step": 8, "api": "B200RWKV.step_greedy (token in from pinned host memory, greedy id read back per step)"},
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -394,6 +394,47 @@ class B200RWKV:
         self.launch_count += 1
         return out
 
+    def step_greedy(self, token: torch.Tensor, state: torch.Tensor, out: torch.Tensor) -> None:
+        """One decode step with the arg-max taken on the device, for a host-driven loop: copies
+        ``token`` (int64[1], ideally pinned host memory) to the device, runs the step and the
+        arg-max kernel (one CUDA-graph replay from the second call with the same ``state`` buffer
+        on), and copies the sampled id into ``out`` (int64[1], ideally pinned).  Asynchronous:
+        synchronise before reading ``out``.  ``state`` is updated in place."""
+        state = self._own_state(state)
+        with torch.cuda.device(self.device):
+            self._tok.copy_(token.reshape(1), non_blocking=True)
+            if not hasattr(self, "_next"):
+                self._next = torch.zeros(1, dtype=torch.int64, device=self.device)
+                self._greedy_graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+                self._greedy_seen: Dict[int, int] = {}
+
+            def one():
+                self._step_raw(self._tok.data_ptr(), state.data_ptr(), self._logits.data_ptr())
+                _lib.check(self._L.b200rwkv_argmax(self._logits.data_ptr(), 1, self.n_vocab, self.n_vocab,
+                                                   self._next.data_ptr(), None, None, 0,
+                                                   torch.cuda.current_stream(self.device).cuda_stream))
+            key = state.data_ptr()
+            g = self._greedy_graphs.get(key) if self.use_graph else None
+            if g is not None:
+                g.replay()
+            else:
+                n = self._greedy_seen.get(key, 0) + 1
+                self._greedy_seen[key] = n
+                if self.use_graph and n >= 2:
+                    if len(self._greedy_graphs) >= 16:
+                        self._greedy_graphs.clear()
+                        self._greedy_seen.clear()
+                    g = torch.cuda.CUDAGraph()
+                    torch.cuda.synchronize(self.device)
+                    with torch.cuda.graph(g):
+                        one()
+                    self._greedy_graphs[key] = g
+                    g.replay()
+                else:
+                    one()
+            out.copy_(self._next, non_blocking=True)
+        self.launch_count += self.launches_per_step + 1
+
     def generate_greedy(self, token, state: torch.Tensor, n: int) -> torch.Tensor:
         """``n`` greedy decode steps that never leave the device: feed ``token``, take the arg-max
         of the logits, feed it back, ...  Each step is one CUDA-graph replay (the decode step

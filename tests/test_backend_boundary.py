@@ -56,3 +56,23 @@ def test_load_through_reference_loader_and_master(reference):
     assert torch.allclose(state_to_reference(so, decay)[:, :4], sr[:, :4].double(), rtol=1e-3, atol=1e-4)
     out = ours.forward(number=2)                    # the reference's sampling loop runs on our logits
     assert out["logits"].shape[0] == 50277 and len(ours.getState()) == 2
+
+
+def test_exported_archive_opens_in_the_reference(reference, tmp_path):
+    """An archive written by rwkvstic_b200.rwkv_archive.export goes through the reference's own
+    OptRWKV(path) branch for ``.rwkv`` files and RWKVMaster, and gives the logits of the
+    reference's FASTQUANT CPU model built from the same checkpoint."""
+    from rwkvstic.agnostic.backends.opt import OptRWKV
+    from rwkvstic_b200 import rwkv_archive
+    from rwkvstic_b200.model import quantize_tensors
+    from rwkvstic_b200.synth import synth_checkpoint, synth_tokens
+    import make_golden
+    ck = synth_checkpoint(2, 128, vocab=257, seed=31)
+    path = rwkv_archive.export(quantize_tensors(ck.items(), "cpu"), str(tmp_path / "exported"))
+    theirs = OptRWKV(path, device="cpu", config=make_golden.CPU_CFG)       # torch.jit.load inside
+    ref = make_golden.load_reference_model(ck)
+    toks = synth_tokens(7, seed=2, vocab=257)
+    a, sa = theirs.forward(toks, theirs.emptyState.clone())
+    b, sb = ref.forward(toks, ref.emptyState.clone())
+    assert float((a - b).abs().max()) < 1e-5
+    assert torch.allclose(sa[:, :4], sb[:, :4], rtol=1e-3, atol=1e-5) and torch.equal(sa[:, 4], sb[:, 4])

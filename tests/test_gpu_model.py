@@ -126,6 +126,16 @@ def test_greedy_on_device_equals_host_argmax_loop(m169, golden):
     eager = B200RWKV(m169.w, use_graph=False)
     ids2 = eager.generate_greedy(int(first), st_eager, 63)
     assert torch.equal(ids, ids2) and torch.equal(st_graph, st_eager)
+    # host-driven loop with the arg-max on the device: same ids
+    st_host = state.clone()
+    tok, nxt = torch.tensor([int(first)]).pin_memory(), torch.zeros(1, dtype=torch.int64).pin_memory()
+    host_ids = []
+    for _ in range(6):
+        m169.step_greedy(tok, st_host, nxt)
+        torch.cuda.synchronize()
+        host_ids.append(int(nxt[0]))
+        tok[0] = int(nxt[0])
+    assert host_ids == ids[:6].cpu().tolist()
     ties = torch.tensor([1.0, 5.0, 5.0, -2.0, 5.0], device=DEV)
     assert int(m169.argmax_token(ties)) == 1
     m169.check_status()

@@ -67,3 +67,32 @@ def test_archive_on_the_gpu_matches_reference_goldens(golden):
         lg, st = model.forward(tok.reshape(1), st)
         assert float((lg.cpu().double() - torch.from_numpy(np.asarray(g["logits_tok"][i]))).abs().max()) < 2e-3
     model.check_status()
+
+
+def test_export_round_trip_and_scripted_forward(tmp_path, golden):
+    g = golden("model_tiny.npz")
+    w = quantize_tensors(synth_checkpoint(2, 128, vocab=257, seed=31).items(), "cpu")
+    path = rwkv_archive.export(w, str(tmp_path / "tiny"))
+    assert path.endswith(".rwkv")
+    m = torch.jit.load(path, map_location="cpu")
+    # the archive runs by itself (what stock rwkvstic does with it) and reproduces the reference's numbers
+    toks = torch.from_numpy(g["tokens"])
+    lg, st = m.forward(toks, m.emptyState.clone())
+    assert float((lg - torch.from_numpy(g["logits_seq"])).abs().max()) < 1e-5
+    assert torch.allclose(st[:, :4], torch.from_numpy(g["state_seq"])[:, :4], rtol=1e-4, atol=1e-6)
+    st = m.emptyState.clone()
+    for i, tok in enumerate(toks):
+        lg, st = m.forward(tok.reshape(1), st)
+        assert float((lg - torch.from_numpy(np.asarray(g["logits_tok"][i]))).abs().max()) < 1e-5
+    # and the harvester reads it back bit-identically
+    back = rwkv_archive.harvest(path, "cpu")
+    assert torch.equal(back.emb, w.emb) and torch.equal(back.head.qt, w.head.qt) and torch.equal(back.head.my64, w.head.my64)
+    for a, b in zip(back.layers, w.layers):
+        for k in b.mat:
+            assert torch.equal(a.mat[k].qt, b.mat[k].qt) and torch.equal(a.mat[k].ry, b.mat[k].ry), k
+        for k in b.vec:
+            assert torch.equal(a.vec[k], b.vec[k]), k
+    with pytest.raises(ValueError):
+        from rwkvstic_b200.quant import quantize_two_axis
+        w.layers[0].mat["att.key"] = quantize_two_axis(torch.randn(128, 128))
+        rwkv_archive.export(w, str(tmp_path / "bad"))

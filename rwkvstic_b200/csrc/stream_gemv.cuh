@@ -173,6 +173,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffAbort);
   volatile int* issued_ptr = reinterpret_cast<volatile int*>(smem + kOffAbort + 4);  // stages the producer issued
+  volatile int* go_flag = reinterpret_cast<volatile int*>(smem + kOffAbort + 16);    // digit planes have landed: stop pacing
   SegScalars* scal = reinterpret_cast<SegScalars*>(smem + kOffScale);
   int* rowsum = reinterpret_cast<int*>(smem + kOffRows);  // [segment][row][4]: sums of the digit columns
   const size_t rows_bytes = (size_t(P.nseg) * P.rpc16 * 16 + 127) / 128 * 128;
@@ -202,6 +203,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
     mbar_init(plane_bar, 1);
     *abort_flag = 0;
     *issued_ptr = 0;
+    *go_flag = 0;
     fence_mbar_init();
     B200_TRACE(0);
   }
@@ -229,8 +231,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
             // All CTAs start their stream at the moment the preparation kernel of this very launch
             // does its one latency-critical round trip; without pacing that load would sit behind
             // ~24 MB of queued weight requests (3+ us).  Once the ring has been filled, requests
-            // follow consumption and the full ring depth may be in flight.
-            if (issued >= kInFlight && issued < P.stages) {
+            // follow consumption and the full ring depth may be in flight; likewise as soon as the
+            // digit planes have landed (go_flag), whatever is left of the first fill goes out at once.
+            if (issued >= kInFlight && issued < P.stages && !*go_flag) {
               const int j = issued - kInFlight;
               if (!mbar_wait_bounded(full0 + 8 * (j % P.stages), uint32_t(j / P.stages) & 1u, abort_flag)) {
                 if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
@@ -280,7 +283,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
     }
     bool dead = !__all_sync(0xffffffffu, mbar_wait_bounded(plane_bar, 0, abort_flag));
     named_bar_sync(1, kConsumers);  // scalars and zeroed row sums visible to every consumer warp
-    if (tid == 0) B200_TRACE(4);
+    if (tid == 0) { *go_flag = 1; B200_TRACE(4); }   // the chain's critical loads are over: the producer may run ahead
 
     // ---- operands of the epilogue for this thread's first row of every segment: requested now,
     // used after the main loop, so their latency hides behind the weight stream

@@ -200,12 +200,15 @@ size_t b200rwkv_gemm_workspace_bytes(int k_in, int nmat, int rows);
  * Two launches: a row-wise preparation kernel, then a tcgen05 (kind::i8) tensor-core kernel with
  * TMA-fed operands and TMEM accumulators: persistent CTAs over tiles of 128 or 256 outputs x
  * 16..80 rows, the shape picked per launch.  rows <= 65535.
- * `workspace`: b200rwkv_gemm_workspace_bytes(k_in, nmat, rows), 256-byte aligned, first int = status.
+ * `workspace`: b200rwkv_gemm_workspace_bytes(k_in, nmat, rows), 256-byte aligned, ZERO-FILLED once
+ * before its first use (first int = status word; it also holds the integer scratch in which launches
+ * with few rows combine their K slices, which every launch leaves zero again).
  */
 int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* x, float* const* y, int rows,
                      void* workspace, size_t workspace_bytes, void* stream);
 
-/* Bytes of device scratch b200rwkv_forward_rows needs (0 if streams * tokens_per_stream > 65535). */
+/* Bytes of device scratch b200rwkv_forward_rows needs (0 if streams * tokens_per_stream > 65535);
+ * zero-fill it once before its first use (status word and K-slice scratch, see b200rwkv_gemm_u8). */
 size_t b200rwkv_rows_workspace_bytes(const b200rwkv_model* m, int streams, int tokens_per_stream);
 
 /*

@@ -458,6 +458,8 @@ wkv_chunk_output_kernel(int B, int T, int C, int NC, const float* __restrict__ w
 struct RowsWorkspace {
   int* status;
   float *xa, *xb, *kb, *vb, *rb, *kk, *shift_new, *wkv_loc;
+  int* sk_acc;
+  unsigned* sk_count;
   signed char* digits;
   SegScalars* scal;
   size_t bytes;
@@ -480,6 +482,8 @@ static RowsWorkspace carve_rows(const b200rwkv_model* m, int B, int T, void* bas
   w.kk = reinterpret_cast<float*>(take(R * F * 4));
   w.shift_new = reinterpret_cast<float*>(take(size_t(B) * D * 4));
   w.wkv_loc = reinterpret_cast<float*>(take(size_t(B) * size_t((T + kWkvChunk - 1) / kWkvChunk) * 3 * D * 4));   // local chunk states
+  w.sk_acc = reinterpret_cast<int*>(take(kSplitAccBytes));        // split-K scratch, zero between launches
+  w.sk_count = reinterpret_cast<unsigned*>(take(size_t(kSplitMaxTiles) * 4));
   w.digits = reinterpret_cast<signed char*>(take(kDigits * Rpad * (3 * D > F ? 3 * D : F)));
   w.scal = reinterpret_cast<SegScalars*>(take(sizeof(SegScalars) * kMaxSeg * R));
   w.bytes = off;
@@ -488,7 +492,8 @@ static RowsWorkspace carve_rows(const b200rwkv_model* m, int B, int T, void* bas
 
 static size_t gemm_workspace_bytes(int k_in, int nmat, int rows) {
   const size_t Rpad = size_t(gemm_padded_rows(rows));
-  return 256 + align256(size_t(nmat) * kDigits * Rpad * k_in) + align256(sizeof(SegScalars) * size_t(nmat) * rows);
+  return 256 + align256(kSplitAccBytes) + align256(size_t(kSplitMaxTiles) * 4) + align256(size_t(nmat) * kDigits * Rpad * k_in) +
+         align256(sizeof(SegScalars) * size_t(nmat) * rows);
 }
 
 // Launch with programmatic stream serialisation: the kernel may start while its predecessor on the
@@ -554,15 +559,23 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
   {
     const long long sms = device_sms() > 0 ? device_sms() : 1;
     const double fixed = 225.0 * 1024;   // ~3 us of a tile (start, accumulator hand-off, epilogue tail) in ingest bytes
+    const int nk = P.K / 128;
     double best = 0.0;
-    P.mt = 128; P.Rt = 16;
+    P.mt = 128; P.Rt = 16; P.ksplit = 1;
     for (int mt = 128; mt <= kGemmM; mt += 128) {
       for (int rt = 16; rt <= kGemmRowsMax; rt += 16) {
         long long tiles = 0;
         for (int s = 0; s < P.nseg; ++s) tiles += (long long)((P.R + rt - 1) / rt) * ((P.seg[s].N + mt - 1) / mt);
-        const double rounds = double((tiles + sms - 1) / sms);
-        const double cost = rounds * (double(P.K / 128) * 128.0 * (mt + kDigits * rt) + fixed);
-        if (best == 0.0 || cost < best) { best = cost; P.mt = mt; P.Rt = rt; }
+        for (int ks = 1; ks <= 8; ks *= 2) {
+          // K slices: only where the scratch exists and fits, and where they create CTAs the launch lacks
+          if (ks > 1 && (!P.sk_acc || mt != 128 || rt > kSplitMaxRt || tiles > kSplitMaxTiles || nk % ks != 0 ||
+                         nk / ks < 4 || tiles * (ks / 2) >= sms))
+            continue;
+          const double rounds = double((tiles * ks + sms - 1) / sms);
+          const double reduce = ks > 1 ? 2.0 * mt * kDigits * rt * 4 + 100.0 * 1024 : 0.0;   // atomics out, totals back, ticket
+          const double cost = rounds * (double(nk / ks) * 128.0 * (mt + kDigits * rt) + fixed + reduce);
+          if (best == 0.0 || cost < best) { best = cost; P.mt = mt; P.Rt = rt; P.ksplit = ks; }
+        }
       }
     }
   }
@@ -583,7 +596,8 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
     P.tiles_seg[s] = P.row_tiles * ((P.seg[s].N + P.mt - 1) / P.mt);
     P.ntiles += P.tiles_seg[s];
   }
-  const dim3 grid(P.ntiles < device_sms() ? P.ntiles : device_sms());
+  const int items = P.ntiles * P.ksplit;
+  const dim3 grid(items < device_sms() ? items : device_sms());
   return launch_chained(tile_gemm_kernel, grid, dim3(kGemmThreads), size_t(kGemmSmem), stream, P);
 }
 
@@ -961,8 +975,11 @@ int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* 
     return fail(B200RWKV_EINVAL, "gemm_u8: workspace %zu < %zu bytes", workspace_bytes, gemm_workspace_bytes(K, nmat, rows));
   const int Rpad = gemm_padded_rows(rows);
   char* wsb = static_cast<char*>(workspace);
-  signed char* digits = reinterpret_cast<signed char*>(wsb + 256);
-  SegScalars* scal = reinterpret_cast<SegScalars*>(wsb + 256 + align256(size_t(nmat) * kDigits * Rpad * K));
+  int* sk_acc = reinterpret_cast<int*>(wsb + 256);
+  unsigned* sk_count = reinterpret_cast<unsigned*>(wsb + 256 + align256(kSplitAccBytes));
+  char* after = wsb + 256 + align256(kSplitAccBytes) + align256(size_t(kSplitMaxTiles) * 4);
+  signed char* digits = reinterpret_cast<signed char*>(after);
+  SegScalars* scal = reinterpret_cast<SegScalars*>(after + align256(size_t(nmat) * kDigits * Rpad * K));
   RowsPrepParams Q;
   GemmParams P;
   memset(&Q, 0, sizeof(Q));
@@ -975,7 +992,7 @@ int b200rwkv_gemm_u8(int nmat, const b200rwkv_matrix* mats, const float* const* 
   }
   Q.nseg = nmat; Q.K = K; Q.R = rows; Q.T = 1; Q.Rpad = Rpad; Q.mode = ROWS_PLAIN; Q.need_sums = 1; Q.ldx = K;
   Q.digits = digits; Q.scal = scal;
-  P.nseg = nmat; P.K = K; P.R = rows; P.Rpad = Rpad; P.status = reinterpret_cast<int*>(wsb);
+  P.nseg = nmat; P.K = K; P.R = rows; P.Rpad = Rpad; P.status = reinterpret_cast<int*>(wsb); P.sk_acc = sk_acc; P.sk_count = sk_count;
   const char* why = "";
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   g_chain_rows = rows <= 1024;
@@ -1032,7 +1049,9 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     Q.ln_x = ln_x; Q.ln_w = ln_w; Q.ln_b = ln_b; Q.shift = shift; Q.shift_stride = state_stride;
     Q.shift_out = mode == ROWS_LN ? ws.shift_new : nullptr; Q.digits = ws.digits; Q.scal = ws.scal;
   };
-  auto gemm_common = [&](int nseg, int K) { P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.status = ws.status; };
+  auto gemm_common = [&](int nseg, int K) {
+    P.nseg = nseg; P.K = K; P.R = R; P.Rpad = Rpad; P.status = ws.status; P.sk_acc = ws.sk_acc; P.sk_count = ws.sk_count;
+  };
   // new token-shift carry of every stream -> its state row, done by the NEXT preparation launch
   // (the launch that parked it had sibling CTAs still reading the old row)
   auto commit_carry = [&](float* dst_row) {
@@ -1136,7 +1155,7 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
     if ((e = launch_rows_prep(Q, s, &why)) != cudaSuccess) goto launch_failed;
     memset(&P, 0, sizeof(P));
     fill_gemm_seg(P.seg[0], m->head, ws.scal, logits, V);
-    P.nseg = 1; P.K = D; P.R = B; P.Rpad = Bpad; P.status = ws.status;
+    P.nseg = 1; P.K = D; P.R = B; P.Rpad = Bpad; P.status = ws.status; P.sk_acc = ws.sk_acc; P.sk_count = ws.sk_count;
     { const b200rwkv_matrix* mp[1] = {&m->head};
       if ((e = launch_tile_gemm(P, mp, ws.digits, s, &why)) != cudaSuccess) goto launch_failed; }
   }

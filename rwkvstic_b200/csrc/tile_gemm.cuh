@@ -40,7 +40,10 @@ constexpr int kGemmTmemCols = 512;                       // both accumulators; o
 constexpr int kGemmAcc1Col = 256;                        // first column of the second accumulator
 constexpr int kGemmEpiWarps = 16;                        // four per TMEM lane quadrant
 constexpr int kGemmThreads = 128 + kGemmEpiWarps * 32;   // warp 0 TMA, 1 MMA, 2 TMEM allocation, 4.. epilogue
-constexpr int kGemmChunk = 8;                            // activation rows an epilogue warp handles per TMEM read
+constexpr int kGemmChunk = 8;
+constexpr int kSplitMaxTiles = 320;                      // tiles a split-K launch may have
+constexpr int kSplitMaxRt = 32;                          // and its tile height
+constexpr size_t kSplitAccBytes = size_t(kSplitMaxTiles) * kDigits * kSplitMaxRt * 128 * 4;   // 15.7 MB                            // activation rows an epilogue warp handles per TMEM read
 constexpr int kGemmOffScal = 1024;                       // SegScalars[80]
 constexpr int kGemmOffRing = 4096;
 constexpr int kGemmSmem = kGemmOffRing + kGemmStages * kGemmStageBytes;
@@ -72,7 +75,14 @@ struct GemmParams {
   int mt;              // weight rows per tile: 256 (two accumulators) or 128 (small grids: more CTAs)
   int row_tiles;       // ceil(R / Rt)
   int tiles_seg[kMaxSeg];  // tiles per matrix = row_tiles * ceil(N / mt)
-  int ntiles;          // all tiles of the launch; the grid is min(ntiles, SMs), CTAs loop over tiles
+  int ntiles;          // all tiles of the launch; the grid is min(ntiles * ksplit, SMs), CTAs loop over work items
+  // Split-K for launches with few tiles (few activation rows): work item = (tile, K slice); every
+  // slice adds its int32 digit sums into sk_acc with integer atomics (exact, order-free), takes a
+  // ticket, and the CTA that draws the last ticket of a tile reads the totals, runs the epilogue and
+  // leaves sk_acc / sk_count zero again.  Nobody waits for anybody.
+  int ksplit;          // 1, 2, 4 or 8 slices (divides K/128; only with 128-row tiles and Rt <= 32)
+  int* sk_acc;         // [kSplitMaxTiles][3*Rt][128] int32, zero between launches
+  unsigned* sk_count;  // [kSplitMaxTiles] tickets, zero between launches
   int* status;
   int dbg;             // measurement only: 1 = no operand copies (MMAs on stale shared memory), 2 = no MMAs, 4 = no epilogue
 };
@@ -143,7 +153,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
   extern __shared__ __align__(1024) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int Rt = P.Rt;
-  const int nk = P.K / 128;
+  const int S = P.ksplit;
+  const int nk = P.K / 128 / S;          // K steps of one work item
+  const int nitems_all = P.ntiles * S;
   const uint32_t a_bytes = uint32_t(P.mt) * 128u;
   const uint32_t b_bytes = uint32_t(kDigits * Rt * 128);
 
@@ -185,9 +197,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
       griddep_wait();   // the digit rows come from the preparation kernel in front of this launch
       int issued = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < P.ntiles && ok; tile += gridDim.x) {
-        const GemmTile T = gemm_tile(P, tile);
-        const GemmSeg& S = P.seg[T.seg];
+      for (int it = blockIdx.x; it < nitems_all && ok; it += gridDim.x) {
+        const GemmTile T = gemm_tile(P, it / S);
+        const GemmSeg& Sg = P.seg[T.seg];
+        const int kbase = (it % S) * nk;
         for (int kc = 0; kc < (P.dbg == 1 ? 0 : nk); ++kc, ++issued) {
           const int slot = issued % kGemmStages;
           const uint32_t phase = uint32_t(issued / kGemmStages) & 1u;
@@ -199,10 +212,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
           const uint32_t bar = full0 + 8 * slot;
           const uint32_t dst = smem_u32(ring + size_t(slot) * kGemmStageBytes);
           mbar_arrive_expect_tx(bar, a_bytes + b_bytes);
-          tma_load_3d(dst, &S.wmap, 0, T.n0, kc, bar);   // rows past N are zero-filled
+          tma_load_3d(dst, &Sg.wmap, 0, T.n0, kbase + kc, bar);   // rows past N are zero-filled
 #pragma unroll
           for (int d = 0; d < kDigits; ++d)
-            tma_load_3d(dst + kGemmABytes + uint32_t(d * Rt * 128), &S.xmap, 0, d * P.Rpad + T.row0, kc, bar);
+            tma_load_3d(dst + kGemmABytes + uint32_t(d * Rt * 128), &Sg.xmap, 0, d * P.Rpad + T.row0, kbase + kc, bar);
         }
       }
       *issued_ptr = issued;
@@ -213,8 +226,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
       const uint32_t idesc = umma_idesc_u8s8(128, kDigits * Rt);
       bool ok = true;
       int step = 0, iter = 0;
-      for (int tile = blockIdx.x; tile < P.ntiles && ok; tile += gridDim.x, ++iter) {
-        const GemmTile T = gemm_tile(P, tile);
+      for (int it = blockIdx.x; it < nitems_all && ok; it += gridDim.x, ++iter) {
+        const GemmTile T = gemm_tile(P, it / S);
         const bool two = P.mt == kGemmM && T.n0 + 128 < P.seg[T.seg].N;   // second 128-row sub-tile holds real rows
         // the epilogue must have read this buffer's previous tile out of TMEM
         const int buf = dbuf ? (iter & 1) : 0, use = dbuf ? (iter >> 1) : iter;
@@ -259,15 +272,17 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
     griddep_wait();
     bool ok = true;
     int iter = 0;
-    for (int tile = blockIdx.x; tile < P.ntiles && ok; tile += gridDim.x, ++iter) {
+    volatile int* last_flag = reinterpret_cast<volatile int*>(smem + 272);   // split-K: this CTA drew a tile's last ticket
+    for (int it = blockIdx.x; it < nitems_all && ok; it += gridDim.x, ++iter) {
+      const int tile = it / S;
       const GemmTile T = gemm_tile(P, tile);
-      const GemmSeg& S = P.seg[T.seg];
+      const GemmSeg& Sg = P.seg[T.seg];
       const int n0 = T.n0, row0 = T.row0;
-      const bool two = P.mt == kGemmM && n0 + 128 < S.N;
+      const bool two = P.mt == kGemmM && n0 + 128 < Sg.N;
       named_bar_sync(1, kGemmEpiWarps * 32);   // every epilogue warp is done with the previous tile's scalars
       for (int i = et; i < Rt * 8; i += kGemmEpiWarps * 32) {
         const int r = row0 + (i >> 3);
-        reinterpret_cast<float*>(scal)[i] = r < P.R ? __ldcg(reinterpret_cast<const float*>(S.scal + r) + (i & 7)) : 0.f;
+        reinterpret_cast<float*>(scal)[i] = r < P.R ? __ldcg(reinterpret_cast<const float*>(Sg.scal + r) + (i & 7)) : 0.f;
       }
       named_bar_sync(1, kGemmEpiWarps * 32);
       const int buf = dbuf ? (iter & 1) : 0, use = dbuf ? (iter >> 1) : iter;
@@ -287,14 +302,58 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         tc_fence_before();
         if (lane == 0) mbar_arrive(acc_empty);
       }
+      // affine terms + fused element-wise op for 8 rows of one output column, from the digit sums
+      auto finish = [&](const int (&da)[CH], const int (&db)[CH], const int (&dc)[CH], int h, int j0) {
+        const int n = n0 + h * 128 + q * 32 + lane;
+        const bool nvalid = n < Sg.N;
+        const int nc = nvalid ? n : Sg.N - 1;   // clamped: loads stay in bounds, the store is predicated
+        const float rx = Sg.rx ? Sg.rx[nc] : 1.f, mx = Sg.mx ? Sg.mx[nc] : 0.f;
+        // branch-free over the rows so that their dependency chains interleave
+        float yv[CH];
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const float4 sc = *reinterpret_cast<const float4*>(&scal[j0 + j]);   // sd, zp, sumxs, sumx
+          const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
+          float y = __fmul_rn(__ll2float_rn(I), sc.x) + Sg.half * sc.z;
+          y *= rx;               // rx = 1, mx = 0 when the matrix has no per-output terms: exact no-ops
+          y += sc.y;
+          y += mx * sc.w;
+          yv[j] = y;
+        }
+        if (Sg.act == ACT_RELUSQ) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) { const float t = fmaxf(yv[j], 0.f); yv[j] = t * t; }
+        } else if (Sg.act == ACT_SIGMOID) {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) yv[j] = sigmoidf_(yv[j]);
+        }
+        const int rlast = P.R - 1;
+        if (Sg.gate) {
+          float gv[CH];
+#pragma unroll
+          for (int j = 0; j < CH; ++j) { const int r = min(row0 + j0 + j, rlast); gv[j] = __ldcg(Sg.gate + size_t(r) * Sg.ldgate + nc); }
+#pragma unroll
+          for (int j = 0; j < CH; ++j) yv[j] *= gv[j];
+        }
+        if (Sg.res) {
+          float rv[CH];
+#pragma unroll
+          for (int j = 0; j < CH; ++j) { const int r = min(row0 + j0 + j, rlast); rv[j] = __ldcg(Sg.res + size_t(r) * Sg.ldres + nc); }
+#pragma unroll
+          for (int j = 0; j < CH; ++j) yv[j] += rv[j];
+        }
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int r = row0 + j0 + j;
+          if (r <= rlast && nvalid) Sg.out[size_t(r) * Sg.ldo + n] = yv[j];
+        }
+      };
+      // split-K scratch of this tile: [column = digit*Rt + row][128 weight rows] (mt = 128 only)
+      int* sk = S > 1 ? P.sk_acc + size_t(tile) * (kDigits * Rt) * 128 + q * 32 + lane : nullptr;
 #pragma unroll 1
       for (int item = eg; item < nitems; item += EG) {
         const int h = item / nchunks, j0 = (item - h * nchunks) * CH;
         if (row0 + j0 >= P.R) continue;   // warp-uniform
-        const int n = n0 + h * 128 + q * 32 + lane;
-        const bool nvalid = n < S.N;
-        const int nc = nvalid ? n : S.N - 1;   // clamped: loads stay in bounds, the store is predicated
-        const float rx = S.rx ? S.rx[nc] : 1.f, mx = S.mx ? S.mx[nc] : 0.f;
         const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t((h + buf) * kGemmAcc1Col + j0);
         int da[CH], db[CH], dc[CH];
         tmem_ld8(tbase, da);
@@ -305,44 +364,45 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
           tc_fence_before();
           if (lane == 0) mbar_arrive(acc_empty);
         }
-        // branch-free over the rows so that their dependency chains interleave
-        float yv[CH];
+        if (S == 1) {
+          finish(da, db, dc, h, j0);
+        } else {
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const float4 sc = *reinterpret_cast<const float4*>(&scal[j0 + j]);   // sd, zp, sumxs, sumx
-          const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
-          float y = __fmul_rn(__ll2float_rn(I), sc.x) + S.half * sc.z;
-          y *= rx;               // rx = 1, mx = 0 when the matrix has no per-output terms: exact no-ops
-          y += sc.y;
-          y += mx * sc.w;
-          yv[j] = y;
+          for (int j = 0; j < CH; ++j) {   // 32 lanes = 32 consecutive ints per atomic instruction
+            atomicAdd(sk + size_t(j0 + j) * 128, da[j]);
+            atomicAdd(sk + size_t(Rt + j0 + j) * 128, db[j]);
+            atomicAdd(sk + size_t(2 * Rt + j0 + j) * 128, dc[j]);
+          }
         }
-        if (S.act == ACT_RELUSQ) {
-#pragma unroll
-          for (int j = 0; j < CH; ++j) { const float t = fmaxf(yv[j], 0.f); yv[j] = t * t; }
-        } else if (S.act == ACT_SIGMOID) {
-#pragma unroll
-          for (int j = 0; j < CH; ++j) yv[j] = sigmoidf_(yv[j]);
+      }
+      if (S > 1) {
+        __threadfence();                                   // this thread's additions are visible before the ticket
+        named_bar_sync(1, kGemmEpiWarps * 32);
+        if (et == 0) {
+          const unsigned ticket = atomicAdd(P.sk_count + tile, 1u);
+          __threadfence();                                 // and the other slices' additions before the reads below
+          *last_flag = ticket == unsigned(S - 1) ? 1 : 0;
         }
-        const int rlast = P.R - 1;
-        if (S.gate) {
-          float gv[CH];
+        named_bar_sync(1, kGemmEpiWarps * 32);
+        if (*last_flag) {
+#pragma unroll 1
+          for (int item = eg; item < nchunks; item += EG) {
+            const int j0 = item * CH;
+            if (row0 + j0 >= P.R) continue;
+            int da[CH], db[CH], dc[CH];
 #pragma unroll
-          for (int j = 0; j < CH; ++j) { const int r = min(row0 + j0 + j, rlast); gv[j] = __ldcg(S.gate + size_t(r) * S.ldgate + nc); }
+            for (int j = 0; j < CH; ++j) {
+              da[j] = __ldcg(sk + size_t(j0 + j) * 128);
+              db[j] = __ldcg(sk + size_t(Rt + j0 + j) * 128);
+              dc[j] = __ldcg(sk + size_t(2 * Rt + j0 + j) * 128);
+            }
 #pragma unroll
-          for (int j = 0; j < CH; ++j) yv[j] *= gv[j];
-        }
-        if (S.res) {
-          float rv[CH];
-#pragma unroll
-          for (int j = 0; j < CH; ++j) { const int r = min(row0 + j0 + j, rlast); rv[j] = __ldcg(S.res + size_t(r) * S.ldres + nc); }
-#pragma unroll
-          for (int j = 0; j < CH; ++j) yv[j] += rv[j];
-        }
-#pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int r = row0 + j0 + j;
-          if (r <= rlast && nvalid) S.out[size_t(r) * S.ldo + n] = yv[j];
+            for (int j = 0; j < CH; ++j) {   // leave the scratch zero for the next launch
+              sk[size_t(j0 + j) * 128] = 0; sk[size_t(Rt + j0 + j) * 128] = 0; sk[size_t(2 * Rt + j0 + j) * 128] = 0;
+            }
+            finish(da, db, dc, 0, j0);
+          }
+          if (et == 0) P.sk_count[tile] = 0u;
         }
       }
     }

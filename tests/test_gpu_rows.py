@@ -55,6 +55,21 @@ def test_gemm_integer_part_is_bit_exact(rows, n, k):
         assert torch.equal(got[r], one)
 
 
+@pytest.mark.parametrize("rows,n,k", [(5, 512, 4096), (20, 4096, 4096), (32, 300, 16384), (2, 2560, 10240)])
+def test_gemm_few_rows_split_k_is_bit_exact_and_leaves_its_scratch_clean(rows, n, k):
+    """Few rows and a long K: the launch is cut into K slices whose integer sums meet in a scratch
+    buffer; the result must stay bit-exact and a second and third call must see a clean scratch."""
+    m = random_matrix(n, k, seed=n + k, zero_offset=True)
+    x = torch.randn(rows, k, generator=torch.Generator().manual_seed(rows + k)) * 3
+    first = run_gemm([m], [x])[0]
+    for r in range(rows):
+        assert torch.equal(first[r], fixed_point_gemv(x[r], m, with_affine=False)), f"row {r}"
+    x2 = torch.randn(rows, k, generator=torch.Generator().manual_seed(99)) * 0.1
+    second = run_gemm([m], [x2])[0]
+    assert torch.equal(second[0], fixed_point_gemv(x2[0], m, with_affine=False))
+    assert torch.equal(run_gemm([m], [x])[0], first)
+
+
 def test_gemm_fastquant_vs_oracle():
     g = torch.Generator().manual_seed(5)
     w = torch.randn(1000, 1024, generator=g) * 0.02

@@ -8,19 +8,22 @@
 // with the uint8 weights are exact integer sums recombined in int64.  Here the digit rows are the
 // B operand of 5th-generation tensor-core MMAs (tcgen05.mma kind::i8, u8 x s8 -> s32):
 //
-//   A  = 2 x 128 weight rows x 128 bytes of K   (one TMA box of qt[N][K], 128-byte swizzle, K-major)
-//   B  = 3*Rt digit rows     x 128 bytes of K   (three TMA boxes, [digit][Rt activation rows], Rt <= 80)
-//   D  = two accumulators of 128 lanes x 3*Rt int32 columns in tensor memory (TMEM),
-//        column = digit*Rt + row; the second accumulator starts at column 256
+//   A  = mt weight rows    x 128 bytes of K   (one TMA box of qt[N][K], 128-byte swizzle, K-major; mt = 128 or 256)
+//   B  = 3*Rt digit rows   x 128 bytes of K   (three TMA boxes, [digit][Rt activation rows], Rt = 16..80)
+//   D  = 128 lanes x 3*Rt int32 columns per 128 weight rows in tensor memory (TMEM),
+//        column = digit*Rt + row.  A 256-row tile keeps its second accumulator at column 256 (two
+//        weight sub-tiles share one digit tile); with 128-row tiles columns 0 and 256 are two
+//        buffers, so the epilogue of one tile runs under the MMAs of the next.
 //
-// One tile = (256 weight rows) x (Rt activation rows) of output; a CTA walks K in 128-byte
-// steps through a ring of shared-memory stages: warp 0 issues the TMA copies, warp 1 issues the
-// MMAs (one elected thread; completion is signalled to the ring by tcgen05.commit on the stage's
-// mbarrier), warps 4-19 read the accumulators with tcgen05.ld and apply the affine terms and the
-// fused element-wise op.  The kernel is bound by operand traffic from L2 to shared memory (int8
-// MMAs need ~250 MACs per byte to saturate, a tile gives M*N/(M+N) = 124), which is why the tile
-// pairs two weight sub-tiles with one digit tile.  CTAs that share a weight tile are adjacent in
-// launch order so the tile is read from HBM once and from L2 afterwards.
+// Persistent kernel, one CTA per SM looping over tiles; a CTA walks K in 128-byte steps through a
+// ring of shared-memory stages that runs on across tiles: warp 0 issues the TMA copies, warp 1
+// issues the MMAs (one elected thread; completion is signalled to the ring by tcgen05.commit on the
+// stage's mbarrier), warps 4-19 read the accumulators with tcgen05.ld and apply the affine terms
+// and the fused element-wise op.  The kernel is bound by operand traffic from L2 to shared memory
+// (int8 MMAs need ~250 MACs per byte to saturate, the 256 x 240 tile gives M*N/(M+N) = 124) until
+// the tensor pipe saturates (81 % active on the largest shapes).  Tiles that share a weight tile
+// are adjacent in issue order so it is read from HBM once and from L2 afterwards.  The host picks
+// mt, Rt and, for launches with too few tiles, a split of K over several CTAs (see GemmParams).
 //
 // Every wait is bounded (common.cuh): on expiry the CTA raises its abort flag, sets a status bit,
 // skips its remaining work, and still frees its tensor memory before it retires.
@@ -40,10 +43,10 @@ constexpr int kGemmTmemCols = 512;                       // both accumulators; o
 constexpr int kGemmAcc1Col = 256;                        // first column of the second accumulator
 constexpr int kGemmEpiWarps = 16;                        // four per TMEM lane quadrant
 constexpr int kGemmThreads = 128 + kGemmEpiWarps * 32;   // warp 0 TMA, 1 MMA, 2 TMEM allocation, 4.. epilogue
-constexpr int kGemmChunk = 8;
+constexpr int kGemmChunk = 8;                            // activation rows an epilogue warp handles per TMEM read
 constexpr int kSplitMaxTiles = 320;                      // tiles a split-K launch may have
 constexpr int kSplitMaxRt = 32;                          // and its tile height
-constexpr size_t kSplitAccBytes = size_t(kSplitMaxTiles) * kDigits * kSplitMaxRt * 128 * 4;   // 15.7 MB                            // activation rows an epilogue warp handles per TMEM read
+constexpr size_t kSplitAccBytes = size_t(kSplitMaxTiles) * kDigits * kSplitMaxRt * 128 * 4;   // 15.7 MB
 constexpr int kGemmOffScal = 1024;                       // SegScalars[80]
 constexpr int kGemmOffRing = 4096;
 constexpr int kGemmSmem = kGemmOffRing + kGemmStages * kGemmStageBytes;

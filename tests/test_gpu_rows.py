@@ -231,3 +231,30 @@ def test_rows_entry_points_reject_bad_shapes(tiny):
     # out-of-range token ids are clamped like the one-row path (never an out-of-bounds gather)
     lg = tiny.forward_rows(torch.tensor([[5, 100000], [-3, 7]]), st)
     assert torch.isfinite(lg).all()
+
+
+def test_rows_path_agrees_with_one_row_path_at_the_1b5_shape():
+    """Full-size shapes (D=2048, F=8192, V=50277, 24 blocks): every tile shape the launcher picks for
+    few rows (K slices), a prompt piece and a batch of streams must reproduce the one-row path."""
+    model = B200RWKV.synthetic(24, 2048, seed=5, device=DEV)
+    toks = synth_tokens(3 * 40, seed=21).reshape(3, 40)
+    st_rows = model.empty_batch_state(3)
+    lg_rows = model.forward_rows(toks, st_rows)                      # 120 rows
+    keep = model.rows_threshold
+    try:
+        model.rows_threshold = 1 << 30
+        st_one = model.empty_batch_state(1)
+        lg_one, _ = model.forward(toks[1], st_one[0])                # 40 one-row steps
+    finally:
+        model.rows_threshold = keep
+    assert float((lg_rows[1] - lg_one).abs().max()) < 1e-3
+    assert torch.allclose(st_rows[1][:, :4], st_one[0][:, :4], rtol=2e-3, atol=2e-4)
+    nxt = lg_rows.argmax(dim=1, keepdim=True)
+    lg3 = model.forward_rows(nxt, st_rows)                           # 3 rows: K slices
+    lg1, _ = model.forward(nxt[1].cpu(), st_one[0])
+    assert float((lg3[1] - lg1).abs().max()) < 1e-3
+    st64 = st_rows[1:2].repeat(64, 1, 1, 1).contiguous()             # 64 rows in lock step
+    tok = lg3[1].argmax().reshape(1, 1).repeat(64, 1)
+    lg64 = model.forward_rows(tok, st64)
+    assert bool((lg64 == lg64[0]).all())
+    model.check_status()

@@ -296,6 +296,11 @@ class B200RWKV:
             raise ValueError(f"state must be [{self.n_layer},5,{self.n_embd}], got {tuple(state.shape)}")
         return state.to(device=self.device, dtype=torch.float32).contiguous()
 
+    def _rows_launches(self, tokens_per_stream: int) -> int:
+        """Kernels one rows-path call launches for its blocks: four preparation and four GEMM launches per
+        block plus the WKV scan (one kernel up to 128 tokens per stream, two passes beyond)."""
+        return (9 if tokens_per_stream <= 128 else 10) * self.n_layer
+
     def forward_rows(self, tokens: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
         """Tensor-core path: ``tokens [B,T]`` int64, ``state [B,L,5,D]`` fp32 contiguous on the
         device (updated in place).  Every matrix is applied to all B*T rows at once
@@ -327,7 +332,7 @@ class B200RWKV:
                 _lib.check(self._L.b200rwkv_forward_rows(C.byref(self._cmodel), piece.data_ptr(), B, tp, state.data_ptr(),
                                                          state.stride(0), out.data_ptr() if last else None,
                                                          ws.data_ptr(), ws.numel(), stream))
-                self.launch_count += 10 * self.n_layer + 1 + (2 if last else 0)
+                self.launch_count += self._rows_launches(tp) + 1 + (2 if last else 0)
                 self._status_host.copy_(ws[:4].view(torch.int32))
                 bits = int(self._status_host[0])
                 if bits:
@@ -368,7 +373,7 @@ class B200RWKV:
             _lib.check(self._L.b200rwkv_forward_rows_stage(
                 C.byref(self._cmodel), None if tokens is None else tokens.data_ptr(), x.data_ptr(), B, T,
                 state.data_ptr(), state.stride(0), None if out is None else out.data_ptr(), ws.data_ptr(), ws.numel(), stream))
-            self.launch_count += 10 * self.n_layer + (1 if tokens is not None else 0) + (2 if want_logits else 0)
+            self.launch_count += self._rows_launches(T) + (1 if tokens is not None else 0) + (2 if want_logits else 0)
             self._last_rows_ws = ws
         return out
 

@@ -41,6 +41,11 @@ def decode_sharded(model, tokens: torch.Tensor, state: torch.Tensor, steps_fn=No
     shard rows only; other rows are left untouched (they belong to other ranks)."""
     rank, world = (dist.get_rank(), dist.get_world_size()) if dist.is_initialized() else (0, 1)
     shard = stream_shard(tokens.shape[0], world, rank)
+    if hasattr(model, "forward_batch") and len(shard) > 0:
+        # the GPU model applies every matrix to all rows of the shard at once (tensor-core rows path)
+        view = state[shard.start:shard.stop]
+        lg, _ = model.forward_batch(tokens[shard.start:shard.stop], view)
+        return shard, lg, view
     outs = []
     for b in shard:
         lg, _ = model.forward(tokens[b], state[b])

@@ -238,23 +238,25 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
   for (int g = tid; g < NG; g += kPrepThreads) store_digits(dst, g, park[g], inv);
 }
 
-// PREP_XS: the previous epilogue already wrote xs and published max / sums; only digits remain.
+// PREP_XS: the previous epilogue already wrote xs and published max / sums; only digits remain, and
+// they need no reduction, so the vector is cut into gridDim.x slices, one CTA (one free SM) each.
 // The xs loads of the first batch and the loads of the published scalars go out together.
 __device__ __forceinline__ void prep_xs(const PrepParams& P) {
   constexpr int GB = 8;
   const int tid = threadIdx.x;
   const int NG = P.K / 4;
+  const int g_lo = int((long long)NG * blockIdx.x / gridDim.x), g_hi = int((long long)NG * (blockIdx.x + 1) / gridDim.x);
   griddep_wait();
-  if (tid == 0 && P.trace) P.trace[1] = globaltimer_ns();
+  if (tid == 0 && P.trace && blockIdx.x == 0) P.trace[1] = globaltimer_ns();
   float4 xs[GB];
 #pragma unroll
   for (int i = 0; i < GB; ++i) {
-    const int g = tid + i * kPrepThreads;
-    if (g < NG) xs[i] = ld_act_v4(reinterpret_cast<const float4*>(P.seg[0].xin) + g);
+    const int g = g_lo + tid + i * kPrepThreads;
+    if (g < g_hi) xs[i] = ld_act_v4(reinterpret_cast<const float4*>(P.seg[0].xin) + g);
   }
   const float amax = __uint_as_float(__ldcg(&P.pub->amax_bits));
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
-  if (tid == 0) {
+  if (tid == 0 && blockIdx.x == 0) {
     SegScalars sc;
     sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;   // IEEE fp32 division, no fp64 on this path
     sc.zp = __ll2float_rn(__ldcg(&P.pub->zp)) * (1.0f / kPubSumScale);
@@ -266,10 +268,10 @@ __device__ __forceinline__ void prep_xs(const PrepParams& P) {
   }
 #pragma unroll
   for (int i = 0; i < GB; ++i) {
-    const int g = tid + i * kPrepThreads;
-    if (g < NG) store_digits(P.planes, g, xs[i], inv);
+    const int g = g_lo + tid + i * kPrepThreads;
+    if (g < g_hi) store_digits(P.planes, g, xs[i], inv);
   }
-  for (int g = tid + GB * kPrepThreads; g < NG; g += kPrepThreads)   // inputs beyond the first batch
+  for (int g = g_lo + tid + GB * kPrepThreads; g < g_hi; g += kPrepThreads)   // inputs beyond the first batch
     store_digits(P.planes, g, ld_act_v4(reinterpret_cast<const float4*>(P.seg[0].xin) + g), inv);
 }
 
@@ -286,6 +288,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1) vector_prep_kernel(const __gr
 }
 
 inline size_t prep_smem_bytes(int K, int mode) { return size_t(kPrepRedBytes) + (mode == PREP_XS ? 0 : size_t(4) * K); }
-inline int prep_grid(int nseg, int mode) { return mode == PREP_XS ? 1 : nseg; }
+inline int prep_grid(int nseg, int mode) { return mode == PREP_XS ? kMaxSeg : nseg; }   // one CTA per SM the GEMV grid leaves free
 
 }  // namespace b200

@@ -349,8 +349,7 @@ def run_ours(args, rank, world, local_rank):
     nxt = torch.zeros(1, dtype=torch.int64).pin_memory()
 
     def e2e_step():
-        model.step_greedy(tok, state, nxt)               # H2D of the token, step + arg-max, D2H of the sampled id
-        torch.cuda.synchronize(dev)
+        model.step_greedy(tok, state, nxt)               # H2D of the token, step + arg-max, D2H of the sampled id, sync
         tok[0] = int(nxt[0])                             # greedy feedback through the host
 
     for i in range(W):

@@ -400,24 +400,28 @@ class B200RWKV:
         return out
 
     def step_greedy(self, token: torch.Tensor, state: torch.Tensor, out: torch.Tensor) -> None:
-        """One decode step with the arg-max taken on the device, for a host-driven loop: copies
-        ``token`` (int64[1], ideally pinned host memory) to the device, runs the step and the
-        arg-max kernel (one CUDA-graph replay from the second call with the same ``state`` buffer
-        on), and copies the sampled id into ``out`` (int64[1], ideally pinned).  Asynchronous:
-        synchronise before reading ``out``.  ``state`` is updated in place."""
+        """One decode step with the arg-max taken on the device, for a host-driven loop: the token
+        (int64[1] on the host) goes to the device, the step and the arg-max kernel run, and the
+        sampled id comes back into ``out`` (int64[1] on the host).  From the second call with the
+        same ``state`` buffer on, all of it - both copies included, through pinned buffers this
+        object owns - is one CUDA-graph replay.  Returns after the id has arrived; ``state`` is
+        updated in place."""
         state = self._own_state(state)
+        if not hasattr(self, "_next"):
+            self._next = torch.zeros(1, dtype=torch.int64, device=self.device)
+            self._tok_host = torch.zeros(1, dtype=torch.int64).pin_memory()
+            self._next_host = torch.zeros(1, dtype=torch.int64).pin_memory()
+            self._greedy_graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+            self._greedy_seen: Dict[int, int] = {}
+        self._tok_host[0] = int(token.reshape(-1)[0])
         with torch.cuda.device(self.device):
-            self._tok.copy_(token.reshape(1), non_blocking=True)
-            if not hasattr(self, "_next"):
-                self._next = torch.zeros(1, dtype=torch.int64, device=self.device)
-                self._greedy_graphs: Dict[int, torch.cuda.CUDAGraph] = {}
-                self._greedy_seen: Dict[int, int] = {}
-
             def one():
+                self._tok.copy_(self._tok_host, non_blocking=True)           # 8 bytes host -> device
                 self._step_raw(self._tok.data_ptr(), state.data_ptr(), self._logits.data_ptr())
                 _lib.check(self._L.b200rwkv_argmax(self._logits.data_ptr(), 1, self.n_vocab, self.n_vocab,
                                                    self._next.data_ptr(), None, None, 0,
                                                    torch.cuda.current_stream(self.device).cuda_stream))
+                self._next_host.copy_(self._next, non_blocking=True)         # 8 bytes device -> host
             key = state.data_ptr()
             g = self._greedy_graphs.get(key) if self.use_graph else None
             if g is not None:
@@ -437,7 +441,8 @@ class B200RWKV:
                     g.replay()
                 else:
                     one()
-            out.copy_(self._next, non_blocking=True)
+            torch.cuda.current_stream(self.device).synchronize()
+        out.reshape(-1)[0] = self._next_host[0]
         self.launch_count += self.launches_per_step + 1
 
     def generate_greedy(self, token, state: torch.Tensor, n: int) -> torch.Tensor:

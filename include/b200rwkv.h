@@ -256,6 +256,27 @@ int b200rwkv_forward_rows_stage(const b200rwkv_model* m, const int64_t* tokens, 
 int b200rwkv_argmax(const float* x, int rows, int n, int64_t ldx, int64_t* out, int64_t* history,
                     int* history_count, int history_capacity, void* stream);
 
+/*
+ * Typical sampling on the device (replaces the reference's host-side sampler,
+ * samplers/typical.py:1-17, called per token from rwkvMaster.py:39-45 after the whole logits
+ * vector has been read back).  Per row: p = softmax(x), s = | -log p - entropy |, the tokens are
+ * kept in order of s until their mass reaches `tau`, kept probabilities are raised to 1/temp and
+ * one token is drawn by inverse CDF in index order with the caller's uniform number.
+ *   x         device f32 [rows][ldx], n values used per row
+ *   temp,tau  > 0 (tau >= 1 keeps every token)
+ *   u         device f32, uniform in [0,1): row r reads u[r + rows*step], step = *history_count
+ *             when a history is given and 0 otherwise (so a captured decode loop draws a fresh
+ *             number per replay from a buffer filled once)
+ *   out       device int64 [rows]
+ *   probs_out optional device f32 [rows][n]: the masked, tempered, unnormalised probabilities
+ *   history   as b200rwkv_argmax; needs rows == 1
+ * The reference draws with torch.multinomial, whose random stream cannot be matched; what is
+ * matched is the distribution it draws from (same kept set, same weights).
+ */
+int b200rwkv_sample_typical(const float* x, int rows, int n, int64_t ldx, float temp, float tau, const float* u,
+                            int64_t* out, float* probs_out, int64_t* history, int* history_count,
+                            int history_capacity, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

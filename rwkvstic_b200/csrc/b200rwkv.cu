@@ -6,6 +6,7 @@
 
 #include "stream_gemv.cuh"
 #include "tile_gemm.cuh"
+#include "sampling.cuh"
 
 namespace b200 {
 
@@ -1187,6 +1188,19 @@ int b200rwkv_argmax(const float* x, int rows, int n, int64_t ldx, int64_t* out, 
       x, n, ldx, reinterpret_cast<long long*>(out), reinterpret_cast<long long*>(history), history_count, history_capacity);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "argmax: %s", cudaGetErrorString(e));
+  return B200RWKV_OK;
+}
+
+int b200rwkv_sample_typical(const float* x, int rows, int n, int64_t ldx, float temp, float tau, const float* u, int64_t* out,
+                            float* probs_out, int64_t* history, int* history_count, int history_capacity, void* stream) {
+  if (!x || !u || !out || rows < 1 || n < 1 || ldx < n || !(temp > 0.f) || !(tau > 0.f) ||
+      (history && (!history_count || history_capacity < 1 || rows != 1)))
+    return fail(B200RWKV_EINVAL, "sample_typical: bad argument (rows=%d n=%d temp=%g tau=%g)", rows, n, double(temp), double(tau));
+  sample_typical_kernel<<<rows, kSampleThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, n, ldx, temp, tau, u, reinterpret_cast<long long*>(out), probs_out, reinterpret_cast<long long*>(history),
+      history_count, history_capacity);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "sample_typical: %s", cudaGetErrorString(e));
   return B200RWKV_OK;
 }
 

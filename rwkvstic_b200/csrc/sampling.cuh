@@ -1,0 +1,199 @@
+// Typical sampling on the device: one CTA per row of logits, no sort and no host round trip.
+//
+// What the reference's sampler computes on the host per token (samplers/typical.py:1-17):
+//   p = softmax(logits); nl = -log p; ent = sum(nl * p) (NaN terms skipped); s = |nl - ent|;
+//   sort by s, running sum of p in that order, cutoff = number of running sums < tau;
+//   every p whose s is larger than the s at the cutoff position becomes 0; p <- p^(1/temp);
+//   one draw from the resulting (unnormalised) distribution.
+// The sort only serves to find one threshold: the smallest value t among the s_i for which the
+// mass of {i : s_i <= t} reaches tau.  Here that threshold is found by a radix select over the
+// bit pattern of s (s >= 0, so float order is unsigned-integer order) weighted by p: four passes
+// of 256-bin mass histograms, each fixing one byte of t.  The draw is an inverse-CDF walk in index
+// order with a uniform number the caller supplies, so a run is reproducible from its seed.
+// The row (V floats, 200 KB at V = 50277) stays in L2; every pass recomputes p and s from the
+// logits with the same instructions, so all passes see identical values.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kSampleThreads = 1024;
+constexpr int kSampleHists = 16;   // mass histograms per CTA; two warps share one
+
+struct TypicalRow {
+  float mx;       // largest logit
+  float inv_z;    // 1 / sum exp(l - mx)
+  float ent;      // entropy in nats, fp32 like the reference's nansum
+};
+
+// p and s of one logit; identical code in every pass.
+__device__ __forceinline__ void typical_eval(float l, const TypicalRow& r, float& p, float& s) {
+  p = expf(l - r.mx) * r.inv_z;
+  const float nl = -logf(p);            // +inf when p underflowed to 0, like the reference
+  s = fabsf(nl - r.ent);
+}
+
+__device__ __forceinline__ double block_sum_f64(double v, double* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();                      // red may still be read from an earlier call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  double t = 0.0;
+  for (int w = 0; w < kSampleThreads / 32; ++w) t += red[w];   // same order in every thread
+  return t;
+}
+
+__device__ __forceinline__ float block_max_f32(float v, double* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if (lane == 0) red[warp] = double(v);
+  __syncthreads();
+  double t = red[0];
+  for (int w = 1; w < kSampleThreads / 32; ++w) t = fmax(t, red[w]);
+  return float(t);
+}
+
+// logits [rows][ldx]; u: one uniform number in [0,1) per draw, read at u[row + rows * step] where
+// step = *history_count when a history is kept and 0 otherwise; out[row] = sampled id;
+// probs_out (nullable) [rows][n]: the masked, tempered, unnormalised probabilities the draw used.
+__global__ void __launch_bounds__(kSampleThreads)
+sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float temp, float tau,
+                      const float* __restrict__ u, long long* __restrict__ out, float* __restrict__ probs_out,
+                      long long* __restrict__ hist, int* __restrict__ hist_count, int hist_cap) {
+  __shared__ double red[kSampleThreads / 32];
+  __shared__ double mass[kSampleHists][256];
+  __shared__ double part[kSampleThreads];
+  __shared__ unsigned int sh_prefix;
+  __shared__ double sh_below;
+  __shared__ int sh_keep_all, sh_chunk;
+  __shared__ double sh_target, sh_before;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int row_id = blockIdx.x;
+  const float* row = x + size_t(row_id) * ldx;
+
+  // ---- softmax statistics and entropy
+  float mx = -INFINITY;
+  for (int i = tid; i < n; i += kSampleThreads) mx = fmaxf(mx, __ldcg(row + i));
+  TypicalRow r;
+  r.mx = block_max_f32(mx, red);
+  double z = 0.0;
+  for (int i = tid; i < n; i += kSampleThreads) z += double(expf(__ldcg(row + i) - r.mx));
+  r.inv_z = float(1.0 / block_sum_f64(z, red));
+  r.ent = 0.f;
+  double e = 0.0;
+  for (int i = tid; i < n; i += kSampleThreads) {
+    const float p = expf(__ldcg(row + i) - r.mx) * r.inv_z;
+    if (p > 0.f) e += double(-logf(p) * p);
+  }
+  r.ent = float(block_sum_f64(e, red));
+
+  // ---- threshold: smallest s whose cumulative mass (in order of s) reaches tau
+  if (tid == 0) { sh_prefix = 0u; sh_below = 0.0; sh_keep_all = 0; }
+  unsigned int known = 0u;                       // mask of the bits of the threshold fixed so far
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    for (int i = tid; i < kSampleHists * 256; i += kSampleThreads) (&mass[0][0])[i] = 0.0;
+    __syncthreads();
+    const unsigned int prefix = sh_prefix;
+    if (!sh_keep_all) {
+      double* h = mass[warp & (kSampleHists - 1)];
+      for (int i = tid; i < n; i += kSampleThreads) {
+        float p, s;
+        typical_eval(__ldcg(row + i), r, p, s);
+        const unsigned int key = __float_as_uint(s);
+        if (p > 0.f && (key & known) == prefix) atomicAdd(&h[(key >> shift) & 255u], double(p));
+      }
+    }
+    __syncthreads();
+    if (tid < 256) {
+      double t = 0.0;
+      for (int k = 0; k < kSampleHists; ++k) t += mass[k][tid];
+      part[tid] = t;
+    }
+    __syncthreads();
+    if (tid == 0 && !sh_keep_all) {
+      double run = sh_below;
+      int b = -1;
+      for (int k = 0; k < 256; ++k) {
+        if (run + part[k] >= double(tau)) { b = k; break; }
+        run += part[k];
+      }
+      if (b < 0) {
+        if (shift == 24) sh_keep_all = 1;        // the whole row has less mass than tau: nothing is cut
+        else { b = 255; run = sh_below; for (int k = 0; k < 255; ++k) run += part[k]; }
+      }
+      if (b >= 0) { sh_prefix = prefix | (unsigned(b) << shift); sh_below = run; }
+    }
+    known |= 255u << shift;
+    __syncthreads();
+  }
+  const bool keep_all = sh_keep_all != 0;
+  const float thresh = __uint_as_float(sh_prefix);
+
+  // ---- the draw: inverse CDF over q_i = keep_i ? p_i^(1/temp) : 0 in index order
+  const float inv_temp = 1.0f / temp;
+  const bool tempered = temp != 1.0f;
+  const int chunk = (n + kSampleThreads - 1) / kSampleThreads;
+  const int i0 = tid * chunk, i1 = min(n, i0 + chunk);
+  double mine = 0.0;
+  for (int i = i0; i < i1; ++i) {
+    float p, s;
+    typical_eval(__ldcg(row + i), r, p, s);
+    float q = (keep_all || s <= thresh) ? p : 0.f;
+    if (tempered && q > 0.f) q = powf(q, inv_temp);
+    if (probs_out) probs_out[size_t(row_id) * n + i] = q;
+    mine += double(q);
+  }
+  part[tid] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    double total = 0.0;
+    for (int k = 0; k < kSampleThreads; ++k) total += part[k];
+    const int step = (hist && hist_count) ? *hist_count : 0;
+    const double target = double(u[row_id + size_t(gridDim.x) * step]) * total;
+    double run = 0.0;
+    int c = -1, last = 0;
+    for (int k = 0; k < kSampleThreads; ++k) {
+      if (part[k] > 0.0) {
+        last = k;
+        if (run + part[k] >= target) { c = k; break; }
+      }
+      run += part[k];
+    }
+    if (c < 0) {                                  // rounding left the target past the end: last non-empty chunk
+      c = last; run = 0.0;
+      for (int k = 0; k < last; ++k) run += part[k];
+    }
+    sh_chunk = c; sh_target = target; sh_before = run;
+  }
+  __syncthreads();
+  if (tid == sh_chunk) {
+    double run = sh_before;
+    long long pick = -1, last = -1;
+    for (int i = i0; i < i1; ++i) {
+      float p, s;
+      typical_eval(__ldcg(row + i), r, p, s);
+      float q = (keep_all || s <= thresh) ? p : 0.f;
+      if (tempered && q > 0.f) q = powf(q, inv_temp);
+      if (q > 0.f) {
+        last = i;
+        run += double(q);
+        if (run >= sh_target) { pick = i; break; }
+      }
+    }
+    if (pick < 0) pick = last < 0 ? i0 : last;
+    out[row_id] = pick;
+    if (hist && hist_count && row_id == 0) {
+      const int cnt = *hist_count;
+      if (cnt < hist_cap) hist[cnt] = pick;
+      *hist_count = cnt + 1;
+    }
+  }
+}
+
+}  // namespace b200

@@ -478,6 +478,43 @@ class B200RWKV:
         self.launch_count += n * (self.launches_per_step + 1)
         return hist[:n]
 
+    def generate_typical(self, token, state: torch.Tensor, n: int, temp: float = 1.0, tau: float = 0.95,
+                         seed: int = 0) -> torch.Tensor:
+        """``n`` decode steps with typical sampling (the reference's sampler, samplers/typical.py:1-17)
+        that never leave the device: like ``generate_greedy`` with the sampling kernel in the
+        arg-max kernel's place.  The uniform numbers of all n draws come from one device
+        generator seeded with ``seed`` before the loop, so a run is reproducible.  Returns the
+        generated ids (device int64); ``state`` is updated in place."""
+        state = self._own_state(state)
+        hist = torch.zeros(max(n, 1), dtype=torch.int64, device=self.device)
+        count = torch.zeros(1, dtype=torch.int32, device=self.device)
+        gen = torch.Generator(device=self.device)
+        gen.manual_seed(seed)
+        u = torch.rand(max(n, 1), device=self.device, dtype=torch.float32, generator=gen)
+        with torch.cuda.device(self.device):
+            self._tok.copy_(torch.as_tensor(token, dtype=torch.int64).reshape(1), non_blocking=True)
+            stream = lambda: torch.cuda.current_stream(self.device).cuda_stream
+
+            def one():
+                self._step_raw(self._tok.data_ptr(), state.data_ptr(), self._logits.data_ptr())
+                _lib.check(self._L.b200rwkv_sample_typical(self._logits.data_ptr(), 1, self.n_vocab, self.n_vocab,
+                                                           float(temp), float(tau), u.data_ptr(), self._tok.data_ptr(),
+                                                           None, hist.data_ptr(), count.data_ptr(), hist.numel(), stream()))
+            if self.use_graph and n >= 3:
+                one()
+                g = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize(self.device)
+                with torch.cuda.graph(g):
+                    one()
+                count.fill_(1)
+                for _ in range(n - 1):
+                    g.replay()
+            else:
+                for _ in range(n):
+                    one()
+        self.launch_count += n * (self.launches_per_step + 1)
+        return hist[:n]
+
     def forward(self, tokens, state: torch.Tensor):
         """``(logits f32[V] on the device, state)`` - see the module docstring."""
         if not torch.is_tensor(tokens):

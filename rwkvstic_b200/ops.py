@@ -132,3 +132,28 @@ def wkv_scan(w: torch.Tensor, u: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                                                 y.data_ptr(), aa.data_ptr(), bb.data_ptr(), pp.data_ptr(),
                                                 convention, _stream(k.device)))
     return y
+
+
+def sample_typical(logits: torch.Tensor, temp: float = 1.0, tau: float = 0.95, u: Optional[torch.Tensor] = None,
+                   generator: Optional[torch.Generator] = None, return_probs: bool = False):
+    """Typical sampling of one token per row of ``logits [rows,V]`` (or ``[V]``) on the device:
+    the arithmetic of the reference's ``typical(logits, temp, tau)`` (samplers/typical.py:1-17)
+    with the draw made by inverse CDF from ``u`` (device f32 [rows] uniform in [0,1); drawn from
+    ``generator`` when absent).  Returns device int64 [rows], and with ``return_probs`` also the
+    masked, tempered, unnormalised probabilities [rows,V] the draw was made from."""
+    x = logits if logits.dim() == 2 else logits.reshape(1, -1)
+    if x.dtype != torch.float32 or x.device.type != "cuda" or x.stride(1) != 1:
+        raise ValueError("sample_typical needs fp32 CUDA logits with contiguous rows")
+    rows, n = x.shape
+    if u is None:
+        u = torch.rand(rows, device=x.device, dtype=torch.float32, generator=generator)
+    if u.dtype != torch.float32 or u.device != x.device or u.numel() != rows or not u.is_contiguous():
+        raise ValueError("u must be a contiguous fp32 tensor of one number per row on the logits' device")
+    out = torch.empty(rows, dtype=torch.int64, device=x.device)
+    probs = torch.empty(rows, n, dtype=torch.float32, device=x.device) if return_probs else None
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().b200rwkv_sample_typical(x.data_ptr(), rows, n, x.stride(0), float(temp), float(tau),
+                                                      u.data_ptr(), out.data_ptr(),
+                                                      probs.data_ptr() if return_probs else None, None, None, 0,
+                                                      _stream(x.device)))
+    return (out, probs) if return_probs else out

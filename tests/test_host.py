@@ -42,6 +42,10 @@ def test_bad_arguments_return_codes_not_aborts():
     assert L.b200rwkv_forward_rows(None, None, 1, 1, None, 0, None, None, 0, None) == _lib.EINVAL
     assert L.b200rwkv_forward_rows_stage(None, None, None, 1, 1, None, 0, None, None, 0, None) == _lib.EINVAL
     assert L.b200rwkv_argmax(None, 1, 8, 8, None, None, None, 0, None) == _lib.EINVAL
+    assert L.b200rwkv_sample_typical(None, 1, 8, 8, 1.0, 0.9, None, None, None, None, None, 0, None) == _lib.EINVAL
+    assert L.b200rwkv_sample_typical(1, 1, 8, 8, 0.0, 0.9, 1, 1, None, None, None, 0, None) == _lib.EINVAL   # temp must be > 0
+    assert L.b200rwkv_sample_typical(1, 2, 8, 8, 1.0, 0.9, 1, 1, None, 1, 1, 4, None) == _lib.EINVAL    # history needs rows == 1
+    assert b"sample_typical" in L.b200rwkv_last_error()
     assert L.b200rwkv_gemm_workspace_bytes(4096, 3, 100) > 3 * 3 * 112 * 4096   # digit rows padded to 16
     assert L.b200rwkv_gemm_workspace_bytes(4096, 4, 100) == 0 and L.b200rwkv_rows_workspace_bytes(None, 1, 1) == 0
     with pytest.raises(_lib.B200RWKVError):

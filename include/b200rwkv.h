@@ -277,6 +277,23 @@ int b200rwkv_sample_typical(const float* x, int rows, int n, int64_t ldx, float 
                             int64_t* out, float* probs_out, int64_t* history, int* history_count,
                             int history_capacity, void* stream);
 
+/*
+ * Unquantised weights: the TORCH-mode matrix-vector product of the reference
+ * (agnostic/backends/torch.py:162-164, `x.to(W.dtype).matmul(W).to(x.dtype)`).
+ *   y[o] = round_T( sum_j round_T(x[j]) * W[o][j] ),  T = the weights' type, fp32 accumulation
+ *   w      device, [n_out][ldw] elements of `dtype` (B200RWKV_BF16 / _F16 / _F32), ldw >= k_in:
+ *          the checkpoint's own [out][in] tensor, which the reference keeps and addresses through a
+ *          transposed view (initTensor, torch.py:146-152).  Rows that start on 16-byte boundaries
+ *          (w and ldw * sizeof(T) multiples of 16, x 16-byte aligned) take the fast path.
+ *   x, y   device f32 [k_in], [n_out]; y is overwritten
+ * No workspace; every output is summed by one warp in a fixed order (deterministic).
+ */
+#define B200RWKV_F32 0
+#define B200RWKV_BF16 1
+#define B200RWKV_F16 2
+int b200rwkv_gemv_dense(const void* w, int dtype, int k_in, int n_out, int64_t ldw, const float* x, float* y,
+                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

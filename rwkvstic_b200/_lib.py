@@ -21,7 +21,7 @@ EXPORTS = (
     "b200rwkv_gemv_u8_traced", "b200rwkv_gemv_workspace_bytes", "b200rwkv_gemv_u8_static",
     "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step", "b200rwkv_decode_step_traced",
     "b200rwkv_gemm_workspace_bytes", "b200rwkv_gemm_u8", "b200rwkv_rows_workspace_bytes", "b200rwkv_forward_rows", "b200rwkv_forward_rows_stage", "b200rwkv_argmax",
-    "b200rwkv_sample_typical",
+    "b200rwkv_sample_typical", "b200rwkv_gemv_dense",
 )
 
 
@@ -106,6 +106,9 @@ def lib() -> C.CDLL:
     L.b200rwkv_sample_typical.restype = C.c_int
     L.b200rwkv_sample_typical.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_float, C.c_float, C.c_void_p,
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    L.b200rwkv_gemv_dense.restype = C.c_int
+    L.b200rwkv_gemv_dense.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p,
+                                      C.c_void_p]
     _lib = L
     return L
 

@@ -7,6 +7,7 @@
 #include "stream_gemv.cuh"
 #include "tile_gemm.cuh"
 #include "sampling.cuh"
+#include "dense_gemv.cuh"
 
 namespace b200 {
 
@@ -1201,6 +1202,39 @@ int b200rwkv_sample_typical(const float* x, int rows, int n, int64_t ldx, float 
       history_count, history_capacity);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "sample_typical: %s", cudaGetErrorString(e));
+  return B200RWKV_OK;
+}
+
+// ---- unquantised weights (TORCH-mode matvec) -----------------------------------------------------
+static int dense_elem_bytes(int dtype) { return dtype == B200RWKV_F32 ? 4 : (dtype == B200RWKV_BF16 || dtype == B200RWKV_F16) ? 2 : 0; }
+
+int b200rwkv_gemv_dense(const void* w, int dtype, int k_in, int n_out, int64_t ldw, const float* x, float* y, void* stream) {
+  const int eb = dense_elem_bytes(dtype);
+  if (!w || !x || !y || k_in < 1 || n_out < 1 || ldw < k_in || !eb)
+    return fail(B200RWKV_EINVAL, "gemv_dense: bad argument (k_in=%d n_out=%d dtype=%d)", k_in, n_out, dtype);
+  DenseParams P;
+  memset(&P, 0, sizeof(P));
+  P.w = w; P.x = x; P.y = y; P.ldw = ldw; P.K = k_in; P.N = n_out;
+  P.vector_ok = reinterpret_cast<uintptr_t>(w) % 16 == 0 && (size_t(ldw) * eb) % 16 == 0 &&
+                reinterpret_cast<uintptr_t>(x) % 16 == 0;
+  // four CTAs fit an SM (56 registers x 256 threads); pairs of rows only when that still fills them
+  const bool pairs = n_out >= device_sms() * 4 * kDenseWarps * 2;
+  const int most = device_sms() * (pairs ? 4 : 8);            // the one-row variant needs 40 registers
+  const int per_cta = kDenseWarps * (pairs ? 2 : 1);
+  const int passes = (n_out + per_cta - 1) / per_cta;
+  const dim3 grid(passes < most ? passes : most);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define B200_DENSE_LAUNCH(T)                                                            \
+  do {                                                                                  \
+    if (pairs) dense_gemv_kernel<T, 2, 4><<<grid, kDenseThreads, 0, st>>>(P);           \
+    else dense_gemv_kernel<T, 1, 8><<<grid, kDenseThreads, 0, st>>>(P);                 \
+  } while (0)
+  if (dtype == B200RWKV_BF16) B200_DENSE_LAUNCH(__nv_bfloat16);
+  else if (dtype == B200RWKV_F16) B200_DENSE_LAUNCH(__half);
+  else B200_DENSE_LAUNCH(float);
+#undef B200_DENSE_LAUNCH
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "gemv_dense: %s", cudaGetErrorString(e));
   return B200RWKV_OK;
 }
 

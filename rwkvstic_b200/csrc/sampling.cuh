@@ -8,8 +8,11 @@
 // The sort only serves to find one threshold: the smallest value t among the s_i for which the
 // mass of {i : s_i <= t} reaches tau.  Here that threshold is found by a radix select over the
 // bit pattern of s (s >= 0, so float order is unsigned-integer order) weighted by p: four passes
-// of 256-bin mass histograms, each fixing one byte of t.  The draw is an inverse-CDF walk in index
-// order with a uniform number the caller supplies, so a run is reproducible from its seed.
+// of 256-bin mass histograms, each fixing one byte of t.  Masses are 64-bit fixed point (p * 2^44:
+// integer atomics in shared memory are native and their sums do not depend on arrival order; a
+// whole row loses at most V * 2^-44 of mass to truncation, far below fp32 resolution).  The draw
+// is an inverse-CDF walk in index order with a uniform number the caller supplies, so a run is
+// reproducible from its seed.
 // The row (V floats, 200 KB at V = 50277) stays in L2; every pass recomputes p and s from the
 // logits with the same instructions, so all passes see identical values.
 #pragma once
@@ -20,6 +23,7 @@ namespace b200 {
 
 constexpr int kSampleThreads = 1024;
 constexpr int kSampleHists = 16;   // mass histograms per CTA; two warps share one
+constexpr float kMassScale = 17592186044416.0f;   // 2^44
 
 struct TypicalRow {
   float mx;       // largest logit
@@ -66,10 +70,11 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
                       const float* __restrict__ u, long long* __restrict__ out, float* __restrict__ probs_out,
                       long long* __restrict__ hist, int* __restrict__ hist_count, int hist_cap) {
   __shared__ double red[kSampleThreads / 32];
-  __shared__ double mass[kSampleHists][256];
+  __shared__ unsigned long long mass[kSampleHists][256];
+  __shared__ unsigned long long tot[256];
   __shared__ double part[kSampleThreads];
   __shared__ unsigned int sh_prefix;
-  __shared__ double sh_below;
+  __shared__ unsigned long long sh_below;
   __shared__ int sh_keep_all, sh_chunk;
   __shared__ double sh_target, sh_before;
 
@@ -94,39 +99,37 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
   r.ent = float(block_sum_f64(e, red));
 
   // ---- threshold: smallest s whose cumulative mass (in order of s) reaches tau
-  if (tid == 0) { sh_prefix = 0u; sh_below = 0.0; sh_keep_all = 0; }
+  if (tid == 0) { sh_prefix = 0u; sh_below = 0ull; sh_keep_all = 0; }
+  const unsigned long long tau_fixed = __double2ull_ru(double(tau) * double(kMassScale));
   unsigned int known = 0u;                       // mask of the bits of the threshold fixed so far
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = tid; i < kSampleHists * 256; i += kSampleThreads) (&mass[0][0])[i] = 0.0;
+    for (int i = tid; i < kSampleHists * 256; i += kSampleThreads) (&mass[0][0])[i] = 0ull;
     __syncthreads();
     const unsigned int prefix = sh_prefix;
     if (!sh_keep_all) {
-      double* h = mass[warp & (kSampleHists - 1)];
+      unsigned long long* h = mass[warp & (kSampleHists - 1)];
       for (int i = tid; i < n; i += kSampleThreads) {
         float p, s;
         typical_eval(__ldcg(row + i), r, p, s);
         const unsigned int key = __float_as_uint(s);
-        if (p > 0.f && (key & known) == prefix) atomicAdd(&h[(key >> shift) & 255u], double(p));
+        if (p > 0.f && (key & known) == prefix) atomicAdd(&h[(key >> shift) & 255u], __float2ull_rn(p * kMassScale));
       }
     }
     __syncthreads();
     if (tid < 256) {
-      double t = 0.0;
+      unsigned long long t = 0ull;
       for (int k = 0; k < kSampleHists; ++k) t += mass[k][tid];
-      part[tid] = t;
+      tot[tid] = t;
     }
     __syncthreads();
     if (tid == 0 && !sh_keep_all) {
-      double run = sh_below;
+      unsigned long long run = sh_below;
       int b = -1;
       for (int k = 0; k < 256; ++k) {
-        if (run + part[k] >= double(tau)) { b = k; break; }
-        run += part[k];
+        if (run + tot[k] >= tau_fixed) { b = k; break; }
+        run += tot[k];
       }
-      if (b < 0) {
-        if (shift == 24) sh_keep_all = 1;        // the whole row has less mass than tau: nothing is cut
-        else { b = 255; run = sh_below; for (int k = 0; k < 255; ++k) run += part[k]; }
-      }
+      if (b < 0) sh_keep_all = 1;                // the whole row has less mass than tau: nothing is cut
       if (b >= 0) { sh_prefix = prefix | (unsigned(b) << shift); sh_below = run; }
     }
     known |= 255u << shift;
@@ -151,25 +154,42 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
   }
   part[tid] = mine;
   __syncthreads();
-  if (tid == 0) {
-    double total = 0.0;
-    for (int k = 0; k < kSampleThreads; ++k) total += part[k];
+  if (warp == 0) {
+    // lane l owns the partial sums of chunks [32 l, 32 l + 32): scan across lanes, then inside one lane
+    const int lane = tid;
+    double loc = 0.0;
+    for (int k = 0; k < 32; ++k) loc += part[lane * 32 + k];
+    double inc = loc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const double t = __shfl_up_sync(0xffffffffu, inc, o);
+      if (lane >= o) inc += t;
+    }
+    const double total = __shfl_sync(0xffffffffu, inc, 31);
     const int step = (hist && hist_count) ? *hist_count : 0;
     const double target = double(u[row_id + size_t(gridDim.x) * step]) * total;
-    double run = 0.0;
-    int c = -1, last = 0;
-    for (int k = 0; k < kSampleThreads; ++k) {
-      if (part[k] > 0.0) {
-        last = k;
-        if (run + part[k] >= target) { c = k; break; }
+    const unsigned hit = __ballot_sync(0xffffffffu, loc > 0.0 && inc >= target);
+    const unsigned nonzero = __ballot_sync(0xffffffffu, loc > 0.0);
+    // rounding can leave the target past the end: then the last lane that holds any mass
+    const int owner = hit ? __ffs(hit) - 1 : (nonzero ? 31 - __clz(nonzero) : 0);
+    if (lane == owner) {
+      double run = inc - loc;
+      int c = -1, last = -1;
+      for (int k = 0; k < 32; ++k) {
+        const double v = part[lane * 32 + k];
+        if (v > 0.0) {
+          last = lane * 32 + k;
+          if (run + v >= target) { c = last; break; }
+        }
+        run += v;
       }
-      run += part[k];
+      if (c < 0) {
+        c = last < 0 ? lane * 32 : last;
+        run = inc - loc;
+        for (int k = lane * 32; k < c; ++k) run += part[k];
+      }
+      sh_chunk = c; sh_target = target; sh_before = run;
     }
-    if (c < 0) {                                  // rounding left the target past the end: last non-empty chunk
-      c = last; run = 0.0;
-      for (int k = 0; k < last; ++k) run += part[k];
-    }
-    sh_chunk = c; sh_target = target; sh_before = run;
   }
   __syncthreads();
   if (tid == sh_chunk) {

@@ -157,3 +157,41 @@ def sample_typical(logits: torch.Tensor, temp: float = 1.0, tau: float = 0.95, u
                                                       probs.data_ptr() if return_probs else None, None, None, 0,
                                                       _stream(x.device)))
     return (out, probs) if return_probs else out
+
+
+_DENSE_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def gemv_dense(w: torch.Tensor, x: torch.Tensor, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Unquantised matrix-vector product ``y[o] = sum_j x[j] * w[o,j]`` for ``w [out,in]`` of bf16,
+    fp16 or fp32 with contiguous rows (a row stride >= in is allowed) and fp32 ``x [in]``:
+    x is rounded to the weights' type, products are summed in fp32, the result is rounded to the
+    weights' type and returned as fp32 - what the reference's TORCH-mode ``matvec`` computes
+    (agnostic/backends/torch.py:162-164)."""
+    if w.dim() != 2 or w.dtype not in _DENSE_DTYPES or w.device.type != "cuda" or w.stride(1) != 1:
+        raise ValueError("gemv_dense needs a CUDA [out,in] matrix of bf16/fp16/fp32 with contiguous rows")
+    n_out, k_in = w.shape
+    if x.dtype != torch.float32 or x.device != w.device or x.numel() != k_in or not x.is_contiguous():
+        raise ValueError(f"x must be a contiguous fp32 vector of {k_in} values on the weights' device")
+    if y is None:
+        y = torch.empty(n_out, dtype=torch.float32, device=w.device)
+    elif y.dtype != torch.float32 or y.device != w.device or y.numel() != n_out or not y.is_contiguous():
+        raise ValueError(f"y must be a contiguous fp32 vector of {n_out} values on the weights' device")
+    with torch.cuda.device(w.device):
+        _lib.check(_lib.lib().b200rwkv_gemv_dense(w.data_ptr(), _DENSE_DTYPES[w.dtype], k_in, n_out, w.stride(0),
+                                                  x.data_ptr(), y.data_ptr(), _stream(w.device)))
+    return y
+
+
+def matvec(W: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """The reference's TORCH-mode op table entry ``matvec(W, x)`` (agnostic/backends/torch.py:162-164)
+    for one vector: ``W`` is the ``[in,out]`` transposed view the reference's ``initTensor`` makes of
+    the checkpoint's ``[out,in]`` tensor; the result has ``x``'s dtype.  A matrix that is not such a
+    view (its transpose does not have contiguous rows) is refused rather than copied."""
+    if W.dim() != 2 or W.stride(0) != 1:
+        raise ValueError("matvec expects the transposed view of an [out,in] matrix (stride 1 along the input index)")
+    xv = x.reshape(-1)
+    if xv.numel() != W.shape[0]:
+        raise ValueError("matvec handles one vector per call")
+    y = gemv_dense(W.t(), xv.float().contiguous())
+    return y.to(x.dtype).reshape(*x.shape[:-1], W.shape[1])

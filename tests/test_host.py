@@ -46,6 +46,9 @@ def test_bad_arguments_return_codes_not_aborts():
     assert L.b200rwkv_sample_typical(1, 1, 8, 8, 0.0, 0.9, 1, 1, None, None, None, 0, None) == _lib.EINVAL   # temp must be > 0
     assert L.b200rwkv_sample_typical(1, 2, 8, 8, 1.0, 0.9, 1, 1, None, 1, 1, 4, None) == _lib.EINVAL    # history needs rows == 1
     assert b"sample_typical" in L.b200rwkv_last_error()
+    assert L.b200rwkv_gemv_dense(None, 1, 8, 8, 8, None, None, None) == _lib.EINVAL
+    assert L.b200rwkv_gemv_dense(1, 7, 8, 8, 8, 1, 1, None) == _lib.EINVAL          # unknown dtype
+    assert L.b200rwkv_gemv_dense(1, 1, 8, 8, 4, 1, 1, None) == _lib.EINVAL          # row stride below k_in
     assert L.b200rwkv_gemm_workspace_bytes(4096, 3, 100) > 3 * 3 * 112 * 4096   # digit rows padded to 16
     assert L.b200rwkv_gemm_workspace_bytes(4096, 4, 100) == 0 and L.b200rwkv_rows_workspace_bytes(None, 1, 1) == 0
     with pytest.raises(_lib.B200RWKVError):

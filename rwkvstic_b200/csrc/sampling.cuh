@@ -22,20 +22,30 @@
 namespace b200 {
 
 constexpr int kSampleThreads = 1024;
-constexpr int kSampleHists = 16;   // mass histograms per CTA; two warps share one
+constexpr int kSampleHists = 16;   // mass histograms per CTA: lane l adds into histogram l % 16, so the
+                                   // lanes of a warp that meet in one bin hit 16 addresses in 16 banks
+constexpr int kSampleHistStride = 257;   // odd stride: equal bins of different histograms in different banks
 constexpr float kMassScale = 17592186044416.0f;   // 2^44
 
 struct TypicalRow {
   float mx;       // largest logit
   float inv_z;    // 1 / sum exp(l - mx)
-  float ent;      // entropy in nats, fp32 like the reference's nansum
+  float log_z;    // log of that sum
+  float ent;      // entropy in nats
 };
 
+// The surprise -log p of a logit is log_z - (l - mx): one subtraction instead of a logarithm of an
+// exponential (and exact where the reference's fp32 -log(softmax) carries the rounding of p).
+__device__ __forceinline__ float typical_shift(float l, const TypicalRow& r) {
+  return fabsf((r.log_z - (l - r.mx)) - r.ent);
+}
+__device__ __forceinline__ float typical_prob(float l, const TypicalRow& r) {
+  return expf(l - r.mx) * r.inv_z;
+}
 // p and s of one logit; identical code in every pass.
 __device__ __forceinline__ void typical_eval(float l, const TypicalRow& r, float& p, float& s) {
-  p = expf(l - r.mx) * r.inv_z;
-  const float nl = -logf(p);            // +inf when p underflowed to 0, like the reference
-  s = fabsf(nl - r.ent);
+  p = typical_prob(l, r);
+  s = typical_shift(l, r);
 }
 
 __device__ __forceinline__ double block_sum_f64(double v, double* red) {
@@ -70,7 +80,7 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
                       const float* __restrict__ u, long long* __restrict__ out, float* __restrict__ probs_out,
                       long long* __restrict__ hist, int* __restrict__ hist_count, int hist_cap) {
   __shared__ double red[kSampleThreads / 32];
-  __shared__ unsigned long long mass[kSampleHists][256];
+  __shared__ unsigned long long mass[kSampleHists][kSampleHistStride];
   __shared__ unsigned long long tot[256];
   __shared__ double part[kSampleThreads];
   __shared__ unsigned int sh_prefix;
@@ -84,35 +94,40 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
 
   // ---- softmax statistics and entropy
   float mx = -INFINITY;
-  for (int i = tid; i < n; i += kSampleThreads) mx = fmaxf(mx, __ldcg(row + i));
+  for (int i = tid; i < n; i += kSampleThreads) mx = fmaxf(mx, __ldg(row + i));
   TypicalRow r;
   r.mx = block_max_f32(mx, red);
-  double z = 0.0;
-  for (int i = tid; i < n; i += kSampleThreads) z += double(expf(__ldcg(row + i) - r.mx));
-  r.inv_z = float(1.0 / block_sum_f64(z, red));
-  r.ent = 0.f;
-  double e = 0.0;
+  // one pass for both sums: Z = sum e^d and sum d e^d (d = l - mx), entropy = log Z - (sum d e^d) / Z
+  double z = 0.0, dz = 0.0;
   for (int i = tid; i < n; i += kSampleThreads) {
-    const float p = expf(__ldcg(row + i) - r.mx) * r.inv_z;
-    if (p > 0.f) e += double(-logf(p) * p);
+    const float d = __ldg(row + i) - r.mx;
+    const float e = expf(d);
+    z += double(e);
+    if (e > 0.f) dz += double(d * e);
   }
-  r.ent = float(block_sum_f64(e, red));
+  z = block_sum_f64(z, red);
+  dz = block_sum_f64(dz, red);
+  r.inv_z = float(1.0 / z);
+  r.log_z = float(log(z));
+  r.ent = float(log(z) - dz / z);
 
   // ---- threshold: smallest s whose cumulative mass (in order of s) reaches tau
   if (tid == 0) { sh_prefix = 0u; sh_below = 0ull; sh_keep_all = 0; }
   const unsigned long long tau_fixed = __double2ull_ru(double(tau) * double(kMassScale));
   unsigned int known = 0u;                       // mask of the bits of the threshold fixed so far
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = tid; i < kSampleHists * 256; i += kSampleThreads) (&mass[0][0])[i] = 0ull;
+    for (int i = tid; i < kSampleHists * kSampleHistStride; i += kSampleThreads) (&mass[0][0])[i] = 0ull;
     __syncthreads();
     const unsigned int prefix = sh_prefix;
     if (!sh_keep_all) {
-      unsigned long long* h = mass[warp & (kSampleHists - 1)];
+      unsigned long long* h = mass[tid & (kSampleHists - 1)];
       for (int i = tid; i < n; i += kSampleThreads) {
-        float p, s;
-        typical_eval(__ldcg(row + i), r, p, s);
-        const unsigned int key = __float_as_uint(s);
-        if (p > 0.f && (key & known) == prefix) atomicAdd(&h[(key >> shift) & 255u], __float2ull_rn(p * kMassScale));
+        const float l = __ldg(row + i);
+        const unsigned int key = __float_as_uint(typical_shift(l, r));
+        if ((key & known) == prefix) {           // the exponential only for logits still in the running
+          const float p = typical_prob(l, r);
+          if (p > 0.f) atomicAdd(&h[(key >> shift) & 255u], __float2ull_rn(p * kMassScale));
+        }
       }
     }
     __syncthreads();
@@ -146,7 +161,7 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
   double mine = 0.0;
   for (int i = i0; i < i1; ++i) {
     float p, s;
-    typical_eval(__ldcg(row + i), r, p, s);
+    typical_eval(__ldg(row + i), r, p, s);
     float q = (keep_all || s <= thresh) ? p : 0.f;
     if (tempered && q > 0.f) q = powf(q, inv_temp);
     if (probs_out) probs_out[size_t(row_id) * n + i] = q;
@@ -197,7 +212,7 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
     long long pick = -1, last = -1;
     for (int i = i0; i < i1; ++i) {
       float p, s;
-      typical_eval(__ldcg(row + i), r, p, s);
+      typical_eval(__ldg(row + i), r, p, s);
       float q = (keep_all || s <= thresh) ? p : 0.f;
       if (tempered && q > 0.f) q = powf(q, inv_temp);
       if (q > 0.f) {

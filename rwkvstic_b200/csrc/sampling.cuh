@@ -8,9 +8,10 @@
 // The sort only serves to find one threshold: the smallest value t among the s_i for which the
 // mass of {i : s_i <= t} reaches tau.  Here that threshold is found by a radix select over the
 // bit pattern of s (s >= 0, so float order is unsigned-integer order) weighted by p: four passes
-// of 256-bin mass histograms, each fixing one byte of t.  Masses are 64-bit fixed point (p * 2^44:
-// integer atomics in shared memory are native and their sums do not depend on arrival order; a
-// whole row loses at most V * 2^-44 of mass to truncation, far below fp32 resolution).  The draw
+// of 256-bin mass histograms, each fixing one byte of t.  Masses are fixed point (p * 2^31 rounded to
+// nearest, 32-bit shared-memory atomics, which are native; 64-bit totals): integer sums do not
+// depend on arrival order, so every pass and every run sees the same totals, and the rounding
+// (2.3e-10 per token) stays below what the reference's fp32 running sum resolves.  The draw
 // is an inverse-CDF walk in index order with a uniform number the caller supplies, so a run is
 // reproducible from its seed.
 // The row (V floats, 200 KB at V = 50277) stays in L2; every pass recomputes p and s from the
@@ -25,7 +26,7 @@ constexpr int kSampleThreads = 1024;
 constexpr int kSampleHists = 16;   // mass histograms per CTA: lane l adds into histogram l % 16, so the
                                    // lanes of a warp that meet in one bin hit 16 addresses in 16 banks
 constexpr int kSampleHistStride = 257;   // odd stride: equal bins of different histograms in different banks
-constexpr float kMassScale = 17592186044416.0f;   // 2^44
+constexpr float kMassScale = 2147483648.0f;   // 2^31
 
 struct TypicalRow {
   float mx;       // largest logit
@@ -46,6 +47,36 @@ __device__ __forceinline__ float typical_prob(float l, const TypicalRow& r) {
 __device__ __forceinline__ void typical_eval(float l, const TypicalRow& r, float& p, float& s) {
   p = typical_prob(l, r);
   s = typical_shift(l, r);
+}
+
+// The passes are bound by load latency (one CTA, a row that does not fit L1), so every loop
+// fetches eight logits before it touches the first: f(index, logit) in increasing index order.
+template <typename F>
+__device__ __forceinline__ void for_each_strided(const float* __restrict__ row, int n, F&& f) {
+  for (int base = threadIdx.x; base < n; base += 8 * kSampleThreads) {
+    float l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = base + j * kSampleThreads;
+      l[j] = i < n ? __ldg(row + i) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = base + j * kSampleThreads;
+      if (i < n) f(i, l[j]);
+    }
+  }
+}
+template <typename F>
+__device__ __forceinline__ void for_each_in_range(const float* __restrict__ row, int i0, int i1, F&& f) {
+  for (int base = i0; base < i1; base += 8) {
+    float l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) l[j] = base + j < i1 ? __ldg(row + base + j) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (base + j < i1) f(base + j, l[j]);
+  }
 }
 
 __device__ __forceinline__ double block_sum_f64(double v, double* red) {
@@ -80,7 +111,7 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
                       const float* __restrict__ u, long long* __restrict__ out, float* __restrict__ probs_out,
                       long long* __restrict__ hist, int* __restrict__ hist_count, int hist_cap) {
   __shared__ double red[kSampleThreads / 32];
-  __shared__ unsigned long long mass[kSampleHists][kSampleHistStride];
+  __shared__ unsigned int mass[kSampleHists][kSampleHistStride];
   __shared__ unsigned long long tot[256];
   __shared__ double part[kSampleThreads];
   __shared__ unsigned int sh_prefix;
@@ -94,17 +125,17 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
 
   // ---- softmax statistics and entropy
   float mx = -INFINITY;
-  for (int i = tid; i < n; i += kSampleThreads) mx = fmaxf(mx, __ldg(row + i));
+  for_each_strided(row, n, [&](int, float l) { mx = fmaxf(mx, l); });
   TypicalRow r;
   r.mx = block_max_f32(mx, red);
   // one pass for both sums: Z = sum e^d and sum d e^d (d = l - mx), entropy = log Z - (sum d e^d) / Z
   double z = 0.0, dz = 0.0;
-  for (int i = tid; i < n; i += kSampleThreads) {
-    const float d = __ldg(row + i) - r.mx;
+  for_each_strided(row, n, [&](int, float l) {
+    const float d = l - r.mx;
     const float e = expf(d);
     z += double(e);
     if (e > 0.f) dz += double(d * e);
-  }
+  });
   z = block_sum_f64(z, red);
   dz = block_sum_f64(dz, red);
   r.inv_z = float(1.0 / z);
@@ -116,19 +147,18 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
   const unsigned long long tau_fixed = __double2ull_ru(double(tau) * double(kMassScale));
   unsigned int known = 0u;                       // mask of the bits of the threshold fixed so far
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = tid; i < kSampleHists * kSampleHistStride; i += kSampleThreads) (&mass[0][0])[i] = 0ull;
+    for (int i = tid; i < kSampleHists * kSampleHistStride; i += kSampleThreads) (&mass[0][0])[i] = 0u;
     __syncthreads();
     const unsigned int prefix = sh_prefix;
     if (!sh_keep_all) {
-      unsigned long long* h = mass[tid & (kSampleHists - 1)];
-      for (int i = tid; i < n; i += kSampleThreads) {
-        const float l = __ldg(row + i);
+      unsigned int* h = mass[tid & (kSampleHists - 1)];
+      for_each_strided(row, n, [&](int, float l) {
         const unsigned int key = __float_as_uint(typical_shift(l, r));
         if ((key & known) == prefix) {           // the exponential only for logits still in the running
           const float p = typical_prob(l, r);
-          if (p > 0.f) atomicAdd(&h[(key >> shift) & 255u], __float2ull_rn(p * kMassScale));
+          if (p > 0.f) atomicAdd(&h[(key >> shift) & 255u], __float2uint_rn(p * kMassScale));
         }
-      }
+      });
     }
     __syncthreads();
     if (tid < 256) {
@@ -159,14 +189,14 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
   const int chunk = (n + kSampleThreads - 1) / kSampleThreads;
   const int i0 = tid * chunk, i1 = min(n, i0 + chunk);
   double mine = 0.0;
-  for (int i = i0; i < i1; ++i) {
+  for_each_in_range(row, i0, i1, [&](int i, float l) {
     float p, s;
-    typical_eval(__ldg(row + i), r, p, s);
+    typical_eval(l, r, p, s);
     float q = (keep_all || s <= thresh) ? p : 0.f;
     if (tempered && q > 0.f) q = powf(q, inv_temp);
     if (probs_out) probs_out[size_t(row_id) * n + i] = q;
     mine += double(q);
-  }
+  });
   part[tid] = mine;
   __syncthreads();
   if (warp == 0) {
@@ -210,17 +240,18 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
   if (tid == sh_chunk) {
     double run = sh_before;
     long long pick = -1, last = -1;
-    for (int i = i0; i < i1; ++i) {
+    for_each_in_range(row, i0, i1, [&](int i, float l) {
+      if (pick >= 0) return;
       float p, s;
-      typical_eval(__ldg(row + i), r, p, s);
+      typical_eval(l, r, p, s);
       float q = (keep_all || s <= thresh) ? p : 0.f;
       if (tempered && q > 0.f) q = powf(q, inv_temp);
       if (q > 0.f) {
         last = i;
         run += double(q);
-        if (run >= sh_target) { pick = i; break; }
+        if (run >= sh_target) pick = i;
       }
-    }
+    });
     if (pick < 0) pick = last < 0 ? i0 : last;
     out[row_id] = pick;
     if (hist && hist_count && row_id == 0) {

@@ -1217,17 +1217,24 @@ int b200rwkv_gemv_dense(const void* w, int dtype, int k_in, int n_out, int64_t l
   P.w = w; P.x = x; P.y = y; P.ldw = ldw; P.K = k_in; P.N = n_out;
   P.vector_ok = reinterpret_cast<uintptr_t>(w) % 16 == 0 && (size_t(ldw) * eb) % 16 == 0 &&
                 reinterpret_cast<uintptr_t>(x) % 16 == 0;
-  // four CTAs fit an SM (56 registers x 256 threads); pairs of rows only when that still fills them
-  const bool pairs = n_out >= device_sms() * 4 * kDenseWarps * 2;
-  const int most = device_sms() * (pairs ? 4 : 8);            // the one-row variant needs 40 registers
-  const int per_cta = kDenseWarps * (pairs ? 2 : 1);
+  // four CTAs fit an SM in the two-row variant (56 registers x 256 threads), eight in the others;
+  // pairs of rows only when that still fills them, shared rows when one warp per row does not
+  const int warps_full = device_sms() * 8 * kDenseWarps;
+  const bool pairs = n_out >= warps_full;
+  // a warp's share of a row should still be one or two passes of eight 16-byte pieces per lane (4 KB each)
+  const size_t row_bytes = size_t(k_in) * eb;
+  const int split = pairs ? 1 : (n_out * 2 <= warps_full && row_bytes >= 32768) ? 4 : (row_bytes >= 8192) ? 2 : 1;
+  const int most = device_sms() * (pairs ? 4 : 8);
+  const int per_cta = pairs ? kDenseWarps * 2 : kDenseWarps / split;
   const int passes = (n_out + per_cta - 1) / per_cta;
   const dim3 grid(passes < most ? passes : most);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define B200_DENSE_LAUNCH(T)                                                            \
   do {                                                                                  \
-    if (pairs) dense_gemv_kernel<T, 2, 4><<<grid, kDenseThreads, 0, st>>>(P);           \
-    else dense_gemv_kernel<T, 1, 8><<<grid, kDenseThreads, 0, st>>>(P);                 \
+    if (pairs) dense_gemv_kernel<T, 2, 4, 1><<<grid, kDenseThreads, 0, st>>>(P);        \
+    else if (split == 4) dense_gemv_kernel<T, 1, 8, 4><<<grid, kDenseThreads, 0, st>>>(P); \
+    else if (split == 2) dense_gemv_kernel<T, 1, 8, 2><<<grid, kDenseThreads, 0, st>>>(P); \
+    else dense_gemv_kernel<T, 1, 8, 1><<<grid, kDenseThreads, 0, st>>>(P);              \
   } while (0)
   if (dtype == B200RWKV_BF16) B200_DENSE_LAUNCH(__nv_bfloat16);
   else if (dtype == B200RWKV_F16) B200_DENSE_LAUNCH(__half);

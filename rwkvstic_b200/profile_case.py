@@ -7,6 +7,10 @@ bytes that are not in L2 while the whole run holds well under 1 GB on the device
 
 With ``--rows R`` (R > 1) the same matrices are applied to R activation rows through the
 tensor-core path instead (row preparation + ``tile_gemm_kernel``): ``ncu -k regex:tile_gemm``.
+
+With ``--dense bf16|fp16|fp32`` the first matrix of the shape is streamed unquantised
+(``dense_gemv_kernel``), and with ``--sampler`` one row of V logits goes through the typical
+sampling kernel (``sample_typical_kernel``).
 """
 from __future__ import annotations
 
@@ -42,6 +46,9 @@ def main():
     ap.add_argument("--network", type=int, default=0, metavar="LAYERS",
                     help="instead of single matrices: a LAYERS-block model of --shape, one forward_rows call of "
                          "--streams x --tokens rows (every kernel of the rows path, for a launch list)")
+    ap.add_argument("--dense", default=None, choices=["bf16", "fp16", "fp32"],
+                    help="stream the first matrix of --matrix unquantised in this type (dense_gemv_kernel)")
+    ap.add_argument("--sampler", action="store_true", help="typical sampling of one row of V logits")
     ap.add_argument("--streams", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
@@ -61,6 +68,39 @@ def main():
         return
     dev = torch.device("cuda", 0)
     _, D = SHAPES[args.shape]
+    if args.sampler:
+        g = torch.Generator(device=dev).manual_seed(2)
+        logits = torch.randn(VOCAB, generator=g, device=dev) * 4.0
+        u = torch.rand(args.launches, generator=g, device=dev)
+        times = []
+        for i in range(args.launches):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ops.sample_typical(logits, 1.0, 0.95, u=u[i:i + 1])
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3)
+        print(f"typical sampling of {VOCAB} logits, event time per launch (us): " + " ".join(f"{t:.1f}" for t in times))
+        return
+    if args.dense:
+        dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dense]
+        F = 4 * D
+        n, k = {"att_kvr": (D, D), "att_out": (D, D), "ffn_kr": (F, D), "ffn_value": (D, F), "head": (VOCAB, D)}[args.matrix]
+        g = torch.Generator(device=dev).manual_seed(1)
+        ws = [(torch.randn(n, k, generator=g, device=dev) * 0.02).to(dt) for _ in range(args.copies)]
+        x, y = torch.randn(k, generator=g, device=dev), torch.empty(n, device=dev)
+        times = []
+        for i in range(args.launches):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ops.gemv_dense(ws[i % len(ws)], x, y)
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3)
+        nb = n * k * ws[0].element_size()
+        print(f"dense {args.dense} [{n},{k}]: {nb / 1e6:.1f} MB of weights per launch, event time per launch (us): "
+              + " ".join(f"{t:.1f}" for t in times))
+        return
     sets = matrices(args.matrix, D, dev, args.copies)
     R = args.rows
     if R > 1:

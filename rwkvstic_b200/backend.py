@@ -70,14 +70,13 @@ def make_ops_class(base_module, model_factory: Optional[Callable] = None, device
                 return new
 
             self.postProcessModule = post
-            from rwkvstic.agnostic.samplers.typical import typical
-
             def sample(logits, temp=1.0, tau=0.95, **kw):
                 # logits that are still on the GPU are sampled there (same arithmetic, 8 bytes come
                 # back instead of the whole vector); anything else goes to the reference's sampler
                 if torch.is_tensor(logits) and logits.device.type == "cuda":
                     from . import ops
                     return int(ops.sample_typical(logits.float().contiguous(), temp, tau)[0])
+                from rwkvstic.agnostic.samplers.typical import typical
                 return typical(logits, temp, tau, **kw)
 
             self.sample = sample

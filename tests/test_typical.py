@@ -125,3 +125,20 @@ def test_generate_typical_is_reproducible_and_low_temperature_tau_follows_greedy
 def ops_sample(logits, temp, tau, u):
     from rwkvstic_b200 import ops
     return ops.sample_typical(logits.to(DEV).float().contiguous(), temp, tau, u=u)[0]
+
+
+@pytest.mark.gpu
+def test_backend_sample_hook_samples_gpu_logits_on_the_device():
+    """The ops object registered in the reference's backend table carries ``sample``; what
+    ``RWKVMaster.sample`` passes it (logits, temp, top_p_usual) must give a kept token."""
+    from rwkvstic_b200.backend import make_ops_class
+
+    class Base:                                    # stands in for agnostic.backends.base.module
+        def __init__(self, layers, embed, *a, **k):
+            pass
+
+    ops_obj = make_ops_class(Base)(2, 128)
+    x = case_logits(50277, 5, 3.0)
+    want = TO.typical_weights(x, 1.0, 0.8) > 0
+    seen = {ops_obj.sample(torch.from_numpy(x).to(DEV), 1.0, 0.8) for _ in range(16)}
+    assert all(isinstance(t, int) and want[t] for t in seen) and len(seen) > 1

@@ -1231,7 +1231,7 @@ int b200rwkv_gemv_dense(const void* w, int dtype, int k_in, int n_out, int64_t l
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define B200_DENSE_LAUNCH(T)                                                            \
   do {                                                                                  \
-    if (pairs) dense_gemv_kernel<T, 2, 4, 1><<<grid, kDenseThreads, 0, st>>>(P);        \
+    if (pairs) dense_gemv_kernel<T, 2, 8, 1><<<grid, kDenseThreads, 0, st>>>(P);        \
     else if (split == 4) dense_gemv_kernel<T, 1, 8, 4><<<grid, kDenseThreads, 0, st>>>(P); \
     else if (split == 2) dense_gemv_kernel<T, 1, 8, 2><<<grid, kDenseThreads, 0, st>>>(P); \
     else dense_gemv_kernel<T, 1, 8, 1><<<grid, kDenseThreads, 0, st>>>(P);              \

@@ -22,7 +22,7 @@ namespace b200 {
 constexpr int kDenseWarps = 8;
 constexpr int kDenseThreads = kDenseWarps * 32;
 // Template arguments: output rows per warp pass, 16-byte pieces of each row in flight per lane,
-// warps that share one row's K.  (2, 4, 1) when there are rows enough to keep every SM's warps busy
+// warps that share one row's K.  (2, 8, 1) when there are rows enough to keep every SM's warps busy
 // that way, (1, 8, 1) for fewer rows, (1, 8, 2 or 4) when even one warp per row leaves SMs short.
 
 template <typename T> struct DenseType;

@@ -167,15 +167,39 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
       tot[tid] = t;
     }
     __syncthreads();
-    if (tid == 0 && !sh_keep_all) {
-      unsigned long long run = sh_below;
-      int b = -1;
-      for (int k = 0; k < 256; ++k) {
-        if (run + tot[k] >= tau_fixed) { b = k; break; }
-        run += tot[k];
+    if (warp == 0) {
+      // lane l owns bins [8 l, 8 l + 8): running totals across the lanes, then inside one lane
+      const int lane = tid;
+      const int keep_all_now = sh_keep_all;
+      const unsigned long long below = sh_below;
+      unsigned long long loc[8], sum = 0ull;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { loc[k] = tot[lane * 8 + k]; sum += loc[k]; }
+      unsigned long long inc = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
       }
-      if (b < 0) sh_keep_all = 1;                // the whole row has less mass than tau: nothing is cut
-      if (b >= 0) { sh_prefix = prefix | (unsigned(b) << shift); sh_below = run; }
+      const unsigned long long before = below + inc - sum;
+      const unsigned hit = __ballot_sync(0xffffffffu, before + sum >= tau_fixed);
+      if (!keep_all_now) {
+        if (hit == 0u) {
+          if (lane == 0) sh_keep_all = 1;        // the whole row has less mass than tau: nothing is cut
+        } else if (lane == __ffs(hit) - 1) {
+          unsigned long long run = before;
+          int b = -1;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            if (b < 0) {
+              if (run + loc[k] >= tau_fixed) b = k;
+              else run += loc[k];
+            }
+          }
+          sh_prefix = prefix | (unsigned(lane * 8 + b) << shift);
+          sh_below = run;
+        }
+      }
     }
     known |= 255u << shift;
     __syncthreads();

@@ -29,7 +29,7 @@ extern "C" {
 /* Bits a kernel may set in the caller's device status word (an int the caller zeroes). */
 #define B200RWKV_STATUS_WAIT_FULL 1    /* consumer gave up waiting for a weight stage   */
 #define B200RWKV_STATUS_WAIT_EMPTY 2   /* producer gave up waiting for a free ring slot */
-#define B200RWKV_STATUS_WAIT_PEER 4    /* layer-split handoff flag never arrived        */
+#define B200RWKV_STATUS_WAIT_PEER 4    /* a CTA of the persistent decode step gave up at a grid barrier */
 
 /*
  * One quantised matrix, used as y = x @ W with W[k_in, n_out].  Bytes are stored
@@ -184,6 +184,39 @@ int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* s
  */
 int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
                                 void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream);
+
+/*
+ * The decode step as ONE persistent kernel (same contract as b200rwkv_decode_step: the fused
+ * replacement for myRWKV.forward, opt.py:61-76, with Block.forward, modules/block.py:56-102, at
+ * T == 1).  One CTA per SM stays resident for the whole step; its weight ring runs on from matrix
+ * to matrix and the CTAs meet at grid barriers (six per block) instead of at kernel boundaries.
+ * The step needs a "plan": a caller-owned device buffer that holds the table of matrices (with
+ * their TMA descriptors), the exchange vectors, the publication lines and the status word.
+ *
+ * b200rwkv_step_plan_bytes   size of the plan buffer for this model
+ * b200rwkv_step_plan_init    fills it (synchronous: one cudaMemset and two cudaMemcpy; call it once,
+ *                            outside any stream capture, with the device current; 256-byte aligned).
+ *                            The model needs emb/ln0; ln_out/head only if logits will be asked for.
+ * b200rwkv_decode_step_persistent
+ *   token, state, logits  as b200rwkv_decode_step (logits NULL skips ln_out + head)
+ *   tuning   NULL, or int32[4] = {weight stages a CTA may have in flight (0: the whole ring), the same
+ *            while its consumers are between two matrices (0: the whole ring), bytes per CTA requested
+ *            from L2 beyond the ring (-1: default), limit of every device-side wait in ms (0: 1000)}
+ *   trace    NULL, or device u64 [4*n_layer + 1][grid][8] of %globaltimer stamps per launch and CTA:
+ *            0 barrier in front of the matrix passed, 1 digit planes built, 2 rows summed, 3 epilogue
+ *            done, 4 layer-norm statistics barrier passed, 5 normalised slice published
+ *   One memset node and one cooperative kernel launch; allocation-free; safe to capture in a CUDA
+ *   graph.  Steps that share a plan must be ordered on one stream.  After B200RWKV_STATUS_* bits
+ *   appear in the status word (first int of the plan) the state is undefined.
+ * b200rwkv_step_geometry  host-only: out[0..7] = {grid, ring_stages, slot_bytes, shared_memory_bytes,
+ *   row_sum_offset, plane_offset, ring_offset, threads} for a GPU with num_sms SMs.
+ * No counterpart in the reference (it launches ~45 kernels per block and token).
+ */
+size_t b200rwkv_step_plan_bytes(const b200rwkv_model* m);
+int b200rwkv_step_plan_init(const b200rwkv_model* m, void* plan, size_t plan_bytes);
+int b200rwkv_decode_step_persistent(const b200rwkv_model* m, void* plan, size_t plan_bytes, const int64_t* token,
+                                    float* state, float* logits, const int32_t* tuning, uint64_t* trace, void* stream);
+int b200rwkv_step_geometry(const b200rwkv_model* m, int num_sms, int64_t* out);
 
 /* Bytes of device scratch b200rwkv_gemm_u8 needs (digit rows: 3 bytes per input per row, rows
  * rounded up to 16; plus 32 bytes per row and matrix). */

@@ -22,6 +22,7 @@ EXPORTS = (
     "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step", "b200rwkv_decode_step_traced",
     "b200rwkv_gemm_workspace_bytes", "b200rwkv_gemm_u8", "b200rwkv_rows_workspace_bytes", "b200rwkv_forward_rows", "b200rwkv_forward_rows_stage", "b200rwkv_argmax",
     "b200rwkv_sample_typical", "b200rwkv_gemv_dense",
+    "b200rwkv_step_plan_bytes", "b200rwkv_step_plan_init", "b200rwkv_decode_step_persistent", "b200rwkv_step_geometry",
 )
 
 
@@ -87,6 +88,15 @@ def lib() -> C.CDLL:
     L.b200rwkv_decode_step_traced.restype = C.c_int
     L.b200rwkv_decode_step_traced.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_size_t, C.c_void_p, C.c_void_p]
+    L.b200rwkv_step_plan_bytes.restype = C.c_size_t
+    L.b200rwkv_step_plan_bytes.argtypes = [C.POINTER(Model)]
+    L.b200rwkv_step_plan_init.restype = C.c_int
+    L.b200rwkv_step_plan_init.argtypes = [C.POINTER(Model), C.c_void_p, C.c_size_t]
+    L.b200rwkv_decode_step_persistent.restype = C.c_int
+    L.b200rwkv_decode_step_persistent.argtypes = [C.POINTER(Model), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p,
+                                                  C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p]
+    L.b200rwkv_step_geometry.restype = C.c_int
+    L.b200rwkv_step_geometry.argtypes = [C.POINTER(Model), C.c_int, C.POINTER(C.c_int64)]
     L.b200rwkv_gemm_workspace_bytes.restype = C.c_size_t
     L.b200rwkv_gemm_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
     L.b200rwkv_gemm_u8.restype = C.c_int

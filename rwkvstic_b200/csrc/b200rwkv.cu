@@ -3,11 +3,13 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <vector>
 
 #include "stream_gemv.cuh"
 #include "tile_gemm.cuh"
 #include "sampling.cuh"
 #include "dense_gemv.cuh"
+#include "decode_step.cuh"
 
 namespace b200 {
 
@@ -382,10 +384,14 @@ wkv_rows_kernel(int B, int T, int C, const float* __restrict__ w, const float* _
 constexpr int kWkvChunk = 64;
 
 // Pass 1: thread (stream, chunk j, channel) runs chunk j from the EMPTY state and stores the
-// resulting local state (no outputs); the last chunk is not needed.
+// resulting local state (no outputs); the last chunk is not needed.  The thread of chunk 0 also
+// copies the stream's state into the scratch (behind the local states): pass 2 reads that snapshot,
+// because its last-chunk thread overwrites the state while the other chunks' threads may not have
+// started yet.
 __global__ void __launch_bounds__(128)
 wkv_chunk_state_kernel(int B, int T, int C, int NC, const float* __restrict__ w, const float* __restrict__ k,
-                       const float* __restrict__ v, float* __restrict__ loc) {
+                       const float* __restrict__ v, float* __restrict__ loc, const float* __restrict__ aa,
+                       const float* __restrict__ bb, const float* __restrict__ pp, long long state_stride) {
   griddep_launch_dependents();
   griddep_wait();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -409,6 +415,11 @@ wkv_chunk_state_kernel(int B, int T, int C, int NC, const float* __restrict__ w,
   }
   float* o = loc + (size_t(s) * (NC - 1) + j) * 3 * C + c;
   o[0] = a; o[size_t(C)] = q; o[2 * size_t(C)] = p;
+  if (j == 0) {
+    const size_t so = size_t(s) * state_stride + c;
+    float* snap = loc + (size_t(B) * (NC - 1) + s) * 3 * C + c;
+    snap[0] = aa[so]; snap[size_t(C)] = bb[so]; snap[2 * size_t(C)] = pp[so];
+  }
 }
 
 // Pass 2: thread (stream, chunk j, channel) rebuilds the state at the start of chunk j from the
@@ -427,7 +438,8 @@ wkv_chunk_output_kernel(int B, int T, int C, int NC, const float* __restrict__ w
   const int j = int((idx / C) % NC), s = int(idx / ((long long)C * NC));
   const float wv = w[c], uv = u[c];
   const size_t so = size_t(s) * state_stride + c;
-  float a = aa[so], q = bb[so], p = pp[so];
+  const float* snap = loc + (size_t(B) * (NC - 1) + s) * 3 * C + c;   // the state as pass 1 found it
+  float a = __ldcg(snap), q = __ldcg(snap + size_t(C)), p = __ldcg(snap + 2 * size_t(C));
   const float wn = wv * float(kWkvChunk);
   for (int i = 0; i < j; ++i) {
     const float* l = loc + (size_t(s) * (NC - 1) + i) * 3 * C + c;
@@ -660,6 +672,63 @@ argmax_rows_kernel(const float* __restrict__ x, int n, long long ldx, long long*
 constexpr size_t kStaticPlaneBytes = 192 * 1024;   // = 3 matrices x 4 x k_in(16384), or 1 x 4 x 49152
 constexpr size_t kStaticScratchBytes = kStaticPlaneBytes + 256;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+
+// ---- whole decode step as one persistent kernel ------------------------------------------------------
+// Plan buffer (device, caller-owned): [status 256 B][publication lines][xs_att D][xs_ffn F][xs_ln 3D]
+// [matrix table][vector table].
+struct StepLayout {
+  size_t off_pub, pub_bytes, off_xs_att, off_xs_ffn, off_xs_ln, off_mats, off_vecs, bytes;
+  int nlines;
+};
+
+static StepLayout step_layout(const b200rwkv_model* m) {
+  StepLayout o;
+  const size_t D = size_t(m->n_embd), F = size_t(m->n_ffn), L = size_t(m->n_layer);
+  size_t off = 256;
+  o.nlines = kStepLineBase + kStepLinesPerLayer * int(L);
+  o.off_pub = off; o.pub_bytes = align256(size_t(o.nlines) * 128); off += o.pub_bytes;
+  o.off_xs_att = off; off += align256(D * 4);
+  o.off_xs_ffn = off; off += align256(F * 4);
+  o.off_xs_ln = off; off += align256(3 * D * 4);
+  o.off_mats = off; off += align256((7 * L + 1) * sizeof(StepMat));
+  o.off_vecs = off; off += align256(L * sizeof(StepVec));
+  o.bytes = off;
+  return o;
+}
+
+static int check_step_model(const b200rwkv_model* m, const char* who) {
+  if (!m || !m->layers || !m->emb || !m->ln0_w || !m->ln0_b) return fail(B200RWKV_EINVAL, "%s: null model field", who);
+  const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab, L = m->n_layer;
+  if (D <= 0 || (D % 128) != 0 || F <= 0 || (F % 128) != 0 || V <= 0 || L <= 0)
+    return fail(B200RWKV_EINVAL, "%s: n_embd=%d n_ffn=%d must be positive multiples of 128", who, D, F);
+  for (int l = 0; l < L; ++l) {
+    const b200rwkv_layer& ly = m->layers[l];
+    const b200rwkv_matrix* chk[7] = {&ly.att_key, &ly.att_value, &ly.att_receptance, &ly.att_output,
+                                     &ly.ffn_key, &ly.ffn_receptance, &ly.ffn_value};
+    const int want_n[7] = {D, D, D, D, F, D, D}, want_k[7] = {D, D, D, D, D, D, F};
+    for (int i = 0; i < 7; ++i) {
+      if (int rc = check_matrix(*chk[i], who)) return rc;
+      if (chk[i]->n_out != want_n[i] || chk[i]->k_in != want_k[i])
+        return fail(B200RWKV_EINVAL, "%s: layer %d matrix %d is %dx%d, expected %dx%d", who, l, i, chk[i]->n_out, chk[i]->k_in,
+                    want_n[i], want_k[i]);
+    }
+  }
+  if (m->head.qt) {
+    if (int rc = check_matrix(m->head, who)) return rc;
+    if (m->head.n_out != V || m->head.k_in != D || !m->ln_out_w || !m->ln_out_b)
+      return fail(B200RWKV_EINVAL, "%s: head is %dx%d or ln_out missing", who, m->head.n_out, m->head.k_in);
+  }
+  return B200RWKV_OK;
+}
+
+static bool fill_step_mat(StepMat& o, const b200rwkv_matrix& m) {
+  memset(&o, 0, sizeof(o));
+  o.qt = m.qt; o.ry = m.ry; o.my = m.my; o.rx = m.rx; o.mx = m.mx; o.half = m.half;
+  o.N = m.n_out; o.K = m.k_in; o.need_sums = wants_sums(m) ? 1 : 0;
+  step_mat_geometry(m.k_in, &o.kc, &o.nchunks);
+  return encode_weight_map(&o.tmap, m.qt, m.n_out, m.k_in, o.kc);
+}
 
 }  // namespace b200
 
@@ -957,6 +1026,114 @@ int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, f
   return decode_step_impl(m, token, state, logits, workspace, workspace_bytes, reinterpret_cast<unsigned long long*>(trace), stream);
 }
 
+
+// ---- persistent decode step --------------------------------------------------------------------------
+size_t b200rwkv_step_plan_bytes(const b200rwkv_model* m) {
+  if (!m || m->n_embd <= 0 || m->n_ffn <= 0 || m->n_layer <= 0) return 0;
+  return step_layout(m).bytes;
+}
+
+int b200rwkv_step_geometry(const b200rwkv_model* m, int num_sms, int64_t* out) {
+  StepPlan p;
+  if (!m || !out || !plan_step(m->n_embd, m->n_ffn, m->n_vocab, m->head.qt != nullptr, num_sms, &p))
+    return fail(B200RWKV_EINVAL, "step_geometry: unsupported shape");
+  const int64_t v[8] = {p.grid, p.stages, p.slot_bytes, (int64_t)p.smem, p.off_rows, p.off_planes, p.off_ring, kStepThreads};
+  for (int i = 0; i < 8; ++i) out[i] = v[i];
+  return B200RWKV_OK;
+}
+
+int b200rwkv_step_plan_init(const b200rwkv_model* m, void* plan, size_t plan_bytes) {
+  if (int rc = check_step_model(m, "step_plan_init")) return rc;
+  if (!plan || (reinterpret_cast<uintptr_t>(plan) & 255u) != 0) return fail(B200RWKV_EINVAL, "step_plan_init: plan must be 256-byte aligned");
+  const StepLayout lay = step_layout(m);
+  if (plan_bytes < lay.bytes) return fail(B200RWKV_EINVAL, "step_plan_init: plan %zu < %zu bytes", plan_bytes, lay.bytes);
+  StepPlan geo;
+  if (device_sms() <= 0 || !plan_step(m->n_embd, m->n_ffn, m->n_vocab, m->head.qt != nullptr, device_sms(), &geo))
+    return fail(B200RWKV_EINVAL, "step_plan_init: the shape does not fit the step kernel's shared memory");
+  const int L = m->n_layer;
+  std::vector<StepMat> mats(static_cast<size_t>(7 * L + 1));
+  std::vector<StepVec> vecs(static_cast<size_t>(L));
+  memset(mats.data(), 0, mats.size() * sizeof(StepMat));
+  memset(vecs.data(), 0, vecs.size() * sizeof(StepVec));
+  for (int l = 0; l < L; ++l) {
+    const b200rwkv_layer& ly = m->layers[l];
+    const b200rwkv_matrix* ms[7] = {&ly.att_key, &ly.att_value, &ly.att_receptance, &ly.att_output,
+                                    &ly.ffn_key, &ly.ffn_receptance, &ly.ffn_value};
+    for (int i = 0; i < 7; ++i)
+      if (!fill_step_mat(mats[size_t(7) * l + i], *ms[i])) return fail(B200RWKV_ECUDA, "step_plan_init: cuTensorMapEncodeTiled failed");
+    StepVec& v = vecs[l];
+    v.ln1_w = ly.ln1_w; v.ln1_b = ly.ln1_b; v.ln2_w = ly.ln2_w; v.ln2_b = ly.ln2_b;
+    v.mix_k = ly.att_mix_k; v.mix_v = ly.att_mix_v; v.mix_r = ly.att_mix_r; v.fmix_k = ly.ffn_mix_k; v.fmix_r = ly.ffn_mix_r;
+    v.decay = ly.time_decay; v.first = ly.time_first;
+    const float* need[11] = {v.ln1_w, v.ln1_b, v.ln2_w, v.ln2_b, v.mix_k, v.mix_v, v.mix_r, v.fmix_k, v.fmix_r, v.decay, v.first};
+    for (int i = 0; i < 11; ++i)
+      if (!need[i]) return fail(B200RWKV_EINVAL, "step_plan_init: layer %d has a null vector parameter", l);
+  }
+  if (m->head.qt && !fill_step_mat(mats[size_t(7) * L], m->head)) return fail(B200RWKV_ECUDA, "step_plan_init: cuTensorMapEncodeTiled failed");
+  char* base = static_cast<char*>(plan);
+  cudaError_t e = cudaMemset(base, 0, lay.bytes);
+  if (e == cudaSuccess) e = cudaMemcpy(base + lay.off_mats, mats.data(), mats.size() * sizeof(StepMat), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(base + lay.off_vecs, vecs.data(), vecs.size() * sizeof(StepVec), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "step_plan_init: %s", cudaGetErrorString(e));
+  return B200RWKV_OK;
+}
+
+int b200rwkv_decode_step_persistent(const b200rwkv_model* m, void* plan, size_t plan_bytes, const int64_t* token, float* state,
+                                    float* logits, const int32_t* tuning, uint64_t* trace, void* stream) {
+  if (!m || !plan || !token || !state) return fail(B200RWKV_EINVAL, "decode_step_persistent: null argument");
+  if ((reinterpret_cast<uintptr_t>(plan) & 255u) != 0 || !aligned16(state))
+    return fail(B200RWKV_EINVAL, "decode_step_persistent: plan must be 256-byte and state 16-byte aligned");
+  if (logits && !m->head.qt) return fail(B200RWKV_EINVAL, "decode_step_persistent: logits wanted but the model has no head");
+  const StepLayout lay = step_layout(m);
+  if (plan_bytes < lay.bytes) return fail(B200RWKV_EINVAL, "decode_step_persistent: plan %zu < %zu bytes", plan_bytes, lay.bytes);
+  StepPlan geo;
+  if (device_sms() <= 0 || !plan_step(m->n_embd, m->n_ffn, m->n_vocab, m->head.qt != nullptr, device_sms(), &geo))
+    return fail(B200RWKV_EINVAL, "decode_step_persistent: the shape does not fit the step kernel's shared memory");
+  static bool configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "decode_step_persistent: %s", cudaGetErrorString(e));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "decode_step_persistent: %s", cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  char* base = static_cast<char*>(plan);
+  StepParams P;
+  memset(&P, 0, sizeof(P));
+  P.mats = reinterpret_cast<const StepMat*>(base + lay.off_mats);
+  P.vecs = reinterpret_cast<const StepVec*>(base + lay.off_vecs);
+  P.L = m->n_layer; P.D = m->n_embd; P.F = m->n_ffn; P.V = m->n_vocab;
+  P.emb = m->emb; P.ln0_w = m->ln0_w; P.ln0_b = m->ln0_b; P.lnout_w = m->ln_out_w; P.lnout_b = m->ln_out_b;
+  P.token = reinterpret_cast<const long long*>(token); P.state = state; P.logits = logits;
+  P.xs_att = reinterpret_cast<float*>(base + lay.off_xs_att);
+  P.xs_ffn = reinterpret_cast<float*>(base + lay.off_xs_ffn);
+  P.xs_ln = reinterpret_cast<float*>(base + lay.off_xs_ln);
+  P.pub = reinterpret_cast<unsigned char*>(base + lay.off_pub);
+  P.status = reinterpret_cast<int*>(base);
+  P.trace = reinterpret_cast<unsigned long long*>(trace);
+  P.slot_bytes = geo.slot_bytes; P.stages = geo.stages; P.off_own = geo.off_own; P.own_rows = geo.own_rows;
+  P.off_park = geo.off_park; P.park_stride = geo.park_stride;
+  P.off_rows = geo.off_rows; P.off_planes = geo.off_planes; P.off_ring = geo.off_ring;
+  P.window = tuning && tuning[0] > 0 ? tuning[0] : geo.stages;
+  P.window_handoff = tuning && tuning[1] > 0 ? tuning[1] : geo.stages;
+  P.pf_bytes = tuning && tuning[2] >= 0 ? tuning[2] : kStepPrefetchDefault;
+  P.wait_limit_ns = (tuning && tuning[3] > 0 ? (unsigned long long)tuning[3] : 1000ull) * 1000000ull;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  e = cudaMemsetAsync(P.pub, 0, size_t(lay.nlines) * 128, s);
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "decode_step_persistent: memset: %s", cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(geo.grid); cfg.blockDim = dim3(kStepThreads); cfg.dynamicSmemBytes = geo.smem; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;     // all CTAs resident at once, or the launch fails
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, decode_step_kernel, P);
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "decode_step_persistent: launch: %s", cudaGetErrorString(e));
+  return B200RWKV_OK;
+}
+
 size_t b200rwkv_gemm_workspace_bytes(int k_in, int nmat, int rows) {
   if (k_in <= 0 || nmat < 1 || nmat > kMaxSeg || rows < 1) return 0;
   return gemm_workspace_bytes(k_in, nmat, rows);
@@ -1098,7 +1275,8 @@ static int forward_rows_impl(const b200rwkv_model* m, const int64_t* tokens, flo
       const int NC = (T + kWkvChunk - 1) / kWkvChunk;
       const long long n1 = (long long)B * (NC - 1) * D, n2 = (long long)B * NC * D;
       e = launch_chained(wkv_chunk_state_kernel, dim3((unsigned)((n1 + 127) / 128)), dim3(128), 0, s, B, T, D, NC, ly.time_decay,
-                         (const float*)ws.kb, (const float*)ws.vb, ws.wkv_loc);
+                         (const float*)ws.kb, (const float*)ws.vb, ws.wkv_loc, (const float*)(st + 2 * size_t(D)),
+                         (const float*)(st + 3 * size_t(D)), (const float*)(st + 4 * size_t(D)), (long long)state_stride);
       if (e == cudaSuccess)
         e = launch_chained(wkv_chunk_output_kernel, dim3((unsigned)((n2 + 127) / 128)), dim3(128), 0, s, B, T, D, NC, ly.time_decay,
                            ly.time_first, ws.kb, (const float*)ws.vb, (const float*)ws.rb, (const float*)ws.wkv_loc,

@@ -152,7 +152,14 @@ class B200RWKV:
 
     RnnOnly = False  # sequence mode is supported (rwkvMaster.py:97 looks this up)
 
-    def __init__(self, weights: QuantizedWeights, use_graph: bool = True, copy_logits: bool = True):
+    def __init__(self, weights: QuantizedWeights, use_graph: bool = True, copy_logits: bool = True,
+                 decode_mode: str = "persistent"):
+        """``decode_mode``: how one-token steps run.  "persistent" (default): the whole step is one
+        resident kernel whose weight stream runs on from matrix to matrix
+        (b200rwkv_decode_step_persistent); "chained": one streaming launch per matrix group, chained
+        by programmatic dependent launch (b200rwkv_decode_step).  Both compute the same step."""
+        if decode_mode not in ("persistent", "chained"):
+            raise ValueError("decode_mode must be 'persistent' or 'chained'")
         self.w = weights
         self.device = weights.ln0[0].device
         if self.device.type != "cuda":
@@ -161,13 +168,24 @@ class B200RWKV:
         self.n_layer, self.n_embd, self.n_ffn, self.n_vocab = weights.n_layer, weights.n_embd, weights.n_ffn, weights.n_vocab
         self.use_graph = use_graph
         self.copy_logits = copy_logits
-        self.launches_per_step = 8 * self.n_layer + 3
+        if weights.emb is None or weights.head is None:
+            decode_mode = "chained"      # a pipeline stage: only the rows path applies to it
+        self.decode_mode = decode_mode
+        self.launches_per_step = 1 if decode_mode == "persistent" else 8 * self.n_layer + 3
+        self.step_tuning = [0, 0, -1, 0]  # b200rwkv_decode_step_persistent's tuning words (0 / -1: library defaults)
         self.time_decay = [ly.vec["att.time_decay"] for ly in weights.layers]
         self.emptyState = torch.zeros(self.n_layer, 5, self.n_embd, dtype=torch.float32, device=self.device)
         self.emptyState[:, 4] = -1e30
         self._build_descriptor()
         nbytes = int(self._L.b200rwkv_decode_workspace_bytes(C.byref(self._cmodel)))
         self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+        self._plan = None
+        if decode_mode == "persistent":
+            with torch.cuda.device(self.device):
+                nplan = int(self._L.b200rwkv_step_plan_bytes(C.byref(self._cmodel)))
+                self._plan = torch.zeros(nplan, dtype=torch.uint8, device=self.device)
+                torch.cuda.synchronize(self.device)
+                _lib.check(self._L.b200rwkv_step_plan_init(C.byref(self._cmodel), self._plan.data_ptr(), nplan))
         self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
         self._tok = torch.zeros(1, dtype=torch.int64, device=self.device)
         self._logits = torch.zeros(self.n_vocab, dtype=torch.float32, device=self.device)
@@ -222,12 +240,17 @@ class B200RWKV:
     # ------------------------------------------------------------------ one decode step
     def _step_raw(self, tok_ptr: int, state_ptr: int, logits_ptr: Optional[int]) -> None:
         stream = torch.cuda.current_stream(self.device).cuda_stream
+        if self._plan is not None:
+            tuning = (C.c_int32 * 4)(*[int(v) for v in self.step_tuning])
+            _lib.check(self._L.b200rwkv_decode_step_persistent(C.byref(self._cmodel), self._plan.data_ptr(), self._plan.numel(),
+                                                               tok_ptr, state_ptr, logits_ptr, tuning, None, stream))
+            return
         _lib.check(self._L.b200rwkv_decode_step(C.byref(self._cmodel), tok_ptr, state_ptr, logits_ptr,
                                                 self._ws.data_ptr(), self._ws.numel(), stream))
 
     def _step(self, state: torch.Tensor, want_logits: bool) -> None:
         """Run one step on the token in ``self._tok``; logits (if any) land in ``self._logits``."""
-        self.launch_count += self.launches_per_step - (0 if want_logits else 2)
+        self.launch_count += self.launches_per_step - (0 if want_logits or self._plan is not None else 2)
         lp = self._logits.data_ptr() if want_logits else None
         if not self.use_graph:
             self._step_raw(self._tok.data_ptr(), state.data_ptr(), lp)
@@ -280,12 +303,45 @@ class B200RWKV:
         return trace.cpu()
 
     def check_status(self) -> None:
-        """Raise if any kernel reported an expired device-side wait (synchronises)."""
-        self._status_host.copy_(self._ws[:4].view(torch.int32))
-        bits = int(self._status_host[0])
-        if bits:
-            self._ws[:4].zero_()
-            raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+        """Raise if any kernel reported an expired device-side wait (synchronises).  After that the
+        state the failed step was given is undefined."""
+        for buf in (self._ws, self._plan):
+            if buf is None:
+                continue
+            self._status_host.copy_(buf[:4].view(torch.int32))
+            bits = int(self._status_host[0])
+            if bits:
+                buf[:4].zero_()
+                raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+
+    def trace_persistent_step(self, token: int, state: torch.Tensor, replays: int = 3) -> torch.Tensor:
+        """Profiling: the %globaltimer timeline of one persistent decode step, an int64 CPU tensor
+        ``[4L+1 launches, grid, 8]`` (slots as documented at b200rwkv_decode_step_persistent), taken from
+        the last of ``replays`` replays of a CUDA graph of the traced step."""
+        if self._plan is None:
+            raise RuntimeError("trace_persistent_step needs decode_mode='persistent'")
+        geo = (C.c_int64 * 8)()
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        _lib.check(self._L.b200rwkv_step_geometry(C.byref(self._cmodel), sms, geo))
+        trace = torch.zeros(4 * self.n_layer + 1, int(geo[0]), 8, dtype=torch.int64, device=self.device)
+        self._tok.fill_(int(token))
+        tuning = (C.c_int32 * 4)(*[int(v) for v in self.step_tuning])
+
+        def step():
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            _lib.check(self._L.b200rwkv_decode_step_persistent(C.byref(self._cmodel), self._plan.data_ptr(), self._plan.numel(),
+                                                               self._tok.data_ptr(), state.data_ptr(), self._logits.data_ptr(),
+                                                               tuning, trace.data_ptr(), stream))
+        with torch.cuda.device(self.device):
+            step()
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(g):
+                step()
+            for _ in range(max(1, replays)):
+                g.replay()
+            torch.cuda.synchronize(self.device)
+        return trace.cpu()
 
     # ------------------------------------------------------------------ public interface
     def _own_state(self, state: torch.Tensor) -> torch.Tensor:

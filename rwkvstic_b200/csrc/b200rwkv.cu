@@ -1074,6 +1074,13 @@ int b200rwkv_step_plan_init(const b200rwkv_model* m, void* plan, size_t plan_byt
   cudaError_t e = cudaMemset(base, 0, lay.bytes);
   if (e == cudaSuccess) e = cudaMemcpy(base + lay.off_mats, mats.data(), mats.size() * sizeof(StepMat), cudaMemcpyHostToDevice);
   if (e == cudaSuccess) e = cudaMemcpy(base + lay.off_vecs, vecs.data(), vecs.size() * sizeof(StepVec), cudaMemcpyHostToDevice);
+#ifdef B200_STEP_TMAP_CONST
+  {
+    std::vector<CUtensorMap> tm(mats.size());
+    for (size_t i = 0; i < mats.size(); ++i) tm[i] = mats[i].tmap;
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(c_step_tmaps, tm.data(), tm.size() * sizeof(CUtensorMap));
+  }
+#endif
   if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "step_plan_init: %s", cudaGetErrorString(e));
   return B200RWKV_OK;
 }
@@ -1103,7 +1110,7 @@ int b200rwkv_decode_step_persistent(const b200rwkv_model* m, void* plan, size_t 
   memset(&P, 0, sizeof(P));
   P.mats = reinterpret_cast<const StepMat*>(base + lay.off_mats);
   P.vecs = reinterpret_cast<const StepVec*>(base + lay.off_vecs);
-  P.L = m->n_layer; P.D = m->n_embd; P.F = m->n_ffn; P.V = m->n_vocab;
+  P.L = m->n_layer; P.D = m->n_embd; P.F = m->n_ffn; P.V = m->n_vocab; P.inv_d = 1.0 / double(m->n_embd);
   P.emb = m->emb; P.ln0_w = m->ln0_w; P.ln0_b = m->ln0_b; P.lnout_w = m->ln_out_w; P.lnout_b = m->ln_out_b;
   P.token = reinterpret_cast<const long long*>(token); P.state = state; P.logits = logits;
   P.xs_att = reinterpret_cast<float*>(base + lay.off_xs_att);

@@ -35,7 +35,12 @@
 
 namespace b200 {
 
-constexpr int kStepThreads = kGemvThreads;      // 16 consumer warps + 1 producer warp
+#ifndef B200_STEP_CONSUMER_WARPS
+#define B200_STEP_CONSUMER_WARPS 8
+#endif
+constexpr int kStepConsumerWarps = B200_STEP_CONSUMER_WARPS;   // a multiple of 4; 8 + the producer = 9 warps
+constexpr int kStepConsumers = kStepConsumerWarps * 32;
+constexpr int kStepThreads = kStepConsumers + 32;   // + one producer warp
 constexpr int kStepLineBase = 5;                // publication lines 0 barrier, 1 abort, 2..4 first block's k/v/r
 constexpr int kStepLinesPerLayer = 9;
 constexpr int kStepTraceSlots = 8;              // u64 stamps per (phase, CTA)
@@ -76,6 +81,10 @@ struct __align__(128) StepVec {
 };
 static_assert(sizeof(StepVec) == 128, "StepVec is 128 bytes");
 
+#ifdef B200_STEP_TMAP_CONST
+__constant__ CUtensorMap c_step_tmaps[449];
+#endif
+
 struct StepParams {
   const StepMat* mats;    // [7*L + 1]: per block key, value, receptance, output, ffn key, ffn receptance, ffn value; then the head
   const StepVec* vecs;    // [L]
@@ -98,6 +107,7 @@ struct StepParams {
   int window_handoff;     // the same while the consumers are between two matrices
   int pf_bytes;           // bytes per CTA requested from L2 ahead of the ring
   unsigned long long wait_limit_ns;
+  double inv_d;           // 1 / D
 };
 
 // ---- scoped memory operations ----------------------------------------------------------------------
@@ -171,7 +181,7 @@ __device__ __forceinline__ void square_limbs(float y, long long& hi, long long& 
 }
 
 
-// Sums of NV int64 quantities and maxima of NM floats over the 512 consumer threads.  Afterwards
+// Sums of NV int64 quantities and maxima of NM floats over the consumer threads.  Afterwards
 // thread i < NV holds total i in v[0] and thread 32 + j holds maximum j in m[0].  One named barrier
 // inside; the scratch is free again after the caller's next named barrier.
 template <int NV, int NM>
@@ -189,15 +199,123 @@ __device__ __forceinline__ void cta_reduce(long long (&v)[NV], float (&m)[NM > 0
 #pragma unroll
     for (int i = 0; i < NM; ++i) red_f[warp * 4 + i] = m[i];
   }
-  named_bar_sync(1, kConsumers);
+  named_bar_sync(1, kStepConsumers);
   if (tid < NV) {
     long long a = 0;
-    for (int w = 0; w < kConsumerWarps; ++w) a += red_ll[w * 12 + tid];
+    for (int w = 0; w < kStepConsumerWarps; ++w) a += red_ll[w * 12 + tid];
     v[0] = a;
   } else if (tid >= 32 && tid < 32 + NM) {
     float a = 0.f;
-    for (int w = 0; w < kConsumerWarps; ++w) a = fmaxf(a, red_f[w * 4 + tid - 32]);
+    for (int w = 0; w < kStepConsumerWarps; ++w) a = fmaxf(a, red_f[w * 4 + tid - 32]);
     m[0] = a;
+  }
+}
+
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// A warp's share of one landed stage: NJ blocks of 32 inputs x 16 rows, block j at a_addr + j * (W/4)
+// * 2048 (weights, swizzled stage) and b_addr + j * W * 96 (digit planes).  Four accumulator chains.
+template <int NJ>
+__device__ __forceinline__ void consume_blocks(int (&c)[4][4], uint32_t a_addr, uint32_t b_addr, bool bvalid) {
+  constexpr uint32_t kAStep = uint32_t(kStepConsumerWarps / 4) * 2048u, kBStep = uint32_t(kStepConsumerWarps) * 96u;
+  uint32_t a[NJ][4], b[NJ][2];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+    ldmatrix_x4(a_addr + uint32_t(j) * kAStep, a[j][0], a[j][1], a[j][2], a[j][3]);
+    b[j][0] = 0u; b[j][1] = 0u;
+    if (bvalid) {
+      b[j][0] = lds_u32(b_addr + uint32_t(j) * kBStep);
+      b[j][1] = lds_u32(b_addr + uint32_t(j) * kBStep + 16u);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) mma_u8s8(c[j & 3], a[j][0], a[j][1], a[j][2], a[j][3], b[j][0], b[j][1]);
+}
+
+// kbn blocks of 32 inputs in the stage (a multiple of 4); the unrolled forms cover every count that
+// divides evenly among the warps, the loop the rest.
+__device__ __forceinline__ void consume_stage(int (&c)[4][4], uint32_t a_addr, uint32_t b_addr, bool bvalid, int kbn, int warp) {
+  static_assert(kStepConsumerWarps % 4 == 0, "a warp's blocks must share their position in the swizzle atom");
+  constexpr int W = kStepConsumerWarps;
+  if (kbn == 8 * W) consume_blocks<8>(c, a_addr, b_addr, bvalid);
+  else if (kbn == 4 * W) consume_blocks<4>(c, a_addr, b_addr, bvalid);
+  else if (kbn == 5 * W) consume_blocks<5>(c, a_addr, b_addr, bvalid);
+  else if (kbn == 7 * W) consume_blocks<7>(c, a_addr, b_addr, bvalid);
+  else if (kbn == 6 * W) consume_blocks<6>(c, a_addr, b_addr, bvalid);
+  else if (kbn == 3 * W) consume_blocks<3>(c, a_addr, b_addr, bvalid);
+  else if (kbn == 2 * W) consume_blocks<2>(c, a_addr, b_addr, bvalid);
+  else {
+    constexpr uint32_t kAStep = uint32_t(W / 4) * 2048u, kBStep = uint32_t(W) * 96u;
+    for (int j0 = 0; warp + j0 * W < kbn; j0 += 4) {
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const int j = j0 + jj;
+        if (warp + j * W < kbn) {
+          uint32_t a0, a1, a2, a3, b0 = 0u, b1 = 0u;
+          ldmatrix_x4(a_addr + uint32_t(j) * kAStep, a0, a1, a2, a3);
+          if (bvalid) { b0 = lds_u32(b_addr + uint32_t(j) * kBStep); b1 = lds_u32(b_addr + uint32_t(j) * kBStep + 16u); }
+          mma_u8s8(c[jj], a0, a1, a2, a3, b0, b1);
+        }
+      }
+    }
+  }
+}
+
+// Digit planes of a launch's nseg segments from the exchanged xs vectors (segment s at
+// xs + s * xs_stride, K inputs each) and their publication lines line0 + s; also the segments'
+// scalars.  Called by all consumer threads.  The loads of all segments go out together: one L2
+// round trip.
+__device__ __forceinline__ void build_digit_planes(unsigned char* planes, SegScalars* scal, const unsigned char* pub,
+                                                   const float* xs, size_t xs_stride, int line0, int nseg, int K, int tid) {
+  constexpr int GB = (4096 + kStepConsumers - 1) / kStepConsumers;   // 16384 inputs in one batch
+  const int NG = K / 4, TG = nseg * NG;
+  float4 v[GB];
+#pragma unroll
+  for (int i = 0; i < GB; ++i) {
+    const int f = tid + i * kStepConsumers;
+    if (f < TG) {
+      const int s = f >= 2 * NG ? 2 : (f >= NG ? 1 : 0), g = f - s * NG;
+      v[i] = ld_act_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g);
+    }
+  }
+  float inv[kMaxSeg];
+#pragma unroll
+  for (int s = 0; s < kMaxSeg; ++s) {
+    inv[s] = 0.f;
+    if (s < nseg) inv[s] = __uint_as_float(ld_act_u32(reinterpret_cast<const unsigned*>(pub + size_t(line0 + s) * 128)));   // max |xs|
+  }
+  if (tid < nseg) {
+    const unsigned char* line = pub + size_t(line0 + tid) * 128;
+    const long long zp = ld_act_s64(reinterpret_cast<const long long*>(line + 32));
+    const long long sxs = ld_act_s64(reinterpret_cast<const long long*>(line + 64));
+    const long long sx = ld_act_s64(reinterpret_cast<const long long*>(line + 96));
+    const float amax = __uint_as_float(ld_act_u32(reinterpret_cast<const unsigned*>(line)));
+    SegScalars sc;
+    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, kQMax / amax) : 0.f;
+    sc.zp = __ll2float_rn(zp) * (1.0f / kPubSumScale);
+    sc.sumxs = __ll2float_rn(sxs) * (1.0f / kPubXsScale);
+    sc.sumx = __ll2float_rn(sx) * (1.0f / kPubSumScale);
+    sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
+    scal[tid] = sc;
+  }
+#pragma unroll
+  for (int s = 0; s < kMaxSeg; ++s) inv[s] = inv[s] > 0.f ? kQMax / inv[s] : 0.f;
+#pragma unroll
+  for (int i = 0; i < GB; ++i) {
+    const int f = tid + i * kStepConsumers;
+    if (f < TG) {
+      const int s = f >= 2 * NG ? 2 : (f >= NG ? 1 : 0), g = f - s * NG;
+      store_digits_compact(planes + size_t(s) * 3 * K, g, v[i], s == 0 ? inv[0] : (s == 1 ? inv[1] : inv[2]));
+    }
+  }
+  for (int f = tid + GB * kStepConsumers; f < TG; f += kStepConsumers) {
+    const int s = f >= 2 * NG ? 2 : (f >= NG ? 1 : 0), g = f - s * NG;
+    store_digits_compact(planes + size_t(s) * 3 * K, g, ld_act_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g),
+                         s == 0 ? inv[0] : (s == 1 ? inv[1] : inv[2]));
   }
 }
 
@@ -235,7 +353,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
   if (tid == 0) {
     for (int i = 0; i < kMaxStages; ++i) {
       mbar_init(full0 + 8 * i, 1);
-      mbar_init(empty0 + 8 * i, kConsumerWarps);
+      mbar_init(empty0 + 8 * i, kStepConsumerWarps);
     }
     *abort_flag = 0;
     *issued_ptr = 0;
@@ -247,7 +365,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
 
   const int nmat = 7 * L + (P.logits ? 1 : 0);
 
-  if (warp == kConsumerWarps) {
+  if (warp == kStepConsumerWarps) {
     // ================================================================== producer: weights only.
     // The stream is the CTA's rows of matrix 0, 1, 2, ... in the order the consumers use them; it
     // depends on no activation, so it runs ahead of them by the ring and, in L2, by pf_bytes more.
@@ -299,7 +417,11 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             }
           }
           mbar_arrive_expect_tx(full0 + 8 * slot, stage_bytes);
+#ifdef B200_STEP_TMAP_CONST
+          tma_load_3d(smem_u32(ring + size_t(slot) * P.slot_bytes), &c_step_tmaps[ic.m], 0, ic.r0 + ic.row, ch * (kc / 128),
+#else
           tma_load_3d(smem_u32(ring + size_t(slot) * P.slot_bytes), &M->tmap, 0, ic.r0 + ic.row, ch * (kc / 128),
+#endif
                       full0 + 8 * slot);
           ++issued;
           if (++slot == P.stages) { slot = 0; phase ^= 1u; }
@@ -337,13 +459,16 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
     unsigned bar_target = 0;
     const int r0D = int((long long)D * cta / G), nrD = int((long long)D * (cta + 1) / G) - r0D;
 
-    // ---- grid barrier over the consumer warps of all CTAs.  Returns true (for every thread alike)
-    // when the step is to be abandoned.
-    auto grid_barrier = [&]() __attribute__((always_inline)) -> bool {
-      named_bar_sync(1, kConsumers);            // every thread's stores and atomics are issued
+    // ---- grid barrier over the consumer warps of all CTAs, in two halves so that work which does not
+    // depend on the other CTAs (table look-ups, operand requests) runs between them.  bar_wait returns
+    // true (for every thread alike) when the step is to be abandoned.
+    auto bar_arrive = [&]() __attribute__((always_inline)) {
+      named_bar_sync(1, kStepConsumers);            // every thread's stores and atomics are issued
       bar_target += unsigned(G);
+      if (tid == 0) red_release_add_u32(bar_counter, 1u);
+    };
+    auto bar_wait = [&]() __attribute__((always_inline)) -> bool {
       if (tid == 0) {
-        red_release_add_u32(bar_counter, 1u);
         bool ok = true;
         if (ld_acquire_u32(bar_counter) < bar_target) {
           const unsigned long long t0 = globaltimer_ns();
@@ -364,7 +489,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         if (!ok) *abort_flag = 1;
         *decision = *abort_flag;
       }
-      named_bar_sync(1, kConsumers);
+      named_bar_sync(1, kStepConsumers);
       return *decision != 0;
     };
 
@@ -391,71 +516,25 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
       const StepMat* M0 = P.mats + m0;
       pK = __ldg(&M0->K); pkc = __ldg(&M0->kc); pnchunks = __ldg(&M0->nchunks);
       prpc16 = (rpc + 15) / 16 * 16;
-      for (int i = tid; i < nseg * prpc16 * 4; i += kConsumers) rowsum[i] = 0;
+      for (int i = tid; i < nseg * prpc16 * 4; i += kStepConsumers) rowsum[i] = 0;
     };
 
-    // ---- digit planes of the current launch's nseg segments from the exchanged xs vectors (segment s
-    // at xs + s * xs_stride) and their publication lines line0 + s.  The loads of all segments go out
-    // together: one L2 round trip.
-    auto build_planes = [&](int nseg, const float* xs, size_t xs_stride, int line0) __attribute__((always_inline)) {
-      constexpr int GB = 10;
-      const int NG = pK / 4, TG = nseg * NG;
-      float4 v[GB];
-#pragma unroll
-      for (int i = 0; i < GB; ++i) {
-        const int f = tid + i * kConsumers;
-        if (f < TG) {
-          const int s = f / NG, g = f - s * NG;
-          v[i] = ld_act_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g);
-        }
-      }
-      float inv[kMaxSeg];
-#pragma unroll
-      for (int s = 0; s < kMaxSeg; ++s) {
-        inv[s] = 0.f;
-        if (s < nseg) inv[s] = __uint_as_float(ld_act_u32(reinterpret_cast<const unsigned*>(P.pub + size_t(line0 + s) * 128)));   // max |xs|
-      }
-      if (tid < nseg) {
-        const unsigned char* line = P.pub + size_t(line0 + tid) * 128;
-        const long long zp = ld_act_s64(reinterpret_cast<const long long*>(line + 32));
-        const long long sxs = ld_act_s64(reinterpret_cast<const long long*>(line + 64));
-        const long long sx = ld_act_s64(reinterpret_cast<const long long*>(line + 96));
-        const float amax = __uint_as_float(ld_act_u32(reinterpret_cast<const unsigned*>(line)));
-        SegScalars sc;
-        sc.sd = amax > 0.f ? __fdiv_rn(1.0f, kQMax / amax) : 0.f;
-        sc.zp = __ll2float_rn(zp) * (1.0f / kPubSumScale);
-        sc.sumxs = __ll2float_rn(sxs) * (1.0f / kPubXsScale);
-        sc.sumx = __ll2float_rn(sx) * (1.0f / kPubSumScale);
-        sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
-        scal[tid] = sc;
-      }
-#pragma unroll
-      for (int s = 0; s < kMaxSeg; ++s) inv[s] = inv[s] > 0.f ? kQMax / inv[s] : 0.f;
-#pragma unroll
-      for (int i = 0; i < GB; ++i) {
-        const int f = tid + i * kConsumers;
-        if (f < TG) {
-          const int s = f / NG, g = f - s * NG;
-          store_digits_compact(planes + size_t(s) * 3 * pK, g, v[i], s == 0 ? inv[0] : (s == 1 ? inv[1] : inv[2]));
-        }
-      }
-      for (int f = tid + GB * kConsumers; f < TG; f += kConsumers) {
-        const int s = f / NG, g = f - s * NG;
-        store_digits_compact(planes + size_t(s) * 3 * pK, g, ld_act_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g),
-                             s == 0 ? inv[0] : (s == 1 ? inv[1] : inv[2]));
-      }
-    };
-
-    // ---- main loop: the rows of the current launch's matrices against the digit planes
+    // ---- main loop: the rows of the current launch's matrices against the digit planes.  Warp w takes
+    // the 32-input blocks w, w + W, w + 2W, ... of every stage (W = consumer warps, a multiple of 4, so
+    // that a warp's blocks share their position inside the 128-byte swizzle atom and every address of
+    // the unrolled loop is a per-thread constant plus an immediate).
+    const uint32_t ring_s32 = smem_u32(ring), planes_s32 = smem_u32(planes);
+    const uint32_t a_lane = lm_row + uint32_t(warp >> 2) * 2048u + (((2u * uint32_t(warp & 3) + lm_half) ^ lm_x) << 4);
+    const uint32_t b_lane = uint32_t(warp) * 96u + uint32_t(gq * 8 + tq) * 4u;
     auto stream_rows = [&]() __attribute__((always_inline)) {
       const int K = pK, kc = pkc, nchunks = pnchunks;
       const int kbpc = kc / 32;
       bool dead = false;
       for (int s = 0; s < pnseg && !dead; ++s) {
         const int nrows = s == 0 ? snr[0] : (s == 1 ? snr[1] : snr[2]);
-        const uint32_t* pw = reinterpret_cast<const uint32_t*>(planes + size_t(s) * 3 * K) + gq * 8 + tq;
+        const uint32_t b_seg = planes_s32 + uint32_t(s) * 3u * uint32_t(K) + b_lane;
         for (int tile = 0; tile * kTileRows < nrows && !dead; ++tile) {
-          int c[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+          int c[4][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}, {0, 0, 0, 0}};
           for (int ch = 0; ch < nchunks; ++ch) {
             const int k0 = ch * kc;
             const int kbn = (K - k0 < kc ? K - k0 : kc) / 32;
@@ -465,33 +544,18 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
               if (lane == 0 && P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
               break;
             }
-            const uint32_t sbase = smem_u32(ring + size_t(slot) * P.slot_bytes) + lm_row;
-            for (int kb0 = warp; kb0 < kbn; kb0 += 4 * kConsumerWarps) {
-              uint32_t a[4][4], b[4][2];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int kbi = kb0 + j * kConsumerWarps;
-                b[j][0] = 0u; b[j][1] = 0u;
-                if (kbi < kbn) {
-                  ldmatrix_x4(sbase + uint32_t(kbi >> 2) * 2048u + (((2u * uint32_t(kbi & 3) + lm_half) ^ lm_x) << 4),
-                              a[j][0], a[j][1], a[j][2], a[j][3]);
-                  if (gq < 3) {
-                    const uint32_t* bp = pw + size_t(ch * kbpc + kbi) * 24;
-                    b[j][0] = bp[0];
-                    b[j][1] = bp[4];
-                  }
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                if (kb0 + j * kConsumerWarps < kbn) mma_u8s8(c[j & 1], a[j][0], a[j][1], a[j][2], a[j][3], b[j][0], b[j][1]);
-            }
+            const uint32_t a_addr = ring_s32 + uint32_t(slot) * uint32_t(P.slot_bytes) + a_lane;
+            const uint32_t b_addr = b_seg + uint32_t(ch * kbpc) * 96u;
+#ifndef B200_STEP_NO_MATH
+            consume_stage(c, a_addr, b_addr, gq < 3, kbn, warp);
+#endif
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * slot);
             if (++slot == P.stages) { slot = 0; ring_phase ^= 1u; }
           }
           if (dead) break;
-          const int d0 = c[0][0] + c[1][0], d1 = c[0][1] + c[1][1], d2 = c[0][2] + c[1][2], d3 = c[0][3] + c[1][3];
+          const int d0 = (c[0][0] + c[1][0]) + (c[2][0] + c[3][0]), d1 = (c[0][1] + c[1][1]) + (c[2][1] + c[3][1]);
+          const int d2 = (c[0][2] + c[1][2]) + (c[2][2] + c[3][2]), d3 = (c[0][3] + c[1][3]) + (c[2][3] + c[3][3]);
           if (tq < 2) {
             const int row_lo = tile * kTileRows + gq, row_hi = row_lo + 8;
             int* lo = rowsum + (size_t(s) * prpc16 + row_lo) * 4 + 2 * tq;
@@ -546,52 +610,43 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
     // ---- operands a thread needs after a matrix has streamed (constants, or state only this thread
     // touches) are requested before the grid barrier in front of that matrix and parked in a
     // thread-private shared-memory slot, so their latency is off the chain and they hold no register
-    // while the weights stream.  Slot j of thread t: park[j * park_stride + t].
+    // while the weights stream.  Slot j of thread t: park[j * park_stride + t], 13 slots.
     float* park = reinterpret_cast<float*>(smem + P.off_park);
     const int pstride = P.park_stride;
     auto ptr_of = [&](const float* const* field) __attribute__((always_inline)) -> const float* {
       return reinterpret_cast<const float*>(__ldg(reinterpret_cast<const unsigned long long*>(field)));
     };
-
-    // layer norm + token-shift mix of this CTA's slice of the residual for the nseg matrices m0.. that
-    // follow (modules/layernorm.py:11-20, modules/block.py:58-67, :82-91): operands w, b, carry, then
-    // per matrix mu, ry, my (13 slots).
-    struct HopRegs { float w, b, carry; float mu[kMaxSeg], ry[kMaxSeg], my[kMaxSeg]; };
-    auto hop_issue = [&](HopRegs& h, const float* ln_w, const float* ln_b, const float* mix0, const float* mix1, const float* mix2,
-                         const float* carry_row, int m0, int nseg) __attribute__((always_inline)) {
-      h.w = 0.f; h.b = 0.f; h.carry = 0.f;
-#pragma unroll
-      for (int s = 0; s < kMaxSeg; ++s) { h.mu[s] = 1.f; h.ry[s] = 0.f; h.my[s] = 0.f; }
+    // operands of a layer-norm hop for this thread's element of the residual: w, b, carry, then per
+    // following matrix mu, ry, my
+    auto hop_issue = [&](float (&pre)[13], const float* ln_w, const float* ln_b, const float* mix0, const float* mix1, const float* mix2,
+                         const float* carry_row, int mfirst, int nseg) __attribute__((always_inline)) {
       if (tid < nrD) {
         const int n = r0D + tid;
-        h.w = ld_param_f32(ln_w + n);
-        h.b = ld_param_f32(ln_b + n);
-        if (carry_row) h.carry = ld_act_f32(carry_row + n);
+        pre[0] = ld_param_f32(ln_w + n);
+        pre[1] = ld_param_f32(ln_b + n);
+        if (carry_row) pre[2] = ld_act_f32(carry_row + n);
 #pragma unroll
         for (int s = 0; s < kMaxSeg; ++s) {
           if (s < nseg) {
-            const StepMat* M = P.mats + m0 + s;
+            const StepMat* M = P.mats + mfirst + s;
             const float* mix = s == 0 ? mix0 : (s == 1 ? mix1 : mix2);
-            if (mix) h.mu[s] = ld_param_f32(mix + n);
-            h.ry[s] = ld_param_f32(ptr_of(&M->ry) + n);
-            h.my[s] = ld_param_f32(ptr_of(&M->my) + n);
+            if (mix) pre[3 + 3 * s] = ld_param_f32(mix + n);
+            pre[4 + 3 * s] = ld_param_f32(ptr_of(&M->ry) + n);
+            pre[5 + 3 * s] = ld_param_f32(ptr_of(&M->my) + n);
           }
         }
       }
     };
-    auto hop_park = [&](const HopRegs& h) __attribute__((always_inline)) {
-      if (tid < nrD) {
-        park[tid] = h.w; park[pstride + tid] = h.b; park[2 * pstride + tid] = h.carry;
+    auto park_all = [&](const float (&pre)[13], int rows) __attribute__((always_inline)) {
+      if (tid < rows) {
 #pragma unroll
-        for (int s = 0; s < kMaxSeg; ++s) {
-          park[(3 + 3 * s) * pstride + tid] = h.mu[s];
-          park[(4 + 3 * s) * pstride + tid] = h.ry[s];
-          park[(5 + 3 * s) * pstride + tid] = h.my[s];
-        }
+        for (int j = 0; j < 13; ++j) park[j * pstride + tid] = pre[j];
       }
     };
-    // writes the xs slices of the next matrices, the new carry, and publishes max / sums per matrix
-    auto ln_hop = [&](float mean, float rstd, float* carry_row, bool mixing, int nseg, int line0) __attribute__((always_inline)) {
+    // layer norm + token-shift mix of this CTA's slice of the residual for the nseg matrices that
+    // follow (modules/layernorm.py:11-20, modules/block.py:58-67, :82-91): writes their xs slices,
+    // the new carry, and publishes max / sums per matrix on lines line0..
+    auto ln_hop = [&](float mean, float rstd, float* carry_row, int nseg, int line0) __attribute__((always_inline)) {
       XsAcc acc[kMaxSeg];
 #pragma unroll
       for (int s = 0; s < kMaxSeg; ++s) { acc[s].zp = 0; acc[s].sxs = 0; acc[s].sx = 0; acc[s].amax = 0.f; }
@@ -605,7 +660,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         for (int s = 0; s < kMaxSeg; ++s) {
           if (s < nseg) {
             const float mu = park[(3 + 3 * s) * pstride + tid];
-            const float v = mixing ? xy * mu + carry * (1.f - mu) : xy;
+            const float v = carry_row ? xy * mu + carry * (1.f - mu) : xy;
             xs_emit(acc[s], P.xs_ln + size_t(s) * D, n, v, park[(4 + 3 * s) * pstride + tid], park[(5 + 3 * s) * pstride + tid]);
           }
         }
@@ -621,19 +676,12 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
     // statistics of the residual from sum and squares (two limbs) in fixed point, fp64 finish:
     // var = E[x^2] - mean^2 on exact sums does not cancel (modules/layernorm.py:11-20 centres first)
     auto stats_finish = [&](long long sum, long long sqhi, long long sqlo, float& mean, float& rstd) __attribute__((always_inline)) {
-      const double s = double(sum) * (1.0 / 4294967296.0);
+      // multiplications and one subtraction in fp64 (no fp64 division or square root: those are subroutines)
+      const double mu = double(sum) * (P.inv_d * (1.0 / 4294967296.0));
       const double q = double(sqhi) * (1.0 / 256.0) + double(sqlo) * (1.0 / 281474976710656.0);
-      const double mu = s / double(D);
-      double var = q / double(D) - mu * mu;
-      var = var > 0.0 ? var : 0.0;
+      const double var = q * P.inv_d - mu * mu;
       mean = float(mu);
-      rstd = float(1.0 / sqrt(var + 1e-5));
-    };
-    auto stats_from_line = [&](const unsigned char* line, float& mean, float& rstd) __attribute__((always_inline)) {
-      const long long a = ld_act_s64(reinterpret_cast<const long long*>(line));
-      const long long b = ld_act_s64(reinterpret_cast<const long long*>(line + 32));
-      const long long c = ld_act_s64(reinterpret_cast<const long long*>(line + 64));
-      stats_finish(a, b, c, mean, rstd);
+      rstd = 1.0f / sqrtf(fmaxf(float(var), 0.f) + 1e-5f);
     };
     // publish the statistics of the residual slice this CTA just wrote into x_own
     auto publish_stats = [&](int line) __attribute__((always_inline)) {
@@ -647,24 +695,14 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
       cta_reduce<3, 0>(v, m, red_ll, red_f);
       if (tid < 3) pub_add(line_of(line), 32 * tid, v[0]);
     };
-    // the part of a launch between "digit planes built" and "all rows summed"
-    auto stream_phase = [&](int ph) __attribute__((always_inline)) {
-      named_bar_sync(1, kConsumers);      // planes, scalars, zeroed row sums, parked operands
-      if (tid == 0) *handoff = 0;
-      STEP_TRACE(ph, 1);
-      stream_rows();
-      named_bar_sync(1, kConsumers);
-      if (tid == 0) *handoff = 1;
-      STEP_TRACE(ph, 2);
-    };
 
     // ================================================================== the step
     float mean = 0.f, rstd = 1.f;
     {   // operands of the first block's ln1 hop
       const StepVec* V0 = P.vecs;
-      HopRegs h;
-      hop_issue(h, ptr_of(&V0->ln1_w), ptr_of(&V0->ln1_b), ptr_of(&V0->mix_k), ptr_of(&V0->mix_v), ptr_of(&V0->mix_r), P.state, 0, 3);
-      hop_park(h);
+      float pre[13] = {0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f};
+      hop_issue(pre, ptr_of(&V0->ln1_w), ptr_of(&V0->ln1_b), ptr_of(&V0->mix_k), ptr_of(&V0->mix_v), ptr_of(&V0->mix_r), P.state, 0, 3);
+      park_all(pre, nrD);
     }
     // ---- embedding row + ln0 (emb.py:8-9, opt.py:63-64).  Every CTA evaluates the whole vector: it
     // needs the statistics of ln0's output for the first block's layer norm and keeps its own slice.
@@ -675,26 +713,26 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
       auto block_sum = [&](float v) __attribute__((always_inline)) -> float {
         v = warp_sum(v);
         if (lane == 0) red_f[warp] = v;
-        named_bar_sync(1, kConsumers);
+        named_bar_sync(1, kStepConsumers);
         if (tid == 0) {
           float a = 0.f;
-          for (int i = 0; i < kConsumerWarps; ++i) a += red_f[i];
+          for (int i = 0; i < kStepConsumerWarps; ++i) a += red_f[i];
           bc[0] = a;
         }
-        named_bar_sync(1, kConsumers);
+        named_bar_sync(1, kStepConsumers);
         const float r = bc[0];
-        named_bar_sync(1, kConsumers);
+        named_bar_sync(1, kStepConsumers);
         return r;
       };
       float s = 0.f;
-      for (int i = tid; i < D; i += kConsumers) s += row[i];
+      for (int i = tid; i < D; i += kStepConsumers) s += row[i];
       const float mean0 = block_sum(s) / float(D);
       s = 0.f;
-      for (int i = tid; i < D; i += kConsumers) { const float c = row[i] - mean0; s += c * c; }
+      for (int i = tid; i < D; i += kStepConsumers) { const float c = row[i] - mean0; s += c * c; }
       const float sdev = sqrtf(block_sum(s) / float(D) + 1e-5f);
       long long v[3] = {0, 0, 0};
       float m[1] = {0.f};
-      for (int i = tid; i < D; i += kConsumers) {
+      for (int i = tid; i < D; i += kStepConsumers) {
         const float y = P.ln0_w[i] * ((row[i] - mean0) / sdev) + P.ln0_b[i];
         if (i >= r0D && i < r0D + nrD) x_own[i - r0D] = y;
         v[0] += __float2ll_rn(y * kPubSumScale);
@@ -702,46 +740,95 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
       }
       cta_reduce<3, 0>(v, m, red_ll, red_f);
       if (tid < 3) red_ll[16 * 12 - 3 + tid] = v[0];   // last three slots of the scratch: totals for everyone
-      named_bar_sync(1, kConsumers);
+      named_bar_sync(1, kStepConsumers);
       if (warp * 32 < nrD) stats_finish(red_ll[16 * 12 - 3], red_ll[16 * 12 - 2], red_ll[16 * 12 - 1], mean, rstd);
-      named_bar_sync(1, kConsumers);
+      named_bar_sync(1, kStepConsumers);
     }
 
-    bool dead = false;
-    int ph = 0;   // launch index for the trace
-    for (int l = 0; l < L && !dead; ++l) {
-      const StepVec* Vv = P.vecs + l;
-      float* st = P.state + size_t(l) * 5 * D;
-      const int m0 = 7 * l;
+    // ---- the launches: per block 0 key/value/receptance + WKV, 1 attention output, 2 ffn key +
+    // receptance, 3 ffn value; then 4 = the head.  One copy of every stage of a launch; what differs
+    // between the launch types is selected by `type`.
+    const int nph = 4 * L + (P.logits ? 1 : 0);
+    for (int ph = 0; ph < nph; ++ph) {
+      const int type = ph < 4 * L ? (ph & 3) : 4;
+      const int l = ph < 4 * L ? (ph >> 2) : L - 1;
       const int lines = kStepLineBase + kStepLinesPerLayer * l;
       const int kvr_line = l == 0 ? 2 : lines - kStepLinesPerLayer + 6;
       const bool more = l + 1 < L;
+      float* st = P.state + size_t(l) * 5 * D;
+      const int mfirst = 7 * l + (type == 0 ? 0 : type == 1 ? 3 : type == 2 ? 4 : type == 3 ? 6 : 7);
+      const int nseg = type == 0 ? 3 : (type == 2 ? 2 : 1);
+      const int line0 = type == 0 ? kvr_line : type == 1 ? lines : type == 2 ? lines + 2 : type == 3 ? lines + 4 : lines + 6;
 
-      // ---------------- 1. ln1 + mix -> key, value, receptance -> WKV -> sigmoid(r) * wkv
-      ln_hop(mean, rstd, st, true, 3, kvr_line);
-      STEP_TRACE(ph, 5);
-      load_phase(m0, 3);
-      {
-        float e[7] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // aa, bb, pp, w, u, ry and my of the output projection
-        if (tid < nrD) {
-          const int n = r0D + tid;
-          const StepMat* Mo = P.mats + m0 + 3;
-          e[0] = ld_act_f32(st + 2 * size_t(D) + n); e[1] = ld_act_f32(st + 3 * size_t(D) + n); e[2] = ld_act_f32(st + 4 * size_t(D) + n);
-          e[3] = ld_param_f32(ptr_of(&Vv->decay) + n);
-          e[4] = ld_param_f32(ptr_of(&Vv->first) + n);
-          e[5] = ld_param_f32(ptr_of(&Mo->ry) + n);
-          e[6] = ld_param_f32(ptr_of(&Mo->my) + n);
-        }
-        if ((dead = grid_barrier())) break;
-        STEP_TRACE(ph, 0);
-        if (tid < nrD) {
-#pragma unroll
-          for (int j = 0; j < 7; ++j) park[j * pstride + tid] = e[j];
-        }
+      // ---- A. a layer norm in front of the matrices: normalise and mix this CTA's slice
+      if (type == 0 || type == 2 || type == 4) {
+        ln_hop(mean, rstd, type == 0 ? st : (type == 2 ? st + size_t(D) : nullptr), nseg, line0);
+        STEP_TRACE(ph, 5);
       }
-      build_planes(3, P.xs_ln, size_t(D), kvr_line);
-      stream_phase(ph);
+      bar_arrive();
+      load_phase(mfirst, nseg);
+#ifdef B200_STEP_STREAM_ONLY
+      named_bar_sync(1, kStepConsumers);
+      STEP_TRACE(ph, 1);
+      stream_rows();
+      named_bar_sync(1, kStepConsumers);
+      STEP_TRACE(ph, 2);
+      continue;
+#endif
+
+      // ---- B. operands for after the stream, grid barrier, digit planes
       {
+        float pre[13] = {0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f};
+        int prows = 0;
+        const StepVec* Vv = P.vecs + l;
+        if (type == 0) {          // WKV state and parameters; ry, my of the output projection
+          prows = nrD;
+          if (tid < nrD) {
+            const int n = r0D + tid;
+            const StepMat* Mo = P.mats + mfirst + 3;
+            pre[0] = ld_act_f32(st + 2 * size_t(D) + n); pre[1] = ld_act_f32(st + 3 * size_t(D) + n); pre[2] = ld_act_f32(st + 4 * size_t(D) + n);
+            pre[3] = ld_param_f32(ptr_of(&Vv->decay) + n);
+            pre[4] = ld_param_f32(ptr_of(&Vv->first) + n);
+            pre[5] = ld_param_f32(ptr_of(&Mo->ry) + n);
+            pre[6] = ld_param_f32(ptr_of(&Mo->my) + n);
+          }
+        } else if (type == 1) {   // the ln2 hop that follows this matrix
+          prows = nrD;
+          hop_issue(pre, ptr_of(&Vv->ln2_w), ptr_of(&Vv->ln2_b), ptr_of(&Vv->fmix_k), ptr_of(&Vv->fmix_r), nullptr, st + size_t(D), mfirst + 1, 2);
+        } else if (type == 2) {   // ry, my of the value projection at this thread's first ffn-key row
+          prows = snr[0];
+          if (tid < snr[0]) {
+            const StepMat* Mv = P.mats + mfirst + 2;
+            pre[0] = ld_param_f32(ptr_of(&Mv->ry) + sr0[0] + tid);
+            pre[1] = ld_param_f32(ptr_of(&Mv->my) + sr0[0] + tid);
+          }
+        } else if (type == 3) {   // the next block's ln1 hop, or ln_out
+          if (more) {
+            prows = nrD;
+            const StepVec* Vn = Vv + 1;
+            hop_issue(pre, ptr_of(&Vn->ln1_w), ptr_of(&Vn->ln1_b), ptr_of(&Vn->mix_k), ptr_of(&Vn->mix_v), ptr_of(&Vn->mix_r),
+                      st + size_t(5) * D, mfirst + 1, 3);
+          } else if (P.logits) {
+            prows = nrD;
+            hop_issue(pre, P.lnout_w, P.lnout_b, nullptr, nullptr, nullptr, nullptr, mfirst + 1, 1);
+          }
+        }
+        if (bar_wait()) break;
+        STEP_TRACE(ph, 0);
+        park_all(pre, prows);
+      }
+      build_digit_planes(planes, scal, P.pub, type == 1 ? P.xs_att : (type == 3 ? P.xs_ffn : P.xs_ln), type == 0 || type == 2 ? size_t(D) : 0,
+                         line0, nseg, pK, tid);
+      named_bar_sync(1, kStepConsumers);      // planes, scalars, zeroed row sums, parked operands
+      if (tid == 0) *handoff = 0;
+      STEP_TRACE(ph, 1);
+      stream_rows();
+      named_bar_sync(1, kStepConsumers);
+      if (tid == 0) *handoff = 1;
+      STEP_TRACE(ph, 2);
+
+      // ---- C. what follows the matrices in the block (modules/block.py:72-100)
+      if (type == 0) {            // WKV update, sigmoid(r) * wkv -> input of the output projection
         XsAcc acc; acc.zp = 0; acc.sxs = 0; acc.sx = 0; acc.amax = 0.f;
         if (tid < nrD) {
           const int n = r0D + tid;
@@ -756,56 +843,16 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         cta_reduce<3, 1>(v3, m1, red_ll, red_f);
         if (tid < 3) pub_add(line_of(lines + 0), 32 + 32 * tid, v3[0]);
         else if (tid == 32) pub_max(line_of(lines + 0), m1[0]);
-      }
-      STEP_TRACE(ph, 3);
-      ++ph;
-
-      // ---------------- 2. attention output projection + residual
-      load_phase(m0 + 3, 1);
-      {
-        HopRegs h;   // operands of the ln2 hop that follows this matrix
-        hop_issue(h, ptr_of(&Vv->ln2_w), ptr_of(&Vv->ln2_b), ptr_of(&Vv->fmix_k), ptr_of(&Vv->fmix_r), nullptr, st + size_t(D), m0 + 4, 2);
-        if ((dead = grid_barrier())) break;
-        STEP_TRACE(ph, 0);
-        hop_park(h);
-      }
-      build_planes(1, P.xs_att, 0, lines + 0);
-      stream_phase(ph);
-      if (tid < nrD) x_own[tid] = value(0, tid) + x_own[tid];
-      publish_stats(lines + 1);
-      STEP_TRACE(ph, 3);
-      ++ph;
-
-      // ---------------- 3. ln2 + mix -> ffn key (relu^2), ffn receptance (sigmoid)
-      if ((dead = grid_barrier())) break;
-      STEP_TRACE(ph, 4);
-      if (warp * 32 < nrD) stats_from_line(line_of(lines + 1), mean, rstd);
-      ln_hop(mean, rstd, st + size_t(D), true, 2, lines + 2);
-      STEP_TRACE(ph, 5);
-      load_phase(m0 + 4, 2);
-      {
-        const StepMat* Mv = P.mats + m0 + 6;
-        float f_ry = 0.f, f_my = 0.f;   // ry, my of the value projection at this thread's first ffn-key row
-        if (tid < snr[0]) {
-          f_ry = ld_param_f32(ptr_of(&Mv->ry) + sr0[0] + tid);
-          f_my = ld_param_f32(ptr_of(&Mv->my) + sr0[0] + tid);
-        }
-        if ((dead = grid_barrier())) break;
-        STEP_TRACE(ph, 0);
-        if (tid < snr[0]) { park[tid] = f_ry; park[pstride + tid] = f_my; }
-      }
-      build_planes(2, P.xs_ln, size_t(D), lines + 2);
-      stream_phase(ph);
-      {
+      } else if (type == 2) {     // relu(key)^2 -> input of the value projection; sigmoid(receptance) stays here
         XsAcc acc; acc.zp = 0; acc.sxs = 0; acc.sx = 0; acc.amax = 0.f;
-        const StepMat* Mv = P.mats + m0 + 6;
+        const StepMat* Mv = P.mats + mfirst + 2;
         const float* vry = ptr_of(&Mv->ry);
         const float* vmy = ptr_of(&Mv->my);
-        for (int row = tid; row < snr[0]; row += kConsumers) {
+        for (int row = tid; row < snr[0]; row += kStepConsumers) {
           const int n = sr0[0] + row;
           float y = fmaxf(value(0, row), 0.f);
           y *= y;
-          const bool parked = row < kConsumers;    // row == tid then: this thread parked them
+          const bool parked = row < kStepConsumers;    // row == tid then: this thread parked them
           xs_emit(acc, P.xs_ffn, n, y, parked ? park[row] : __ldg(vry + n), parked ? park[pstride + row] : __ldg(vmy + n));
         }
         if (tid < nrD) rf_own[tid] = sigmoidf_(value(1, tid));
@@ -814,52 +861,28 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
         cta_reduce<3, 1>(v3, m1, red_ll, red_f);
         if (tid < 3) pub_add(line_of(lines + 4), 32 + 32 * tid, v3[0]);
         else if (tid == 32) pub_max(line_of(lines + 4), m1[0]);
+      } else if (type == 4) {     // logits
+        for (int row = tid; row < snr[0]; row += kStepConsumers) P.logits[sr0[0] + row] = value(0, row);
+      } else {                    // residual update; a layer norm follows unless the step ends here
+        if (tid < nrD) x_own[tid] = type == 1 ? value(0, tid) + x_own[tid] : value(0, tid) * rf_own[tid] + x_own[tid];
+        if (type == 1 || more || P.logits) {
+          const int sline = type == 1 ? lines + 1 : lines + 5;
+          publish_stats(sline);
+          STEP_TRACE(ph, 3);
+          bar_arrive();
+          if (bar_wait()) break;
+          STEP_TRACE(ph + 1, 4);
+          if (warp * 32 < nrD) {
+            const unsigned char* line = line_of(sline);
+            const long long a = ld_act_s64(reinterpret_cast<const long long*>(line));
+            const long long b = ld_act_s64(reinterpret_cast<const long long*>(line + 32));
+            const long long c = ld_act_s64(reinterpret_cast<const long long*>(line + 64));
+            stats_finish(a, b, c, mean, rstd);
+          }
+          continue;
+        }
       }
       STEP_TRACE(ph, 3);
-      ++ph;
-
-      // ---------------- 4. ffn value projection, gated, + residual
-      load_phase(m0 + 6, 1);
-      {
-        HopRegs h;   // operands of the next block's ln1 hop, or of ln_out
-        if (more) {
-          const StepVec* Vn = P.vecs + l + 1;
-          hop_issue(h, ptr_of(&Vn->ln1_w), ptr_of(&Vn->ln1_b), ptr_of(&Vn->mix_k), ptr_of(&Vn->mix_v), ptr_of(&Vn->mix_r),
-                    P.state + size_t(l + 1) * 5 * D, m0 + 7, 3);
-        } else if (P.logits) {
-          hop_issue(h, P.lnout_w, P.lnout_b, nullptr, nullptr, nullptr, nullptr, m0 + 7, 1);
-        }
-        if ((dead = grid_barrier())) break;
-        STEP_TRACE(ph, 0);
-        if (more || P.logits) hop_park(h);
-      }
-      build_planes(1, P.xs_ffn, 0, lines + 4);
-      stream_phase(ph);
-      if (tid < nrD) x_own[tid] = value(0, tid) * rf_own[tid] + x_own[tid];
-      if (more || P.logits) {
-        publish_stats(lines + 5);
-        STEP_TRACE(ph, 3);
-        ++ph;
-        if ((dead = grid_barrier())) break;
-        STEP_TRACE(ph, 4);
-        if (warp * 32 < nrD) stats_from_line(line_of(lines + 5), mean, rstd);
-      } else {
-        STEP_TRACE(ph, 3);
-        ++ph;
-      }
-
-      if (!more && P.logits) {
-        // ---------------- ln_out + head (opt.py:73-75)
-        ln_hop(mean, rstd, nullptr, false, 1, lines + 6);
-        STEP_TRACE(ph, 5);
-        load_phase(m0 + 7, 1);
-        if ((dead = grid_barrier())) break;
-        STEP_TRACE(ph, 0);
-        build_planes(1, P.xs_ln, 0, lines + 6);
-        stream_phase(ph);
-        for (int row = tid; row < snr[0]; row += kConsumers) P.logits[sr0[0] + row] = value(0, row);
-        STEP_TRACE(ph, 3);
-      }
     }
   }
 
@@ -897,7 +920,7 @@ inline bool plan_step(int D, int F, int V, bool head, int num_sms, StepPlan* p) 
   const int G = p->grid;
   auto rpc16 = [&](int N) { return ((N + G - 1) / G + 15) / 16 * 16; };
   const int rD = rpc16(D), rF = rpc16(F), rV = head ? rpc16(V) : 16;
-  if ((D + G - 1) / G > kConsumers) return false;      // the layer-norm hop handles one row per consumer thread
+  if ((D + G - 1) / G > kStepConsumers) return false;      // the layer-norm hop handles one row per consumer thread
   int kcD, kcF, n;
   step_mat_geometry(D, &kcD, &n);
   step_mat_geometry(F, &kcF, &n);

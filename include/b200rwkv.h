@@ -29,7 +29,7 @@ extern "C" {
 /* Bits a kernel may set in the caller's device status word (an int the caller zeroes). */
 #define B200RWKV_STATUS_WAIT_FULL 1    /* consumer gave up waiting for a weight stage   */
 #define B200RWKV_STATUS_WAIT_EMPTY 2   /* producer gave up waiting for a free ring slot */
-#define B200RWKV_STATUS_WAIT_PEER 4    /* a CTA of the persistent decode step gave up at a grid barrier */
+#define B200RWKV_STATUS_WAIT_PEER 4    /* a CTA of the persistent decode step gave up waiting for another CTA's data */
 
 /*
  * One quantised matrix, used as y = x @ W with W[k_in, n_out].  Bytes are stored
@@ -189,25 +189,30 @@ int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, f
  * The decode step as ONE persistent kernel (same contract as b200rwkv_decode_step: the fused
  * replacement for myRWKV.forward, opt.py:61-76, with Block.forward, modules/block.py:56-102, at
  * T == 1).  One CTA per SM stays resident for the whole step; its weight ring runs on from matrix
- * to matrix and the CTAs meet at grid barriers (six per block) instead of at kernel boundaries.
+ * to matrix, and the CTAs exchange activations (six exchanges per block) through words in L2 that
+ * carry the parity of their buffer's use count, so there is no barrier, atomic or fence between
+ * them.  On a B200 the chained path (b200rwkv_decode_step) is the faster of the two; this one is
+ * kept because it is a single launch per token.
  * The step needs a "plan": a caller-owned device buffer that holds the table of matrices (with
- * their TMA descriptors), the exchange vectors, the publication lines and the status word.
+ * their TMA descriptors), copies of the vector parameters at fixed offsets, the exchange buffers,
+ * their use counts and the status word.
  *
  * b200rwkv_step_plan_bytes   size of the plan buffer for this model
- * b200rwkv_step_plan_init    fills it (synchronous: one cudaMemset and two cudaMemcpy; call it once,
- *                            outside any stream capture, with the device current; 256-byte aligned).
- *                            The model needs emb/ln0; ln_out/head only if logits will be asked for.
+ * b200rwkv_step_plan_init    fills it (synchronous: cudaMemset / cudaMemcpy; call it once, outside any
+ *                            stream capture, with the device current; 256-byte aligned).  The model
+ *                            needs emb/ln0; ln_out/head only if logits will be asked for.  The vector
+ *                            parameters are COPIED: call it again if they change.
  * b200rwkv_decode_step_persistent
  *   token, state, logits  as b200rwkv_decode_step (logits NULL skips ln_out + head)
  *   tuning   NULL, or int32[4] = {weight stages a CTA may have in flight (0: the whole ring), the same
  *            while its consumers are between two matrices (0: the whole ring), bytes per CTA requested
  *            from L2 beyond the ring (-1: default), limit of every device-side wait in ms (0: 1000)}
  *   trace    NULL, or device u64 [4*n_layer + 1][grid][8] of %globaltimer stamps per launch and CTA:
- *            0 barrier in front of the matrix passed, 1 digit planes built, 2 rows summed, 3 epilogue
- *            done, 4 layer-norm statistics barrier passed, 5 normalised slice published
- *   One memset node and one cooperative kernel launch; allocation-free; safe to capture in a CUDA
- *   graph.  Steps that share a plan must be ordered on one stream.  After B200RWKV_STATUS_* bits
- *   appear in the status word (first int of the plan) the state is undefined.
+ *            1 exchange read and digit planes built, 2 rows summed, 3 epilogue done, 4 layer-norm
+ *            statistics gathered, 5 normalised slice published
+ *   One cooperative kernel launch; allocation-free; safe to capture in a CUDA graph.  Steps that
+ *   share a plan must be ordered on one stream.  When B200RWKV_STATUS_* bits appear in the status
+ *   word (first int of the plan) the state is undefined and the plan must be initialised again.
  * b200rwkv_step_geometry  host-only: out[0..7] = {grid, ring_stages, slot_bytes, shared_memory_bytes,
  *   row_sum_offset, plane_offset, ring_offset, threads} for a GPU with num_sms SMs.
  * No counterpart in the reference (it launches ~45 kernels per block and token).

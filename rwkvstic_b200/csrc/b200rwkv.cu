@@ -675,24 +675,33 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 
 
 // ---- whole decode step as one persistent kernel ------------------------------------------------------
-// Plan buffer (device, caller-owned): [status 256 B][publication lines][xs_att D][xs_ffn F][xs_ln 3D]
-// [matrix table][vector table].
+// Plan buffer (device, caller-owned): [status 256 B][use counts, abort word 256 B][exchange vectors]
+// [per-CTA records][matrix table][vector table].
 struct StepLayout {
-  size_t off_pub, pub_bytes, off_xs_att, off_xs_ffn, off_xs_ln, off_mats, off_vecs, bytes;
-  int nlines;
+  size_t off_uses, off_xs_kvr, off_xs_att, off_xs_fkr, off_xs_ffn, off_xs_head;
+  size_t off_part_kvr, off_part_att, off_part_fkr, off_part_ffn, off_part_head, off_part_st, off_mats, off_vpack, off_rym, bytes;
 };
 
 static StepLayout step_layout(const b200rwkv_model* m) {
   StepLayout o;
   const size_t D = size_t(m->n_embd), F = size_t(m->n_ffn), L = size_t(m->n_layer);
+  const size_t G = size_t(32) * kStepPartPerLane * kRecStride;   // records of the largest grid the kernel supports, one 128-byte line each
   size_t off = 256;
-  o.nlines = kStepLineBase + kStepLinesPerLayer * int(L);
-  o.off_pub = off; o.pub_bytes = align256(size_t(o.nlines) * 128); off += o.pub_bytes;
+  o.off_uses = off; off += 256;
+  o.off_xs_kvr = off; off += align256(3 * D * 4);
   o.off_xs_att = off; off += align256(D * 4);
+  o.off_xs_fkr = off; off += align256(2 * D * 4);
   o.off_xs_ffn = off; off += align256(F * 4);
-  o.off_xs_ln = off; off += align256(3 * D * 4);
+  o.off_xs_head = off; off += align256(D * 4);
+  o.off_part_kvr = off; off += align256(3 * G * 16);
+  o.off_part_att = off; off += align256(G * 16);
+  o.off_part_fkr = off; off += align256(2 * G * 16);
+  o.off_part_ffn = off; off += align256(G * 16);
+  o.off_part_head = off; off += align256(G * 16);
+  o.off_part_st = off; off += align256(G * 16);
   o.off_mats = off; off += align256((7 * L + 1) * sizeof(StepMat));
-  o.off_vecs = off; off += align256(L * sizeof(StepVec));
+  o.off_vpack = off; off += align256(L * kStepVecs * D * 4);
+  o.off_rym = off; off += align256((L * (12 * D + 2 * F) + 2 * D) * 4);
   o.bytes = off;
   return o;
 }
@@ -1052,35 +1061,44 @@ int b200rwkv_step_plan_init(const b200rwkv_model* m, void* plan, size_t plan_byt
     return fail(B200RWKV_EINVAL, "step_plan_init: the shape does not fit the step kernel's shared memory");
   const int L = m->n_layer;
   std::vector<StepMat> mats(static_cast<size_t>(7 * L + 1));
-  std::vector<StepVec> vecs(static_cast<size_t>(L));
   memset(mats.data(), 0, mats.size() * sizeof(StepMat));
-  memset(vecs.data(), 0, vecs.size() * sizeof(StepVec));
+  char* base = static_cast<char*>(plan);
+  cudaError_t e = cudaMemset(base, 0, lay.bytes);
+  const size_t D = size_t(m->n_embd), F = size_t(m->n_ffn);
+  float* vpack = reinterpret_cast<float*>(base + lay.off_vpack);
+  float* rym = reinterpret_cast<float*>(base + lay.off_rym);
+  const size_t rym_stride = 12 * D + 2 * F;
+  auto copy_vec = [&](float* dst, const float* src, size_t n) {
+    if (e == cudaSuccess) e = cudaMemcpy(dst, src, n * sizeof(float), cudaMemcpyDeviceToDevice);
+  };
   for (int l = 0; l < L; ++l) {
     const b200rwkv_layer& ly = m->layers[l];
     const b200rwkv_matrix* ms[7] = {&ly.att_key, &ly.att_value, &ly.att_receptance, &ly.att_output,
                                     &ly.ffn_key, &ly.ffn_receptance, &ly.ffn_value};
     for (int i = 0; i < 7; ++i)
       if (!fill_step_mat(mats[size_t(7) * l + i], *ms[i])) return fail(B200RWKV_ECUDA, "step_plan_init: cuTensorMapEncodeTiled failed");
-    StepVec& v = vecs[l];
-    v.ln1_w = ly.ln1_w; v.ln1_b = ly.ln1_b; v.ln2_w = ly.ln2_w; v.ln2_b = ly.ln2_b;
-    v.mix_k = ly.att_mix_k; v.mix_v = ly.att_mix_v; v.mix_r = ly.att_mix_r; v.fmix_k = ly.ffn_mix_k; v.fmix_r = ly.ffn_mix_r;
-    v.decay = ly.time_decay; v.first = ly.time_first;
-    const float* need[11] = {v.ln1_w, v.ln1_b, v.ln2_w, v.ln2_b, v.mix_k, v.mix_v, v.mix_r, v.fmix_k, v.fmix_r, v.decay, v.first};
-    for (int i = 0; i < 11; ++i)
-      if (!need[i]) return fail(B200RWKV_EINVAL, "step_plan_init: layer %d has a null vector parameter", l);
+    const float* vec[kStepVecs] = {ly.ln1_w, ly.ln1_b, ly.ln2_w, ly.ln2_b, ly.att_mix_k, ly.att_mix_v, ly.att_mix_r,
+                                   ly.ffn_mix_k, ly.ffn_mix_r, ly.time_decay, ly.time_first};
+    for (int i = 0; i < kStepVecs; ++i) {
+      if (!vec[i]) return fail(B200RWKV_EINVAL, "step_plan_init: layer %d has a null vector parameter", l);
+      copy_vec(vpack + (size_t(l) * kStepVecs + i) * D, vec[i], D);
+    }
+    // D-input matrices in the order key, value, receptance, output, ffn key, ffn receptance; then ffn value
+    const b200rwkv_matrix* dm[6] = {&ly.att_key, &ly.att_value, &ly.att_receptance, &ly.att_output, &ly.ffn_key, &ly.ffn_receptance};
+    for (int i = 0; i < 6; ++i) {
+      copy_vec(rym + size_t(l) * rym_stride + (size_t(i) * 2 + 0) * D, dm[i]->ry, D);
+      copy_vec(rym + size_t(l) * rym_stride + (size_t(i) * 2 + 1) * D, dm[i]->my, D);
+    }
+    copy_vec(rym + size_t(l) * rym_stride + 12 * D, ly.ffn_value.ry, F);
+    copy_vec(rym + size_t(l) * rym_stride + 12 * D + F, ly.ffn_value.my, F);
   }
-  if (m->head.qt && !fill_step_mat(mats[size_t(7) * L], m->head)) return fail(B200RWKV_ECUDA, "step_plan_init: cuTensorMapEncodeTiled failed");
-  char* base = static_cast<char*>(plan);
-  cudaError_t e = cudaMemset(base, 0, lay.bytes);
+  if (m->head.qt) {
+    if (!fill_step_mat(mats[size_t(7) * L], m->head)) return fail(B200RWKV_ECUDA, "step_plan_init: cuTensorMapEncodeTiled failed");
+    copy_vec(rym + size_t(L) * rym_stride, m->head.ry, D);
+    copy_vec(rym + size_t(L) * rym_stride + D, m->head.my, D);
+  }
   if (e == cudaSuccess) e = cudaMemcpy(base + lay.off_mats, mats.data(), mats.size() * sizeof(StepMat), cudaMemcpyHostToDevice);
-  if (e == cudaSuccess) e = cudaMemcpy(base + lay.off_vecs, vecs.data(), vecs.size() * sizeof(StepVec), cudaMemcpyHostToDevice);
-#ifdef B200_STEP_TMAP_CONST
-  {
-    std::vector<CUtensorMap> tm(mats.size());
-    for (size_t i = 0; i < mats.size(); ++i) tm[i] = mats[i].tmap;
-    if (e == cudaSuccess) e = cudaMemcpyToSymbol(c_step_tmaps, tm.data(), tm.size() * sizeof(CUtensorMap));
-  }
-#endif
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "step_plan_init: %s", cudaGetErrorString(e));
   return B200RWKV_OK;
 }
@@ -1109,14 +1127,24 @@ int b200rwkv_decode_step_persistent(const b200rwkv_model* m, void* plan, size_t 
   StepParams P;
   memset(&P, 0, sizeof(P));
   P.mats = reinterpret_cast<const StepMat*>(base + lay.off_mats);
-  P.vecs = reinterpret_cast<const StepVec*>(base + lay.off_vecs);
+  P.vpack = reinterpret_cast<const float*>(base + lay.off_vpack);
+  P.rympack = reinterpret_cast<const float*>(base + lay.off_rym);
   P.L = m->n_layer; P.D = m->n_embd; P.F = m->n_ffn; P.V = m->n_vocab; P.inv_d = 1.0 / double(m->n_embd);
   P.emb = m->emb; P.ln0_w = m->ln0_w; P.ln0_b = m->ln0_b; P.lnout_w = m->ln_out_w; P.lnout_b = m->ln_out_b;
   P.token = reinterpret_cast<const long long*>(token); P.state = state; P.logits = logits;
+  P.xs_kvr = reinterpret_cast<float*>(base + lay.off_xs_kvr);
   P.xs_att = reinterpret_cast<float*>(base + lay.off_xs_att);
+  P.xs_fkr = reinterpret_cast<float*>(base + lay.off_xs_fkr);
   P.xs_ffn = reinterpret_cast<float*>(base + lay.off_xs_ffn);
-  P.xs_ln = reinterpret_cast<float*>(base + lay.off_xs_ln);
-  P.pub = reinterpret_cast<unsigned char*>(base + lay.off_pub);
+  P.xs_head = reinterpret_cast<float*>(base + lay.off_xs_head);
+  P.part_kvr = reinterpret_cast<float4*>(base + lay.off_part_kvr);
+  P.part_att = reinterpret_cast<float4*>(base + lay.off_part_att);
+  P.part_fkr = reinterpret_cast<float4*>(base + lay.off_part_fkr);
+  P.part_ffn = reinterpret_cast<float4*>(base + lay.off_part_ffn);
+  P.part_head = reinterpret_cast<float4*>(base + lay.off_part_head);
+  P.part_st = reinterpret_cast<float4*>(base + lay.off_part_st);
+  P.uses = reinterpret_cast<unsigned*>(base + lay.off_uses);
+  P.abort_word = reinterpret_cast<unsigned*>(base + lay.off_uses + 128);
   P.status = reinterpret_cast<int*>(base);
   P.trace = reinterpret_cast<unsigned long long*>(trace);
   P.slot_bytes = geo.slot_bytes; P.stages = geo.stages; P.off_own = geo.off_own; P.own_rows = geo.own_rows;
@@ -1127,8 +1155,6 @@ int b200rwkv_decode_step_persistent(const b200rwkv_model* m, void* plan, size_t 
   P.pf_bytes = tuning && tuning[2] >= 0 ? tuning[2] : kStepPrefetchDefault;
   P.wait_limit_ns = (tuning && tuning[3] > 0 ? (unsigned long long)tuning[3] : 1000ull) * 1000000ull;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  e = cudaMemsetAsync(P.pub, 0, size_t(lay.nlines) * 128, s);
-  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "decode_step_persistent: memset: %s", cudaGetErrorString(e));
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(geo.grid); cfg.blockDim = dim3(kStepThreads); cfg.dynamicSmemBytes = geo.smem; cfg.stream = s;

@@ -5,30 +5,34 @@
 // a CTA's shared-memory ring - the only place weight bytes can wait - is torn down and rebuilt at
 // each kernel boundary.  Here every SM runs one CTA for the whole step.  Its producer lane streams
 // the CTA's rows of ALL matrices, one after the other, through one ring that never drains (weights
-// are constants, so the stream does not depend on any activation) and asks L2 for the bytes that
-// follow the ring; the 16 consumer warps meet the other CTAs only where the mathematics needs
-// every output of a matrix: at a grid barrier (one release-increment and one acquire-poll of a
-// counter in L2 per CTA).
+// are constants, so the stream does not depend on any activation); the consumer warps meet the
+// other CTAs only where the mathematics needs every output of a matrix.
 //
 // What crosses CTAs, and how.  CTA c owns rows [N*c/G, N*(c+1)/G) of every matrix.  For the D-wide
 // vectors (residual stream, receptance gates, WKV state, token-shift carries) that is the same
 // slice in every block, so they never leave their CTA: the residual lives in shared memory for the
-// whole step.  Only three things are exchanged through global memory (L2):
+// whole step.  Two kinds of data are exchanged through global memory (L2):
 //   * the input of the next matrix, already multiplied by its per-input scale (xs = v * ry), one
-//     slice per CTA, with max|xs| (integer atomicMax on the float bits) and the fixed-point sums the
-//     affine terms need (int64 atomics): exact and order-free, so a step is bit-reproducible;
-//   * for a layer norm, the sum and sum of squares of the residual (int64 fixed point; the squares
-//     in two limbs so that neither large nor tiny activations lose bits), finished in fp64 with the
-//     centred form var = E[x^2] - mean^2 evaluated where it cannot cancel;
-//   * the barrier counter.
-// After the barrier every CTA reads the whole xs vector (4 bytes per input, L2 hits), turns it into
-// the three signed base-256 digit planes in its own shared memory and runs the same integer
-// tensor-core main loop as stream_gemv_kernel.  A layer norm needs two hops (statistics, then the
-// normalised and mixed slices), an element-wise hand-off (attention output, ffn value) one.
+//     slice per CTA, plus one 16-byte record per CTA with the slice's max|xs| and the sums the affine
+//     terms need;
+//   * for a layer norm, one record per CTA with the mean and the centred sum of squares of its
+//     slice of the residual; every CTA combines the G records (Chan's parallel variance, fp64) in
+//     the same order, so all CTAs get the same statistics bit for bit.
+// There is no barrier, no atomic and no fence in the exchange: every 32-bit word that crosses carries
+// the parity of its buffer's use count in its lowest mantissa bit (a relative change of 2^-23 at
+// most, below the 24-bit fixed point the value is about to be rounded to).  A reader simply loads
+// the words it needs and repeats the load of those whose bit is still the old one; the poll IS the
+// read.  A buffer is rewritten completely at every use and a CTA cannot get a whole block ahead of
+// another (every exchange needs everyone's data), so a word with the right parity is the right
+// word.  A hand-off costs one store transit plus one load round trip.
+// After the exchange every CTA turns the xs vector into the three signed base-256 digit planes in
+// its own shared memory and runs the integer tensor-core main loop of stream_gemv_kernel.  A layer
+// norm needs two exchanges (statistics, then the normalised and mixed slices), an element-wise
+// hand-off (attention output, ffn value) one.
 //
-// Every wait (mbarrier, grid barrier) is bounded by wait_limit_ns; on expiry the CTA raises a
+// Every wait (mbarrier, exchange poll) is bounded by wait_limit_ns; on expiry the CTA raises a
 // status bit and an abort word that the other CTAs see at their next poll, drains its own copies
-// in flight and returns.
+// in flight and returns.  After an abandoned step the plan (use counts) has to be initialised again.
 #pragma once
 
 #include "stream_gemv.cuh"
@@ -36,27 +40,25 @@
 namespace b200 {
 
 #ifndef B200_STEP_CONSUMER_WARPS
-#define B200_STEP_CONSUMER_WARPS 8
+#define B200_STEP_CONSUMER_WARPS 16
 #endif
-constexpr int kStepConsumerWarps = B200_STEP_CONSUMER_WARPS;   // a multiple of 4; 8 + the producer = 9 warps
+constexpr int kStepConsumerWarps = B200_STEP_CONSUMER_WARPS;   // a multiple of 4; 16 + the producer = 17 warps: 96 registers per thread
 constexpr int kStepConsumers = kStepConsumerWarps * 32;
 constexpr int kStepThreads = kStepConsumers + 32;   // + one producer warp
-constexpr int kStepLineBase = 5;                // publication lines 0 barrier, 1 abort, 2..4 first block's k/v/r
-constexpr int kStepLinesPerLayer = 9;
-constexpr int kStepTraceSlots = 8;              // u64 stamps per (phase, CTA)
+constexpr int kStepTraceSlots = 8;              // u64 stamps per (launch, CTA)
 constexpr int kStepPrefetchPiece = 16384;       // bytes per L2 prefetch request
-constexpr int kStepPrefetchDefault = 256 * 1024; // bytes per CTA requested from L2 beyond the ring
+constexpr int kStepPrefetchDefault = 0;         // bytes per CTA requested from L2 beyond the ring (measured: no gain)
+constexpr int kStepPartPerLane = 5;             // warps of 32 per-CTA records: up to 160 CTAs
+constexpr int kRecStride = 8;                   // float4s between two CTAs' records: one 128-byte line each, so that pollers spread over L2
+constexpr int kStepGather = (4096 + kStepConsumers - 1) / kStepConsumers;   // float4 per thread in one exchange read: 16384 inputs
 
 // Shared-memory map of the step kernel (byte offsets; the rest is laid out by the host, see StepParams)
-constexpr int kSOffDecision = 272;   // int: uniform abort decision of the last grid barrier
-constexpr int kSOffRed = 512;        // reduction scratch: long long [16 warps][12], then float [16][4], then 16 floats
-constexpr int kSOffRedF = kSOffRed + 16 * 12 * 8;
-constexpr int kSOffBc = kSOffRedF + 16 * 4 * 4;
+constexpr int kSOffConsAbort = 272;  // int: set by consumer threads only, read after named barriers (uniform decisions)
+constexpr int kSOffInv = 288;        // float[3]: fixed-point scale of each segment's digit planes
+constexpr int kSOffRed = 512;        // reduction scratch: float [warps <= 16][16]
+constexpr int kSOffBc = kSOffRed + 16 * 16 * 4;   // 16 floats
+constexpr int kSOffStat = kSOffBc + 64;            // 2 * kStepPartPerLane doubles
 constexpr int kSOffDyn = 2560;       // first byte the host lays out
-
-// Fixed-point units of the published quantities
-constexpr float kSqHiScale = 256.0f;                 // 2^8: high limb of a square
-constexpr float kSqLoScale = 1099511627776.0f;       // 2^40 on top of the 2^8: low limb in 2^-48 units
 
 // One matrix as the step kernel sees it: a 256-byte entry of a table in global memory.
 struct __align__(128) StepMat {
@@ -72,34 +74,41 @@ struct __align__(128) StepMat {
 };
 static_assert(sizeof(StepMat) == 256, "StepMat is 256 bytes");
 
-// The vector parameters of one block (all f32 [D]).
-struct __align__(128) StepVec {
-  const float *ln1_w, *ln1_b, *ln2_w, *ln2_b;
-  const float *mix_k, *mix_v, *mix_r, *fmix_k, *fmix_r;
-  const float *decay, *first;
-  const float* pad[5];
-};
-static_assert(sizeof(StepVec) == 128, "StepVec is 128 bytes");
-
-#ifdef B200_STEP_TMAP_CONST
-__constant__ CUtensorMap c_step_tmaps[449];
-#endif
+// The vector parameters are copied into the plan at fixed offsets so that the kernel computes their
+// addresses instead of chasing pointers.  Per block kStepVecs vectors of D floats, in this order:
+enum StepVecId : int { VEC_LN1_W = 0, VEC_LN1_B, VEC_LN2_W, VEC_LN2_B, VEC_MIX_K, VEC_MIX_V, VEC_MIX_R, VEC_FMIX_K, VEC_FMIX_R,
+                       VEC_DECAY, VEC_FIRST, kStepVecs };
+// ... and the per-input scale / offset (ry, my) of every matrix: per block [6 matrices with D inputs:
+// key, value, receptance, output, ffn key, ffn receptance][ry, my][D], then [ffn value][ry, my][F];
+// after the last block [head][ry, my][D].
 
 struct StepParams {
   const StepMat* mats;    // [7*L + 1]: per block key, value, receptance, output, ffn key, ffn receptance, ffn value; then the head
-  const StepVec* vecs;    // [L]
+  const float* vpack;     // [L][kStepVecs][D]
+  const float* rympack;   // [L][12*D + 2*F], then [2][D] for the head
   int L, D, F, V;
   const float* emb;
   const float *ln0_w, *ln0_b, *lnout_w, *lnout_b;
   const long long* token;
   float* state;           // [L][5][D]
   float* logits;          // [V] or null (no head)
-  float* xs_att;          // [D]   exchange buffers
-  float* xs_ffn;          // [F]
-  float* xs_ln;           // [3][D]
-  unsigned char* pub;     // publication lines of 128 bytes, zero at kernel entry
+  // exchange buffers: tagged words (see the header comment)
+  // (each buffer is written completely at every one of its uses, which is what makes the tag sufficient)
+  float* xs_kvr;          // [3][D]  inputs of key / value / receptance
+  float* xs_att;          // [D]     input of the attention output projection
+  float* xs_fkr;          // [2][D]  inputs of ffn key / receptance
+  float* xs_ffn;          // [F]     input of the ffn value projection
+  float* xs_head;         // [D]     input of the head
+  float4* part_kvr;       // [3][G]  per CTA: max|xs|, sum v*my, sum xs, sum v of its slice
+  float4* part_att;       // [G]
+  float4* part_fkr;       // [2][G]
+  float4* part_ffn;       // [G]
+  float4* part_head;      // [G]
+  float4* part_st;        // [G]     per CTA: mean and centred sum of squares of its slice of the residual
+  unsigned* uses;         // [6]: how often the kvr, att, fkr, ffn, head buffers and part_st have been written so far
+  unsigned* abort_word;
   int* status;
-  unsigned long long* trace;   // optional: [4L+1 phases][G][kStepTraceSlots]
+  unsigned long long* trace;   // optional: [4L+1 launches][G][kStepTraceSlots]
   // shared-memory geometry (host: plan_step)
   int slot_bytes, stages, off_own, own_rows, off_park, park_stride, off_rows, off_planes, off_ring;
   // tuning
@@ -110,28 +119,10 @@ struct StepParams {
   double inv_d;           // 1 / D
 };
 
-// ---- scoped memory operations ----------------------------------------------------------------------
-__device__ __forceinline__ void red_release_add_u32(unsigned* p, unsigned v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
+// ---- memory operations -------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
   unsigned v;
   asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ long long ld_act_s64(const long long* p) {
-  long long v;
-  asm volatile("ld.global.cg.s64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ unsigned ld_act_u32(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.global.cg.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 
@@ -139,14 +130,41 @@ __device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity,
                                                   unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
-  for (;;) {
+  for (unsigned it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > limit_ns) {
+    if ((it & 63u) == 0u && globaltimer_ns() - t0 > limit_ns) {
       *abort_flag = 1;
       return false;
     }
   }
+}
+
+// Exchange words are read and written with strong (relaxed, gpu-scope) accesses: a weak load, even
+// one that bypasses L1, may be served from a stale copy for microseconds.
+__device__ __forceinline__ float4 ld_xchg_v4(const float4* p) {
+  float4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_xchg_f32(float* p, float v) {
+  asm volatile("st.relaxed.gpu.global.f32 [%0], %1;" ::"l"(p), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_xchg_v4(float4* p, float4 v) {
+  asm volatile("st.relaxed.gpu.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// ---- tagged words ------------------------------------------------------------------------------------
+__device__ __forceinline__ float tag_f32(float v, unsigned tag) { return __uint_as_float((__float_as_uint(v) & ~1u) | tag); }
+__device__ __forceinline__ bool tagged(float v, unsigned tag) { return (__float_as_uint(v) & 1u) == tag; }
+__device__ __forceinline__ bool tagged4(float4 v, unsigned tag) {
+  return ((__float_as_uint(v.x) & __float_as_uint(v.y) & __float_as_uint(v.z) & __float_as_uint(v.w)) & 1u) == tag &&
+         ((__float_as_uint(v.x) | __float_as_uint(v.y) | __float_as_uint(v.z) | __float_as_uint(v.w)) & 1u) == tag;
 }
 
 // Digits of four inputs -> one word per plane in the compact shared-memory layout: 96 bytes per
@@ -170,43 +188,31 @@ __device__ __forceinline__ void store_digits_compact(unsigned char* planes, int 
   blk[16 + j] = __byte_perm(c01, c23, 0x5410);
 }
 
-// y^2 as two integers: hi = rint(y^2 * 2^8), lo = (y^2 * 2^8 - hi) * 2^40.  Both products are exact
-// (power-of-two scaling; the remainder of a float against its own rounding to an integer is a float),
-// so the pair carries y^2 exactly for 2^-60 <= y^2 < 2^55 and sums of either limb are order-free.
-__device__ __forceinline__ void square_limbs(float y, long long& hi, long long& lo) {
-  const float s = __fmul_rn(__fmul_rn(y, y), kSqHiScale);
-  const float sh = rintf(s);
-  hi += __float2ll_rn(sh);
-  lo += __float2ll_rn(__fmul_rn(__fsub_rn(s, sh), kSqLoScale));
-}
-
-
-// Sums of NV int64 quantities and maxima of NM floats over the consumer threads.  Afterwards
-// thread i < NV holds total i in v[0] and thread 32 + j holds maximum j in m[0].  One named barrier
-// inside; the scratch is free again after the caller's next named barrier.
+// Sums of NV floats and maxima of NM floats over the consumer threads, in a fixed order (the same
+// inputs give the same bits).  Afterwards thread i < NV holds total i in v[0] and thread 32 + j holds
+// maximum j in m[0].  One named barrier inside; the scratch is free again after the caller's next one.
 template <int NV, int NM>
-__device__ __forceinline__ void cta_reduce(long long (&v)[NV], float (&m)[NM > 0 ? NM : 1], long long* red_ll, float* red_f) {
+__device__ __forceinline__ void cta_reduce(float (&v)[NV], float (&m)[NM > 0 ? NM : 1], float* red) {
+  static_assert(NV + NM <= 16, "scratch row holds 16 floats");
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v[i] += __shfl_xor_sync(0xffffffffu, v[i], o);
+  for (int i = 0; i < NV; ++i) v[i] = warp_sum(v[i]);
 #pragma unroll
   for (int i = 0; i < NM; ++i) m[i] = warp_max(m[i]);
   if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < NV; ++i) red_ll[warp * 12 + i] = v[i];
+    for (int i = 0; i < NV; ++i) red[warp * 16 + i] = v[i];
 #pragma unroll
-    for (int i = 0; i < NM; ++i) red_f[warp * 4 + i] = m[i];
+    for (int i = 0; i < NM; ++i) red[warp * 16 + NV + i] = m[i];
   }
   named_bar_sync(1, kStepConsumers);
   if (tid < NV) {
-    long long a = 0;
-    for (int w = 0; w < kStepConsumerWarps; ++w) a += red_ll[w * 12 + tid];
+    float a = 0.f;
+    for (int w = 0; w < kStepConsumerWarps; ++w) a += red[w * 16 + tid];
     v[0] = a;
   } else if (tid >= 32 && tid < 32 + NM) {
     float a = 0.f;
-    for (int w = 0; w < kStepConsumerWarps; ++w) a = fmaxf(a, red_f[w * 4 + tid - 32]);
+    for (int w = 0; w < kStepConsumerWarps; ++w) a = fmaxf(a, red[w * 16 + NV + tid - 32]);
     m[0] = a;
   }
 }
@@ -265,58 +271,159 @@ __device__ __forceinline__ void consume_stage(int (&c)[4][4], uint32_t a_addr, u
   }
 }
 
-// Digit planes of a launch's nseg segments from the exchanged xs vectors (segment s at
-// xs + s * xs_stride, K inputs each) and their publication lines line0 + s; also the segments'
-// scalars.  Called by all consumer threads.  The loads of all segments go out together: one L2
-// round trip.
-__device__ __forceinline__ void build_digit_planes(unsigned char* planes, SegScalars* scal, const unsigned char* pub,
-                                                   const float* xs, size_t xs_stride, int line0, int nseg, int K, int tid) {
-  constexpr int GB = (4096 + kStepConsumers - 1) / kStepConsumers;   // 16384 inputs in one batch
+
+// What a thread needs to give up a poll: the flags, the limit, where to report.
+struct StepWaitCtx {
+  volatile int* abort_flag;     // shared: anyone may raise it; waits return early when it is set
+  volatile int* cons_abort;     // shared: raised by consumer threads only
+  const unsigned* abort_word;   // global: another CTA gave up
+  int* status;
+  unsigned long long limit;
+};
+
+// true: go on polling.  Called every few iterations of a poll loop.
+__device__ __forceinline__ bool poll_check(const StepWaitCtx& w, unsigned long long t0) {
+  if (*w.abort_flag || ld_relaxed_u32(w.abort_word) != 0u) {
+    *w.abort_flag = 1; *w.cons_abort = 1;
+    return false;
+  }
+  if (globaltimer_ns() - t0 > w.limit) {
+    if (w.status) atomicOr(w.status, B200RWKV_STATUS_WAIT_PEER);
+    atomicExch(const_cast<unsigned*>(w.abort_word), 1u);
+    *w.abort_flag = 1; *w.cons_abort = 1;
+    return false;
+  }
+  return true;
+}
+
+// The read side of an xs exchange, called by all consumer threads: gathers the nseg vectors of K
+// inputs (segment s at xs + s * xs_stride) and the G per-CTA records of each (segment s at
+// part + s * G), repeating the loads of words that still carry the old tag, then writes the digit
+// planes and the segments' scalars to shared memory.  Thread t reads record t % 160 of segment
+// t / 160 beside its share of the vectors.  Two named barriers inside; the planes are complete after
+// the caller's next one.
+__device__ __forceinline__ void gather_digit_planes(unsigned char* planes, SegScalars* scal, float* inv_s, float* red, const float* xs,
+                                                    size_t xs_stride, const float4* part, int G, int nseg, int K, unsigned tag,
+                                                    const StepWaitCtx& w) {
+  constexpr int kRecSpan = 32 * kStepPartPerLane;   // threads (and five warps) per segment's records
+  static_assert(kStepConsumers >= kMaxSeg * kRecSpan, "one consumer thread per record of three segments");
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int NG = K / 4, TG = nseg * NG;
-  float4 v[GB];
-#pragma unroll
-  for (int i = 0; i < GB; ++i) {
-    const int f = tid + i * kStepConsumers;
-    if (f < TG) {
-      const int s = f >= 2 * NG ? 2 : (f >= NG ? 1 : 0), g = f - s * NG;
-      v[i] = ld_act_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g);
+  const int rs = tid / kRecSpan, rc = tid - rs * kRecSpan;
+  const bool has_rec = rs < nseg && rc < G;
+  float4 v[kStepGather], p = make_float4(0.f, 0.f, 0.f, 0.f);
+  const unsigned long long t0 = globaltimer_ns();
+  // 1. the records: small, one line per CTA, so polling them is cheap; they are written after the
+  //    slice they describe
+  if (has_rec) {
+    const float4* rec = part + (size_t(rs) * G + rc) * kRecStride;
+    p = ld_xchg_v4(rec);
+    for (unsigned it = 1; !tagged4(p, tag); ++it) {
+      if ((it & 15u) == 0u && !poll_check(w, t0)) break;
+      __nanosleep(64);
+      p = ld_xchg_v4(rec);
     }
   }
-  float inv[kMaxSeg];
+  named_bar_sync(2, kStepConsumers);      // every record has arrived: the slices are (almost always) visible too
+  // 2. the vectors: one read; words that still carry the old tag are read again
+  unsigned need = 0u;        // bit i: v[i] not yet valid
 #pragma unroll
-  for (int s = 0; s < kMaxSeg; ++s) {
-    inv[s] = 0.f;
-    if (s < nseg) inv[s] = __uint_as_float(ld_act_u32(reinterpret_cast<const unsigned*>(pub + size_t(line0 + s) * 128)));   // max |xs|
+  for (int i = 0; i < kStepGather; ++i) if (tid + i * kStepConsumers < TG) need |= 1u << i;
+  for (unsigned it = 1; need != 0u; ++it) {
+#pragma unroll
+    for (int i = 0; i < kStepGather; ++i) {
+      if (need & (1u << i)) {
+        const int f = tid + i * kStepConsumers;
+        const int s = f >= 2 * NG ? 2 : (f >= NG ? 1 : 0), g = f - s * NG;
+        v[i] = ld_xchg_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kStepGather; ++i)
+      if ((need & (1u << i)) && tagged4(v[i], tag)) need &= ~(1u << i);
+    if (need != 0u && (it & 15u) == 0u && !poll_check(w, t0)) break;
   }
+  // the records: maximum and sums over the CTAs, in the same order in every CTA (warp, then the
+  // five warps of a segment in sequence)
+  {
+    float amax = has_rec ? p.x : 0.f, zp = has_rec ? p.y : 0.f, sxs = has_rec ? p.z : 0.f, sx = has_rec ? p.w : 0.f;
+    amax = warp_max(amax); zp = warp_sum(zp); sxs = warp_sum(sxs); sx = warp_sum(sx);
+    if (lane == 0) { red[warp * 4] = amax; red[warp * 4 + 1] = zp; red[warp * 4 + 2] = sxs; red[warp * 4 + 3] = sx; }
+  }
+  named_bar_sync(1, kStepConsumers);
   if (tid < nseg) {
-    const unsigned char* line = pub + size_t(line0 + tid) * 128;
-    const long long zp = ld_act_s64(reinterpret_cast<const long long*>(line + 32));
-    const long long sxs = ld_act_s64(reinterpret_cast<const long long*>(line + 64));
-    const long long sx = ld_act_s64(reinterpret_cast<const long long*>(line + 96));
-    const float amax = __uint_as_float(ld_act_u32(reinterpret_cast<const unsigned*>(line)));
+    float amax = 0.f, zp = 0.f, sxs = 0.f, sx = 0.f;
+#pragma unroll
+    for (int j = 0; j < kStepPartPerLane; ++j) {
+      const float* r = red + (tid * kStepPartPerLane + j) * 4;
+      amax = fmaxf(amax, r[0]); zp += r[1]; sxs += r[2]; sx += r[3];
+    }
+    const float inv = amax > 0.f ? kQMax / amax : 0.f;
     SegScalars sc;
-    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, kQMax / amax) : 0.f;
-    sc.zp = __ll2float_rn(zp) * (1.0f / kPubSumScale);
-    sc.sumxs = __ll2float_rn(sxs) * (1.0f / kPubXsScale);
-    sc.sumx = __ll2float_rn(sx) * (1.0f / kPubSumScale);
+    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;
+    sc.zp = zp; sc.sumxs = sxs; sc.sumx = sx;
     sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
     scal[tid] = sc;
+    inv_s[tid] = inv;
   }
+  named_bar_sync(1, kStepConsumers);
+  const float inv0 = inv_s[0], inv1 = inv_s[1], inv2 = inv_s[2];
 #pragma unroll
-  for (int s = 0; s < kMaxSeg; ++s) inv[s] = inv[s] > 0.f ? kQMax / inv[s] : 0.f;
-#pragma unroll
-  for (int i = 0; i < GB; ++i) {
+  for (int i = 0; i < kStepGather; ++i) {
     const int f = tid + i * kStepConsumers;
     if (f < TG) {
       const int s = f >= 2 * NG ? 2 : (f >= NG ? 1 : 0), g = f - s * NG;
-      store_digits_compact(planes + size_t(s) * 3 * K, g, v[i], s == 0 ? inv[0] : (s == 1 ? inv[1] : inv[2]));
+      store_digits_compact(planes + size_t(s) * 3 * K, g, v[i], s == 0 ? inv0 : (s == 1 ? inv1 : inv2));
     }
   }
-  for (int f = tid + GB * kStepConsumers; f < TG; f += kStepConsumers) {
+  // inputs beyond what one pass holds in registers (nseg * K > 16384): one more poll per piece
+  for (int f = tid + kStepGather * kStepConsumers; f < TG; f += kStepConsumers) {
     const int s = f >= 2 * NG ? 2 : (f >= NG ? 1 : 0), g = f - s * NG;
-    store_digits_compact(planes + size_t(s) * 3 * K, g, ld_act_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g),
-                         s == 0 ? inv[0] : (s == 1 ? inv[1] : inv[2]));
+    float4 x = ld_xchg_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g);
+    for (unsigned it = 1; !tagged4(x, tag); ++it) {
+      if ((it & 15u) == 0u && !poll_check(w, t0)) break;
+      x = ld_xchg_v4(reinterpret_cast<const float4*>(xs + size_t(s) * xs_stride) + g);
+    }
+    store_digits_compact(planes + size_t(s) * 3 * K, g, x, s == 0 ? inv0 : (s == 1 ? inv1 : inv2));
   }
+}
+
+// The read side of a statistics exchange, called by all consumer threads: thread c < G gathers the
+// record of CTA c (mean and centred sum of squares of its n_c elements), the records are combined in
+// fp64 in a fixed order, and every thread gets mean and 1/sqrt(var + 1e-5) of the whole vector
+// (modules/layernorm.py:11-20).  var = (sum_c M2_c + n_c mean_c^2  -  D mean^2) / D: the inputs are
+// fp32 numbers, so the fp64 subtraction loses nothing that matters.  One named barrier inside.
+__device__ __forceinline__ void gather_statistics(double* scratch, const float4* part, int G, int D, double inv_d, unsigned tag,
+                                                  const StepWaitCtx& w, float& mean_out, float& rstd_out) {
+  constexpr int kRecWarps = kStepPartPerLane;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  double a = 0.0, b = 0.0;
+  if (warp < kRecWarps) {
+    const bool has = tid < G;
+    float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (has) {
+      p = ld_xchg_v4(part + size_t(tid) * kRecStride);
+      const unsigned long long t0 = globaltimer_ns();
+      for (unsigned it = 1; !tagged4(p, tag); ++it) {
+        if ((it & 15u) == 0u && !poll_check(w, t0)) break;
+        __nanosleep(64);
+        p = ld_xchg_v4(part + size_t(tid) * kRecStride);
+      }
+      const double n = double(int((long long)D * (tid + 1) / G) - int((long long)D * tid / G));
+      a = n * double(p.x);
+      b = double(p.y) + a * double(p.x);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { a += __shfl_xor_sync(0xffffffffu, a, o); b += __shfl_xor_sync(0xffffffffu, b, o); }
+    if (lane == 0) { scratch[2 * warp] = a; scratch[2 * warp + 1] = b; }
+  }
+  named_bar_sync(1, kStepConsumers);
+  a = 0.0; b = 0.0;
+#pragma unroll
+  for (int j = 0; j < kRecWarps; ++j) { a += scratch[2 * j]; b += scratch[2 * j + 1]; }
+  const double mean = a * inv_d;
+  mean_out = float(mean);
+  rstd_out = 1.0f / sqrtf(fmaxf(float((b - a * mean) * inv_d), 0.f) + 1e-5f);
 }
 
 #define STEP_TRACE(ph, i)                                                                               \
@@ -335,10 +442,10 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffAbort);
   volatile int* issued_ptr = reinterpret_cast<volatile int*>(smem + kOffAbort + 4);
   volatile int* handoff = reinterpret_cast<volatile int*>(smem + kOffAbort + 8);
-  volatile int* decision = reinterpret_cast<volatile int*>(smem + kSOffDecision);
+  volatile int* cons_abort = reinterpret_cast<volatile int*>(smem + kSOffConsAbort);
   SegScalars* scal = reinterpret_cast<SegScalars*>(smem + kOffScale);
-  long long* red_ll = reinterpret_cast<long long*>(smem + kSOffRed);
-  float* red_f = reinterpret_cast<float*>(smem + kSOffRedF);
+  float* inv_s = reinterpret_cast<float*>(smem + kSOffInv);
+  float* red = reinterpret_cast<float*>(smem + kSOffRed);
   float* bc = reinterpret_cast<float*>(smem + kSOffBc);
   float* x_own = reinterpret_cast<float*>(smem + P.off_own);   // this CTA's slice of the residual stream
   float* rf_own = x_own + P.own_rows;                          // ... of sigmoid(ffn receptance)
@@ -346,8 +453,6 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
   unsigned char* planes = smem + P.off_planes;
   unsigned char* ring = smem + P.off_ring;
   const uint32_t full0 = smem_u32(smem + kOffFull), empty0 = smem_u32(smem + kOffEmpty);
-  unsigned* bar_counter = reinterpret_cast<unsigned*>(P.pub);
-  unsigned* abort_word = reinterpret_cast<unsigned*>(P.pub + 128);
   const unsigned long long limit = P.wait_limit_ns;
 
   if (tid == 0) {
@@ -358,7 +463,8 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
     *abort_flag = 0;
     *issued_ptr = 0;
     *handoff = 1;
-    *decision = 0;
+    *cons_abort = 0;
+    inv_s[0] = inv_s[1] = inv_s[2] = 0.f;
     fence_mbar_init();
   }
   __syncthreads();
@@ -417,11 +523,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             }
           }
           mbar_arrive_expect_tx(full0 + 8 * slot, stage_bytes);
-#ifdef B200_STEP_TMAP_CONST
-          tma_load_3d(smem_u32(ring + size_t(slot) * P.slot_bytes), &c_step_tmaps[ic.m], 0, ic.r0 + ic.row, ch * (kc / 128),
-#else
           tma_load_3d(smem_u32(ring + size_t(slot) * P.slot_bytes), &M->tmap, 0, ic.r0 + ic.row, ch * (kc / 128),
-#endif
                       full0 + 8 * slot);
           ++issued;
           if (++slot == P.stages) { slot = 0; phase ^= 1u; }
@@ -456,42 +558,11 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
     const uint32_t lm_half = uint32_t(lane >> 4), lm_x = uint32_t(lane & 7);
     int slot = 0;
     uint32_t ring_phase = 0;
-    unsigned bar_target = 0;
     const int r0D = int((long long)D * cta / G), nrD = int((long long)D * (cta + 1) / G) - r0D;
-
-    // ---- grid barrier over the consumer warps of all CTAs, in two halves so that work which does not
-    // depend on the other CTAs (table look-ups, operand requests) runs between them.  bar_wait returns
-    // true (for every thread alike) when the step is to be abandoned.
-    auto bar_arrive = [&]() __attribute__((always_inline)) {
-      named_bar_sync(1, kStepConsumers);            // every thread's stores and atomics are issued
-      bar_target += unsigned(G);
-      if (tid == 0) red_release_add_u32(bar_counter, 1u);
-    };
-    auto bar_wait = [&]() __attribute__((always_inline)) -> bool {
-      if (tid == 0) {
-        bool ok = true;
-        if (ld_acquire_u32(bar_counter) < bar_target) {
-          const unsigned long long t0 = globaltimer_ns();
-          unsigned it = 0;
-          for (;;) {
-            if (ld_acquire_u32(bar_counter) >= bar_target) break;
-            if ((++it & 15u) == 0u) {
-              if (*abort_flag || ld_relaxed_u32(abort_word) != 0u) { ok = false; break; }
-              if (globaltimer_ns() - t0 > limit) {
-                if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_PEER);
-                atomicExch(abort_word, 1u);
-                ok = false;
-                break;
-              }
-            }
-          }
-        }
-        if (!ok) *abort_flag = 1;
-        *decision = *abort_flag;
-      }
-      named_bar_sync(1, kStepConsumers);
-      return *decision != 0;
-    };
+    StepWaitCtx wctx;
+    wctx.abort_flag = abort_flag; wctx.cons_abort = cons_abort; wctx.abort_word = P.abort_word; wctx.status = P.status; wctx.limit = limit;
+    // use counts of the exchange buffers so far (the same in every CTA); the parity of a count tags the words of that use
+    unsigned u_kvr = P.uses[0], u_att = P.uses[1], u_fkr = P.uses[2], u_ffn = P.uses[3], u_head = P.uses[4], u_st = P.uses[5];
 
     // ---- headers of the matrices of the current launch
     int sr0[kMaxSeg], snr[kMaxSeg];
@@ -541,14 +612,13 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
             const bool ok = mbar_wait_limited(full0 + 8 * slot, ring_phase, abort_flag, limit);
             if (!__all_sync(0xffffffffu, ok)) {
               dead = true;
+              *cons_abort = 1;
               if (lane == 0 && P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
               break;
             }
             const uint32_t a_addr = ring_s32 + uint32_t(slot) * uint32_t(P.slot_bytes) + a_lane;
             const uint32_t b_addr = b_seg + uint32_t(ch * kbpc) * 96u;
-#ifndef B200_STEP_NO_MATH
             consume_stage(c, a_addr, b_addr, gq < 3, kbn, warp);
-#endif
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * slot);
             if (++slot == P.stages) { slot = 0; ring_phase ^= 1u; }
@@ -588,68 +658,60 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
       return y;
     };
 
-    auto pub_add = [&](unsigned char* line, int off, long long v) __attribute__((always_inline)) {
-      atomicAdd(reinterpret_cast<unsigned long long*>(line + off), (unsigned long long)v);
-    };
-    auto pub_max = [&](unsigned char* line, float m) __attribute__((always_inline)) {
-      atomicMax(reinterpret_cast<unsigned*>(line), __float_as_uint(m));   // non-negative floats order like their bits
-    };
-    auto line_of = [&](int i) -> unsigned char* { return P.pub + size_t(i) * 128; };
-
-    // ---- one element-wise producer of a next-matrix input: xs = v * ry, partial max and sums
-    struct XsAcc { long long zp, sxs, sx; float amax; };
-    auto xs_emit = [&](XsAcc& a, float* dst, int n, float v, float ry, float my) __attribute__((always_inline)) {
-      const float xs = v * ry;
-      dst[n] = xs;
+    // ---- the write side of an xs exchange: one element of a next-matrix input, xs = v * ry with the
+    // use's tag, and this thread's share of the slice's record
+    struct XsAcc { float zp, sxs, sx, amax; };
+    auto xs_emit = [&](XsAcc& a, float* dst, int n, float v, float ry, float my, unsigned tag) __attribute__((always_inline)) {
+      const float xs = tag_f32(v * ry, tag);
+      st_xchg_f32(dst + n, xs);
       a.amax = fmaxf(a.amax, fabsf(xs));
-      a.zp += __float2ll_rn(v * my * kPubSumScale);
-      a.sxs += __float2ll_rn(xs * kPubXsScale);
-      a.sx += __float2ll_rn(v * kPubSumScale);
+      a.zp += v * my;
+      a.sxs += xs;
+      a.sx += v;
+    };
+    // ... and the record itself, by the four threads that hold its fields after cta_reduce<3 * n, n>
+    auto write_record = [&](float4* rec, int field, float v, unsigned tag) __attribute__((always_inline)) {
+      st_xchg_f32(reinterpret_cast<float*>(rec) + field, tag_f32(v, tag));
     };
 
     // ---- operands a thread needs after a matrix has streamed (constants, or state only this thread
-    // touches) are requested before the grid barrier in front of that matrix and parked in a
-    // thread-private shared-memory slot, so their latency is off the chain and they hold no register
-    // while the weights stream.  Slot j of thread t: park[j * park_stride + t], 13 slots.
+    // touches) are copied asynchronously (cp.async, no register) into a thread-private shared-memory
+    // slot before the exchange in front of that matrix is read, so their latency is off the chain.
+    // Slot j of thread t: park[j * park_stride + t], 13 slots.
     float* park = reinterpret_cast<float*>(smem + P.off_park);
     const int pstride = P.park_stride;
-    auto ptr_of = [&](const float* const* field) __attribute__((always_inline)) -> const float* {
-      return reinterpret_cast<const float*>(__ldg(reinterpret_cast<const unsigned long long*>(field)));
+    const size_t rym_stride = size_t(12) * D + size_t(2) * P.F;
+    auto vec_of = [&](int l, int id) __attribute__((always_inline)) -> const float* { return P.vpack + (size_t(l) * kStepVecs + id) * D; };
+    // ry (which = 0) or my (1) of matrix m of block l: 0..5 the D-input matrices, 6 ffn value; l == L: the head
+    auto rym_of = [&](int l, int m, int which) __attribute__((always_inline)) -> const float* {
+      const float* base = P.rympack + size_t(l) * rym_stride;
+      return m < 6 ? base + (size_t(m) * 2 + which) * D : base + size_t(12) * D + size_t(which) * P.F;
     };
     // operands of a layer-norm hop for this thread's element of the residual: w, b, carry, then per
-    // following matrix mu, ry, my
-    auto hop_issue = [&](float (&pre)[13], const float* ln_w, const float* ln_b, const float* mix0, const float* mix1, const float* mix2,
-                         const float* carry_row, int mfirst, int nseg) __attribute__((always_inline)) {
+    // following matrix mu, ry, my.  lv / lw, lb: block and ids of the layer norm; m0: first following matrix.
+    auto hop_async = [&](int lv, int id_w, int id_b, int id_mix0, int nmix, const float* carry_row, int lm, int m0, int nseg) __attribute__((always_inline)) {
       if (tid < nrD) {
         const int n = r0D + tid;
-        pre[0] = ld_param_f32(ln_w + n);
-        pre[1] = ld_param_f32(ln_b + n);
-        if (carry_row) pre[2] = ld_act_f32(carry_row + n);
+        cp_async_f32(park + tid, (lv < 0 ? P.lnout_w : vec_of(lv, id_w)) + n);
+        cp_async_f32(park + pstride + tid, (lv < 0 ? P.lnout_b : vec_of(lv, id_b)) + n);
+        if (carry_row) cp_async_f32(park + 2 * pstride + tid, carry_row + n);
 #pragma unroll
         for (int s = 0; s < kMaxSeg; ++s) {
           if (s < nseg) {
-            const StepMat* M = P.mats + mfirst + s;
-            const float* mix = s == 0 ? mix0 : (s == 1 ? mix1 : mix2);
-            if (mix) pre[3 + 3 * s] = ld_param_f32(mix + n);
-            pre[4 + 3 * s] = ld_param_f32(ptr_of(&M->ry) + n);
-            pre[5 + 3 * s] = ld_param_f32(ptr_of(&M->my) + n);
+            if (s < nmix) cp_async_f32(park + (3 + 3 * s) * pstride + tid, vec_of(lv, id_mix0 + s) + n);
+            cp_async_f32(park + (4 + 3 * s) * pstride + tid, rym_of(lm, m0 + s, 0) + n);
+            cp_async_f32(park + (5 + 3 * s) * pstride + tid, rym_of(lm, m0 + s, 1) + n);
           }
         }
       }
     };
-    auto park_all = [&](const float (&pre)[13], int rows) __attribute__((always_inline)) {
-      if (tid < rows) {
-#pragma unroll
-        for (int j = 0; j < 13; ++j) park[j * pstride + tid] = pre[j];
-      }
-    };
     // layer norm + token-shift mix of this CTA's slice of the residual for the nseg matrices that
     // follow (modules/layernorm.py:11-20, modules/block.py:58-67, :82-91): writes their xs slices,
-    // the new carry, and publishes max / sums per matrix on lines line0..
-    auto ln_hop = [&](float mean, float rstd, float* carry_row, int nseg, int line0) __attribute__((always_inline)) {
+    // the new carry, and the slice's record per matrix
+    auto ln_hop = [&](float mean, float rstd, float* carry_row, int nseg, float* xs_dst, float4* part_dst, unsigned tag) __attribute__((always_inline)) {
       XsAcc acc[kMaxSeg];
 #pragma unroll
-      for (int s = 0; s < kMaxSeg; ++s) { acc[s].zp = 0; acc[s].sxs = 0; acc[s].sx = 0; acc[s].amax = 0.f; }
+      for (int s = 0; s < kMaxSeg; ++s) { acc[s].zp = 0.f; acc[s].sxs = 0.f; acc[s].sx = 0.f; acc[s].amax = 0.f; }
       if (tid < nrD) {
         const int n = r0D + tid;
         const float x = x_own[tid];
@@ -661,49 +723,33 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
           if (s < nseg) {
             const float mu = park[(3 + 3 * s) * pstride + tid];
             const float v = carry_row ? xy * mu + carry * (1.f - mu) : xy;
-            xs_emit(acc[s], P.xs_ln + size_t(s) * D, n, v, park[(4 + 3 * s) * pstride + tid], park[(5 + 3 * s) * pstride + tid]);
+            xs_emit(acc[s], xs_dst + size_t(s) * D, n, v, park[(4 + 3 * s) * pstride + tid], park[(5 + 3 * s) * pstride + tid], tag);
           }
         }
       }
-      long long v[9];
-      float m[3];
+      float v[9], m[3];
 #pragma unroll
       for (int s = 0; s < kMaxSeg; ++s) { v[3 * s] = acc[s].zp; v[3 * s + 1] = acc[s].sxs; v[3 * s + 2] = acc[s].sx; m[s] = acc[s].amax; }
-      cta_reduce<9, 3>(v, m, red_ll, red_f);
-      if (tid < 3 * nseg) pub_add(line_of(line0 + tid / 3), 32 + 32 * (tid % 3), v[0]);
-      else if (tid >= 32 && tid < 32 + nseg) pub_max(line_of(line0 + tid - 32), m[0]);
+      cta_reduce<9, 3>(v, m, red);
+      if (tid < 3 * nseg) write_record(part_dst + (size_t(tid / 3) * G + cta) * kRecStride, 1 + tid % 3, v[0], tag);
+      else if (tid >= 32 && tid < 32 + nseg) write_record(part_dst + (size_t(tid - 32) * G + cta) * kRecStride, 0, m[0], tag);
     };
-    // statistics of the residual from sum and squares (two limbs) in fixed point, fp64 finish:
-    // var = E[x^2] - mean^2 on exact sums does not cancel (modules/layernorm.py:11-20 centres first)
-    auto stats_finish = [&](long long sum, long long sqhi, long long sqlo, float& mean, float& rstd) __attribute__((always_inline)) {
-      // multiplications and one subtraction in fp64 (no fp64 division or square root: those are subroutines)
-      const double mu = double(sum) * (P.inv_d * (1.0 / 4294967296.0));
-      const double q = double(sqhi) * (1.0 / 256.0) + double(sqlo) * (1.0 / 281474976710656.0);
-      const double var = q * P.inv_d - mu * mu;
-      mean = float(mu);
-      rstd = 1.0f / sqrtf(fmaxf(float(var), 0.f) + 1e-5f);
-    };
-    // publish the statistics of the residual slice this CTA just wrote into x_own
-    auto publish_stats = [&](int line) __attribute__((always_inline)) {
-      long long v[3] = {0, 0, 0};
-      float m[1] = {0.f};
-      if (tid < nrD) {
-        const float y = x_own[tid];
-        v[0] = __float2ll_rn(y * kPubSumScale);
-        square_limbs(y, v[1], v[2]);
+    // the record of this CTA's slice of the residual for the next layer norm: mean and centred sum of squares
+    auto publish_stats = [&](unsigned tag) __attribute__((always_inline)) {
+      if (tid < 32) {
+        float s = 0.f;
+        for (int i = lane; i < nrD; i += 32) s += x_own[i];
+        const float mc = warp_sum(s) / float(nrD);
+        float q = 0.f;
+        for (int i = lane; i < nrD; i += 32) { const float d = x_own[i] - mc; q += d * d; }
+        q = warp_sum(q);
+        if (lane == 0) st_xchg_v4(P.part_st + size_t(cta) * kRecStride, make_float4(tag_f32(mc, tag), tag_f32(q, tag), tag_f32(0.f, tag), tag_f32(0.f, tag)));
       }
-      cta_reduce<3, 0>(v, m, red_ll, red_f);
-      if (tid < 3) pub_add(line_of(line), 32 * tid, v[0]);
     };
 
     // ================================================================== the step
     float mean = 0.f, rstd = 1.f;
-    {   // operands of the first block's ln1 hop
-      const StepVec* V0 = P.vecs;
-      float pre[13] = {0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f};
-      hop_issue(pre, ptr_of(&V0->ln1_w), ptr_of(&V0->ln1_b), ptr_of(&V0->mix_k), ptr_of(&V0->mix_v), ptr_of(&V0->mix_r), P.state, 0, 3);
-      park_all(pre, nrD);
-    }
+    hop_async(0, VEC_LN1_W, VEC_LN1_B, VEC_MIX_K, 3, P.state, 0, 0, 3);   // operands of the first block's ln1 hop
     // ---- embedding row + ln0 (emb.py:8-9, opt.py:63-64).  Every CTA evaluates the whole vector: it
     // needs the statistics of ln0's output for the first block's layer norm and keeps its own slice.
     {
@@ -712,11 +758,11 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
       const float* row = P.emb + size_t(tok) * D;
       auto block_sum = [&](float v) __attribute__((always_inline)) -> float {
         v = warp_sum(v);
-        if (lane == 0) red_f[warp] = v;
+        if (lane == 0) red[warp] = v;
         named_bar_sync(1, kStepConsumers);
         if (tid == 0) {
           float a = 0.f;
-          for (int i = 0; i < kStepConsumerWarps; ++i) a += red_f[i];
+          for (int i = 0; i < kStepConsumerWarps; ++i) a += red[i];
           bc[0] = a;
         }
         named_bar_sync(1, kStepConsumers);
@@ -730,159 +776,145 @@ __global__ void __launch_bounds__(kStepThreads, 1) decode_step_kernel(const __gr
       s = 0.f;
       for (int i = tid; i < D; i += kStepConsumers) { const float c = row[i] - mean0; s += c * c; }
       const float sdev = sqrtf(block_sum(s) / float(D) + 1e-5f);
-      long long v[3] = {0, 0, 0};
-      float m[1] = {0.f};
+      s = 0.f;
       for (int i = tid; i < D; i += kStepConsumers) {
         const float y = P.ln0_w[i] * ((row[i] - mean0) / sdev) + P.ln0_b[i];
         if (i >= r0D && i < r0D + nrD) x_own[i - r0D] = y;
-        v[0] += __float2ll_rn(y * kPubSumScale);
-        square_limbs(y, v[1], v[2]);
+        s += y;
       }
-      cta_reduce<3, 0>(v, m, red_ll, red_f);
-      if (tid < 3) red_ll[16 * 12 - 3 + tid] = v[0];   // last three slots of the scratch: totals for everyone
-      named_bar_sync(1, kStepConsumers);
-      if (warp * 32 < nrD) stats_finish(red_ll[16 * 12 - 3], red_ll[16 * 12 - 2], red_ll[16 * 12 - 1], mean, rstd);
-      named_bar_sync(1, kStepConsumers);
+      mean = block_sum(s) / float(D);
+      s = 0.f;
+      for (int i = tid; i < D; i += kStepConsumers) {
+        const float c = (P.ln0_w[i] * ((row[i] - mean0) / sdev) + P.ln0_b[i]) - mean;
+        s += c * c;
+      }
+      rstd = 1.0f / sqrtf(block_sum(s) / float(D) + 1e-5f);
     }
+    cp_async_wait_all();
 
     // ---- the launches: per block 0 key/value/receptance + WKV, 1 attention output, 2 ffn key +
     // receptance, 3 ffn value; then 4 = the head.  One copy of every stage of a launch; what differs
     // between the launch types is selected by `type`.
     const int nph = 4 * L + (P.logits ? 1 : 0);
+    bool dead = false;
     for (int ph = 0; ph < nph; ++ph) {
       const int type = ph < 4 * L ? (ph & 3) : 4;
       const int l = ph < 4 * L ? (ph >> 2) : L - 1;
-      const int lines = kStepLineBase + kStepLinesPerLayer * l;
-      const int kvr_line = l == 0 ? 2 : lines - kStepLinesPerLayer + 6;
       const bool more = l + 1 < L;
       float* st = P.state + size_t(l) * 5 * D;
       const int mfirst = 7 * l + (type == 0 ? 0 : type == 1 ? 3 : type == 2 ? 4 : type == 3 ? 6 : 7);
       const int nseg = type == 0 ? 3 : (type == 2 ? 2 : 1);
-      const int line0 = type == 0 ? kvr_line : type == 1 ? lines : type == 2 ? lines + 2 : type == 3 ? lines + 4 : lines + 6;
 
       // ---- A. a layer norm in front of the matrices: normalise and mix this CTA's slice
-      if (type == 0 || type == 2 || type == 4) {
-        ln_hop(mean, rstd, type == 0 ? st : (type == 2 ? st + size_t(D) : nullptr), nseg, line0);
+      // (the named barriers inside the previous launch's epilogue already separate its reads of the row
+      // sums from their zeroing in load_phase)
+      if (type == 0) {
+        ++u_kvr;
+        ln_hop(mean, rstd, st, 3, P.xs_kvr, P.part_kvr, u_kvr & 1u);
+        STEP_TRACE(ph, 5);
+      } else if (type == 2) {
+        ++u_fkr;
+        ln_hop(mean, rstd, st + size_t(D), 2, P.xs_fkr, P.part_fkr, u_fkr & 1u);
+        STEP_TRACE(ph, 5);
+      } else if (type == 4) {
+        ++u_head;
+        ln_hop(mean, rstd, nullptr, 1, P.xs_head, P.part_head, u_head & 1u);
         STEP_TRACE(ph, 5);
       }
-      bar_arrive();
       load_phase(mfirst, nseg);
-#ifdef B200_STEP_STREAM_ONLY
-      named_bar_sync(1, kStepConsumers);
-      STEP_TRACE(ph, 1);
-      stream_rows();
-      named_bar_sync(1, kStepConsumers);
-      STEP_TRACE(ph, 2);
-      continue;
-#endif
 
-      // ---- B. operands for after the stream, grid barrier, digit planes
-      {
-        float pre[13] = {0.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 1.f, 0.f, 0.f, 0.f};
-        int prows = 0;
-        const StepVec* Vv = P.vecs + l;
-        if (type == 0) {          // WKV state and parameters; ry, my of the output projection
-          prows = nrD;
-          if (tid < nrD) {
-            const int n = r0D + tid;
-            const StepMat* Mo = P.mats + mfirst + 3;
-            pre[0] = ld_act_f32(st + 2 * size_t(D) + n); pre[1] = ld_act_f32(st + 3 * size_t(D) + n); pre[2] = ld_act_f32(st + 4 * size_t(D) + n);
-            pre[3] = ld_param_f32(ptr_of(&Vv->decay) + n);
-            pre[4] = ld_param_f32(ptr_of(&Vv->first) + n);
-            pre[5] = ld_param_f32(ptr_of(&Mo->ry) + n);
-            pre[6] = ld_param_f32(ptr_of(&Mo->my) + n);
-          }
-        } else if (type == 1) {   // the ln2 hop that follows this matrix
-          prows = nrD;
-          hop_issue(pre, ptr_of(&Vv->ln2_w), ptr_of(&Vv->ln2_b), ptr_of(&Vv->fmix_k), ptr_of(&Vv->fmix_r), nullptr, st + size_t(D), mfirst + 1, 2);
-        } else if (type == 2) {   // ry, my of the value projection at this thread's first ffn-key row
-          prows = snr[0];
-          if (tid < snr[0]) {
-            const StepMat* Mv = P.mats + mfirst + 2;
-            pre[0] = ld_param_f32(ptr_of(&Mv->ry) + sr0[0] + tid);
-            pre[1] = ld_param_f32(ptr_of(&Mv->my) + sr0[0] + tid);
-          }
-        } else if (type == 3) {   // the next block's ln1 hop, or ln_out
-          if (more) {
-            prows = nrD;
-            const StepVec* Vn = Vv + 1;
-            hop_issue(pre, ptr_of(&Vn->ln1_w), ptr_of(&Vn->ln1_b), ptr_of(&Vn->mix_k), ptr_of(&Vn->mix_v), ptr_of(&Vn->mix_r),
-                      st + size_t(5) * D, mfirst + 1, 3);
-          } else if (P.logits) {
-            prows = nrD;
-            hop_issue(pre, P.lnout_w, P.lnout_b, nullptr, nullptr, nullptr, nullptr, mfirst + 1, 1);
-          }
+      // ---- B. operands for after the stream; the exchange read; digit planes
+      if (type == 0) {          // WKV state and parameters; ry, my of the output projection
+        if (tid < nrD) {
+          const int n = r0D + tid;
+          cp_async_f32(park + tid, st + 2 * size_t(D) + n);
+          cp_async_f32(park + pstride + tid, st + 3 * size_t(D) + n);
+          cp_async_f32(park + 2 * pstride + tid, st + 4 * size_t(D) + n);
+          cp_async_f32(park + 3 * pstride + tid, vec_of(l, VEC_DECAY) + n);
+          cp_async_f32(park + 4 * pstride + tid, vec_of(l, VEC_FIRST) + n);
+          cp_async_f32(park + 5 * pstride + tid, rym_of(l, 3, 0) + n);
+          cp_async_f32(park + 6 * pstride + tid, rym_of(l, 3, 1) + n);
         }
-        if (bar_wait()) break;
-        STEP_TRACE(ph, 0);
-        park_all(pre, prows);
+      } else if (type == 1) {   // the ln2 hop that follows this matrix
+        hop_async(l, VEC_LN2_W, VEC_LN2_B, VEC_FMIX_K, 2, st + size_t(D), l, 4, 2);
+      } else if (type == 2) {   // ry, my of the value projection at this thread's first ffn-key row
+        if (tid < snr[0]) {
+          cp_async_f32(park + tid, rym_of(l, 6, 0) + sr0[0] + tid);
+          cp_async_f32(park + pstride + tid, rym_of(l, 6, 1) + sr0[0] + tid);
+        }
+      } else if (type == 3) {   // the next block's ln1 hop, or ln_out
+        if (more) hop_async(l + 1, VEC_LN1_W, VEC_LN1_B, VEC_MIX_K, 3, st + size_t(5) * D, l + 1, 0, 3);
+        else if (P.logits) hop_async(-1, 0, 0, 0, 0, nullptr, L, 0, 1);
       }
-      build_digit_planes(planes, scal, P.pub, type == 1 ? P.xs_att : (type == 3 ? P.xs_ffn : P.xs_ln), type == 0 || type == 2 ? size_t(D) : 0,
-                         line0, nseg, pK, tid);
-      named_bar_sync(1, kStepConsumers);      // planes, scalars, zeroed row sums, parked operands
+      {
+        const unsigned tag = (type == 0 ? u_kvr : type == 1 ? u_att : type == 2 ? u_fkr : type == 3 ? u_ffn : u_head) & 1u;
+        const float* xs_src = type == 0 ? P.xs_kvr : type == 1 ? P.xs_att : type == 2 ? P.xs_fkr : type == 3 ? P.xs_ffn : P.xs_head;
+        const float4* part_src = type == 0 ? P.part_kvr : type == 1 ? P.part_att : type == 2 ? P.part_fkr : type == 3 ? P.part_ffn : P.part_head;
+        gather_digit_planes(planes, scal, inv_s, red, xs_src, size_t(D), part_src, G, nseg, pK, tag, wctx);
+      }
+      named_bar_sync(1, kStepConsumers);      // planes, zeroed row sums, parked operands
+      if (*cons_abort) { dead = true; break; }
       if (tid == 0) *handoff = 0;
       STEP_TRACE(ph, 1);
       stream_rows();
+      cp_async_wait_all();                    // this thread's parked operands have landed
       named_bar_sync(1, kStepConsumers);
+      if (*cons_abort) { dead = true; break; }
       if (tid == 0) *handoff = 1;
       STEP_TRACE(ph, 2);
 
       // ---- C. what follows the matrices in the block (modules/block.py:72-100)
       if (type == 0) {            // WKV update, sigmoid(r) * wkv -> input of the output projection
-        XsAcc acc; acc.zp = 0; acc.sxs = 0; acc.sx = 0; acc.amax = 0.f;
+        ++u_att;
+        XsAcc acc; acc.zp = 0.f; acc.sxs = 0.f; acc.sx = 0.f; acc.amax = 0.f;
         if (tid < nrD) {
           const int n = r0D + tid;
           const float k = value(0, tid), v = value(1, tid), r = sigmoidf_(value(2, tid));
           float aa = park[tid], bb = park[pstride + tid], pp = park[2 * pstride + tid];
           const float y = wkv_step(k, v, park[3 * pstride + tid], park[4 * pstride + tid], aa, bb, pp);
           st[2 * size_t(D) + n] = aa; st[3 * size_t(D) + n] = bb; st[4 * size_t(D) + n] = pp;
-          xs_emit(acc, P.xs_att, n, r * y, park[5 * pstride + tid], park[6 * pstride + tid]);
+          xs_emit(acc, P.xs_att, n, r * y, park[5 * pstride + tid], park[6 * pstride + tid], u_att & 1u);
         }
-        long long v3[3] = {acc.zp, acc.sxs, acc.sx};
-        float m1[1] = {acc.amax};
-        cta_reduce<3, 1>(v3, m1, red_ll, red_f);
-        if (tid < 3) pub_add(line_of(lines + 0), 32 + 32 * tid, v3[0]);
-        else if (tid == 32) pub_max(line_of(lines + 0), m1[0]);
+        float v3[3] = {acc.zp, acc.sxs, acc.sx}, m1[1] = {acc.amax};
+        cta_reduce<3, 1>(v3, m1, red);
+        if (tid < 3) write_record(P.part_att + size_t(cta) * kRecStride, 1 + tid, v3[0], u_att & 1u);
+        else if (tid == 32) write_record(P.part_att + size_t(cta) * kRecStride, 0, m1[0], u_att & 1u);
       } else if (type == 2) {     // relu(key)^2 -> input of the value projection; sigmoid(receptance) stays here
-        XsAcc acc; acc.zp = 0; acc.sxs = 0; acc.sx = 0; acc.amax = 0.f;
-        const StepMat* Mv = P.mats + mfirst + 2;
-        const float* vry = ptr_of(&Mv->ry);
-        const float* vmy = ptr_of(&Mv->my);
+        ++u_ffn;
+        XsAcc acc; acc.zp = 0.f; acc.sxs = 0.f; acc.sx = 0.f; acc.amax = 0.f;
+        const float* vry = rym_of(l, 6, 0);
+        const float* vmy = rym_of(l, 6, 1);
         for (int row = tid; row < snr[0]; row += kStepConsumers) {
           const int n = sr0[0] + row;
           float y = fmaxf(value(0, row), 0.f);
           y *= y;
           const bool parked = row < kStepConsumers;    // row == tid then: this thread parked them
-          xs_emit(acc, P.xs_ffn, n, y, parked ? park[row] : __ldg(vry + n), parked ? park[pstride + row] : __ldg(vmy + n));
+          xs_emit(acc, P.xs_ffn, n, y, parked ? park[row] : __ldg(vry + n), parked ? park[pstride + row] : __ldg(vmy + n), u_ffn & 1u);
         }
         if (tid < nrD) rf_own[tid] = sigmoidf_(value(1, tid));
-        long long v3[3] = {acc.zp, acc.sxs, acc.sx};
-        float m1[1] = {acc.amax};
-        cta_reduce<3, 1>(v3, m1, red_ll, red_f);
-        if (tid < 3) pub_add(line_of(lines + 4), 32 + 32 * tid, v3[0]);
-        else if (tid == 32) pub_max(line_of(lines + 4), m1[0]);
+        float v3[3] = {acc.zp, acc.sxs, acc.sx}, m1[1] = {acc.amax};
+        cta_reduce<3, 1>(v3, m1, red);
+        if (tid < 3) write_record(P.part_ffn + size_t(cta) * kRecStride, 1 + tid, v3[0], u_ffn & 1u);
+        else if (tid == 32) write_record(P.part_ffn + size_t(cta) * kRecStride, 0, m1[0], u_ffn & 1u);
       } else if (type == 4) {     // logits
         for (int row = tid; row < snr[0]; row += kStepConsumers) P.logits[sr0[0] + row] = value(0, row);
       } else {                    // residual update; a layer norm follows unless the step ends here
         if (tid < nrD) x_own[tid] = type == 1 ? value(0, tid) + x_own[tid] : value(0, tid) * rf_own[tid] + x_own[tid];
         if (type == 1 || more || P.logits) {
-          const int sline = type == 1 ? lines + 1 : lines + 5;
-          publish_stats(sline);
+          named_bar_sync(1, kStepConsumers);    // x_own complete
+          ++u_st;
+          publish_stats(u_st & 1u);
           STEP_TRACE(ph, 3);
-          bar_arrive();
-          if (bar_wait()) break;
+          gather_statistics(reinterpret_cast<double*>(smem + kSOffStat), P.part_st, G, D, P.inv_d, u_st & 1u, wctx, mean, rstd);
+          if (*cons_abort) { dead = true; break; }
           STEP_TRACE(ph + 1, 4);
-          if (warp * 32 < nrD) {
-            const unsigned char* line = line_of(sline);
-            const long long a = ld_act_s64(reinterpret_cast<const long long*>(line));
-            const long long b = ld_act_s64(reinterpret_cast<const long long*>(line + 32));
-            const long long c = ld_act_s64(reinterpret_cast<const long long*>(line + 64));
-            stats_finish(a, b, c, mean, rstd);
-          }
           continue;
         }
       }
       STEP_TRACE(ph, 3);
+    }
+    if (!dead && cta == 0 && tid == 0) {
+      P.uses[0] = u_kvr; P.uses[1] = u_att; P.uses[2] = u_fkr; P.uses[3] = u_ffn; P.uses[4] = u_head; P.uses[5] = u_st;
     }
   }
 
@@ -921,6 +953,7 @@ inline bool plan_step(int D, int F, int V, bool head, int num_sms, StepPlan* p) 
   auto rpc16 = [&](int N) { return ((N + G - 1) / G + 15) / 16 * 16; };
   const int rD = rpc16(D), rF = rpc16(F), rV = head ? rpc16(V) : 16;
   if ((D + G - 1) / G > kStepConsumers) return false;      // the layer-norm hop handles one row per consumer thread
+  if (G > 32 * kStepPartPerLane) return false;             // a warp gathers the CTAs' partial results, kStepPartPerLane per lane
   int kcD, kcF, n;
   step_mat_geometry(D, &kcD, &n);
   step_mat_geometry(F, &kcF, &n);

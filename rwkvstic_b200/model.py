@@ -153,11 +153,12 @@ class B200RWKV:
     RnnOnly = False  # sequence mode is supported (rwkvMaster.py:97 looks this up)
 
     def __init__(self, weights: QuantizedWeights, use_graph: bool = True, copy_logits: bool = True,
-                 decode_mode: str = "persistent"):
-        """``decode_mode``: how one-token steps run.  "persistent" (default): the whole step is one
-        resident kernel whose weight stream runs on from matrix to matrix
-        (b200rwkv_decode_step_persistent); "chained": one streaming launch per matrix group, chained
-        by programmatic dependent launch (b200rwkv_decode_step).  Both compute the same step."""
+                 decode_mode: str = "chained"):
+        """``decode_mode``: how one-token steps run.  "chained" (default, the faster one on a B200):
+        one streaming launch per matrix group, chained by programmatic dependent launch
+        (b200rwkv_decode_step); "persistent": the whole step is one resident kernel whose weight
+        stream runs on from matrix to matrix and whose CTAs exchange activations through tagged
+        words in L2 (b200rwkv_decode_step_persistent).  Both compute the same step."""
         if decode_mode not in ("persistent", "chained"):
             raise ValueError("decode_mode must be 'persistent' or 'chained'")
         self.w = weights
@@ -312,6 +313,8 @@ class B200RWKV:
             bits = int(self._status_host[0])
             if bits:
                 buf[:4].zero_()
+                if buf is self._plan:       # the exchange buffers' use counts are stale after an abandoned step
+                    _lib.check(self._L.b200rwkv_step_plan_init(C.byref(self._cmodel), self._plan.data_ptr(), self._plan.numel()))
                 raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
 
     def trace_persistent_step(self, token: int, state: torch.Tensor, replays: int = 3) -> torch.Tensor:

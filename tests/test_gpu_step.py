@@ -31,7 +31,7 @@ def states_agree(mine, ref, rtol=2e-3, atol=2e-4, row_rel=2e-5):
 def test_persistent_step_equals_chained_step(layers, embed, vocab):
     """Same weights, same tokens: the one-kernel step and the launch-per-matrix step give the same
     logits and state up to the fp32 rounding of the offset sums (the integer parts are exact in both)."""
-    one = B200RWKV.synthetic(layers, embed, vocab=vocab, seed=5, device=DEV, use_graph=False)
+    one = B200RWKV.synthetic(layers, embed, vocab=vocab, seed=5, device=DEV, use_graph=False, decode_mode="persistent")
     assert one.decode_mode == "persistent"
     many = B200RWKV(one.w, use_graph=False, decode_mode="chained")
     toks = synth_tokens(7, seed=9, vocab=vocab)
@@ -48,8 +48,8 @@ def test_persistent_step_equals_chained_step(layers, embed, vocab):
 
 
 def test_persistent_step_is_deterministic_and_graph_safe():
-    m = B200RWKV.synthetic(2, 768, vocab=1000, seed=6, device=DEV)       # graph path after the second call
-    eager = B200RWKV(m.w, use_graph=False)
+    m = B200RWKV.synthetic(2, 768, vocab=1000, seed=6, device=DEV, decode_mode="persistent")   # graph path after the second call
+    eager = B200RWKV(m.w, use_graph=False, decode_mode="persistent")
     toks = synth_tokens(10, seed=2, vocab=1000)
     sg, se = m.emptyState.clone(), eager.emptyState.clone()
     for t in toks:
@@ -65,7 +65,7 @@ def test_persistent_step_is_deterministic_and_graph_safe():
 
 
 def test_persistent_step_without_logits_leaves_the_same_state():
-    m = B200RWKV.synthetic(2, 256, vocab=300, seed=8, device=DEV, use_graph=False)
+    m = B200RWKV.synthetic(2, 256, vocab=300, seed=8, device=DEV, use_graph=False, decode_mode="persistent")
     toks = synth_tokens(4, seed=3, vocab=300)
     a, b = m.emptyState.clone(), m.emptyState.clone()
     for t in toks:
@@ -76,7 +76,7 @@ def test_persistent_step_without_logits_leaves_the_same_state():
 
 
 def test_step_geometry_and_plan_validation():
-    m = B200RWKV.synthetic(1, 128, vocab=300, seed=1, device=DEV, use_graph=False)
+    m = B200RWKV.synthetic(1, 128, vocab=300, seed=1, device=DEV, use_graph=False, decode_mode="persistent")
     geo = (C.c_int64 * 8)()
     _lib.check(m._L.b200rwkv_step_geometry(C.byref(m._cmodel), 148, geo))
     grid, stages, slot, smem = (int(geo[i]) for i in range(4))
@@ -93,22 +93,26 @@ def test_step_geometry_and_plan_validation():
 @pytest.mark.parametrize("embed", [2048, 2560, 4096, 5120])
 def test_two_block_model_against_the_oracle_at_the_large_widths(embed):
     """L = 2, V = 1024 at the widths of the 1.5B, 3B, 7B and 14B models: 32 tokens one at a time through
-    the persistent step, and 8 streams x 64 tokens through the tensor-core rows path, both against the
-    oracle's sequence mode (final logits and state)."""
+    both one-row paths (chained launches, persistent kernel), and 8 streams x 64 tokens through the
+    tensor-core rows path, all against the oracle's sequence mode (final logits and state)."""
     vocab = 1024
     ck = synth_checkpoint(2, embed, vocab=vocab, seed=40 + embed % 7)
     ref = OracleRWKV(ck)
     model = B200RWKV.from_checkpoint(ck, device=DEV, use_graph=False)
     toks = synth_tokens(32, seed=embed, vocab=vocab)
     want, wstate = ref.forward(toks, ref.emptyState.clone())
-    state = model.emptyState.clone()
-    for t in toks:
-        got, state = model.forward(t.reshape(1), state)
-    err = float((got.cpu().double() - want).abs().max())
-    assert err < TOL, f"D={embed} one-row path: max |dlogit| {err}"
-    ok, where = states_agree(model.to_reference_state(state), wstate)
-    assert ok, where
-    model.check_status()
+    errs = {}
+    for mode in ("chained", "persistent"):          # both one-row paths, token by token
+        m1 = model if mode == "chained" else B200RWKV(model.w, use_graph=False, decode_mode=mode)
+        state = m1.emptyState.clone()
+        for t in toks:
+            got, state = m1.forward(t.reshape(1), state)
+        errs[mode] = float((got.cpu().double() - want).abs().max())
+        assert errs[mode] < TOL, f"D={embed} one-row path ({mode}): max |dlogit| {errs[mode]}"
+        ok, where = states_agree(m1.to_reference_state(state), wstate)
+        assert ok, (mode, where)
+        m1.check_status()
+    err = max(errs.values())
 
     B, T = 8, 64
     btoks = synth_tokens(B * T, seed=embed + 1, vocab=vocab).reshape(B, T)
@@ -122,4 +126,4 @@ def test_two_block_model_against_the_oracle_at_the_large_widths(embed):
             ok, where = states_agree(model.to_reference_state(bstate[b]), ws)
             assert ok, where
     assert worst < TOL, f"D={embed} rows path: max |dlogit| {worst}"
-    print(f"D={embed}: max |dlogit| one-row {err:.2e}, rows {worst:.2e}")
+    print(f"D={embed}: max |dlogit| one-row chained {errs['chained']:.2e}, persistent {errs['persistent']:.2e}, rows {worst:.2e}")

@@ -304,7 +304,8 @@ int b200rwkv_argmax(const float* x, int rows, int n, int64_t ldx, int64_t* out, 
  *   temp,tau  > 0 (tau >= 1 keeps every token)
  *   u         device f32, uniform in [0,1): row r reads u[r + rows*step], step = *history_count
  *             when a history is given and 0 otherwise (so a captured decode loop draws a fresh
- *             number per replay from a buffer filled once)
+ *             number per replay from a buffer filled once); with a history u must hold
+ *             rows * history_capacity numbers, and steps beyond the capacity reuse the last one
  *   out       device int64 [rows]
  *   probs_out optional device f32 [rows][n]: the masked, tempered, unnormalised probabilities
  *   history   as b200rwkv_argmax; needs rows == 1

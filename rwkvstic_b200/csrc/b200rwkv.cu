@@ -185,7 +185,7 @@ embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ to
                  const float* __restrict__ w, const float* __restrict__ b, float* __restrict__ out,
                  PubSlot* __restrict__ pub, int npub) {
   __shared__ float red[16];
-  __shared__ long long redl[32];
+  __shared__ long long redl[48];
   __shared__ float bc;
   griddep_launch_dependents();
   griddep_wait();
@@ -214,21 +214,23 @@ embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ to
   s = 0.f;
   for (int i = tid; i < D; i += 512) { const float c = row[i] - mean; s += c * c; }
   const float sdev = sqrtf(block_sum(s) / float(D) + 1e-5f);
-  long long p_sum = 0, p_sq = 0;
+  long long p_sum = 0, p_sq = 0, p_sqlo = 0;
   for (int i = tid; i < D; i += 512) {
     const float y = w[i] * ((row[i] - mean) / sdev) + b[i];
     out[i] = y;
     p_sum += __float2ll_rn(y * kPubSumScale);
-    p_sq += __float2ll_rn(__fmul_rn(y, y) * kPubSqScale);
+    square_limbs(y, p_sq, p_sqlo);
   }
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) { p_sum += __shfl_xor_sync(0xffffffffu, p_sum, o); p_sq += __shfl_xor_sync(0xffffffffu, p_sq, o); }
-  if (lane == 0) { redl[warp * 2] = p_sum; redl[warp * 2 + 1] = p_sq; }
+  for (int o = 16; o > 0; o >>= 1) {
+    p_sum += __shfl_xor_sync(0xffffffffu, p_sum, o); p_sq += __shfl_xor_sync(0xffffffffu, p_sq, o); p_sqlo += __shfl_xor_sync(0xffffffffu, p_sqlo, o);
+  }
+  if (lane == 0) { redl[warp * 3] = p_sum; redl[warp * 3 + 1] = p_sq; redl[warp * 3 + 2] = p_sqlo; }
   __syncthreads();                      // also orders the zeroing of slot 0 before the store below
-  if (tid < 2) {
+  if (tid < 3) {
     long long a = 0;
-    for (int i = 0; i < 16; ++i) a += redl[i * 2 + tid];
-    if (tid == 0) pub[0].sum = a; else pub[0].sq = a;
+    for (int i = 0; i < 16; ++i) a += redl[i * 3 + tid];
+    if (tid == 0) pub[0].sum = a; else if (tid == 1) pub[0].sq = a; else pub[0].sq_lo = a;
   }
 }
 

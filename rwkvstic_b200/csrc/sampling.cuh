@@ -235,7 +235,9 @@ sample_typical_kernel(const float* __restrict__ x, int n, long long ldx, float t
       if (lane >= o) inc += t;
     }
     const double total = __shfl_sync(0xffffffffu, inc, 31);
-    const int step = (hist && hist_count) ? *hist_count : 0;
+    // u holds rows * history_capacity numbers when a history is kept: replays beyond the capacity reuse the last one
+    int step = (hist && hist_count) ? *hist_count : 0;
+    if (step >= hist_cap && hist_cap > 0) step = hist_cap - 1;
     const double target = double(u[row_id + size_t(gridDim.x) * step]) * total;
     const unsigned hit = __ballot_sync(0xffffffffu, loc > 0.0 && inc >= target);
     const unsigned nonzero = __ballot_sync(0xffffffffu, loc > 0.0);

@@ -386,7 +386,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
       return y;
     };
     // per-thread partials of what this launch publishes for the next one
-    long long p_sum = 0, p_sq = 0, p_zp = 0, p_sxs = 0, p_sx = 0;
+    long long p_sum = 0, p_sq = 0, p_sqlo = 0, p_zp = 0, p_sxs = 0, p_sx = 0;
     float p_amax = 0.f;
     PubSlot* pub_xs = nullptr;
     auto publish_xs = [&](const GemvSeg& sg, int n, float v, float ry, float my) {
@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
               publish_xs(P.seg[s], n, y, first ? e_ry[s] : P.seg[s].xs_ry[n], first ? e_my[s] : P.seg[s].xs_my[n]);
             if (s == 0 && P.pub_ln) {
               p_sum += __float2ll_rn(y * kPubSumScale);
-              p_sq += __float2ll_rn(__fmul_rn(y, y) * kPubSqScale);
+              square_limbs(y, p_sq, p_sqlo);
             }
           }
         }
@@ -438,29 +438,29 @@ __global__ void __launch_bounds__(kGemvThreads, 1) stream_gemv_kernel(const __gr
       // exact block totals (integers; the max is order-independent too), one atomic per quantity and CTA
       long long* esum = reinterpret_cast<long long*>(smem + kOffEpi);
       float* emax = reinterpret_cast<float*>(smem + kOffEpi + kConsumerWarps * 6 * 8);
-      long long v5[5] = {p_sum, p_sq, p_zp, p_sxs, p_sx};
+      long long v6[6] = {p_sum, p_sq, p_sqlo, p_zp, p_sxs, p_sx};
 #pragma unroll
-      for (int i = 0; i < 5; ++i)
+      for (int i = 0; i < 6; ++i)
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v5[i] += __shfl_xor_sync(0xffffffffu, v5[i], o);
+        for (int o = 16; o > 0; o >>= 1) v6[i] += __shfl_xor_sync(0xffffffffu, v6[i], o);
       p_amax = warp_max(p_amax);
       if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < 5; ++i) esum[warp * 6 + i] = v5[i];
+        for (int i = 0; i < 6; ++i) esum[warp * 6 + i] = v6[i];
         emax[warp] = p_amax;
       }
       named_bar_sync(1, kConsumers);
-      if (tid < 5) {
+      if (tid < 6) {
         long long a = 0;
         for (int w = 0; w < kConsumerWarps; ++w) a += esum[w * 6 + tid];
-        if (tid < 2) {
-          if (P.pub_ln) atomicAdd(reinterpret_cast<unsigned long long*>(tid == 0 ? &P.pub_ln->sum : &P.pub_ln->sq),
+        if (tid < 3) {
+          if (P.pub_ln) atomicAdd(reinterpret_cast<unsigned long long*>(tid == 0 ? &P.pub_ln->sum : (tid == 1 ? &P.pub_ln->sq : &P.pub_ln->sq_lo)),
                                   (unsigned long long)a);
         } else if (pub_xs) {
-          long long* dst = tid == 2 ? &pub_xs->zp : (tid == 3 ? &pub_xs->sumxs : &pub_xs->sumx);
+          long long* dst = tid == 3 ? &pub_xs->zp : (tid == 4 ? &pub_xs->sumxs : &pub_xs->sumx);
           atomicAdd(reinterpret_cast<unsigned long long*>(dst), (unsigned long long)a);
         }
-      } else if (tid == 5 && pub_xs) {
+      } else if (tid == 6 && pub_xs) {
         float m = 0.f;
         for (int w = 0; w < kConsumerWarps; ++w) m = fmaxf(m, emax[w]);
         atomicMax(&pub_xs->amax_bits, __float_as_uint(m));   // non-negative floats order like their bits

@@ -560,26 +560,39 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
 
   float mean = 0.f, rstd = 1.f, meanp = 0.f, rstdp = 1.f;
   if (ln) {
-    // sum and sum of squares of this row and of the previous one in a single pass and a single
-    // block reduction; variance = E[x^2] - mean^2 (the residual stream's mean is small against its spread)
+    // mean of this row and of the previous one, then the sums of squared deviations: two passes over
+    // registers and two block reductions, the centred form of modules/layernorm.py:11-20 (a single
+    // pass with E[x^2] - mean^2 cancels in fp32 when |mean| is large against the spread)
     float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < (REG ? G : 1); ++i)
       for (int g = tid + i * NT; g < NG; g += REG ? NG : NT) {
         const float4 x = x_at(i, g);
         s[0] += (x.x + x.y) + (x.z + x.w);
-        s[1] += (x.x * x.x + x.y * x.y) + (x.z * x.z + x.w * x.w);
         if (xp) {
           const float4 y = p_at(i, g);
           s[2] += (y.x + y.y) + (y.z + y.w);
-          s[3] += (y.x * y.x + y.y * y.y) + (y.z * y.z + y.w * y.w);
         }
       }
     block_sum4<NT>(s, red);
     const float invk = 1.0f / float(K);
     mean = s[0] * invk; meanp = s[2] * invk;
-    rstd = 1.0f / sqrtf(fmaxf(s[1] * invk - mean * mean, 0.f) + 1e-5f);
-    rstdp = 1.0f / sqrtf(fmaxf(s[3] * invk - meanp * meanp, 0.f) + 1e-5f);
+    float q[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < (REG ? G : 1); ++i)
+      for (int g = tid + i * NT; g < NG; g += REG ? NG : NT) {
+        const float4 x = x_at(i, g);
+        const float a0 = x.x - mean, a1 = x.y - mean, a2 = x.z - mean, a3 = x.w - mean;
+        q[0] += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+        if (xp) {
+          const float4 y = p_at(i, g);
+          const float b0 = y.x - meanp, b1 = y.y - meanp, b2 = y.z - meanp, b3 = y.w - meanp;
+          q[2] += (b0 * b0 + b1 * b1) + (b2 * b2 + b3 * b3);
+        }
+      }
+    block_sum4<NT>(q, red);
+    rstd = 1.0f / sqrtf(q[0] * invk + 1e-5f);
+    rstdp = 1.0f / sqrtf(q[2] * invk + 1e-5f);
     __syncthreads();   // red is reused by the statistics reduction below
   }
 

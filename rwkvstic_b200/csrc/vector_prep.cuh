@@ -28,19 +28,22 @@ constexpr int kMaxSeg = 3;
 constexpr float kQMax = 8355000.0f;  // |X| <= QMAX keeps all three signed digits inside int8
 
 // Fixed-point units of the published sums (int64 accumulators: exact, order-independent).  The
-// ranges they leave: |sum x|, sum x^2, |sum v*my|, |sum v| < 2.1e9 and |sum xs| < 8.3e6.
+// ranges they leave: |sum x|, |sum v*my|, |sum v| < 2.1e9 and |sum xs| < 8.3e6.  Squares are carried
+// in two limbs (see square_limbs): exact from 2^-60 to 2^55 per element, sums up to 3.6e16.
 constexpr float kPubSumScale = 4294967296.0f;        // 2^32
-constexpr float kPubSqScale = 4294967296.0f;         // 2^32
+constexpr float kPubSqHiScale = 256.0f;              // 2^8: high limb of a square
+constexpr float kPubSqLoScale = 1099511627776.0f;    // 2^40 on top of the 2^8: low limb in 2^-48 units
 constexpr float kPubXsScale = 1099511627776.0f;      // 2^40 (xs = v * ry is small: ry ~ 1e-3)
 
 // What the epilogue of one launch publishes for the preparation of the next (zeroed once per step).
 struct PubSlot {
   long long sum;              // sum_n x[n]   * 2^32   (x = the residual stream the launch wrote)
-  long long sq;               // sum_n x[n]^2 * 2^32
+  long long sq;               // high limb of sum_n x[n]^2: units of 2^-8
   unsigned amax_bits;         // float bits of max_n |xs[n]|  (xs = next input, already times ry)
   unsigned pad;
   long long zp, sumxs, sumx;  // sum v*my * 2^32, sum xs * 2^40, sum v * 2^32
-  long long reserved[10];
+  long long sq_lo;            // low limb of sum_n x[n]^2: units of 2^-48
+  long long reserved[9];
 };
 static_assert(sizeof(PubSlot) == 128, "PubSlot is one 128-byte line");
 
@@ -79,6 +82,34 @@ struct PrepParams {
   SegScalars* scal;       // out: nseg entries
   unsigned long long* trace;  // optional: 4 stamps (entry, dependency resolved, statistics, done)
 };
+
+// y^2, exactly, as two integers added to hi (units of 2^-8) and lo (units of 2^-48): the rounded
+// product p = fl(y*y) is split into rint(p * 2^8) and its remainder, and the rounding error of the
+// product itself, e = fma(y, y, -p), goes to lo as well.  Every step is exact (power-of-two
+// scalings; the remainder of a float against its rounding to an integer and the error of a product
+// are floats), so sums of either limb are order-free and carry sum y^2 without any rounding for
+// 2^-24 <= |y| < 2^27.
+__device__ __forceinline__ void square_limbs(float y, long long& hi, long long& lo) {
+  const float p = __fmul_rn(y, y);
+  const float e = __fmaf_rn(y, y, -p);
+  const float s = __fmul_rn(p, kPubSqHiScale);
+  const float sh = rintf(s);
+  hi += __float2ll_rn(sh);
+  lo += __float2ll_rn(__fmul_rn(__fsub_rn(s, sh), kPubSqLoScale)) + __float2ll_rn(__fmul_rn(e, 281474976710656.0f));
+}
+
+// Mean and 1/sqrt(variance + 1e-5) of K values from their published sums.  var = E[x^2] - mean^2 is
+// evaluated in fp64 on exact sums, so it does not cancel when |mean| is large against the spread
+// (the reference centres first, modules/layernorm.py:11-20).  Multiplications only: fp64 division
+// and square root are subroutines.
+__device__ __forceinline__ void stats_from_sums(long long sum, long long sq_hi, long long sq_lo, int K, float& mean, float& rstd) {
+  const double inv_k = double(1.0f / float(K)) * (2.0 - double(K) * double(1.0f / float(K)));   // one Newton step: 1/K to fp64 accuracy
+  const double mu = double(sum) * (1.0 / 4294967296.0) * inv_k;
+  const double q = double(sq_hi) * (1.0 / 256.0) + double(sq_lo) * (1.0 / 281474976710656.0);
+  const double var = q * inv_k - mu * mu;
+  mean = float(mu);
+  rstd = 1.0f / sqrtf(fmaxf(float(var), 0.f) + 1e-5f);
+}
 
 // rint(v) for 0 <= v < 2^23 without the conversion pipe: the sum with 2^23 holds it in the mantissa.
 __device__ __forceinline__ int rint_nonneg(float v) { return __float_as_int(__fadd_rn(v, 8388608.0f)) - 0x4B000000; }
@@ -180,10 +211,8 @@ __device__ __forceinline__ void prep_body(const PrepParams& P, unsigned char* st
     }
     if (LN && batch == 0) {
       // same round trip: the launch that wrote ln_x published its sum and sum of squares (exact
-      // integer atomics).  fp32 from here on: the fp64 pipe of this GPU is slow.
-      mean = __ll2float_rn(__ldcg(&P.pub->sum)) * (1.0f / (kPubSumScale * float(K)));
-      const float ex2 = __ll2float_rn(__ldcg(&P.pub->sq)) * (1.0f / (kPubSqScale * float(K)));
-      rstd = 1.0f / sqrtf(fmaxf(ex2 - mean * mean, 0.f) + 1e-5f);
+      // integer atomics); a handful of fp64 multiplications finish them
+      stats_from_sums(__ldcg(&P.pub->sum), __ldcg(&P.pub->sq), __ldcg(&P.pub->sq_lo), K, mean, rstd);
       if (tid == 0 && P.trace && sidx == 0) P.trace[2] = globaltimer_ns();
     }
 #pragma unroll

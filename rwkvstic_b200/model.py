@@ -373,31 +373,95 @@ class B200RWKV:
             raise ValueError(f"forward_rows needs a contiguous fp32 state [{B},{self.n_layer},5,{self.n_embd}] on the model's device")
         if B > 65535:
             raise ValueError("forward_rows: at most 65535 streams per call")
+        self._raise_rows_status()            # the previous call's status word, read back without blocking
+        if T == 1 and self.use_graph:
+            return self._rows_decode_replay(tokens, state)
         out = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device)
         step = max(1, min(self.rows_per_call, 65535) // B)
         with torch.cuda.device(self.device):
             toks = tokens.to(device=self.device, dtype=torch.int64)
-            stream = torch.cuda.current_stream(self.device).cuda_stream
             for t0 in range(0, T, step):
                 piece = toks[:, t0:t0 + step].contiguous()
                 tp = piece.shape[1]
-                ws = self._rows_ws.get((B, tp))
-                if ws is None:
-                    n = int(self._L.b200rwkv_rows_workspace_bytes(C.byref(self._cmodel), B, tp))
-                    if len(self._rows_ws) >= 4:
-                        self._rows_ws.clear()
-                    ws = self._rows_ws[(B, tp)] = torch.zeros(n, dtype=torch.uint8, device=self.device)
+                ws = self._rows_workspace(B, tp)
                 last = t0 + step >= T
-                _lib.check(self._L.b200rwkv_forward_rows(C.byref(self._cmodel), piece.data_ptr(), B, tp, state.data_ptr(),
-                                                         state.stride(0), out.data_ptr() if last else None,
-                                                         ws.data_ptr(), ws.numel(), stream))
-                self.launch_count += self._rows_launches(tp) + 1 + (2 if last else 0)
-                self._status_host.copy_(ws[:4].view(torch.int32))
-                bits = int(self._status_host[0])
-                if bits:
-                    ws[:4].zero_()
-                    raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+                self._rows_call(piece, B, tp, state, out if last else None, ws)
+            self._queue_rows_status(ws)
         return out
+
+    def _rows_workspace(self, B: int, tp: int) -> torch.Tensor:
+        ws = self._rows_ws.get((B, tp))
+        if ws is None:
+            n = int(self._L.b200rwkv_rows_workspace_bytes(C.byref(self._cmodel), B, tp))
+            if len(self._rows_ws) >= 4:
+                self._rows_ws.clear()
+            ws = self._rows_ws[(B, tp)] = torch.zeros(n, dtype=torch.uint8, device=self.device)
+        return ws
+
+    def _rows_call(self, piece: torch.Tensor, B: int, tp: int, state: torch.Tensor, out: Optional[torch.Tensor],
+                   ws: torch.Tensor) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(self._L.b200rwkv_forward_rows(C.byref(self._cmodel), piece.data_ptr(), B, tp, state.data_ptr(),
+                                                 state.stride(0), None if out is None else out.data_ptr(),
+                                                 ws.data_ptr(), ws.numel(), stream))
+        self.launch_count += self._rows_launches(tp) + 1 + (2 if out is not None else 0)
+
+    def _queue_rows_status(self, ws: torch.Tensor) -> None:
+        """Start a non-blocking copy of a rows workspace's status word to pinned host memory; the next
+        rows call (or check_rows_status) looks at it, so an expired device-side wait is reported one call
+        late instead of costing every call a device synchronisation."""
+        if not hasattr(self, "_rows_status_host"):
+            self._rows_status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._rows_status_event = torch.cuda.Event()
+        self._rows_status_host.copy_(ws[:4].view(torch.int32), non_blocking=True)
+        self._rows_status_event.record(torch.cuda.current_stream(self.device))
+        self._rows_status_ws = ws
+
+    def _raise_rows_status(self) -> None:
+        ws = getattr(self, "_rows_status_ws", None)
+        if ws is None:
+            return
+        self._rows_status_event.synchronize()      # recorded one call ago: long since reached
+        self._rows_status_ws = None
+        bits = int(self._rows_status_host[0])
+        if bits:
+            ws[:4].zero_()
+            raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+
+    def _rows_decode_replay(self, tokens: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        """One token for each of B streams (batched decode) as a CUDA-graph replay: the ~9 launches per
+        block are captured once per (B, state buffer) - from the second call with the same state buffer
+        on - into static token and logits buffers.  Returns the logits ``[B,V]``; with
+        ``copy_logits=False`` that is the static buffer, valid until the next call."""
+        B = tokens.shape[0]
+        key = (B, state.data_ptr())
+        if not hasattr(self, "_rows_graphs"):
+            self._rows_graphs: Dict[Tuple[int, int], dict] = {}
+        ent = self._rows_graphs.get(key)
+        with torch.cuda.device(self.device):
+            if ent is None:
+                if len(self._rows_graphs) >= 8:
+                    self._rows_graphs.clear()
+                ent = self._rows_graphs[key] = {"tok": torch.zeros(B, 1, dtype=torch.int64, device=self.device),
+                                                "out": torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device),
+                                                "ws": self._rows_workspace(B, 1), "graph": None, "seen": 0}
+            ent["tok"].copy_(tokens.reshape(B, 1), non_blocking=True)
+            ent["seen"] += 1
+            if ent["graph"] is None and ent["seen"] >= 2:
+                g = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize(self.device)
+                count = self.launch_count
+                with torch.cuda.graph(g):
+                    self._rows_call(ent["tok"], B, 1, state, ent["out"], ent["ws"])
+                self.launch_count = count       # the capture itself runs nothing
+                ent["graph"] = g
+            if ent["graph"] is not None:
+                ent["graph"].replay()
+                self.launch_count += self._rows_launches(1) + 3
+            else:
+                self._rows_call(ent["tok"], B, 1, state, ent["out"], ent["ws"])
+            self._queue_rows_status(ent["ws"])
+        return ent["out"].clone() if self.copy_logits else ent["out"]
 
     def forward_rows_stage(self, tokens: Optional[torch.Tensor], x: torch.Tensor, state: torch.Tensor,
                            want_logits: bool) -> Optional[torch.Tensor]:
@@ -437,7 +501,9 @@ class B200RWKV:
         return out
 
     def check_rows_status(self) -> None:
-        """Raise if a kernel of the last ``forward_rows_stage`` call reported an expired wait (synchronises)."""
+        """Raise if a kernel of the last ``forward_rows`` / ``forward_rows_stage`` call reported an expired
+        wait (synchronises)."""
+        self._raise_rows_status()
         ws = getattr(self, "_last_rows_ws", None)
         if ws is None:
             return

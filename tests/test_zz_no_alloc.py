@@ -24,14 +24,14 @@ def _matrix(n, k, seed):
                        ry=torch.rand(k, generator=g) * 1e-3 + 1e-4, my=torch.randn(k, generator=g) * 0.05).to(DEV)
 
 
-def _static_call(mats, xs, ys, status):
+def _static_call(mats, xs, ys, status, accumulate=0):
     n = len(mats)
     cm = (_lib.Matrix * n)(*[_lib.Matrix(m.qt.data_ptr(), m.ry.data_ptr(), m.my.data_ptr(), None, None, 0.0,
                                          m.n_out, m.k_in) for m in mats])
     cx = (C.c_void_p * n)(*[x.data_ptr() for x in xs])
     cy = (C.c_void_p * n)(*[y.data_ptr() for y in ys])
     stream = torch.cuda.current_stream(torch.device(DEV)).cuda_stream
-    return _lib.lib().b200rwkv_gemv_u8_static(n, cm, cx, cy, 0, status.data_ptr(), stream)
+    return _lib.lib().b200rwkv_gemv_u8_static(n, cm, cx, cy, accumulate, None if status is None else status.data_ptr(), stream)
 
 
 def test_static_scratch_variant_matches_workspace_variant_twice_in_a_row():
@@ -49,6 +49,28 @@ def test_static_scratch_variant_matches_workspace_variant_twice_in_a_row():
         for a, b in zip(got, want):
             assert torch.equal(a, b)                               # same kernels, same bits
     assert int(status.item()) == 0
+
+
+def test_static_scratch_variant_without_status_word_and_with_accumulate():
+    """The two documented options: no status word (NULL), and adding onto the caller's outputs."""
+    torch.cuda.set_device(0)
+    mats = [_matrix(515, 1024, s) for s in (7, 8)]
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.randn(1024, generator=g).to(DEV) for _ in mats]
+    want = ops.gemv_u8(mats, xs)
+    got = [torch.full((m.n_out,), 5.0, device=DEV) for m in mats]
+    assert _static_call(mats, xs, got, None) == _lib.OK, _lib.lib().b200rwkv_last_error()
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    base = [torch.randn(m.n_out, generator=g).to(DEV) for m in mats]
+    acc_want = [b.clone() for b in base]
+    ops.gemv_u8(mats, xs, acc_want, accumulate=True)
+    acc_got = [b.clone() for b in base]
+    assert _static_call(mats, xs, acc_got, None, accumulate=1) == _lib.OK, _lib.lib().b200rwkv_last_error()
+    torch.cuda.synchronize()
+    for a, b in zip(acc_got, acc_want):
+        assert torch.equal(a, b)
 
 
 def test_static_scratch_variant_rejects_oversize_requests():

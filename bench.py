@@ -16,9 +16,20 @@ Keys beyond the basic contract:
              free): algorithmic bytes per launch / average launch duration vs the measured
              copy bandwidth of this pool's B200s.
   kernels    the same kernel timed alone (CUDA events around single launches), per matrix shape.
+  decode_1b5 the same batch-1 decode at the 1.5B shape (the configuration whose purpose is the GEMV's
+             HBM bandwidth when the launch chain, not the stream, dominates).
+  batched_decode, prefill
+             256 streams per GPU / the 3B 8 x 1024 prompt through the tensor-core rows path; each with
+             library_baseline = the reference's own GPU formulation of the same matrices (cast the
+             uint8 weights to bf16, cuBLAS GEMM: modules/matmul.py:57, :87-89) timed with stock torch on
+             the same box - a comparison only, never on the product path.
+  split_decode, layer_split (N > 1), config4_one_gpu (N = 1)
+             256 streams SPLIT over the ranks (strong scaling, no collective); the 14B shape with its
+             blocks partitioned over the ranks (NCCL point-to-point hand-off), and the same model on one GPU.
   cpu_baseline / --impl reference
-             the CPU oracle (a port of the reference's FASTQUANT CPU path) timed on the host
-             cores on a bounded sample: one 7B-shape block + the head, extrapolated to 32 blocks.
+             the CPU oracle (a port of the reference's FASTQUANT CPU path) timed on the host cores:
+             the whole 169M-shape schedule (32 prompt + 64 greedy tokens), and a bounded sample at
+             the 7B shape (one block + the head, extrapolated to 32 blocks; "extrapolated": true).
 """
 from __future__ import annotations
 
@@ -48,6 +59,19 @@ def measured_peaks():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+def measured_traffic_ratio():
+    """DRAM (read + write) bytes of one stream_gemv_kernel launch over its algorithmic bytes, as the
+    committed ncu summary of the current build states it (line `traffic_ratio = X`)."""
+    import re
+    path = os.path.join(ROOT, "profiles", "stream_gemv_kernel_7b_ffn_key_rec_ncu.md")
+    try:
+        with open(path) as f:
+            m = re.search(r"traffic_ratio\s*=\s*([0-9.]+)", f.read())
+        return (float(m.group(1)), os.path.relpath(path, ROOT)) if m else (None, None)
+    except OSError:
+        return None, None
 
 
 def decode_bytes_per_token(L, D, V=VOCAB, F=None):
@@ -118,7 +142,26 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------- CPU reference arm
-def cpu_reference(shape, steps, warmup):
+def cpu_full_schedule(layers, embed, prompt_len, decode_steps, vocab=VOCAB):
+    """The oracle through a whole schedule (prompt in sequence mode, then greedy decode), timed."""
+    from oracle.fastquant_oracle import OracleRWKV
+    from rwkvstic_b200.synth import synth_checkpoint, synth_tokens
+    t0 = time.perf_counter()
+    model = OracleRWKV(synth_checkpoint(layers, embed, vocab=vocab, seed=1234))
+    t_load = time.perf_counter() - t0
+    state = model.emptyState.clone()
+    t0 = time.perf_counter()
+    logits, state = model.forward(synth_tokens(prompt_len, seed=38, vocab=vocab), state)
+    t_prompt = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    for _ in range(decode_steps):
+        logits, state = model.forward(torch.tensor([int(torch.argmax(logits))]), state)
+    t_dec = time.perf_counter() - t0
+    return {"shape": f"L={layers} D={embed} V={vocab}", "load_quantise_s": t_load, "prompt_tokens": prompt_len, "prompt_s": t_prompt,
+            "decode_steps": decode_steps, "decode_tokens_per_s": decode_steps / t_dec, "extrapolated": False}
+
+
+def cpu_reference(shape, steps, warmup, with_1b5=False):
     """tokens/s of the CPU oracle at this shape, from a bounded sample (one block + head)."""
     from oracle.fastquant_oracle import OracleRWKV
     from rwkvstic_b200.synth import synth_checkpoint
@@ -145,17 +188,25 @@ def cpu_reference(shape, steps, warmup):
     t_head = (time.perf_counter() - t0) / n
     t_block = max(t_model - t_head, 1e-9)
     t_token = L * t_block + t_head
-    return {"value": 1.0 / t_token, "unit": UNIT, "cores": cores, "kind": "port",
+    del model
+    # whole schedules where they fit the time budget: the 169M shape in full; the 1.5B shape (reference arm
+    # only) with its 64-token prompt and a bounded number of decode steps
+    full = {"169m": cpu_full_schedule(*SHAPES["169m"], 32, 64)}
+    if with_1b5:
+        full["1b5"] = cpu_full_schedule(*SHAPES["1b5"], 64, 8)
+        full["1b5"]["note"] = "64-token prompt in full, 8 of the 512 decode steps"
+    return {"value": 1.0 / t_token, "unit": UNIT, "cores": cores, "kind": "port", "extrapolated": True,
             "sample": f"oracle port of the reference FASTQUANT CPU path (uint8 weights cast to fp32 per call, "
                       f"fp32 matmul, fp64 vectors), {n} decode steps of a 1-block D={D} model + head: "
-                      f"{t_block * 1e3:.1f} ms/block, {t_head * 1e3:.1f} ms/head, extrapolated to {L} blocks"}
+                      f"{t_block * 1e3:.1f} ms/block, {t_head * 1e3:.1f} ms/head, extrapolated to {L} blocks",
+            "full_schedules": full}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
     L, D = SHAPES[args.shape]
-    base = cpu_reference(args.shape, args.steps, args.warmup)
+    base = cpu_reference(args.shape, args.steps, args.warmup, with_1b5=True)
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / base["value"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 weights, f32 matmul, f64 vectors",
@@ -225,6 +276,185 @@ def matrix_params(L, D, V=VOCAB):
     return L * (4 * D * D + 2 * D * F + D * D) + V * D
 
 
+def library_baseline_ms(model, rows, head_rows=None, reps=3):
+    """The reference's own GPU formulation of the network's matrices for `rows` activation rows
+    (modules/matmul.py:57, :87-89): scale the activations by `range`, cast them and the uint8 weights
+    to bf16, one cuBLAS GEMM per matrix, plus the offset term; timed with stock torch over all
+    blocks + head.  A comparison figure (how fast the library path is on this box), not a product path."""
+    dev = model.device
+    D, F = model.n_embd, model.n_ffn
+    xs = {D: torch.randn(rows, D, device=dev), F: torch.randn(rows, F, device=dev)}
+
+    def one_pass():
+        for ly in model.w.layers:
+            for m in ly.mat.values():
+                x = xs[m.k_in]
+                y = ((x * m.ry).to(torch.bfloat16) @ m.qt.to(torch.bfloat16).t()).float()     # qt is [out][in]
+                y += (x @ m.my).unsqueeze(1)
+        h = model.w.head
+        x = xs[D][:head_rows if head_rows else rows]
+        y = ((x * h.ry).to(torch.bfloat16) @ h.qt.to(torch.bfloat16).t()).float()
+        y += (x @ h.my).unsqueeze(1)
+    one_pass()
+    times = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        one_pass()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def time_decode_shape(shape, dev, steps=128, warm=8):
+    """Batch-1 decode at another shape (graph-replayed steps, tokens resident): tokens/s and roofline."""
+    from rwkvstic_b200.model import B200RWKV
+    L, D = SHAPES[shape]
+    model = B200RWKV.synthetic(L, D, seed=1234, device=dev, copy_logits=False)
+    toks = torch.randint(0, VOCAB, (steps + warm,), generator=torch.Generator().manual_seed(11), dtype=torch.int64).to(dev)
+    state = model.emptyState.clone()
+    for i in range(warm):
+        model.forward(toks[i:i + 1], state)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(warm, warm + steps):
+        model.forward(toks[i:i + 1], state)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    model.check_status()
+    ms = e0.elapsed_time(e1) / steps
+    _, total = decode_bytes_per_token(L, D)
+    peak, _ = measured_peaks()
+    gbs = total / (ms * 1e-3) / 1e9
+    return {"workload": f"RWKV-4 {shape} shape L={L} D={D} V={VOCAB}, batch-1 decode", "value": 1e3 / ms, "unit": UNIT,
+            "ms_per_step": ms, "steps": steps,
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                         "frac_of_nominal_8TBs": gbs / 8000.0}}
+
+
+def trace_spans(model, dev):
+    """Mean over the 4L+1 GEMV launches of a graph-replayed traced step: from "launch dependency resolved"
+    (median over CTAs) to "epilogue done" (last CTA) = the launch's working span, and from "digit planes
+    in shared memory" to "all rows summed" (medians) = the part in which weights stream."""
+    state = model.emptyState.clone()
+    tr = model.trace_step(17, state, graph=True).double()          # [4L+1, 1024, 8] ns
+    grid = int((tr[0, :1023, 0] > 0).sum())
+    g = tr[:, :grid]
+    dep, planes, rows, epi = g[:, :, 1].median(dim=1).values, g[:, :, 4].median(dim=1).values, g[:, :, 5].median(dim=1).values, g[:, :, 6].max(dim=1).values
+    return {"launch_us": float((epi - dep).mean() / 1e3), "stream_us": float((rows - planes).mean() / 1e3),
+            "step_us_in_trace": float((g[-1, :, 6].max() - tr[0, 1023, 0]) / 1e3), "grid": grid}
+
+
+def time_config4_one_gpu(dev, streams=64, steps=16):
+    """The 14B shape whole on one GPU: `streams`-stream decode and a 2048-token prompt (512-token pieces),
+    the figures the layer split over several GPUs is to be read against."""
+    from rwkvstic_b200.model import B200RWKV
+    L, D = SHAPES["14b"]
+    model = B200RWKV.synthetic(L, D, seed=1234, device=dev, copy_logits=False)
+    tok = torch.randint(0, VOCAB, (streams, 1), generator=torch.Generator().manual_seed(5), dtype=torch.int64).to(dev)
+    state = model.empty_batch_state(streams)
+    for _ in range(3):
+        tok = model.forward_rows(tok, state).argmax(dim=1, keepdim=True)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        tok = model.forward_rows(tok, state).argmax(dim=1, keepdim=True)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    dec_ms = e0.elapsed_time(e1) / steps
+    prompt = torch.randint(0, VOCAB, (1, 2048), generator=torch.Generator().manual_seed(6), dtype=torch.int64).to(dev)
+    model.rows_per_call = 512
+    pst = model.empty_batch_state(1)
+    model.forward_rows(prompt, pst)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    model.forward_rows(prompt, model.empty_batch_state(1))
+    e1.record()
+    torch.cuda.synchronize(dev)
+    model.check_rows_status()
+    pre_ms = e0.elapsed_time(e1)
+    return {"workload": f"RWKV-4 14b shape L={L} D={D}, all blocks on one GPU", "streams": streams, "decode_ms_per_step": dec_ms,
+            "decode_tokens_per_s": streams / (dec_ms * 1e-3), "prefill_tokens": 2048, "prefill_ms": pre_ms,
+            "prefill_tokens_per_s": 2048 / (pre_ms * 1e-3)}
+
+
+def time_layer_split(rank, world, dev, streams=64, steps=16):
+    """The 14B shape with its blocks partitioned over the ranks: decode of `streams` streams and a
+    2048-token prompt in 512-token pieces.  CUDA events, max over ranks."""
+    import torch.distributed as dist
+    from rwkvstic_b200 import layer_split as LS
+    from rwkvstic_b200.synth import iter_synth_tensors
+    L, D = SHAPES["14b"]
+    model = LS.build_stage(iter_synth_tensors(L, D, VOCAB, 1234, device=str(dev)), rank, world, L, dev)
+    pipe = LS.make_pipeline(model, rank, world)
+
+    def timed(fn):
+        torch.cuda.synchronize(dev); dist.barrier(); torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize(dev); dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    state = LS.empty_stage_state(model, streams)
+    tok = torch.randint(0, VOCAB, (streams, 1), generator=torch.Generator().manual_seed(5), dtype=torch.int64)
+    pipe.decode_greedy(tok, state, 3, 1)
+    dec_ms = timed(lambda: pipe.decode_greedy(tok, state, steps, 1)) / steps
+    pstate = LS.empty_stage_state(model, 1)
+    prompt = torch.randint(0, VOCAB, (1, 2048), generator=torch.Generator().manual_seed(6), dtype=torch.int64).to(dev)
+    pipe.rows_per_item = 512
+    pipe.forward_rows(prompt, pstate)
+    pre_ms = timed(lambda: pipe.forward_rows(prompt, pstate))
+    model.check_rows_status()
+    del model, pipe, state, pstate
+    torch.cuda.empty_cache()
+    return {"workload": f"RWKV-4 14b shape L={L} D={D}, blocks split contiguously over {world} GPUs, {streams} streams, "
+                        "one stream group", "decode_ms_per_step": dec_ms, "decode_tokens_per_s": streams / (dec_ms * 1e-3),
+            "prefill_tokens": 2048, "prefill_ms": pre_ms, "prefill_tokens_per_s": 2048 / (pre_ms * 1e-3),
+            "handoff": "NCCL send/recv of the fp32 residual stream [rows, D] between consecutive ranks; sampled ids last -> first rank",
+            "limit": "a decode step is a chain through all stages (each streams its blocks' weights once), so the split adds "
+                     "capacity, not decode speed; the prompt's 512-token pieces pipeline across the stages"}
+
+
+def time_split_decode(model, rank, world, dev, total_streams=256, steps=16):
+    """BASELINE config 3 as written: `total_streams` independent streams SPLIT over the ranks
+    (strong scaling), each rank decoding its shard on a replica; no collective on the data path."""
+    import torch.distributed as dist
+    from rwkvstic_b200.parallel import decode_sharded, stream_shard
+    shard = stream_shard(total_streams, world, rank)
+    gen = torch.Generator().manual_seed(21)
+    toks = torch.randint(0, VOCAB, (total_streams, 1), generator=gen, dtype=torch.int64).to(dev)
+    state = model.empty_batch_state(total_streams)[shard.start:shard.stop].contiguous()
+    full_state_view = {"s": state}
+
+    def step(tk):
+        lg = model.forward_rows(tk, full_state_view["s"])
+        return lg.argmax(dim=1, keepdim=True)
+    tk = toks[shard.start:shard.stop].contiguous()
+    for _ in range(3):
+        tk = step(tk)
+    torch.cuda.synchronize(dev); dist.barrier(); torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        tk = step(tk)
+    e1.record()
+    torch.cuda.synchronize(dev); dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0]) / steps
+    return {"total_streams": total_streams, "streams_per_gpu": len(shard), "ms_per_step": ms,
+            "value": total_streams / (ms * 1e-3), "unit": UNIT, "scaling": "strong",
+            "api": "parallel.stream_shard + B200RWKV.forward_rows on each rank's shard (the kernels of parallel.decode_sharded)"}
+
+
 def time_prefill(dev, tf_peak, B=8, T=1024):
     """Prompt ingestion at the 3B shape: B streams x T tokens in sequence mode through forward_rows."""
     from rwkvstic_b200.model import B200RWKV
@@ -244,9 +474,13 @@ def time_prefill(dev, tf_peak, B=8, T=1024):
             times.append(e0.elapsed_time(e1))
     ms = statistics.median(times)
     alg = 2.0 * (matrix_params(L, D) - VOCAB * D) * B * T / (ms * 1e-3) / 1e12   # the head runs on B rows only
+    lib_ms = library_baseline_ms(model, B * T, head_rows=B, reps=2)
     return {"workload": f"RWKV-4 3b shape L={L} D={D}, {B} streams x {T} tokens, sequence mode", "ms": ms,
             "value": B * T / (ms * 1e-3), "unit": UNIT, "rows_per_call": model.rows_per_call,
-            "tensor": {"algorithmic_tflops": alg, "peak_bf16_tflops": tf_peak, "frac_of_measured_bf16": alg / tf_peak}}
+            "tensor": {"algorithmic_tflops": alg, "peak_bf16_tflops": tf_peak, "frac_of_measured_bf16": alg / tf_peak},
+            "library_baseline": {"what": "matrices only (all blocks + the head on the last rows): activations * range and uint8 weights "
+                                         "cast to bf16 per call, cuBLAS GEMM, offset term; stock torch, same box",
+                                 "ms": lib_ms, "ours_over_library": ms / lib_ms}}
 
 
 def run_layer_split(args, rank, world, local_rank):
@@ -385,6 +619,10 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.stop(set(range(world))) if rank == 0 else None
     launches_b = model.launch_count - launches_b0
     del bstate
+    model.check_rows_status()
+    extra = {}
+    if world > 1:
+        extra["split_decode"] = time_split_decode(model, rank, world, dev, total_streams=args.streams)
 
     if world > 1:
         t = torch.tensor([ms, e2e_ms, batched_ms], device=dev, dtype=torch.float64)
@@ -399,6 +637,7 @@ def run_ours(args, rank, world, local_rank):
         peak, peak_src = measured_peaks()
         step_ms = ms / K
         n_gemv = 4 * L + 1   # streaming GEMV launches per step; the preparation CTAs run beside them
+        traffic_ratio, traffic_src = measured_traffic_ratio()
         achieved = total_bytes / (step_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": world * K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
@@ -413,9 +652,10 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         # DRAM read+write bytes per launch: the ncu capture of one 83.9 MB launch of this
-                         # kernel moved 1.043x its algorithmic bytes; traffic scales with the bytes streamed
-                         "traffic": 1.043 * total_bytes / n_gemv, "peak_source": peak_src,
+                         # DRAM read + write bytes per launch: algorithmic bytes x the ratio the committed ncu
+                         # summary of one 83.9 MB launch of the current build states (traffic grows with the bytes streamed)
+                         "traffic": (traffic_ratio * total_bytes / n_gemv) if traffic_ratio else None,
+                         "traffic_source": traffic_src, "peak_source": peak_src,
                          "kernel": "stream_gemv_kernel", "launches_per_step": n_gemv,
                          "algorithmic_bytes_per_launch": total_bytes / n_gemv,
                          "avg_launch_us": step_ms * 1e3 / n_gemv,
@@ -430,17 +670,38 @@ def run_ours(args, rank, world, local_rank):
             "kernel": "tile_gemm_kernel (tcgen05 kind::i8, three 8-bit activation digits per row)",
             "tensor": {"algorithmic_tflops": alg_tflops, "peak_bf16_tflops": tf_peak,
                        "frac_of_measured_bf16": alg_tflops / tf_peak if tf_peak else None}}
+        line.update(extra)
         if world == 1:
+            spans = trace_spans(model, dev)
+            line["roofline"]["avg_launch_us"] = spans["launch_us"]
+            line["roofline"]["avg_stream_us"] = spans["stream_us"]
+            line["roofline"]["launch_span"] = ("graph-replayed traced step: per GEMV launch, dependency resolved (median CTA) -> "
+                                               "epilogue done (last CTA); stream = digit planes in shared memory -> rows summed")
+            lib_ms = library_baseline_ms(model, Bs)
+            line["batched_decode"]["library_baseline"] = {
+                "what": "matrices only (all blocks + head): activations * range and uint8 weights cast to bf16 per call, "
+                        "cuBLAS GEMM, offset term; stock torch, same box", "ms_per_step": lib_ms,
+                "ours_over_library": (batched_ms / Kb) / lib_ms}
             line["kernels"] = time_isolated_kernels(model)
-            if not args.no_prefill:
-                del model
-                torch.cuda.empty_cache()
-                model = None
-                line["prefill"] = time_prefill(dev, tf_peak)
-            if not args.no_cpu_baseline:
-                model = None
-                torch.cuda.empty_cache()
-                line["cpu_baseline"] = cpu_reference(args.shape, 4, 1)
+    if world > 1:
+        del model
+        torch.cuda.empty_cache()
+        ls = time_layer_split(rank, world, dev)
+        if rank == 0:
+            line["layer_split"] = ls
+    elif rank == 0:
+        del model
+        torch.cuda.empty_cache()
+        model = None
+        line["decode_1b5"] = time_decode_shape("1b5", dev)
+        if not args.no_prefill:
+            line["prefill"] = time_prefill(dev, tf_peak)
+            torch.cuda.empty_cache()
+            line["config4_one_gpu"] = time_config4_one_gpu(dev)
+        if not args.no_cpu_baseline:
+            torch.cuda.empty_cache()
+            line["cpu_baseline"] = cpu_reference(args.shape, 4, 1)
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -10,7 +10,7 @@ import os
 from typing import Optional
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.environ.get("B200RWKV_LIB", os.path.join(HERE, "libb200rwkv.so"))  # override: an alternative build
+LIB_PATH = os.path.join(HERE, "libb200rwkv.so")
 
 OK, EINVAL, ECUDA, ETIMEOUT = 0, -1, -2, -3
 STATUS_WAIT_FULL, STATUS_WAIT_EMPTY, STATUS_WAIT_PEER = 1, 2, 4

@@ -604,8 +604,6 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
       return cudaErrorInvalidValue;
     }
   }
-  { const char* d = getenv("B200RWKV_GEMM_DEBUG"); P.dbg = d ? atoi(d) : 0; }
-  if (P.dbg == 3) return cudaSuccess;   // measurement only: preparation kernel alone
   P.row_tiles = (P.R + P.Rt - 1) / P.Rt;
   P.ntiles = 0;
   for (int s = 0; s < P.nseg; ++s) {

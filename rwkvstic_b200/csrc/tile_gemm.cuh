@@ -87,7 +87,6 @@ struct GemmParams {
   int* sk_acc;         // [kSplitMaxTiles][3*Rt][128] int32, zero between launches
   unsigned* sk_count;  // [kSplitMaxTiles] tickets, zero between launches
   int* status;
-  int dbg;             // measurement only: 1 = no operand copies (MMAs on stale shared memory), 2 = no MMAs, 4 = no epilogue
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------------
@@ -204,7 +203,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         const GemmTile T = gemm_tile(P, it / S);
         const GemmSeg& Sg = P.seg[T.seg];
         const int kbase = (it % S) * nk;
-        for (int kc = 0; kc < (P.dbg == 1 ? 0 : nk); ++kc, ++issued) {
+        for (int kc = 0; kc < nk; ++kc, ++issued) {
           const int slot = issued % kGemmStages;
           const uint32_t phase = uint32_t(issued / kGemmStages) & 1u;
           if (!mbar_wait_bounded(empty0 + 8 * slot, phase ^ 1u, abort_flag)) {
@@ -244,13 +243,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         for (int kc = 0; kc < nk; ++kc, ++step) {
           const int slot = step % kGemmStages;
           const uint32_t phase = uint32_t(step / kGemmStages) & 1u;
-          if (P.dbg != 1 && !mbar_wait_bounded(full0 + 8 * slot, phase, abort_flag)) {
+          if (!mbar_wait_bounded(full0 + 8 * slot, phase, abort_flag)) {
             if (P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
             ok = false;
             break;
           }
           tc_fence_after();
-          if (P.dbg == 2) { mbar_arrive(empty0 + 8 * slot); continue; }
           const uint32_t a = smem_u32(ring + size_t(slot) * kGemmStageBytes);
           const uint64_t ad0 = umma_desc(a), ad1 = umma_desc(a + 128 * 128), bd = umma_desc(a + kGemmABytes);
 #pragma unroll
@@ -296,7 +294,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         break;
       }
       tc_fence_after();
-      const int nchunks = Rt / CH, nitems = P.dbg == 4 ? 0 : (two ? 2 : 1) * nchunks;
+      const int nchunks = Rt / CH, nitems = (two ? 2 : 1) * nchunks;
       // this warp's last item that really reads TMEM: after it the accumulators may be overwritten
       int last_item = -1;
       for (int item = eg; item < nitems; item += EG)

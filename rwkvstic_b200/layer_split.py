@@ -18,7 +18,8 @@ through the state and stay in order on every stage.
 Decode steps are bound by streaming the stage's weights, and every stream group streams them
 again, so ``microbatches=1`` is the fastest setting for decode (measured at the 14B shape, 64
 streams, 2 GPUs: 8.8 / 11.7 / 19.0 ms per step with 1 / 2 / 4 groups); prompts are compute-bound
-and their token pieces do overlap across the stages.
+and their token pieces do overlap across the stages.  The split buys capacity, not decode speed: a
+decode step is a chain through all stages, and a model that fits one GPU decodes as fast there.
 """
 from __future__ import annotations
 
@@ -100,20 +101,31 @@ class LayerSplitPipeline:
                 req.wait()
         return logits
 
-    def decode_greedy(self, tokens: torch.Tensor, state: torch.Tensor, steps: int, microbatches: int = 1) -> torch.Tensor:
-        """``steps`` greedy decode steps for B streams starting from ``tokens [B,1]``; the next
-        tokens go from the last rank back to the first with a broadcast of B integers per step.
-        Returns the generated ids ``[B, steps]`` (on every rank)."""
+    def decode_greedy(self, tokens: torch.Tensor, state: torch.Tensor, steps: int, microbatches: int = 1) -> Optional[torch.Tensor]:
+        """``steps`` greedy decode steps for B streams starting from ``tokens [B,1]``.  The sampled ids
+        travel from the last rank straight to the first one (the only rank that reads token ids) as a
+        point-to-point message of B integers per step, stream-ordered like the hand-off of the residual:
+        no collective, and the ranks in between never wait for them.  Returns the generated ids
+        ``[B, steps]`` on the first and the last rank, None on the others."""
         B = tokens.shape[0]
         tok = tokens.to(self.device).reshape(B, 1).clone()
-        out = torch.empty(B, steps, dtype=torch.int64, device=self.device)
+        out = torch.empty(B, steps, dtype=torch.int64, device=self.device) if (self.first or self.last) else None
+        keep = []
         for i in range(steps):
             lg = self.forward_rows(tok, state, microbatches)
             if self.last:
                 tok = lg.argmax(dim=1, keepdim=True)
-            if self.world > 1:
-                dist.broadcast(tok, src=self.world - 1, group=self.group)
-            out[:, i] = tok[:, 0]
+                out[:, i] = tok[:, 0]
+                if not self.first:
+                    keep.append((dist.batch_isend_irecv([dist.P2POp(dist.isend, tok, 0, group=self.group)]), tok))
+            elif self.first:
+                tok = torch.empty(B, 1, dtype=torch.int64, device=self.device)
+                for req in dist.batch_isend_irecv([dist.P2POp(dist.irecv, tok, self.world - 1, group=self.group)]):
+                    req.wait()
+                out[:, i] = tok[:, 0]
+        for reqs, _ in keep:
+            for req in reqs:
+                req.wait()
         return out
 
 

@@ -317,6 +317,29 @@ class B200RWKV:
                     _lib.check(self._L.b200rwkv_step_plan_init(C.byref(self._cmodel), self._plan.data_ptr(), self._plan.numel()))
                 raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
 
+    def _status_buffer(self) -> torch.Tensor:
+        return self._plan if self._plan is not None else self._ws
+
+    def _queue_step_status(self) -> None:
+        """Non-blocking copy of the one-row path's status word to pinned host memory; looked at by the next
+        call of forward / generate_* (or check_status) once the copy has completed, so an expired
+        device-side wait is reported a call or two late instead of costing every call a device
+        synchronisation.  The state a
+        failed step was given is undefined."""
+        if not hasattr(self, "_step_status_host"):
+            self._step_status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._step_status_event = torch.cuda.Event()
+        self._step_status_host.copy_(self._status_buffer()[:4].view(torch.int32), non_blocking=True)
+        self._step_status_event.record(torch.cuda.current_stream(self.device))
+        self._step_status_pending = True
+
+    def _raise_step_status(self) -> None:
+        if not getattr(self, "_step_status_pending", False) or not self._step_status_event.query():
+            return                      # nothing queued, or the copy has not run yet: look again at the next call
+        self._step_status_pending = False
+        if int(self._step_status_host[0]):
+            self.check_status()
+
     def trace_persistent_step(self, token: int, state: torch.Tensor, replays: int = 3) -> torch.Tensor:
         """Profiling: the %globaltimer timeline of one persistent decode step, an int64 CPU tensor
         ``[4L+1 launches, grid, 8]`` (slots as documented at b200rwkv_decode_step_persistent), taken from
@@ -408,8 +431,9 @@ class B200RWKV:
 
     def _queue_rows_status(self, ws: torch.Tensor) -> None:
         """Start a non-blocking copy of a rows workspace's status word to pinned host memory; the next
-        rows call (or check_rows_status) looks at it, so an expired device-side wait is reported one call
-        late instead of costing every call a device synchronisation."""
+        rows call looks at it once the copy has completed (check_rows_status waits for it), so an expired
+        device-side wait is reported a call or two late instead of costing every call a device
+        synchronisation."""
         if not hasattr(self, "_rows_status_host"):
             self._rows_status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
             self._rows_status_event = torch.cuda.Event()
@@ -419,9 +443,8 @@ class B200RWKV:
 
     def _raise_rows_status(self) -> None:
         ws = getattr(self, "_rows_status_ws", None)
-        if ws is None:
-            return
-        self._rows_status_event.synchronize()      # recorded one call ago: long since reached
+        if ws is None or not self._rows_status_event.query():
+            return                      # nothing queued, or the copy has not run yet: look again at the next call
         self._rows_status_ws = None
         bits = int(self._rows_status_host[0])
         if bits:
@@ -503,6 +526,8 @@ class B200RWKV:
     def check_rows_status(self) -> None:
         """Raise if a kernel of the last ``forward_rows`` / ``forward_rows_stage`` call reported an expired
         wait (synchronises)."""
+        if getattr(self, "_rows_status_ws", None) is not None:
+            self._rows_status_event.synchronize()
         self._raise_rows_status()
         ws = getattr(self, "_last_rows_ws", None)
         if ws is None:
@@ -536,6 +561,7 @@ class B200RWKV:
             self._next = torch.zeros(1, dtype=torch.int64, device=self.device)
             self._tok_host = torch.zeros(1, dtype=torch.int64).pin_memory()
             self._next_host = torch.zeros(1, dtype=torch.int64).pin_memory()
+            self._greedy_status = torch.zeros(1, dtype=torch.int32).pin_memory()
             self._greedy_graphs: Dict[int, torch.cuda.CUDAGraph] = {}
             self._greedy_seen: Dict[int, int] = {}
         self._tok_host[0] = int(token.reshape(-1)[0])
@@ -547,6 +573,7 @@ class B200RWKV:
                                                    self._next.data_ptr(), None, None, 0,
                                                    torch.cuda.current_stream(self.device).cuda_stream))
                 self._next_host.copy_(self._next, non_blocking=True)         # 8 bytes device -> host
+                self._greedy_status.copy_(self._status_buffer()[:4].view(torch.int32), non_blocking=True)
             key = state.data_ptr()
             g = self._greedy_graphs.get(key) if self.use_graph else None
             if g is not None:
@@ -567,6 +594,8 @@ class B200RWKV:
                 else:
                     one()
             torch.cuda.current_stream(self.device).synchronize()
+        if int(self._greedy_status[0]):
+            self.check_status()              # raises: a device-side wait expired during this step
         out.reshape(-1)[0] = self._next_host[0]
         self.launch_count += self.launches_per_step + 1
 
@@ -576,6 +605,7 @@ class B200RWKV:
         plus an arg-max kernel that writes the next token into the step's own input buffer and
         appends it to a history buffer).  Returns the ``n`` generated ids (device int64);
         ``state`` is updated in place.  Same tokens as calling ``forward`` + ``torch.argmax`` n times."""
+        self._raise_step_status()
         state = self._own_state(state)
         hist = torch.zeros(max(n, 1), dtype=torch.int64, device=self.device)
         count = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -601,6 +631,8 @@ class B200RWKV:
                 for _ in range(n):
                     one()
         self.launch_count += n * (self.launches_per_step + 1)
+        with torch.cuda.device(self.device):
+            self._queue_step_status()
         return hist[:n]
 
     def generate_typical(self, token, state: torch.Tensor, n: int, temp: float = 1.0, tau: float = 0.95,
@@ -610,6 +642,7 @@ class B200RWKV:
         arg-max kernel's place.  The uniform numbers of all n draws come from one device
         generator seeded with ``seed`` before the loop, so a run is reproducible.  Returns the
         generated ids (device int64); ``state`` is updated in place."""
+        self._raise_step_status()
         state = self._own_state(state)
         hist = torch.zeros(max(n, 1), dtype=torch.int64, device=self.device)
         count = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -638,6 +671,8 @@ class B200RWKV:
                 for _ in range(n):
                     one()
         self.launch_count += n * (self.launches_per_step + 1)
+        with torch.cuda.device(self.device):
+            self._queue_step_status()
         return hist[:n]
 
     def forward(self, tokens, state: torch.Tensor):
@@ -647,6 +682,7 @@ class B200RWKV:
         tokens = tokens.reshape(-1).to(torch.int64)
         if tokens.numel() == 0:
             raise ValueError("forward needs at least one token")
+        self._raise_step_status()
         state = self._own_state(state)
         if tokens.numel() >= self.rows_threshold:
             self._logits.copy_(self.forward_rows(tokens.reshape(1, -1), state.unsqueeze(0))[0])
@@ -657,6 +693,7 @@ class B200RWKV:
             for i in range(T):
                 self._tok.copy_(toks[i:i + 1], non_blocking=True)
                 self._step(state, want_logits=(i == T - 1))
+            self._queue_step_status()
         return (self._logits.clone() if self.copy_logits else self._logits), state
 
     __call__ = forward

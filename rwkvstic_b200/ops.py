@@ -29,10 +29,11 @@ _workspaces = {}
 
 
 def gemv_workspace(device, k_in: int, nmat: int) -> torch.Tensor:
-    """Zeroed scratch for ``gemv_u8`` (cached per device and size; calls sharing it must be ordered
-    on one stream).  Its first int32 is the kernels' status word."""
+    """Zeroed scratch for ``gemv_u8``, cached per device, size AND current CUDA stream: calls that share
+    a workspace must be ordered on one stream, so every stream gets its own.  Its first int32 is the
+    kernels' status word."""
     n = int(_lib.lib().b200rwkv_gemv_workspace_bytes(k_in, nmat))
-    key = (str(device), n)
+    key = (str(device), n, _stream(device))
     if key not in _workspaces:
         _workspaces[key] = torch.zeros(n, dtype=torch.uint8, device=device)
     return _workspaces[key]

@@ -49,9 +49,41 @@ def main():
     ap.add_argument("--dense", default=None, choices=["bf16", "fp16", "fp32"],
                     help="stream the first matrix of --matrix unquantised in this type (dense_gemv_kernel)")
     ap.add_argument("--sampler", action="store_true", help="typical sampling of one row of V logits")
+    ap.add_argument("--trace", default=None, choices=["chained", "persistent"],
+                    help="print the %%globaltimer timeline of one block of a graph-replayed decode step of --shape "
+                         "(--network LAYERS blocks, default 4) in this decode mode")
     ap.add_argument("--streams", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
+    if args.trace:
+        from .model import B200RWKV
+        L, D = args.network or 4, SHAPES[args.shape][1]
+        model = B200RWKV.synthetic(L, D, seed=1234, device="cuda:0", decode_mode=args.trace)
+        state = model.emptyState.clone()
+        names = ["key/value/receptance", "attention output", "ffn key + receptance", "ffn value"]
+        if args.trace == "chained":
+            tr = model.trace_step(17, state, graph=True).double() / 1e3        # [4L+1, 1024, 8] us
+            grid = int((tr[0, :1023, 0] > 0).sum())
+            t0 = float(tr[4, 1023, 0])
+            print(f"chained decode step, {args.shape} width, block 1 of {L}; us since the block's first preparation kernel started")
+            print("launch | prep: entry dep stats done | gemv: dep(med) planes(med) rows(med) rows(max) epilogue(max)")
+            for j in range(4):
+                g, pr = tr[4 + j, :grid], tr[4 + j, 1023]
+                print(f"{names[j]:22s} | {float(pr[0]) - t0:7.2f} {float(pr[1]) - t0:7.2f} {float(pr[2]) - t0:7.2f} {float(pr[3]) - t0:7.2f} | "
+                      f"{float(g[:, 1].median()) - t0:7.2f} {float(g[:, 4].median()) - t0:7.2f} {float(g[:, 5].median()) - t0:7.2f} "
+                      f"{float(g[:, 5].max()) - t0:7.2f} {float(g[:, 6].max()) - t0:7.2f}")
+            print(f"block time: {float(tr[8, 1023, 0] - tr[4, 1023, 0]):.2f} us; whole step {float(tr[-1, :grid, 6].max() - tr[0, 1023, 0]):.1f} us")
+        else:
+            tr = model.trace_persistent_step(17, state).double() / 1e3        # [4L+1, grid, 8] us
+            t0 = float(tr[4, :, 5].median())
+            print(f"persistent decode step, {args.shape} width, block 1 of {L}; us since the block's ln1 slices were published (medians over CTAs)")
+            print("launch | statistics gathered, slice published | exchange read + planes, rows summed, epilogue done")
+            for j in range(4):
+                g = tr[4 + j]
+                st = f"{float(g[:, 4].median()) - t0:7.2f} {float(g[:, 5].median()) - t0:7.2f}" if j in (0, 2) else "      -       -"
+                print(f"{names[j]:22s} | {st} | {float(g[:, 1].median()) - t0:7.2f} {float(g[:, 2].median()) - t0:7.2f} {float(g[:, 3].median()) - t0:7.2f}")
+            print(f"block time: {float(tr[8, :, 5].median() - tr[4, :, 5].median()):.2f} us")
+        return
     if args.network > 0:
         from .model import B200RWKV
         _, D = SHAPES[args.shape]

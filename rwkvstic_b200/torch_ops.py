@@ -17,11 +17,15 @@ Semantics kept from the reference kernels (cuda/operators32.cu:18-115, cuda/oper
   cuda/operators.cu:24-33 on fp64 tensors; ``y, aa, bb`` written in place, ``pp`` untouched.
 
 Cost of the compatibility layer: the kernels stream weights output-major, so each ``w`` is
-transposed once and cached (keyed by its storage pointer) - twice the weight memory.  New code
-should use ``rwkvstic_b200.model.B200RWKV`` instead, which keeps one copy.
+transposed once and cached - twice the weight memory while ``w`` is alive.  The cache entry is
+tied to the tensor object by a weak reference and checked against its version counter: when
+``w`` is freed the transposed copy goes with it, and an address reused by another matrix (or
+bytes modified in place) never gets stale data.  New code should use
+``rwkvstic_b200.model.B200RWKV`` instead, which keeps one copy.
 """
 from __future__ import annotations
 
+import weakref
 from typing import Dict, Tuple
 
 import torch
@@ -30,20 +34,21 @@ from . import ops
 from .quant import QuantMatrix
 
 _lib_handle = None
-_cache: Dict[Tuple[int, int, int], QuantMatrix] = {}
+_cache: Dict[int, Tuple[weakref.ref, int, QuantMatrix]] = {}     # id(w) -> (weak reference to w, its version, transposed copy)
 
 
 def _matrix(w: torch.Tensor, r: torch.Tensor) -> QuantMatrix:
     if w.dtype != torch.uint8 or w.dim() != 2 or w.stride(1) != 1:
         raise RuntimeError("rwkv::mm8: w must be a uint8 [N, M] matrix with unit inner stride")
-    key = (w.data_ptr(), w.shape[0], w.shape[1])
-    m = _cache.get(key)
-    if m is None:
-        zeros = torch.zeros(w.shape[0], dtype=torch.float32, device=w.device)
-        m = QuantMatrix(qt=w.t().contiguous(), ry=r.to(torch.float32).contiguous(), my=zeros)
-        _cache[key] = m
-    else:
+    key = id(w)
+    hit = _cache.get(key)
+    if hit is not None and hit[0]() is w and hit[1] == w._version:
+        m = hit[2]
         m.ry = r.to(torch.float32).contiguous()
+        return m
+    zeros = torch.zeros(w.shape[0], dtype=torch.float32, device=w.device)
+    m = QuantMatrix(qt=w.t().contiguous(), ry=r.to(torch.float32).contiguous(), my=zeros)
+    _cache[key] = (weakref.ref(w, lambda _ref, k=key: _cache.pop(k, None)), w._version, m)
     return m
 
 

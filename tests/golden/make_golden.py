@@ -18,7 +18,7 @@ building blocks on small seeded inputs.
 Outputs:
   ops_small.npz     per-op vectors (quantiser, mm8, layernorm, wkv, one Block)
   model_tiny.npz    L=2 D=128 V=257 model: sequence mode and token-by-token
-  model_169m.npz    BASELINE config 0: L=12 D=768 V=50277, 32 prompt + 64 greedy tokens
+  model_169m.npz    the 169M shape: L=12 D=768 V=50277, 32 prompt + 64 greedy tokens
 """
 from __future__ import annotations
 

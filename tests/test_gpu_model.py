@@ -89,7 +89,7 @@ def test_batched_streams_equal_single_streams(tiny):
 
 
 def test_169m_prompt_then_64_greedy_tokens(m169, golden):
-    """BASELINE config 0: 32 prompt tokens in sequence mode, 64 greedy steps, batch 1."""
+    """The 169M shape (L=12, D=768, V=50277): 32 prompt tokens in sequence mode, 64 greedy steps, batch 1."""
     g = golden("model_169m.npz")
     probe = torch.from_numpy(g["probe_idx"]).to(DEV)
     state = m169.emptyState.clone()

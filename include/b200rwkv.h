@@ -333,6 +333,49 @@ int b200rwkv_sample_typical(const float* x, int rows, int n, int64_t ldx, float 
 int b200rwkv_gemv_dense(const void* w, int dtype, int k_in, int n_out, int64_t ldw, const float* x, float* y,
                         void* stream);
 
+
+/*
+ * Unquantised weights: one token through the whole network, the reference's TORCH mode
+ * (helpers/loadWeights.py:11-85 with agnostic/backends/torch.py:125-166 as the op table, network
+ * agnostic/agnosticRwkv.py:123-187).  Matrices are the checkpoint's own [out][in] tensors in `dtype`
+ * (rows contiguous, every row on a 16-byte boundary); vectors are f32, time_decay already
+ * -exp(raw) as loadWeights leaves it (loadWeights.py:63-64).  Every product rounds the activation to
+ * `dtype`, sums in f32 and rounds the result to `dtype` (torch.py:162-164); the rest is f32.
+ */
+typedef struct b200rwkv_dense_layer {
+  const float *ln1_w, *ln1_b, *ln2_w, *ln2_b;
+  const float *att_mix_k, *att_mix_v, *att_mix_r, *ffn_mix_k, *ffn_mix_r;
+  const float *time_decay, *time_first;
+  const void *att_key, *att_value, *att_receptance, *att_output;   /* [n_embd][n_embd] */
+  const void *ffn_key;                                             /* [n_ffn][n_embd] */
+  const void *ffn_receptance;                                      /* [n_embd][n_embd] */
+  const void *ffn_value;                                           /* [n_embd][n_ffn] */
+} b200rwkv_dense_layer;
+
+typedef struct b200rwkv_dense_model {
+  int32_t n_layer, n_embd, n_ffn, n_vocab;
+  int32_t dtype;                       /* B200RWKV_F32 / _BF16 / _F16: the matrices' type */
+  const float* emb;                    /* device f32 [n_vocab][n_embd] */
+  const float *ln0_w, *ln0_b, *ln_out_w, *ln_out_b;
+  const void* head;                    /* [n_vocab][n_embd] */
+  const b200rwkv_dense_layer* layers;  /* HOST array of n_layer entries (device pointers inside) */
+} b200rwkv_dense_model;
+
+size_t b200rwkv_dense_workspace_bytes(const b200rwkv_dense_model* m);
+
+/*
+ * forward(token, state) -> (logits, state) for one token (agnosticRwkv.py:171-187 with T = 1).
+ *   token   device int64[1]
+ *   state   device f32 [n_layer][5][n_embd] in the reference's own convention (base.py:61-62 and
+ *           agnosticRwkv.py:68-103): rows 0, 1 the token-shift carries, rows 2, 3 the WKV sums scaled
+ *           by exp(-row 4), row 4 the running maximum exponent (-1e30 when empty); updated in place
+ *   logits  device f32 [n_vocab], or NULL to advance the state only
+ * n_embd and n_ffn multiples of 8, n_embd <= 12160.  Enqueues 6 * n_layer + 3 kernels on `stream`
+ * (capturable in a CUDA graph), no allocation, no host synchronisation; deterministic.
+ */
+int b200rwkv_dense_step(const b200rwkv_dense_model* m, const int64_t* token, float* state, float* logits,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,6 +22,7 @@ EXPORTS = (
     "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step", "b200rwkv_decode_step_traced",
     "b200rwkv_gemm_workspace_bytes", "b200rwkv_gemm_u8", "b200rwkv_rows_workspace_bytes", "b200rwkv_forward_rows", "b200rwkv_forward_rows_stage", "b200rwkv_argmax",
     "b200rwkv_sample_typical", "b200rwkv_gemv_dense",
+    "b200rwkv_dense_workspace_bytes", "b200rwkv_dense_step",
     "b200rwkv_step_plan_bytes", "b200rwkv_step_plan_init", "b200rwkv_decode_step_persistent", "b200rwkv_step_geometry",
 )
 
@@ -44,6 +45,20 @@ class Model(C.Structure):
                 ("emb", C.c_void_p), ("ln0_w", C.c_void_p), ("ln0_b", C.c_void_p),
                 ("ln_out_w", C.c_void_p), ("ln_out_b", C.c_void_p), ("head", Matrix),
                 ("layers", C.POINTER(Layer))]
+
+
+class DenseLayer(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "ln1_w", "ln1_b", "ln2_w", "ln2_b", "att_mix_k", "att_mix_v", "att_mix_r", "ffn_mix_k", "ffn_mix_r",
+        "time_decay", "time_first", "att_key", "att_value", "att_receptance", "att_output",
+        "ffn_key", "ffn_receptance", "ffn_value")]
+
+
+class DenseModel(C.Structure):
+    _fields_ = [("n_layer", C.c_int32), ("n_embd", C.c_int32), ("n_ffn", C.c_int32), ("n_vocab", C.c_int32),
+                ("dtype", C.c_int32), ("emb", C.c_void_p), ("ln0_w", C.c_void_p), ("ln0_b", C.c_void_p),
+                ("ln_out_w", C.c_void_p), ("ln_out_b", C.c_void_p), ("head", C.c_void_p),
+                ("layers", C.POINTER(DenseLayer))]
 
 
 class B200RWKVError(RuntimeError):
@@ -118,6 +133,11 @@ def lib() -> C.CDLL:
                                           C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
     L.b200rwkv_gemv_dense.restype = C.c_int
     L.b200rwkv_gemv_dense.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_void_p, C.c_void_p,
+                                      C.c_void_p]
+    L.b200rwkv_dense_workspace_bytes.restype = C.c_size_t
+    L.b200rwkv_dense_workspace_bytes.argtypes = [C.POINTER(DenseModel)]
+    L.b200rwkv_dense_step.restype = C.c_int
+    L.b200rwkv_dense_step.argtypes = [C.POINTER(DenseModel), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                       C.c_void_p]
     _lib = L
     return L

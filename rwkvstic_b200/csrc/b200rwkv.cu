@@ -10,6 +10,7 @@
 #include "sampling.cuh"
 #include "dense_gemv.cuh"
 #include "decode_step.cuh"
+#include "dense_step.cuh"
 
 namespace b200 {
 
@@ -743,6 +744,177 @@ static bool fill_step_mat(StepMat& o, const b200rwkv_matrix& m) {
 
 using namespace b200;
 
+static int dense_elem_bytes(int dtype) { return dtype == B200RWKV_F32 ? 4 : (dtype == B200RWKV_BF16 || dtype == B200RWKV_F16) ? 2 : 0; }
+
+// ---- unquantised weights: one token through the network -------------------------------------------
+struct DenseWorkspace {
+  float *x, *gate;
+  void *xk, *xv, *xr, *rw, *fk, *fr, *kk, *hx;
+  size_t bytes;
+};
+
+static DenseWorkspace dense_carve(const b200rwkv_dense_model* m, void* base) {
+  DenseWorkspace w;
+  char* p = static_cast<char*>(base);
+  size_t off = 0;
+  auto take = [&](size_t n) { char* r = p ? p + off : nullptr; off += align256(n); return r; };
+  const size_t D = size_t(m->n_embd) * 4, F = size_t(m->n_ffn) * 4;    // sized for the widest type
+  w.x = reinterpret_cast<float*>(take(D));
+  w.gate = reinterpret_cast<float*>(take(D));
+  w.xk = take(D); w.xv = take(D); w.xr = take(D); w.rw = take(D);
+  w.fk = take(D); w.fr = take(D); w.hx = take(D);
+  w.kk = take(F);
+  w.bytes = off;
+  return w;
+}
+
+template <typename T>
+static cudaError_t dense_launch_vec(const DenseVecParams& P, bool chained, cudaStream_t stream) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(1); cfg.blockDim = dim3(kDsVecThreads); cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = chained ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, dense_vec_kernel<T>, P);
+}
+
+// Grid and K split for one rows launch: as many CTAs as fit the GPU at once, and enough warps per
+// task that every SM has several rounds of work while a warp's share of a row is still one full
+// batch of 16-byte pieces per lane.
+template <typename T, int R>
+static cudaError_t dense_launch_rows(DenseRowsParams& P, cudaStream_t stream) {
+  static bool configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  auto kernel = dense_rows_kernel<T, R>;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDsMaxStage);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int nx = R == 3 ? 3 : P.nseg;
+  const size_t smem = size_t(nx) * P.K * sizeof(T);
+  if (smem > size_t(kDsMaxStage)) return cudaErrorInvalidValue;
+  int per_sm = 0;
+  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kDsThreads, smem);
+  if (e != cudaSuccess) return e;
+  if (per_sm < 1) return cudaErrorInvalidValue;
+  const int sms = device_sms();
+  const int warps = sms * per_sm * kDsWarps;
+  const int batch = 32 * (R == 3 ? 4 : 6);                       // pieces one warp takes per batch
+  const int pieces = P.K / (16 / int(sizeof(T)));
+  int split = 1;
+  while (split < kDsWarps && (long long)P.tasks * split < 4ll * warps && pieces / (split * 2) >= batch) split *= 2;
+  P.split = split;
+  const int per_pass = kDsWarps / split;
+  const int passes = (P.tasks + per_pass - 1) / per_pass;
+  const int most = sms * per_sm;
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(passes < most ? passes : most); cfg.blockDim = dim3(kDsThreads);
+  cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, P);
+}
+
+template <typename T>
+static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, float* state, float* logits,
+                           const DenseWorkspace& ws, cudaStream_t st) {
+  const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab;
+  cudaError_t e;
+#define B200_DS_CHECK(call, what)                                                        \
+  do {                                                                                   \
+    e = (call);                                                                          \
+    if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "dense_step: %s: %s", what, cudaGetErrorString(e)); \
+  } while (0)
+  DenseVecParams vp;
+  memset(&vp, 0, sizeof(vp));
+  vp.emb = m->emb; vp.token = reinterpret_cast<const long long*>(token);
+  vp.ln_w = m->ln0_w; vp.ln_b = m->ln0_b; vp.x_out = ws.x; vp.D = D;
+  B200_DS_CHECK(dense_launch_vec<T>(vp, false, st), "embedding");
+  for (int l = 0; l < m->n_layer; ++l) {
+    const b200rwkv_dense_layer& Lr = m->layers[l];
+    float* sl = state + size_t(l) * 5 * D;
+    memset(&vp, 0, sizeof(vp));
+    vp.x = ws.x; vp.ln_w = Lr.ln1_w; vp.ln_b = Lr.ln1_b; vp.carry = sl; vp.D = D; vp.nmix = 3;
+    vp.mix[0] = Lr.att_mix_k; vp.mix[1] = Lr.att_mix_v; vp.mix[2] = Lr.att_mix_r;
+    vp.out[0] = ws.xk; vp.out[1] = ws.xv; vp.out[2] = ws.xr;
+    B200_DS_CHECK(dense_launch_vec<T>(vp, true, st), "attention mix");
+
+    DenseRowsParams rp;
+    memset(&rp, 0, sizeof(rp));
+    rp.nseg = 3; rp.K = D; rp.tasks = D;
+    rp.seg[0] = DenseSeg{Lr.att_key, ws.xk, nullptr, D, D, 0};
+    rp.seg[1] = DenseSeg{Lr.att_value, ws.xv, nullptr, D, D, 0};
+    rp.seg[2] = DenseSeg{Lr.att_receptance, ws.xr, nullptr, D, D, 0};
+    rp.state = sl; rp.decay = Lr.time_decay; rp.first = Lr.time_first; rp.wkv_out = ws.rw;
+    B200_DS_CHECK((dense_launch_rows<T, 3>(rp, st)), "key/value/receptance rows");
+
+    memset(&rp, 0, sizeof(rp));
+    rp.nseg = 1; rp.K = D; rp.tasks = (D + 1) / 2;
+    rp.seg[0] = DenseSeg{Lr.att_output, ws.rw, nullptr, D, D, kEpResid};
+    rp.resid = ws.x;
+    B200_DS_CHECK((dense_launch_rows<T, 2>(rp, st)), "attention output rows");
+
+    memset(&vp, 0, sizeof(vp));
+    vp.x = ws.x; vp.ln_w = Lr.ln2_w; vp.ln_b = Lr.ln2_b; vp.carry = sl + D; vp.D = D; vp.nmix = 2;
+    vp.mix[0] = Lr.ffn_mix_k; vp.mix[1] = Lr.ffn_mix_r;
+    vp.out[0] = ws.fk; vp.out[1] = ws.fr;
+    B200_DS_CHECK(dense_launch_vec<T>(vp, true, st), "ffn mix");
+
+    memset(&rp, 0, sizeof(rp));
+    rp.nseg = 2; rp.K = D; rp.tasks = (F + D + 1) / 2;
+    rp.seg[0] = DenseSeg{Lr.ffn_key, ws.fk, ws.kk, D, F, kEpRelu2};
+    rp.seg[1] = DenseSeg{Lr.ffn_receptance, ws.fr, ws.gate, D, D, kEpSigmoid};
+    B200_DS_CHECK((dense_launch_rows<T, 2>(rp, st)), "ffn key and receptance rows");
+
+    memset(&rp, 0, sizeof(rp));
+    rp.nseg = 1; rp.K = F; rp.tasks = (D + 1) / 2;
+    rp.seg[0] = DenseSeg{Lr.ffn_value, ws.kk, nullptr, F, D, kEpGated};
+    rp.resid = ws.x; rp.gate = ws.gate;
+    B200_DS_CHECK((dense_launch_rows<T, 2>(rp, st)), "ffn value rows");
+  }
+  if (logits) {
+    memset(&vp, 0, sizeof(vp));
+    vp.x = ws.x; vp.ln_w = m->ln_out_w; vp.ln_b = m->ln_out_b; vp.D = D; vp.out[0] = ws.hx;
+    B200_DS_CHECK(dense_launch_vec<T>(vp, true, st), "output layer norm");
+    DenseRowsParams rp;
+    memset(&rp, 0, sizeof(rp));
+    rp.nseg = 1; rp.K = D; rp.tasks = (V + 1) / 2;
+    rp.seg[0] = DenseSeg{m->head, ws.hx, logits, D, V, kEpStore};
+    B200_DS_CHECK((dense_launch_rows<T, 2>(rp, st)), "head rows");
+  }
+#undef B200_DS_CHECK
+  return B200RWKV_OK;
+}
+
+static const char* dense_model_problem(const b200rwkv_dense_model* m) {
+  if (!m || !m->layers || !m->emb || !m->head || !m->ln0_w || !m->ln0_b || !m->ln_out_w || !m->ln_out_b) return "null pointer in the model";
+  if (m->n_layer < 1 || m->n_vocab < 1 || m->n_embd < 8 || m->n_ffn < 8) return "bad dimensions";
+  if (m->n_embd % 8 || m->n_ffn % 8) return "n_embd and n_ffn must be multiples of 8";
+  if (m->n_embd > kDsMaxEmbd) return "n_embd above 12160";
+  const int eb = dense_elem_bytes(m->dtype);
+  if (!eb) return "unknown dtype";
+  if (size_t(3) * m->n_embd * eb > size_t(kDsMaxStage) || size_t(m->n_ffn) * eb > size_t(kDsMaxStage)) return "rows too long to stage in shared memory";
+  if (!aligned16(m->head)) return "head not 16-byte aligned";
+  for (int l = 0; l < m->n_layer; ++l) {
+    const b200rwkv_dense_layer& L = m->layers[l];
+    const void* ptrs[] = {L.ln1_w, L.ln1_b, L.ln2_w, L.ln2_b, L.att_mix_k, L.att_mix_v, L.att_mix_r, L.ffn_mix_k, L.ffn_mix_r,
+                          L.time_decay, L.time_first, L.att_key, L.att_value, L.att_receptance, L.att_output, L.ffn_key,
+                          L.ffn_receptance, L.ffn_value};
+    for (const void* q : ptrs) if (!q) return "null pointer in a layer";
+    const void* mats[] = {L.att_key, L.att_value, L.att_receptance, L.att_output, L.ffn_key, L.ffn_receptance, L.ffn_value};
+    for (const void* q : mats) if (!aligned16(q)) return "a matrix is not 16-byte aligned";
+  }
+  return nullptr;
+}
+
 extern "C" {
 
 int b200rwkv_version(void) { return 100; }
@@ -1417,7 +1589,6 @@ int b200rwkv_sample_typical(const float* x, int rows, int n, int64_t ldx, float 
 }
 
 // ---- unquantised weights (TORCH-mode matvec) -----------------------------------------------------
-static int dense_elem_bytes(int dtype) { return dtype == B200RWKV_F32 ? 4 : (dtype == B200RWKV_BF16 || dtype == B200RWKV_F16) ? 2 : 0; }
 
 int b200rwkv_gemv_dense(const void* w, int dtype, int k_in, int n_out, int64_t ldw, const float* x, float* y, void* stream) {
   const int eb = dense_elem_bytes(dtype);
@@ -1455,5 +1626,26 @@ int b200rwkv_gemv_dense(const void* w, int dtype, int k_in, int n_out, int64_t l
   if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "gemv_dense: %s", cudaGetErrorString(e));
   return B200RWKV_OK;
 }
+
+// ---- unquantised weights: one token through the network (entry points; helpers above the C block)
+size_t b200rwkv_dense_workspace_bytes(const b200rwkv_dense_model* m) {
+  if (!m || m->n_embd < 1 || m->n_ffn < 1) return 0;
+  return dense_carve(m, nullptr).bytes;
+}
+
+int b200rwkv_dense_step(const b200rwkv_dense_model* m, const int64_t* token, float* state, float* logits,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (const char* why = dense_model_problem(m)) return fail(B200RWKV_EINVAL, "dense_step: %s", why);
+  if (!token || !state || !workspace || !aligned16(workspace))
+    return fail(B200RWKV_EINVAL, "dense_step: token, state and a 16-byte aligned workspace are required");
+  const DenseWorkspace ws = dense_carve(m, workspace);
+  if (workspace_bytes < ws.bytes)
+    return fail(B200RWKV_EINVAL, "dense_step: workspace of %zu bytes, %zu needed", workspace_bytes, ws.bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (m->dtype == B200RWKV_BF16) return dense_step_impl<__nv_bfloat16>(m, token, state, logits, ws, st);
+  if (m->dtype == B200RWKV_F16) return dense_step_impl<__half>(m, token, state, logits, ws, st);
+  return dense_step_impl<float>(m, token, state, logits, ws, st);
+}
+
 
 }  // extern "C"

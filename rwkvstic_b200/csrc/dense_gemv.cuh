@@ -29,14 +29,17 @@ template <typename T> struct DenseType;
 template <> struct DenseType<__nv_bfloat16> {
   static __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
   static __device__ __forceinline__ float round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
 };
 template <> struct DenseType<__half> {
   static __device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
   static __device__ __forceinline__ float round(float v) { return __half2float(__float2half_rn(v)); }
+  static __device__ __forceinline__ __half from_f32(float v) { return __float2half_rn(v); }
 };
 template <> struct DenseType<float> {
   static __device__ __forceinline__ float to_f32(float v) { return v; }
   static __device__ __forceinline__ float round(float v) { return v; }
+  static __device__ __forceinline__ float from_f32(float v) { return v; }
 };
 
 struct DenseParams {

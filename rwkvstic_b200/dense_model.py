@@ -1,0 +1,154 @@
+"""RWKV-4 with unquantised weights on the sm_100a kernels: the reference's TORCH mode.
+
+The reference builds this model with ``loadWeights(TORCH, path, dtype=..., runtimedtype=...)``
+(helpers/loadWeights.py:11-85; op table ``RWKVCudaOps``, agnostic/backends/torch.py:125-166) and runs
+it through ``AgnosticRWKV`` (agnostic/agnosticRwkv.py:123-187): matrices in ``dtype``, vectors and
+state in ``runtimedtype``.  ``B200DenseRWKV`` keeps the matrices as the checkpoint has them
+(``[out,in]``, rows contiguous) in bf16 / fp16 / fp32, everything else in fp32, and runs one token per
+call of ``b200rwkv_dense_step`` (6 kernels per block, replayed from a CUDA graph).
+
+    model = B200DenseRWKV.from_checkpoint("model.pth", dtype=torch.bfloat16)
+    logits, state = model.forward(tokens, model.emptyState.clone())
+
+``forward(tokens int64[T], state f32[L,5,D]) -> (logits f32[V] on the device, state)``; the state is
+the reference's own (max-trick WKV rows 2..4, ``-1e30`` in row 4 when empty) and is updated in
+place.  Several tokens are fed one after another.  There is no CPU fallback: without the CUDA
+library the constructor raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Iterable, Optional, Tuple, Union
+
+import torch
+
+from . import _lib
+from .synth import VOCAB, iter_synth_tensors
+
+DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+_MATS = ("att.key", "att.value", "att.receptance", "att.output", "ffn.key", "ffn.receptance", "ffn.value")
+_VECS = ("ln1.weight", "ln1.bias", "ln2.weight", "ln2.bias", "att.time_mix_k", "att.time_mix_v", "att.time_mix_r",
+         "ffn.time_mix_k", "ffn.time_mix_r", "att.time_decay", "att.time_first")
+
+
+class B200DenseRWKV:
+    def __init__(self, tensors: Iterable[Tuple[str, torch.Tensor]], dtype: torch.dtype = torch.bfloat16, device="cuda:0",
+                 use_graph: bool = True, decay_is_final: bool = False):
+        """``tensors``: (name, tensor) pairs under the checkpoint's key names; matrices ``[out,in]``.
+        ``decay_is_final``: ``att.time_decay`` already holds ``-exp(raw)`` (what loadWeights hands to the
+        ops object, loadWeights.py:63-64) instead of the checkpoint's raw value."""
+        if dtype not in DTYPES:
+            raise ValueError("dtype must be torch.float32, torch.bfloat16 or torch.float16")
+        self._L = _lib.lib()
+        self.device = torch.device(device)
+        self.dtype, self.use_graph = dtype, use_graph
+        t: Dict[str, torch.Tensor] = {}
+        for name, v in tensors:
+            v = v.detach()
+            if name.endswith("att.time_decay_final"):
+                name, final = name[:-len("_final")], True
+            else:
+                final = decay_is_final
+            if ".time_" in name:
+                v = v.reshape(-1)
+            if name.endswith("att.time_decay") and not final:
+                v = -torch.exp(v.double())
+            if v.dim() == 2 and name != "emb.weight":
+                t[name] = v.to(device=self.device, dtype=dtype).contiguous()       # initTensor, torch.py:146-152
+            else:
+                t[name] = v.to(device=self.device, dtype=torch.float32).contiguous()
+        self.t = t
+        self.n_layer = 1 + max(int(k.split(".")[1]) for k in t if k.startswith("blocks."))
+        self.n_vocab, self.n_embd = t["emb.weight"].shape
+        self.n_ffn = t["blocks.0.ffn.key.weight"].shape[0]
+        self._clayers = (_lib.DenseLayer * self.n_layer)()
+        for i in range(self.n_layer):
+            c, p = self._clayers[i], f"blocks.{i}."
+            (c.ln1_w, c.ln1_b, c.ln2_w, c.ln2_b, c.att_mix_k, c.att_mix_v, c.att_mix_r, c.ffn_mix_k, c.ffn_mix_r,
+             c.time_decay, c.time_first) = (t[p + k].data_ptr() for k in _VECS)
+            (c.att_key, c.att_value, c.att_receptance, c.att_output, c.ffn_key, c.ffn_receptance,
+             c.ffn_value) = (t[p + k + ".weight"].data_ptr() for k in _MATS)
+        self._cmodel = _lib.DenseModel(self.n_layer, self.n_embd, self.n_ffn, self.n_vocab, DTYPES[dtype],
+                                       t["emb.weight"].data_ptr(), t["blocks.0.ln0.weight"].data_ptr(),
+                                       t["blocks.0.ln0.bias"].data_ptr(), t["ln_out.weight"].data_ptr(),
+                                       t["ln_out.bias"].data_ptr(), t["head.weight"].data_ptr(),
+                                       C.cast(self._clayers, C.POINTER(_lib.DenseLayer)))
+        need = int(self._L.b200rwkv_dense_workspace_bytes(C.byref(self._cmodel)))
+        self._ws = torch.zeros(need, dtype=torch.uint8, device=self.device)
+        self._tok = torch.zeros(1, dtype=torch.int64, device=self.device)
+        self._logits = torch.zeros(self.n_vocab, dtype=torch.float32, device=self.device)
+        self.emptyState = torch.zeros(self.n_layer, 5, self.n_embd, dtype=torch.float32, device=self.device)
+        self.emptyState[:, 4] = -1e30                                               # base.py:61-62
+        self._graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
+        self._seen: Dict[Tuple[int, bool], int] = {}
+        self.launches_per_step = 6 * self.n_layer + 3
+        self.launch_count = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_checkpoint(cls, ck: Union[str, Dict[str, torch.Tensor]], dtype: torch.dtype = torch.bfloat16, device="cuda:0",
+                        use_graph: bool = True) -> "B200DenseRWKV":
+        if isinstance(ck, str):
+            ck = torch.load(ck, map_location="cpu")
+        return cls(ck.items(), dtype=dtype, device=device, use_graph=use_graph)
+
+    @classmethod
+    def synthetic(cls, layers: int, embed: int, vocab: int = VOCAB, seed: int = 1234, dtype: torch.dtype = torch.bfloat16,
+                  device="cuda:0", use_graph: bool = True) -> "B200DenseRWKV":
+        """Seeded random weights of the RWKV-4 architecture, generated on the device one tensor at a time."""
+        return cls(iter_synth_tensors(layers, embed, vocab=vocab, seed=seed, device=str(device)), dtype=dtype,
+                   device=device, use_graph=use_graph)
+
+    def weight_bytes(self) -> int:
+        """Bytes of matrix weights one token reads (embedding row excluded)."""
+        return sum(v.numel() * v.element_size() for k, v in self.t.items() if v.dim() == 2 and k != "emb.weight")
+
+    # ------------------------------------------------------------------ one token
+    def _step_raw(self, state_ptr: int, logits_ptr: Optional[int]) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _lib.check(self._L.b200rwkv_dense_step(C.byref(self._cmodel), self._tok.data_ptr(), state_ptr, logits_ptr,
+                                               self._ws.data_ptr(), self._ws.numel(), stream))
+
+    def _step(self, state: torch.Tensor, want_logits: bool) -> None:
+        self.launch_count += self.launches_per_step - (0 if want_logits else 2)
+        lp = self._logits.data_ptr() if want_logits else None
+        if not self.use_graph:
+            self._step_raw(state.data_ptr(), lp)
+            return
+        key = (state.data_ptr(), want_logits)
+        g = self._graphs.get(key)
+        if g is None:
+            n = self._seen.get(key, 0) + 1          # capture when a state buffer shows up for the second time
+            self._seen[key] = n
+            if n < 2:
+                self._step_raw(state.data_ptr(), lp)
+                return
+            if len(self._graphs) >= 16:
+                self._graphs.clear()
+                self._seen.clear()
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(g):
+                self._step_raw(state.data_ptr(), lp)
+            self._graphs[key] = g
+        g.replay()
+
+    def forward(self, tokens, state: torch.Tensor):
+        if not torch.is_tensor(tokens):
+            tokens = torch.tensor(tokens if isinstance(tokens, (list, tuple)) else [tokens], dtype=torch.int64)
+        tokens = tokens.reshape(-1).to(torch.int64)
+        if tokens.numel() == 0:
+            raise ValueError("forward needs at least one token")
+        if tuple(state.shape) != (self.n_layer, 5, self.n_embd):
+            raise ValueError(f"state must be [{self.n_layer},5,{self.n_embd}], got {tuple(state.shape)}")
+        if state.dtype != torch.float32 or state.device != self.device or not state.is_contiguous():
+            state = state.to(device=self.device, dtype=torch.float32).contiguous()
+        with torch.cuda.device(self.device):
+            toks = tokens.to(self.device, non_blocking=True)
+            T = toks.numel()
+            for i in range(T):
+                self._tok.copy_(toks[i:i + 1], non_blocking=True)
+                self._step(state, want_logits=(i == T - 1))
+        return self._logits.clone(), state
+
+    __call__ = forward

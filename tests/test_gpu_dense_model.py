@@ -1,0 +1,105 @@
+"""GPU tests of the unquantised (TORCH-mode) model: against logits and states the reference itself
+produced on CPU (tests/golden/torch_mode.npz), and against the CPU oracle at the large widths."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle.torch_mode_oracle import OracleTorchMode
+from rwkvstic_b200 import _lib
+from rwkvstic_b200.dense_model import B200DenseRWKV
+from rwkvstic_b200.synth import synth_checkpoint, synth_tokens
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TYPES = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+# Largest |dlogit| allowed, as a fraction of the largest |logit|.  Every product is rounded to the
+# matrices' type (8 / 11 / 24 significant bits); a sum formed in another order can land on the other
+# side of a rounding boundary, so the bound is a few units in the last place of that type.
+REL_TOL = {"f32": 2e-5, "bf16": 4 * 2.0 ** -8, "f16": 4 * 2.0 ** -11}
+SHAPES = {"tiny": (2, 128, 257, 31, 9), "mid": (3, 768, 1000, 32, 12)}
+
+
+def state_excess(mine, ref, rel):
+    """Worst violation of |mine - ref| <= rel * (|ref| + row max) over the rows of a state (row 4, the
+    running exponent, holds -1e30 only before the first token)."""
+    a, b = mine.double().cpu(), ref.double().cpu()
+    bound = rel * (b.abs() + b.abs().amax(dim=2, keepdim=True)) + 1e-6
+    return float(((a - b).abs() - bound).max())
+
+
+@pytest.mark.parametrize("name", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("shape", ["tiny", "mid"])
+def test_dense_model_against_the_reference_outputs(golden, shape, name):
+    L, D, V, seed, n_tok = SHAPES[shape]
+    g = golden("torch_mode.npz")
+    model = B200DenseRWKV.from_checkpoint(synth_checkpoint(L, D, vocab=V, seed=seed), dtype=TYPES[name], device=DEV,
+                                          use_graph=False)
+    toks = torch.from_numpy(g[f"{shape}_tokens"])
+    want = torch.from_numpy(g[f"{shape}_{name}_logits_tok"])
+    state = model.emptyState.clone()
+    worst = 0.0
+    for i, tok in enumerate(toks):
+        got, state = model.forward(tok.reshape(1), state)
+        worst = max(worst, float((got.cpu() - want[i]).abs().max()) / float(want[i].abs().max()))
+    print(f"{shape} {name}: worst |dlogit| / max |logit| over {n_tok} tokens = {worst:.2e}")
+    assert worst <= REL_TOL[name], worst
+    assert state_excess(state, torch.from_numpy(g[f"{shape}_{name}_state_tok"]), REL_TOL[name]) <= 0
+    # several tokens in one call are fed one after another: same result as the calls above
+    again = model.emptyState.clone()
+    got2, _ = model.forward(toks, again)
+    assert torch.equal(got2, got) and torch.equal(again, state)
+
+
+@pytest.mark.parametrize("embed,name", [(2048, "bf16"), (2560, "f16"), (4096, "bf16"), (5120, "bf16"), (4096, "f32")])
+def test_dense_model_against_the_oracle_at_the_large_widths(embed, name):
+    """Two blocks and a 1024-token vocabulary at the widths of the 1.5B ... 14B models, 12 tokens."""
+    V = 1024
+    ck = synth_checkpoint(2, embed, vocab=V, seed=60 + embed % 11)
+    ref = OracleTorchMode(ck, TYPES[name])
+    toks = synth_tokens(12, seed=embed, vocab=V)
+    want, wstate = ref.forward(toks, ref.emptyState.clone())
+    model = B200DenseRWKV.from_checkpoint(ck, dtype=TYPES[name], device=DEV, use_graph=False)
+    got, state = model.forward(toks, model.emptyState.clone())
+    err = float((got.cpu() - want).abs().max()) / float(want.abs().max())
+    print(f"D={embed} {name}: |dlogit| / max |logit| = {err:.2e}")
+    assert err <= REL_TOL[name], err
+    assert state_excess(state, wstate, REL_TOL[name]) <= 0
+
+
+def test_dense_step_graph_replay_is_bit_identical_and_deterministic():
+    m = B200DenseRWKV.synthetic(2, 768, vocab=1000, seed=6, dtype=torch.bfloat16, device=DEV)     # graph from the second call on
+    eager = B200DenseRWKV(m.t.items(), dtype=torch.bfloat16, device=DEV, use_graph=False, decay_is_final=True)
+    toks = synth_tokens(10, seed=2, vocab=1000)
+    sg, se = m.emptyState.clone(), eager.emptyState.clone()
+    for t in toks:
+        lg, _ = m.forward(t.reshape(1), sg)
+        le, _ = eager.forward(t.reshape(1), se)
+        assert torch.equal(lg, le)
+    assert torch.equal(sg, se) and len(m._graphs) >= 1
+    again = m.emptyState.clone()
+    for t in toks:
+        l2, _ = m.forward(t.reshape(1), again)
+    assert torch.equal(l2, lg) and torch.equal(again, sg)
+
+
+def test_dense_step_without_logits_and_bad_arguments():
+    m = B200DenseRWKV.synthetic(1, 128, vocab=300, seed=1, dtype=torch.float16, device=DEV, use_graph=False)
+    a, b = m.emptyState.clone(), m.emptyState.clone()
+    for t in synth_tokens(3, seed=3, vocab=300):
+        m._tok.copy_(t.reshape(1))
+        m._step(a, want_logits=True)
+        m._step(b, want_logits=False)
+    assert torch.equal(a, b)
+    L = m._L
+    args = (m._tok.data_ptr(), a.data_ptr(), None, m._ws.data_ptr(), m._ws.numel(), None)
+    assert L.b200rwkv_dense_step(None, *args) == _lib.EINVAL
+    assert L.b200rwkv_dense_step(C.byref(m._cmodel), m._tok.data_ptr(), a.data_ptr(), None, m._ws.data_ptr(),
+                                 m._ws.numel() - 1, None) == _lib.EINVAL
+    bad = _lib.DenseModel.from_buffer_copy(m._cmodel)
+    bad.n_embd = 132                                               # not a multiple of 8
+    assert L.b200rwkv_dense_step(C.byref(bad), *args) == _lib.EINVAL
+    bad = _lib.DenseModel.from_buffer_copy(m._cmodel)
+    bad.dtype = 7
+    assert L.b200rwkv_dense_step(C.byref(bad), *args) == _lib.EINVAL

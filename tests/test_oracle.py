@@ -1,4 +1,5 @@
 """The CPU oracle against fixtures produced by the unmodified reference (tests/golden/make_golden.py)."""
+import pytest
 import numpy as np
 import torch
 
@@ -99,3 +100,24 @@ def test_two_axis_scheme_self_consistent():
     assert float(((w_hat - w.double().t()).abs() / step).max()) <= 0.5 + 1e-6
     x = torch.randn(3, 24, generator=gen, dtype=torch.float64)
     assert torch.allclose(O.two_axis_mm8(x, q, my, ry, mx, rx), x @ w_hat)
+
+
+@pytest.mark.parametrize("name,dtype", [("f32", torch.float32), ("bf16", torch.bfloat16), ("f16", torch.float16)])
+def test_torch_mode_oracle_reproduces_the_reference(golden, name, dtype):
+    """The unquantised (TORCH-mode) restatement against logits and states the reference's own
+    loadWeights + AgnosticRWKV produced on CPU: same torch operators in the same order, so identical."""
+    from oracle.torch_mode_oracle import OracleTorchMode
+    from rwkvstic_b200.synth import synth_tokens
+    g = golden("torch_mode.npz")
+    for shape, (L, D, V, seed, n_tok) in {"tiny": (2, 128, 257, 31, 9), "mid": (3, 768, 1000, 32, 12)}.items():
+        m = OracleTorchMode(synth_checkpoint(L, D, vocab=V, seed=seed), dtype)
+        toks = synth_tokens(n_tok, seed=5, vocab=V)
+        assert toks.tolist() == g[f"{shape}_tokens"].tolist()
+        s = m.emptyState.clone()
+        for i, tok in enumerate(toks):
+            lg, s = m.forward(tok.reshape(1), s)
+            assert torch.equal(lg, t(g[f"{shape}_{name}_logits_tok"][i])), (shape, i)
+        assert torch.equal(s, t(g[f"{shape}_{name}_state_tok"]))
+        if shape == "tiny":
+            lg, s = m.forward(toks, m.emptyState.clone())
+            assert torch.equal(lg, t(g[f"{shape}_{name}_logits_seq"])) and torch.equal(s, t(g[f"{shape}_{name}_state_seq"]))

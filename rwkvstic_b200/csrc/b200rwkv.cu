@@ -748,6 +748,7 @@ static int dense_elem_bytes(int dtype) { return dtype == B200RWKV_F32 ? 4 : (dty
 
 // ---- unquantised weights: one token through the network -------------------------------------------
 struct DenseWorkspace {
+  int* status;
   float *x, *gate;
   void *xk, *xv, *xr, *rw, *fk, *fr, *kk, *hx;
   size_t bytes;
@@ -759,6 +760,7 @@ static DenseWorkspace dense_carve(const b200rwkv_dense_model* m, void* base) {
   size_t off = 0;
   auto take = [&](size_t n) { char* r = p ? p + off : nullptr; off += align256(n); return r; };
   const size_t D = size_t(m->n_embd) * 4, F = size_t(m->n_ffn) * 4;    // sized for the widest type
+  w.status = reinterpret_cast<int*>(take(256));
   w.x = reinterpret_cast<float*>(take(D));
   w.gate = reinterpret_cast<float*>(take(D));
   w.xk = take(D); w.xv = take(D); w.xr = take(D); w.rw = take(D);
@@ -777,44 +779,70 @@ static cudaError_t dense_launch_vec(const DenseVecParams& P, bool chained, cudaS
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr; cfg.numAttrs = chained ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, dense_vec_kernel<T>, P);
+  // Same shared-memory carve-out as the rows kernels it alternates with: an SM whose split between L1
+  // and shared memory has to change first drains, which would serialise the chain.
+  static bool configured[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(dense_vec_kernel<T, 1>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dense_vec_kernel<T, 2>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dense_vec_kernel<T, 3>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int groups = (P.D / 4 + kDsVecThreads - 1) / kDsVecThreads;    // float4 groups per thread
+  if (groups <= 1) return cudaLaunchKernelEx(&cfg, dense_vec_kernel<T, 1>, P);
+  if (groups == 2) return cudaLaunchKernelEx(&cfg, dense_vec_kernel<T, 2>, P);
+  return cudaLaunchKernelEx(&cfg, dense_vec_kernel<T, 3>, P);
 }
 
-// Grid and K split for one rows launch: as many CTAs as fit the GPU at once, and enough warps per
-// task that every SM has several rounds of work while a warp's share of a row is still one full
-// batch of 16-byte pieces per lane.
+// Geometry of one rows launch: one CTA per SM, each owning an equal share of the tasks.  A task is cut
+// into the fewest K ranges for which 32 ring slots fit beside the staged activation vectors (so the
+// ring is as deep in bytes as shared memory allows), and into more while a CTA would have fewer than
+// 64 items and a range still has two 16-byte pieces per lane.
+static bool dense_rows_geometry(DenseRowsParams& P, int R, int elem_bytes, int sms, int* grid, size_t* smem) {
+  const int nx = R == 3 ? 3 : P.nseg;
+  const int pieces = P.K * elem_bytes / 16;
+  *grid = sms < P.tasks ? sms : P.tasks;
+  if (*grid < 1 || pieces < 1) return false;
+  P.max_local = (P.tasks + *grid - 1) / *grid;
+  const int want = (64 + P.max_local - 1) / P.max_local;
+  for (int split = 1; split <= pieces; ++split) {
+    const int range = (pieces + split - 1) / split;
+    if ((split - 1) * range >= pieces) continue;            // a split whose last range would be empty
+    P.row_stride = range * 16;
+    P.stage_bytes = (R * P.row_stride + 127) / 128 * 128;
+    const DenseRowsLayout lay = dense_rows_layout(nx, P.K, elem_bytes, P.max_local, split, R, P.stage_bytes);
+    if (lay.total > size_t(kDrSmemLimit)) continue;
+    if (split < want && range >= 128) continue;
+    P.split = split;
+    *smem = lay.total;
+    return true;
+  }
+  return false;
+}
+
 template <typename T, int R>
 static cudaError_t dense_launch_rows(DenseRowsParams& P, cudaStream_t stream) {
   static bool configured[64];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   auto kernel = dense_rows_kernel<T, R>;
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDsMaxStage);
+  if (!configured[dev]) {
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDrSmemLimit);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
-  const int nx = R == 3 ? 3 : P.nseg;
-  const size_t smem = size_t(nx) * P.K * sizeof(T);
-  if (smem > size_t(kDsMaxStage)) return cudaErrorInvalidValue;
-  int per_sm = 0;
-  e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kDsThreads, smem);
-  if (e != cudaSuccess) return e;
-  if (per_sm < 1) return cudaErrorInvalidValue;
-  const int sms = device_sms();
-  const int warps = sms * per_sm * kDsWarps;
-  const int batch = 32 * (R == 3 ? 4 : 6);                       // pieces one warp takes per batch
-  const int pieces = P.K / (16 / int(sizeof(T)));
-  int split = 1;
-  while (split < kDsWarps && (long long)P.tasks * split < 4ll * warps && pieces / (split * 2) >= batch) split *= 2;
-  P.split = split;
-  const int per_pass = kDsWarps / split;
-  const int passes = (P.tasks + per_pass - 1) / per_pass;
-  const int most = sms * per_sm;
+  int grid = 0;
+  size_t smem = 0;
+  if (!dense_rows_geometry(P, R, int(sizeof(T)), device_sms(), &grid, &smem)) return cudaErrorInvalidValue;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(passes < most ? passes : most); cfg.blockDim = dim3(kDsThreads);
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kDrThreads);
   cfg.dynamicSmemBytes = smem; cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -849,6 +877,7 @@ static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, 
 
     DenseRowsParams rp;
     memset(&rp, 0, sizeof(rp));
+    rp.status = ws.status;
     rp.nseg = 3; rp.K = D; rp.tasks = D;
     rp.seg[0] = DenseSeg{Lr.att_key, ws.xk, nullptr, D, D, 0};
     rp.seg[1] = DenseSeg{Lr.att_value, ws.xv, nullptr, D, D, 0};
@@ -857,6 +886,7 @@ static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, 
     B200_DS_CHECK((dense_launch_rows<T, 3>(rp, st)), "key/value/receptance rows");
 
     memset(&rp, 0, sizeof(rp));
+    rp.status = ws.status;
     rp.nseg = 1; rp.K = D; rp.tasks = (D + 1) / 2;
     rp.seg[0] = DenseSeg{Lr.att_output, ws.rw, nullptr, D, D, kEpResid};
     rp.resid = ws.x;
@@ -869,12 +899,14 @@ static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, 
     B200_DS_CHECK(dense_launch_vec<T>(vp, true, st), "ffn mix");
 
     memset(&rp, 0, sizeof(rp));
+    rp.status = ws.status;
     rp.nseg = 2; rp.K = D; rp.tasks = (F + D + 1) / 2;
     rp.seg[0] = DenseSeg{Lr.ffn_key, ws.fk, ws.kk, D, F, kEpRelu2};
     rp.seg[1] = DenseSeg{Lr.ffn_receptance, ws.fr, ws.gate, D, D, kEpSigmoid};
     B200_DS_CHECK((dense_launch_rows<T, 2>(rp, st)), "ffn key and receptance rows");
 
     memset(&rp, 0, sizeof(rp));
+    rp.status = ws.status;
     rp.nseg = 1; rp.K = F; rp.tasks = (D + 1) / 2;
     rp.seg[0] = DenseSeg{Lr.ffn_value, ws.kk, nullptr, F, D, kEpGated};
     rp.resid = ws.x; rp.gate = ws.gate;
@@ -886,6 +918,7 @@ static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, 
     B200_DS_CHECK(dense_launch_vec<T>(vp, true, st), "output layer norm");
     DenseRowsParams rp;
     memset(&rp, 0, sizeof(rp));
+    rp.status = ws.status;
     rp.nseg = 1; rp.K = D; rp.tasks = (V + 1) / 2;
     rp.seg[0] = DenseSeg{m->head, ws.hx, logits, D, V, kEpStore};
     B200_DS_CHECK((dense_launch_rows<T, 2>(rp, st)), "head rows");
@@ -901,7 +934,7 @@ static const char* dense_model_problem(const b200rwkv_dense_model* m) {
   if (m->n_embd > kDsMaxEmbd) return "n_embd above 12160";
   const int eb = dense_elem_bytes(m->dtype);
   if (!eb) return "unknown dtype";
-  if (size_t(3) * m->n_embd * eb > size_t(kDsMaxStage) || size_t(m->n_ffn) * eb > size_t(kDsMaxStage)) return "rows too long to stage in shared memory";
+  if (size_t(3) * m->n_embd * eb > size_t(160) * 1024 || size_t(m->n_ffn) * eb > size_t(160) * 1024) return "rows too long to stage in shared memory";
   if (!aligned16(m->head)) return "head not 16-byte aligned";
   for (int l = 0; l < m->n_layer; ++l) {
     const b200rwkv_dense_layer& L = m->layers[l];

@@ -19,15 +19,14 @@
 // step is deterministic.
 #pragma once
 
+#include <type_traits>
+
 #include "dense_gemv.cuh"
 
 namespace b200 {
 
-constexpr int kDsWarps = 8;
-constexpr int kDsThreads = kDsWarps * 32;
 constexpr int kDsVecThreads = 1024;
 constexpr int kDsMaxEmbd = 12160;          // the vector kernel keeps one fp32 row in its 48 KB of static shared memory
-constexpr int kDsMaxStage = 200 * 1024;    // staged activation vectors per CTA of the rows kernel
 
 enum DenseEpilogue { kEpStore = 0, kEpResid = 1, kEpRelu2 = 2, kEpSigmoid = 3, kEpGated = 4 };
 
@@ -67,43 +66,87 @@ __device__ __forceinline__ float block_sum_1024(float v, float* red) {
 }
 
 template <typename T>
+__device__ __forceinline__ void store_t4(T* dst, float a, float b, float c, float d) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+  } else {
+    T v[4] = {DenseType<T>::from_f32(a), DenseType<T>::from_f32(b), DenseType<T>::from_f32(c), DenseType<T>::from_f32(d)};
+    *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(v);
+  }
+}
+
+// One CTA of 1024 threads; thread t owns the float4 groups t, t + 1024, ... (NV of them cover D).
+// The parameter vectors are requested before the dependency wait, the row and the carried row
+// right after it, so that every load of the kernel is in flight at once.
+template <typename T, int NV>
 __global__ void __launch_bounds__(kDsVecThreads)
 dense_vec_kernel(const DenseVecParams P) {
-  __shared__ float row[kDsMaxEmbd];
   __shared__ float red[32];
   griddep_launch_dependents();
-  griddep_wait();
-  const int tid = threadIdx.x, D = P.D;
-  const float* src = P.x ? P.x : P.emb + size_t(*P.token) * D;
-  float s = 0.f;
-  for (int j = tid; j < D; j += kDsVecThreads) {
-    const float v = P.x ? ld_act_f32(src + j) : ld_param_f32(src + j);
-    row[j] = v;
-    s += v;
-  }
-  const float mean = block_sum_1024(s, red) / float(D);
-  float q = 0.f;
-  for (int j = tid; j < D; j += kDsVecThreads) {
-    const float c = row[j] - mean;
-    q = fmaf(c, c, q);
-  }
-  const float sd = sqrtf(block_sum_1024(q, red) / float(D) + 1e-5f);
-  for (int j = tid; j < D; j += kDsVecThreads) {
-    const float y = P.ln_w[j] * ((row[j] - mean) / sd) + P.ln_b[j];      // torch.py:102-110
-    if (P.x_out) P.x_out[j] = y;
-    if (P.carry) {
-      const float prev = ld_act_f32(P.carry + j);
+  const int tid = threadIdx.x, D4 = P.D >> 2;
+  float4 lw[NV], lb[NV], xv[NV], cv[NV];
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int m = 0; m < 3; ++m)
-        if (m < P.nmix) static_cast<T*>(P.out[m])[j] = DenseType<T>::from_f32(lerp_like_torch(prev, y, P.mix[m][j]));
-      P.carry[j] = y;
+  for (int i = 0; i < NV; ++i) {
+    const int g = tid + i * kDsVecThreads;
+    const bool in = g < D4;
+    lw[i] = in ? ld_param_v4(reinterpret_cast<const float4*>(P.ln_w) + g) : zero;
+    lb[i] = in ? ld_param_v4(reinterpret_cast<const float4*>(P.ln_b) + g) : zero;
+  }
+  griddep_wait();
+  const float4* src = reinterpret_cast<const float4*>(P.x ? P.x : P.emb + size_t(*P.token) * P.D);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int g = tid + i * kDsVecThreads;
+    const bool in = g < D4;
+    xv[i] = in ? ld_act_v4(src + g) : zero;
+    cv[i] = in && P.carry ? ld_act_v4(reinterpret_cast<const float4*>(P.carry) + g) : zero;
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) s += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
+  const float mean = block_sum_1024(s, red) / float(P.D);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (tid + i * kDsVecThreads < D4) {
+      xv[i].x -= mean; xv[i].y -= mean; xv[i].z -= mean; xv[i].w -= mean;
+      q = fmaf(xv[i].x, xv[i].x, q); q = fmaf(xv[i].y, xv[i].y, q); q = fmaf(xv[i].z, xv[i].z, q); q = fmaf(xv[i].w, xv[i].w, q);
+    }
+  }
+  const float sd = sqrtf(block_sum_1024(q, red) / float(P.D) + 1e-5f);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int g = tid + i * kDsVecThreads;
+    if (g >= D4) continue;
+    float4 y;                                                            // torch.py:102-110
+    y.x = lw[i].x * (xv[i].x / sd) + lb[i].x; y.y = lw[i].y * (xv[i].y / sd) + lb[i].y;
+    y.z = lw[i].z * (xv[i].z / sd) + lb[i].z; y.w = lw[i].w * (xv[i].w / sd) + lb[i].w;
+    if (P.x_out) reinterpret_cast<float4*>(P.x_out)[g] = y;
+    if (P.carry) {
+#pragma unroll
+      for (int m = 0; m < 3; ++m) {
+        if (m < P.nmix) {
+          const float4 w = ld_param_v4(reinterpret_cast<const float4*>(P.mix[m]) + g);
+          store_t4(static_cast<T*>(P.out[m]) + 4 * size_t(g), lerp_like_torch(cv[i].x, y.x, w.x), lerp_like_torch(cv[i].y, y.y, w.y),
+                   lerp_like_torch(cv[i].z, y.z, w.z), lerp_like_torch(cv[i].w, y.w, w.w));
+        }
+      }
+      reinterpret_cast<float4*>(P.carry)[g] = y;
     } else if (P.out[0]) {
-      static_cast<T*>(P.out[0])[j] = DenseType<T>::from_f32(y);
+      store_t4(static_cast<T*>(P.out[0]) + 4 * size_t(g), y.x, y.y, y.z, y.w);
     }
   }
 }
 
 // ------------------------------------------------------------------------------------ rows kernel
+constexpr int kDrWarps = 16;
+constexpr int kDrThreads = kDrWarps * 32;
+constexpr int kDrSlots = 2;                            // ring slots per warp
+constexpr int kDrStages = kDrWarps * kDrSlots;
+constexpr int kDrOffFull = 0, kDrOffAbort = 512, kDrOffData = 1024;
+constexpr int kDrSmemLimit = 227 * 1024;
+
 struct DenseSeg {
   const void* w;        // [n][ldw] of T
   const void* x;        // [K] of T, written by an earlier kernel of the step
@@ -115,151 +158,278 @@ struct DenseSeg {
 struct DenseRowsParams {
   DenseSeg seg[3];
   int nseg, K, tasks, split;
+  int max_local;           // most tasks one CTA owns
+  int row_stride;          // bytes between the rows of one ring slot (>= the longest K range, multiple of 16)
+  int stage_bytes;         // R * row_stride rounded up to 128
   float* resid;            // fp32 residual stream [n] (kEpResid, kEpGated)
   const float* gate;       // sigmoid(ffn receptance) [n] (kEpGated)
   float* state;            // WKV launch: this block's [5][n] rows
   const float *decay, *first;
   void* wkv_out;           // WKV launch: T[n] = sigmoid(r) * wkv
+  int* status;             // device status word (B200RWKV_STATUS_* bits)
+#ifdef B200_DENSE_TRACE
+  unsigned long long* trace;   // profiling builds: CTA 0, [warp][item 0..63][8] %globaltimer stamps
+#endif
 };
 
-// R == 3: task o = row o of the key, value and receptance matrices (segments 0..2, each with its own
-//         activation vector); the epilogue advances channel o of the WKV state.
-// R == 2: task t = rows 2t, 2t+1 of the segments laid end to end (every segment but the last has an
-//         even row count); the rows of a pair share their activation vector.
-// `split` warps (1, 2, 4 or 8) share the K range of a task; their sums meet in shared memory in part order.
+#ifdef B200_DENSE_TRACE
+#define B200_DENSE_STAMP(i) do { if (lane == 0 && blockIdx.x == 0 && P.trace && k < 64) P.trace[(size_t(warp) * 64 + k) * 8 + (i)] = globaltimer_ns(); } while (0)
+#else
+#define B200_DENSE_STAMP(i) do { } while (0)
+#endif
+
+// Shared memory after the barriers: activation vectors, partial sums + arrival counters, epilogue
+// operands of the CTA's tasks, ring.
+struct DenseRowsLayout { size_t x_off, part_off, arrived_off, ep_off, ring_off, total; };
+__host__ __device__ inline DenseRowsLayout dense_rows_layout(int nx, int K, int elem_bytes, int max_local, int split, int R, int stage_bytes) {
+  DenseRowsLayout l;
+  l.x_off = kDrOffData;
+  l.part_off = (l.x_off + size_t(nx) * K * elem_bytes + 127) / 128 * 128;
+  l.arrived_off = l.part_off + size_t(max_local) * split * R * 4;
+  l.ep_off = l.arrived_off + size_t(max_local) * 4;
+  l.ring_off = (l.ep_off + size_t(max_local) * (R == 3 ? 5 : 4) * 4 + 127) / 128 * 128;
+  l.total = l.ring_off + size_t(kDrStages) * stage_bytes;
+  return l;
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Sixteen bytes of activations times sixteen bytes of weights, added to two running sums (even and
+// odd elements).  bf16 widens to fp32 with a shift or a mask: the conversion instruction runs at a
+// fraction of the FMA rate and would bound the kernel.
+template <typename T>
+__device__ __forceinline__ void dot_piece(const uint4& a, const uint4& b, float& s0, float& s1) {
+  if constexpr (sizeof(T) == 4) {
+    s0 = fmaf(__uint_as_float(a.x), __uint_as_float(b.x), s0); s1 = fmaf(__uint_as_float(a.y), __uint_as_float(b.y), s1);
+    s0 = fmaf(__uint_as_float(a.z), __uint_as_float(b.z), s0); s1 = fmaf(__uint_as_float(a.w), __uint_as_float(b.w), s1);
+  } else {
+    const uint32_t xa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+        s0 = fmaf(__uint_as_float(xa[i] << 16), __uint_as_float(wb[i] << 16), s0);
+        s1 = fmaf(__uint_as_float(xa[i] & 0xffff0000u), __uint_as_float(wb[i] & 0xffff0000u), s1);
+      } else {
+        const float2 xf = __half22float2(*reinterpret_cast<const __half2*>(&xa[i]));
+        const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&wb[i]));
+        s0 = fmaf(xf.x, wf.x, s0);
+        s1 = fmaf(xf.y, wf.y, s1);
+      }
+    }
+  }
+}
+
+// One CTA of 16 warps per SM.  CTA b owns the contiguous tasks [tasks*b/grid, tasks*(b+1)/grid):
+//   R == 3: task o = row o of the key, value and receptance matrices (segments 0..2, each with its own
+//           activation vector); the epilogue advances channel o of the WKV state.
+//   R == 2: task t = rows 2t, 2t+1 of the segments laid end to end (every segment but the last has an
+//           even row count); the rows of a pair share their activation vector.
+// A task is cut into `split` K ranges; item i = (task, range) in order; warp w takes items w, w + 16, ...
+// Every warp runs its own two-slot ring: lane 0 requests an item's weight bytes with bulk copies that
+// complete on the slot's mbarrier, the warp multiplies the landed slot against the activation vector
+// staged in shared memory, and lane 0 refills the slot with the warp's item after next.  The first two
+// items of every warp are requested before the dependency wait (no kernel writes weights), so the
+// whole ring is in flight while the previous kernel drains.  Partial sums of a task meet in shared
+// memory; whichever warp completes the task adds them in range order and runs the epilogue.  Warps
+// never wait for one another, and every sum is formed in a fixed order.
 template <typename T, int R>
-__global__ void __launch_bounds__(kDsThreads, R == 3 ? 2 : 3)
+__global__ void __launch_bounds__(kDrThreads, 1)
 dense_rows_kernel(const DenseRowsParams P) {
   constexpr int VEC = 16 / int(sizeof(T));
-  constexpr int U = R == 3 ? 4 : 6;                  // 16-byte pieces of each row in flight per lane
-  extern __shared__ __align__(16) unsigned char ds_smem[];
-  __shared__ float partial[kDsWarps][R];
-  uint4* xs = reinterpret_cast<uint4*>(ds_smem);     // [nx][K / VEC]
+  extern __shared__ __align__(128) unsigned char ds_smem[];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int pieces = P.K / VEC;
   const int nx = R == 3 ? 3 : P.nseg;
+  const int split = P.split;
+  const DenseRowsLayout lay = dense_rows_layout(nx, P.K, int(sizeof(T)), P.max_local, split, R, P.stage_bytes);
+  const uint32_t full0 = smem_u32(ds_smem + kDrOffFull) + uint32_t(warp * kDrSlots) * 8u;     // this warp's barriers
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(ds_smem + kDrOffAbort);
+  uint4* xs = reinterpret_cast<uint4*>(ds_smem + lay.x_off);                     // [nx][pieces]
+  float* partial = reinterpret_cast<float*>(ds_smem + lay.part_off);             // [max_local * split][R]
+  int* arrived = reinterpret_cast<int*>(ds_smem + lay.arrived_off);              // [max_local]
+  float* eps = reinterpret_cast<float*>(ds_smem + lay.ep_off);                   // R == 3: [5][max_local]; R == 2: [2][2 * max_local]
+  unsigned char* ring = ds_smem + lay.ring_off + size_t(warp * kDrSlots) * P.stage_bytes;   // this warp's slots
 
   griddep_launch_dependents();
+  const int t0 = int((long long)P.tasks * blockIdx.x / gridDim.x);
+  const int t1 = int((long long)P.tasks * (blockIdx.x + 1) / gridDim.x);
+  if (tid == 0) *abort_flag = 0;
+  if (lane == 0) {
+    for (int i = 0; i < kDrSlots; ++i) mbar_init(full0 + 8 * i, 1);
+    fence_mbar_init();
+  }
+  __syncwarp();
+
+  // K ranges are `range` pieces long (the last one of a row may be shorter); item -> (task, range)
+  // indices advance by kDrWarps items without divisions.
+  const int range = P.row_stride >> 4;
+  const int adv_lt = kDrWarps / split, adv_part = kDrWarps % split;
+  auto advance = [&](int& lt, int& part) __attribute__((always_inline)) {
+    lt += adv_lt; part += adv_part;
+    if (part >= split) { part -= split; ++lt; }
+  };
+  // lane 0: request item (lt, part), the warp's k-th, into slot k % 2
+  auto request = [&](int k, int lt, int part) __attribute__((always_inline)) {
+    if (lt >= t1 - t0) return;
+    const int task = t0 + lt;
+    const int c0 = part * range, c1 = min(c0 + range, pieces);
+    const uint32_t bytes = uint32_t(c1 - c0) * 16u;
+    const uint32_t bar = full0 + 8 * (k % kDrSlots);
+    const uint32_t dst = smem_u32(ring + size_t(k % kDrSlots) * P.stage_bytes);
+    mbar_arrive_expect_tx(bar, bytes * R);
+    if constexpr (R == 3) {
+#pragma unroll
+      for (int r = 0; r < 3; ++r)
+        bulk_g2s(dst + r * P.row_stride,
+                 reinterpret_cast<const uint4*>(static_cast<const T*>(P.seg[r].w) + size_t(task) * P.seg[r].ldw) + c0, bytes, bar);
+    } else {
+      int sidx = 0, local = 2 * task;
+      while (sidx + 1 < P.nseg && local >= P.seg[sidx].n) { local -= P.seg[sidx].n; ++sidx; }
+      const T* W = static_cast<const T*>(P.seg[sidx].w);
+      bulk_g2s(dst, reinterpret_cast<const uint4*>(W + size_t(local) * P.seg[sidx].ldw) + c0, bytes, bar);
+      bulk_g2s(dst + P.row_stride,
+               reinterpret_cast<const uint4*>(W + size_t(min(local + 1, P.seg[sidx].n - 1)) * P.seg[sidx].ldw) + c0, bytes, bar);
+    }
+  };
+  int lt = warp / split, part = warp % split;          // the item being consumed
+  int rlt = lt, rpart = part;                          // the next item to request
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < kDrSlots; ++k) {
+      request(k, rlt, rpart);
+      advance(rlt, rpart);
+    }
+  }
+
   griddep_wait();
+  for (int i = tid; i < t1 - t0; i += kDrThreads) arrived[i] = 0;
+  // Operands of the epilogues of all the CTA's tasks, fetched now in one latency: a load issued
+  // later would queue behind the megabytes of weight requests in flight.
+  if constexpr (R == 3) {
+    const int n = P.seg[0].n;
+    for (int i = tid; i < 5 * (t1 - t0); i += kDrThreads) {
+      const int a = i / (t1 - t0), j = i - a * (t1 - t0);
+      eps[a * P.max_local + j] = a < 3 ? ld_act_f32(P.state + size_t(2 + a) * n + t0 + j)
+                                       : ld_param_f32((a == 3 ? P.decay : P.first) + t0 + j);
+    }
+  } else if (P.resid) {                   // residual epilogues: one segment, outputs 2*t0 .. 2*t1-1
+    const int n = P.seg[0].n, cnt = min(2 * t1, n) - 2 * t0;
+    for (int i = tid; i < cnt; i += kDrThreads) {
+      eps[i] = ld_act_f32(P.resid + 2 * t0 + i);
+      if (P.gate) eps[2 * P.max_local + i] = ld_act_f32(P.gate + 2 * t0 + i);
+    }
+  }
   for (int v = 0; v < nx; ++v) {
     const uint4* src = static_cast<const uint4*>(P.seg[v].x);
-    for (int c = tid; c < pieces; c += kDsThreads) xs[v * pieces + c] = ld_act_u4(src + c);
+    for (int c = tid; c < pieces; c += kDrThreads) xs[v * pieces + c] = ld_act_u4(src + c);
   }
   __syncthreads();
 
-  const int split = P.split, per_pass = kDsWarps / split;
-  const int slot = warp / split, part = warp - slot * split;
-  const int c_begin = int((long long)pieces * part / split), c_end = int((long long)pieces * (part + 1) / split);
-
-  for (int base = blockIdx.x * per_pass; base < P.tasks; base += gridDim.x * per_pass) {
-    const int task = base + slot;
-    const bool live = task < P.tasks;
-    const int tk = live ? task : P.tasks - 1;          // idle slots re-read the last task and store nothing
-    const uint4* row[R];
-    const uint4* xv[R];
-    int sidx = 0, local = tk;                          // R == 2: segment and row inside it of the pair's first row
-    if constexpr (R == 3) {
-#pragma unroll
-      for (int r = 0; r < 3; ++r) {
-        row[r] = reinterpret_cast<const uint4*>(static_cast<const T*>(P.seg[r].w) + size_t(tk) * P.seg[r].ldw);
-        xv[r] = xs + r * pieces;
-      }
-    } else {
-      local = 2 * tk;
+  int k = 0;
+  bool dead = false;
+  for (; lt < t1 - t0; advance(lt, part), ++k) {
+    const int task = t0 + lt, item = lt * split + part;
+    const int c0 = part * range, c1 = min(c0 + range, pieces);
+    int sidx = 0, local = task;
+    if constexpr (R == 2) {
+      local = 2 * task;
       while (sidx + 1 < P.nseg && local >= P.seg[sidx].n) { local -= P.seg[sidx].n; ++sidx; }
-      const DenseSeg& S = P.seg[sidx];
-      const T* W = static_cast<const T*>(S.w);
-      row[0] = reinterpret_cast<const uint4*>(W + size_t(local) * S.ldw);
-      row[1] = reinterpret_cast<const uint4*>(W + size_t(min(local + 1, S.n - 1)) * S.ldw);
-      xv[0] = xv[1] = xs + sidx * pieces;
     }
-    float sum[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) sum[r] = 0.f;
-
-    int c = c_begin + lane;
-    for (; c + (U - 1) * 32 < c_end; c += U * 32) {
-      uint4 w[R][U];
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int j = 0; j < U; ++j) w[r][j] = __ldcs(row[r] + c + j * 32);
-#pragma unroll
-      for (int j = 0; j < U; ++j) {
-        if constexpr (R == 3) {
-#pragma unroll
-          for (int r = 0; r < 3; ++r) {
-            const uint4 a = xv[r][c + j * 32];
-            const T* xe = reinterpret_cast<const T*>(&a);
-            const T* we = reinterpret_cast<const T*>(&w[r][j]);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) sum[r] = fmaf(DenseType<T>::to_f32(xe[i]), DenseType<T>::to_f32(we[i]), sum[r]);
-          }
-        } else {
-          const uint4 a = xv[0][c + j * 32];
-          const T* xe = reinterpret_cast<const T*>(&a);
-#pragma unroll
-          for (int r = 0; r < 2; ++r) {
-            const T* we = reinterpret_cast<const T*>(&w[r][j]);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) sum[r] = fmaf(DenseType<T>::to_f32(xe[i]), DenseType<T>::to_f32(we[i]), sum[r]);
-          }
-        }
-      }
+    const int slot = k % kDrSlots;
+    B200_DENSE_STAMP(0);
+    const bool ok = mbar_wait_bounded(full0 + 8 * slot, uint32_t(k / kDrSlots) & 1u, abort_flag);
+    if (!__all_sync(0xffffffffu, ok)) {
+      if (lane == 0 && P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
+      dead = true;
+      break;
     }
-    for (; c < c_end; c += 32) {
+    B200_DENSE_STAMP(1);
+    const uint4* st = reinterpret_cast<const uint4*>(ring + size_t(slot) * P.stage_bytes);
+    const int rs = P.row_stride >> 4, n = c1 - c0;
+    float acc[R][2];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r][0] = acc[r][1] = 0.f;
+    const uint4* x0 = xs + (R == 3 ? 0 : sidx * pieces) + c0;
+#pragma unroll 4
+    for (int p = lane; p < n; p += 32) {
+      uint4 a = x0[p];
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const uint4 wv = __ldcs(row[r] + c);
-        const uint4 a = xv[r][c];
-        const T* xe = reinterpret_cast<const T*>(&a);
-        const T* we = reinterpret_cast<const T*>(&wv);
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) sum[r] = fmaf(DenseType<T>::to_f32(xe[i]), DenseType<T>::to_f32(we[i]), sum[r]);
+        if (R == 3 && r > 0) a = x0[r * pieces + p];
+        dot_piece<T>(a, st[r * rs + p], acc[r][0], acc[r][1]);
       }
     }
+    __syncwarp();
+    B200_DENSE_STAMP(2);
+    if (lane == 0) {                       // the slot has been read: refill it with the item after next
+      fence_proxy_async_smem();
+      request(k + kDrSlots, rlt, rpart);
+      advance(rlt, rpart);
+    }
+    B200_DENSE_STAMP(4);
+    float sum[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) sum[r] = warp_sum(sum[r]);
-    if (split > 1) {                                   // uniform over the CTA
+    for (int r = 0; r < R; ++r) sum[r] = warp_sum(acc[r][0] + acc[r][1]);
+    B200_DENSE_STAMP(5);
+    // Lane 0 runs the shared-memory hand-over of the partial sums; lane 1 does the epilogue's global
+    // stores, so that lane 0's fences never wait for a store on its way to L2.
+    int last = 1;
+    if (split > 1) {
       if (lane == 0) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) partial[warp][r] = sum[r];
-      }
-      __syncthreads();
-      if (lane == 0 && part == 0) {
+        for (int r = 0; r < R; ++r) partial[size_t(item) * R + r] = sum[r];
+        __threadfence_block();
+        last = atomicAdd(&arrived[lt], 1) == split - 1;
+        if (last) {
+          __threadfence_block();
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-          float t = 0.f;
-          for (int q = 0; q < split; ++q) t += partial[warp + q][r];
-          sum[r] = t;
+          for (int r = 0; r < R; ++r) {
+            float t = 0.f;
+            for (int q = 0; q < split; ++q) t += partial[(size_t(lt) * split + q) * R + r];
+            sum[r] = t;
+          }
         }
       }
-      __syncthreads();
+      last = __shfl_sync(0xffffffffu, last, 0);
+#pragma unroll
+      for (int r = 0; r < R; ++r) sum[r] = __shfl_sync(0xffffffffu, sum[r], 0);
     }
-    if (lane != 0 || part != 0 || !live) continue;
-
-    if constexpr (R == 3) {
-      const int n = P.seg[0].n, o = tk;
-      const float k = DenseType<T>::round(sum[0]), v = DenseType<T>::round(sum[1]), r = DenseType<T>::round(sum[2]);
-      float aa = ld_act_f32(P.state + 2 * size_t(n) + o), bb = ld_act_f32(P.state + 3 * size_t(n) + o);
-      float pp = ld_act_f32(P.state + 4 * size_t(n) + o);
-      const float y = wkv_step(k, v, P.decay[o], P.first[o], aa, bb, pp);      // agnosticRwkv.py:68-103
-      P.state[2 * size_t(n) + o] = aa; P.state[3 * size_t(n) + o] = bb; P.state[4 * size_t(n) + o] = pp;
-      static_cast<T*>(P.wkv_out)[o] = DenseType<T>::from_f32(sigmoidf_(r) * y);
-    } else {
-      const DenseSeg& S = P.seg[sidx];
+    if (last && lane == 1) {
+      if constexpr (R == 3) {
+        const int nn = P.seg[0].n, o = local;
+        const float kk = DenseType<T>::round(sum[0]), v = DenseType<T>::round(sum[1]), r = DenseType<T>::round(sum[2]);
+        float aa = eps[lt], bb = eps[P.max_local + lt], pp = eps[2 * P.max_local + lt];
+        const float y = wkv_step(kk, v, eps[3 * P.max_local + lt], eps[4 * P.max_local + lt], aa, bb, pp);   // agnosticRwkv.py:68-103
+        P.state[2 * size_t(nn) + o] = aa; P.state[3 * size_t(nn) + o] = bb; P.state[4 * size_t(nn) + o] = pp;
+        static_cast<T*>(P.wkv_out)[o] = DenseType<T>::from_f32(sigmoidf_(r) * y);
+      } else {
+        const DenseSeg& S = P.seg[sidx];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int o = local + i;
-        if (o >= S.n) break;
-        const float v = DenseType<T>::round(sum[i]);
-        switch (S.ep) {
-          case kEpStore: static_cast<float*>(S.out)[o] = v; break;
-          case kEpResid: P.resid[o] = __fadd_rn(ld_act_f32(P.resid + o), v); break;
-          case kEpRelu2: { const float t = fmaxf(v, 0.f); static_cast<T*>(S.out)[o] = DenseType<T>::from_f32(__fmul_rn(t, t)); break; }
-          case kEpSigmoid: static_cast<float*>(S.out)[o] = sigmoidf_(v); break;
-          default: P.resid[o] = __fadd_rn(ld_act_f32(P.resid + o), __fmul_rn(v, ld_act_f32(P.gate + o))); break;
+        for (int i = 0; i < 2; ++i) {
+          const int o = local + i;
+          if (o < S.n) {
+            const float v = DenseType<T>::round(sum[i]);
+            switch (S.ep) {
+              case kEpStore: static_cast<float*>(S.out)[o] = v; break;
+              case kEpResid: P.resid[o] = __fadd_rn(eps[2 * lt + i], v); break;
+              case kEpRelu2: { const float t = fmaxf(v, 0.f); static_cast<T*>(S.out)[o] = DenseType<T>::from_f32(__fmul_rn(t, t)); break; }
+              case kEpSigmoid: static_cast<float*>(S.out)[o] = sigmoidf_(v); break;
+              default: P.resid[o] = __fadd_rn(eps[2 * lt + i], __fmul_rn(v, eps[2 * P.max_local + 2 * lt + i])); break;
+            }
+          }
         }
+      }
+    }
+    B200_DENSE_STAMP(3);
+    __syncwarp();
+  }
+  // After an abandoned wait the warp's requests may still be in flight into its slots: give each a
+  // bounded chance to land before the CTA retires.
+  if (dead && lane == 0) {
+    const unsigned long long t_start = globaltimer_ns();
+    for (int j = k; j < k + kDrSlots; ++j) {
+      if (warp + j * kDrWarps >= (t1 - t0) * split) break;
+      while (!mbar_try_wait(full0 + 8 * (j % kDrSlots), uint32_t(j / kDrSlots) & 1u) && globaltimer_ns() - t_start < kWaitLimitNs / 10) {
       }
     }
   }

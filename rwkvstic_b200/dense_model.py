@@ -82,6 +82,7 @@ class B200DenseRWKV:
         self._graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self._seen: Dict[Tuple[int, bool], int] = {}
         self.launches_per_step = 6 * self.n_layer + 3
+        self._status_host, self._status_event, self._status_pending = None, None, False
         self.launch_count = 0
 
     # ------------------------------------------------------------------ construction
@@ -133,6 +134,30 @@ class B200DenseRWKV:
             self._graphs[key] = g
         g.replay()
 
+    def check_status(self) -> None:
+        """Raise if a kernel gave up a bounded device-side wait (synchronises).  The state the failed
+        step was given is undefined after that."""
+        bits = int(self._ws[:4].view(torch.int32).cpu()[0])
+        if bits:
+            self._ws[:4].zero_()
+            raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+
+    def _queue_status(self) -> None:
+        """Non-blocking copy of the status word to pinned memory; looked at by a later call once it has landed."""
+        if self._status_host is None:
+            self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+            self._status_event = torch.cuda.Event()
+        self._status_host.copy_(self._ws[:4].view(torch.int32), non_blocking=True)
+        self._status_event.record(torch.cuda.current_stream(self.device))
+        self._status_pending = True
+
+    def _raise_status(self) -> None:
+        if not self._status_pending or not self._status_event.query():
+            return
+        self._status_pending = False
+        if int(self._status_host[0]):
+            self.check_status()
+
     def forward(self, tokens, state: torch.Tensor):
         if not torch.is_tensor(tokens):
             tokens = torch.tensor(tokens if isinstance(tokens, (list, tuple)) else [tokens], dtype=torch.int64)
@@ -143,12 +168,14 @@ class B200DenseRWKV:
             raise ValueError(f"state must be [{self.n_layer},5,{self.n_embd}], got {tuple(state.shape)}")
         if state.dtype != torch.float32 or state.device != self.device or not state.is_contiguous():
             state = state.to(device=self.device, dtype=torch.float32).contiguous()
+        self._raise_status()
         with torch.cuda.device(self.device):
             toks = tokens.to(self.device, non_blocking=True)
             T = toks.numel()
             for i in range(T):
                 self._tok.copy_(toks[i:i + 1], non_blocking=True)
                 self._step(state, want_logits=(i == T - 1))
+            self._queue_status()
         return self._logits.clone(), state
 
     __call__ = forward

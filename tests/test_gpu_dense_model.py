@@ -66,6 +66,7 @@ def test_dense_model_against_the_oracle_at_the_large_widths(embed, name):
     print(f"D={embed} {name}: |dlogit| / max |logit| = {err:.2e}")
     assert err <= REL_TOL[name], err
     assert state_excess(state, wstate, REL_TOL[name]) <= 0
+    model.check_status()
 
 
 def test_dense_step_graph_replay_is_bit_identical_and_deterministic():
@@ -82,6 +83,7 @@ def test_dense_step_graph_replay_is_bit_identical_and_deterministic():
     for t in toks:
         l2, _ = m.forward(t.reshape(1), again)
     assert torch.equal(l2, lg) and torch.equal(again, sg)
+    m.check_status()
 
 
 def test_dense_step_without_logits_and_bad_arguments():

@@ -335,6 +335,53 @@ def time_decode_shape(shape, dev, steps=128, warm=8):
                          "frac_of_nominal_8TBs": gbs / 8000.0}}
 
 
+def time_dense_decode(shape, dev, dtype=torch.bfloat16, steps=64, warm=6):
+    """Batch-1 decode with UNQUANTISED weights (the reference's TORCH mode) at `shape`: tokens/s, the HBM
+    roofline at sizeof(dtype) bytes per weight, and beside it the same matrices through stock torch
+    (one cuBLAS ``torch.mv`` per matrix, no vector work) as the library baseline."""
+    from rwkvstic_b200.dense_model import B200DenseRWKV
+    L, D = SHAPES[shape]
+    model = B200DenseRWKV.synthetic(L, D, seed=1234, dtype=dtype, device=dev)
+    toks = torch.randint(0, VOCAB, (steps + warm,), generator=torch.Generator().manual_seed(12), dtype=torch.int64).to(dev)
+    state = model.emptyState.clone()
+    for i in range(warm):
+        model.forward(toks[i:i + 1], state)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(warm, warm + steps):
+        model._tok.copy_(toks[i:i + 1])
+        model._step(state, True)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    model.check_status()
+    ms = e0.elapsed_time(e1) / steps
+    wbytes = model.weight_bytes()
+    peak, _ = measured_peaks()
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    mats = [v for k, v in model.t.items() if v.dim() == 2 and k != "emb.weight"]
+    xs = {n: torch.randn(n, device=dev).to(dtype) for n in {m.shape[1] for m in mats}}
+    for m in mats[:8]:
+        torch.mv(m, xs[m.shape[1]])
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(3):
+        for m in mats:
+            torch.mv(m, xs[m.shape[1]])
+    e1.record()
+    torch.cuda.synchronize(dev)
+    lib_ms = e0.elapsed_time(e1) / 3
+    name = str(dtype).replace("torch.", "")
+    return {"workload": f"RWKV-4 {shape} shape L={L} D={D} V={VOCAB}, {name} weights unquantised (TORCH mode), batch-1 decode",
+            "value": 1e3 / ms, "unit": UNIT, "ms_per_step": ms, "steps": steps, "dtype": name,
+            "gpu_launches_per_step": model.launches_per_step, "kernel": "dense_rows_kernel + dense_vec_kernel",
+            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                         "algorithmic_bytes_per_step": wbytes},
+            "library_baseline": {"what": "the same matrices through torch.mv (cuBLAS), one call per matrix, no layer norm / "
+                                         "mix / WKV work; stock torch, same box", "ms_per_step": lib_ms,
+                                 "ours_over_library": ms / lib_ms}}
+
+
 def trace_spans(model, dev):
     """Mean over the 4L+1 GEMV launches of a graph-replayed traced step: from "launch dependency resolved"
     (median over CTAs) to "epilogue done" (last CTA) = the launch's working span, and from "digit planes
@@ -694,6 +741,9 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.empty_cache()
         model = None
         line["decode_1b5"] = time_decode_shape("1b5", dev)
+        torch.cuda.empty_cache()
+        line["torch_mode_bf16"] = time_dense_decode(args.shape, dev)
+        torch.cuda.empty_cache()
         if not args.no_prefill:
             line["prefill"] = time_prefill(dev, tf_peak)
             torch.cuda.empty_cache()

@@ -13,6 +13,11 @@ and whose ``postProcessModule`` returns a ``B200RWKV`` built from them, so
 
 runs the reference's session code (rwkvMaster.py:28-105) on the sm_100a kernels.  Nothing
 here imports the reference at module import time; ``install()`` needs it to be importable.
+
+The reference's TORCH mode takes ``dtype=`` for the matrices (agnostic/backends/torch.py:8-22).  The
+same keyword selects the model here: ``dtype=torch.bfloat16`` / ``float16`` / ``float32`` keeps the
+weights unquantised (``B200DenseRWKV``, the arithmetic of torch.py:125-166), no ``dtype`` or
+``torch.uint8`` gives the FASTQUANT model (``B200RWKV``).
 """
 from __future__ import annotations
 
@@ -45,8 +50,11 @@ def make_ops_class(base_module, model_factory: Optional[Callable] = None, device
     """Subclass of the reference's ``agnostic.backends.base.module`` for ``Backends[MODE]``."""
 
     class RWKVB200Ops(base_module):
-        def __init__(self, layers, embed, *args, **kwargs):
+        def __init__(self, layers, embed, *args, dtype=None, **kwargs):
             super().__init__(layers, embed, *args, **kwargs)
+            if dtype not in (None, torch.uint8, torch.float32, torch.bfloat16, torch.float16):
+                raise ValueError("dtype must be torch.uint8 (FASTQUANT), torch.float32, torch.bfloat16 or torch.float16")
+            self.dtype = dtype
             self.initTensor = lambda x: x.detach().float() if x.is_floating_point() else x   # keep [out,in] fp32
             self.initCpuTensor = self.initTensor
             self.intTensor = lambda x: torch.tensor(x if isinstance(x, list) else [x], dtype=torch.int64)
@@ -63,6 +71,9 @@ def make_ops_class(base_module, model_factory: Optional[Callable] = None, device
                 ck = checkpoint_from_agnostic(model)
                 if factory is not None:
                     new = factory(ck)
+                elif self.dtype in (torch.float32, torch.bfloat16, torch.float16):
+                    from .dense_model import B200DenseRWKV
+                    new = B200DenseRWKV(ck.items(), dtype=self.dtype, device=device)
                 else:
                     from .model import B200RWKV
                     new = B200RWKV.from_checkpoint(ck, device=device, scheme=scheme)

@@ -105,3 +105,43 @@ def test_dense_step_without_logits_and_bad_arguments():
     bad = _lib.DenseModel.from_buffer_copy(m._cmodel)
     bad.dtype = 7
     assert L.b200rwkv_dense_step(C.byref(bad), *args) == _lib.EINVAL
+
+
+def test_loader_hook_with_dtype_builds_the_unquantised_model():
+    """``dtype=`` on the registered ops class (the keyword of the reference's TORCH mode,
+    agnostic/backends/torch.py:8-22) makes postProcessModule hand back the unquantised model, built from
+    the attributes AgnosticRWKV holds (agnosticRwkv.py:22-63; time_decay already -exp(raw))."""
+    from rwkvstic_b200.backend import make_ops_class
+    L, D, V = 2, 256, 300
+    ck = synth_checkpoint(L, D, vocab=V, seed=9)
+
+    class Agnostic:
+        pass
+
+    a = Agnostic()
+    a.emb, a.emb1, a.emb2 = ck["emb.weight"], ck["blocks.0.ln0.weight"], ck["blocks.0.ln0.bias"]
+    a.postprocess0, a.postprocess1, a.postprocess2 = ck["ln_out.weight"], ck["ln_out.bias"], ck["head.weight"]
+    per_layer = {"ln1w": "ln1.weight", "ln1b": "ln1.bias", "ln2w": "ln2.weight", "ln2b": "ln2.bias",
+                 "time_first": "att.time_first", "kktk": "att.time_mix_k", "vvtv": "att.time_mix_v", "rrtr": "att.time_mix_r",
+                 "key": "att.key.weight", "value": "att.value.weight", "receptance": "att.receptance.weight",
+                 "outputvv": "att.output.weight", "time_mix_k_ffn": "ffn.time_mix_k", "time_mix_r_ffn": "ffn.time_mix_r",
+                 "key_ffn": "ffn.key.weight", "receptance_ffn": "ffn.receptance.weight", "value_ffn": "ffn.value.weight"}
+    for attr, name in per_layer.items():
+        setattr(a, attr, [ck[f"blocks.{i}.{name}"].squeeze() if "time_" in name else ck[f"blocks.{i}.{name}"] for i in range(L)])
+    a.time_decay = [-torch.exp(ck[f"blocks.{i}.att.time_decay"].double()) for i in range(L)]
+
+    class Base:            # stands in for agnostic.backends.base.module
+        def __init__(self, layers, embed, *args, **kwargs):
+            pass
+
+    ops_cls = make_ops_class(Base, device=DEV)
+    with pytest.raises(ValueError):
+        ops_cls(L, D, dtype=torch.int8)
+    ops_obj = ops_cls(L, D, dtype=torch.bfloat16)
+    model = ops_obj.postProcessModule(a)
+    assert isinstance(model, B200DenseRWKV) and model.dtype == torch.bfloat16 and ops_obj.emptyState is model.emptyState
+    ref = OracleTorchMode(ck, torch.bfloat16)
+    toks = synth_tokens(6, seed=4, vocab=V)
+    want, _ = ref.forward(toks, ref.emptyState.clone())
+    got, _ = model.forward(toks, model.emptyState.clone())
+    assert float((got.cpu() - want).abs().max()) <= REL_TOL["bf16"] * float(want.abs().max())

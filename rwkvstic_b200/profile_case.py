@@ -10,7 +10,9 @@ tensor-core path instead (row preparation + ``tile_gemm_kernel``): ``ncu -k rege
 
 With ``--dense bf16|fp16|fp32`` the first matrix of the shape is streamed unquantised
 (``dense_gemv_kernel``), and with ``--sampler`` one row of V logits goes through the typical
-sampling kernel (``sample_typical_kernel``).
+sampling kernel (``sample_typical_kernel``).  ``--dense-step bf16|fp16|fp32`` runs --launches
+tokens through the unquantised model of --shape (``dense_rows_kernel``, ``dense_vec_kernel``;
+``--network LAYERS`` truncates it), graph-replayed, and prints the time per token.
 """
 from __future__ import annotations
 
@@ -48,6 +50,8 @@ def main():
                          "--streams x --tokens rows (every kernel of the rows path, for a launch list)")
     ap.add_argument("--dense", default=None, choices=["bf16", "fp16", "fp32"],
                     help="stream the first matrix of --matrix unquantised in this type (dense_gemv_kernel)")
+    ap.add_argument("--dense-step", default=None, choices=["bf16", "fp16", "fp32"],
+                    help="decode --launches tokens with the unquantised model of --shape in this type")
     ap.add_argument("--sampler", action="store_true", help="typical sampling of one row of V logits")
     ap.add_argument("--trace", default=None, choices=["chained", "persistent"],
                     help="print the %%globaltimer timeline of one block of a graph-replayed decode step of --shape "
@@ -55,6 +59,28 @@ def main():
     ap.add_argument("--streams", type=int, default=8)
     ap.add_argument("--tokens", type=int, default=512)
     args = ap.parse_args()
+    if args.dense_step:
+        from .dense_model import B200DenseRWKV
+        dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dense_step]
+        L, D = SHAPES[args.shape]
+        model = B200DenseRWKV.synthetic(args.network or L, D, dtype=dt, device="cuda:0")
+        state = model.emptyState.clone()
+        tok = torch.tensor([17])
+        for _ in range(3):                                   # the third call replays the graph
+            model.forward(tok, state)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.launches):
+            model._step(state, True)
+        e1.record()
+        torch.cuda.synchronize()
+        model.check_status()
+        ms = e0.elapsed_time(e1) / args.launches
+        print(f"unquantised {args.dense_step} decode, {args.shape} width, {model.n_layer} blocks: {ms:.4f} ms per token, "
+              f"{model.weight_bytes() / 1e9:.2f} GB of weights -> {model.weight_bytes() / ms / 1e6:.0f} GB/s; "
+              f"{model.launches_per_step} launches per token")
+        return
     if args.trace:
         from .model import B200RWKV
         L, D = args.network or 4, SHAPES[args.shape][1]

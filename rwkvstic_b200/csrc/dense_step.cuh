@@ -179,15 +179,17 @@ struct DenseRowsParams {
 #endif
 
 // Shared memory after the barriers: activation vectors, partial sums + arrival counters, epilogue
-// operands of the CTA's tasks, ring.
-struct DenseRowsLayout { size_t x_off, part_off, arrived_off, ep_off, ring_off, total; };
+// operands of the CTA's tasks, one 16-byte record per task (R == 2: address of its first row, segment
+// and row index inside it), ring.
+struct DenseRowsLayout { size_t x_off, part_off, arrived_off, ep_off, table_off, ring_off, total; };
 __host__ __device__ inline DenseRowsLayout dense_rows_layout(int nx, int K, int elem_bytes, int max_local, int split, int R, int stage_bytes) {
   DenseRowsLayout l;
   l.x_off = kDrOffData;
   l.part_off = (l.x_off + size_t(nx) * K * elem_bytes + 127) / 128 * 128;
   l.arrived_off = l.part_off + size_t(max_local) * split * R * 4;
   l.ep_off = l.arrived_off + size_t(max_local) * 4;
-  l.ring_off = (l.ep_off + size_t(max_local) * (R == 3 ? 5 : 4) * 4 + 127) / 128 * 128;
+  l.table_off = (l.ep_off + size_t(max_local) * (R == 3 ? 5 : 4) * 4 + 15) / 16 * 16;
+  l.ring_off = (l.table_off + size_t(max_local) * 16 + 127) / 128 * 128;
   l.total = l.ring_off + size_t(kDrStages) * stage_bytes;
   return l;
 }
@@ -248,6 +250,7 @@ dense_rows_kernel(const DenseRowsParams P) {
   float* partial = reinterpret_cast<float*>(ds_smem + lay.part_off);             // [max_local * split][R]
   int* arrived = reinterpret_cast<int*>(ds_smem + lay.arrived_off);              // [max_local]
   float* eps = reinterpret_cast<float*>(ds_smem + lay.ep_off);                   // R == 3: [5][max_local]; R == 2: [2][2 * max_local]
+  ulonglong2* table = reinterpret_cast<ulonglong2*>(ds_smem + lay.table_off);    // [max_local]: {row address, segment | row << 2}
   unsigned char* ring = ds_smem + lay.ring_off + size_t(warp * kDrSlots) * P.stage_bytes;   // this warp's slots
 
   griddep_launch_dependents();
@@ -258,7 +261,19 @@ dense_rows_kernel(const DenseRowsParams P) {
     for (int i = 0; i < kDrSlots; ++i) mbar_init(full0 + 8 * i, 1);
     fence_mbar_init();
   }
-  __syncwarp();
+  if constexpr (R == 2) {
+    for (int i = tid; i < t1 - t0; i += kDrThreads) {
+      int sidx = 0, local = 2 * (t0 + i);
+      while (sidx + 1 < P.nseg && local >= P.seg[sidx].n) { local -= P.seg[sidx].n; ++sidx; }
+      const T* W = static_cast<const T*>(P.seg[sidx].w) + size_t(local) * P.seg[sidx].ldw;
+      // the second row of the pair follows ldw elements later; a pair past the end repeats its first row
+      table[i] = make_ulonglong2(reinterpret_cast<unsigned long long>(W),
+                                 (unsigned long long)(unsigned(sidx) | (unsigned(local) << 2) | (local + 1 < P.seg[sidx].n ? 0x80000000u : 0u)));
+    }
+    __syncthreads();
+  } else {
+    __syncwarp();
+  }
 
   // K ranges are `range` pieces long (the last one of a row may be shorter); item -> (task, range)
   // indices advance by kDrWarps items without divisions.
@@ -283,12 +298,11 @@ dense_rows_kernel(const DenseRowsParams P) {
         bulk_g2s(dst + r * P.row_stride,
                  reinterpret_cast<const uint4*>(static_cast<const T*>(P.seg[r].w) + size_t(task) * P.seg[r].ldw) + c0, bytes, bar);
     } else {
-      int sidx = 0, local = 2 * task;
-      while (sidx + 1 < P.nseg && local >= P.seg[sidx].n) { local -= P.seg[sidx].n; ++sidx; }
-      const T* W = static_cast<const T*>(P.seg[sidx].w);
-      bulk_g2s(dst, reinterpret_cast<const uint4*>(W + size_t(local) * P.seg[sidx].ldw) + c0, bytes, bar);
-      bulk_g2s(dst + P.row_stride,
-               reinterpret_cast<const uint4*>(W + size_t(min(local + 1, P.seg[sidx].n - 1)) * P.seg[sidx].ldw) + c0, bytes, bar);
+      const ulonglong2 rec = table[lt];
+      const unsigned meta = unsigned(rec.y);
+      const T* W = reinterpret_cast<const T*>(rec.x);
+      bulk_g2s(dst, reinterpret_cast<const uint4*>(W) + c0, bytes, bar);
+      bulk_g2s(dst + P.row_stride, reinterpret_cast<const uint4*>(W + ((meta >> 31) ? P.seg[meta & 3u].ldw : 0)) + c0, bytes, bar);
     }
   };
   int lt = warp / split, part = warp % split;          // the item being consumed
@@ -332,8 +346,9 @@ dense_rows_kernel(const DenseRowsParams P) {
     const int c0 = part * range, c1 = min(c0 + range, pieces);
     int sidx = 0, local = task;
     if constexpr (R == 2) {
-      local = 2 * task;
-      while (sidx + 1 < P.nseg && local >= P.seg[sidx].n) { local -= P.seg[sidx].n; ++sidx; }
+      const unsigned meta = unsigned(table[lt].y);
+      sidx = int(meta & 3u);
+      local = int((meta & 0x7fffffffu) >> 2);
     }
     const int slot = k % kDrSlots;
     B200_DENSE_STAMP(0);
@@ -368,8 +383,19 @@ dense_rows_kernel(const DenseRowsParams P) {
     }
     B200_DENSE_STAMP(4);
     float sum[R];
+    if constexpr (R == 2) {
+      // both rows in five shuffles: the lower half of the warp ends up with row 0's total, the upper with row 1's
+      const float mine = acc[0][0] + acc[0][1], other = acc[1][0] + acc[1][1];
+      const bool up = lane >= 16;
+      float v = (up ? other : mine) + __shfl_xor_sync(0xffffffffu, up ? mine : other, 16);
 #pragma unroll
-    for (int r = 0; r < R; ++r) sum[r] = warp_sum(acc[r][0] + acc[r][1]);
+      for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      sum[0] = __shfl_sync(0xffffffffu, v, 0);
+      sum[1] = __shfl_sync(0xffffffffu, v, 16);
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r) sum[r] = warp_sum(acc[r][0] + acc[r][1]);
+    }
     B200_DENSE_STAMP(5);
     // Lane 0 runs the shared-memory hand-over of the partial sums; lane 1 does the epilogue's global
     // stores, so that lane 0's fences never wait for a store on its way to L2.

@@ -376,6 +376,22 @@ size_t b200rwkv_dense_workspace_bytes(const b200rwkv_dense_model* m);
 int b200rwkv_dense_step(const b200rwkv_dense_model* m, const int64_t* token, float* state, float* logits,
                         void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * The same network for `streams` independent sequences of `tokens_per_stream` tokens each (row r =
+ * stream r / tokens_per_stream): every matrix is applied to all rows at once on the tensor cores, as
+ * AgnosticRWKV does with a sequence (agnosticRwkv.py:123-187; matvec of a [T, D] input, torch.py:162-164).
+ * bf16 and fp16 matrices only (an fp32 product has no exact tensor-core form; feed such a model
+ * token by token).  n_embd and n_ffn multiples of 64.
+ *   tokens  device int64 [streams][tokens_per_stream]
+ *   state   device f32, stream b at state + b * state_stride, [n_layer][5][n_embd] each, updated in place
+ *   logits  device f32 [streams][n_vocab] after each stream's last token, or NULL
+ * Enqueues about 12 kernels per block on `stream`; no allocation, no host synchronisation.
+ */
+size_t b200rwkv_dense_rows_workspace_bytes(const b200rwkv_dense_model* m, int streams, int tokens_per_stream);
+int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* tokens, int streams, int tokens_per_stream,
+                                float* state, int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
 #ifdef __cplusplus
 }
 #endif

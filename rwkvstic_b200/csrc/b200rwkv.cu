@@ -1,5 +1,6 @@
 // C ABI of the library (declarations and per-function contracts: include/b200rwkv.h) and the small
 // vector kernels that sit between the streaming GEMV launches.
+#include <algorithm>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -11,6 +12,7 @@
 #include "dense_gemv.cuh"
 #include "decode_step.cuh"
 #include "dense_step.cuh"
+#include "dense_gemm.cuh"
 
 namespace b200 {
 
@@ -927,6 +929,80 @@ static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, 
   return B200RWKV_OK;
 }
 
+// ---- unquantised weights: many rows ------------------------------------------------------------------
+struct DenseRowsWorkspace {
+  int* status;
+  float *xa, *xb, *kb, *vb, *rb, *carry_new, *wkv_loc;
+  unsigned short *t0, *t1, *t2, *kk, *hx;
+  size_t bytes;
+};
+
+static DenseRowsWorkspace dense_carve_rows(const b200rwkv_dense_model* m, int B, int T, void* base) {
+  DenseRowsWorkspace w;
+  char* p = static_cast<char*>(base);
+  size_t off = 0;
+  auto take = [&](size_t n) { char* r = p ? p + off : nullptr; off += align256(n); return r; };
+  const size_t R = size_t(B) * T, Rpad = size_t(gemm_padded_rows(int(R))), Bpad = size_t(gemm_padded_rows(B));
+  const size_t D = size_t(m->n_embd), F = size_t(m->n_ffn);
+  w.status = reinterpret_cast<int*>(take(256));
+  w.xa = reinterpret_cast<float*>(take(R * D * 4));
+  w.xb = reinterpret_cast<float*>(take(R * D * 4));
+  w.kb = reinterpret_cast<float*>(take(R * D * 4));
+  w.vb = reinterpret_cast<float*>(take(R * D * 4));
+  w.rb = reinterpret_cast<float*>(take(R * D * 4));
+  w.carry_new = reinterpret_cast<float*>(take(size_t(B) * D * 4));
+  w.wkv_loc = reinterpret_cast<float*>(take(size_t(B) * size_t((T + kWkvChunk - 1) / kWkvChunk) * 3 * D * 4));
+  w.t0 = reinterpret_cast<unsigned short*>(take(Rpad * D * 2));
+  w.t1 = reinterpret_cast<unsigned short*>(take(Rpad * D * 2));
+  w.t2 = reinterpret_cast<unsigned short*>(take(Rpad * D * 2));
+  w.kk = reinterpret_cast<unsigned short*>(take(Rpad * F * 2));
+  w.hx = reinterpret_cast<unsigned short*>(take(Bpad * D * 2));
+  w.bytes = off;
+  return w;
+}
+
+// Picks the tile (all rows in one row tile up to 240, else equal row tiles; 256 weight rows per tile when
+// that still gives every SM a tile), encodes the tensor maps and launches.  w[s]: [N_s][K] of the 16-bit
+// type; x[s]: [rows_alloc][K] of the same type.
+static cudaError_t launch_dense_gemm(DGemmParams& P, const void* const* w, const unsigned short* const* x, int K, int rows_alloc,
+                                     cudaStream_t stream, const char** why) {
+  static bool configured[64];
+  *why = "dense_tile_gemm launch failed";
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    e = cudaFuncSetAttribute(dense_tile_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDgSmem);
+    if (e != cudaSuccess) return e;
+    configured[dev] = true;
+  }
+  const int sms = device_sms();
+  const int row_tiles = (P.R + kDgRowsMax - 1) / kDgRowsMax;
+  P.Rt = gemm_padded_rows((P.R + row_tiles - 1) / row_tiles);
+  P.row_tiles = (P.R + P.Rt - 1) / P.Rt;
+  int t256 = 0;
+  for (int s = 0; s < P.nseg; ++s) t256 += P.row_tiles * ((P.seg[s].N + 255) / 256);
+  P.mt = t256 >= sms ? 256 : 128;
+  P.ksteps = K * 2 / 128;
+  P.ntiles = 0;
+  for (int s = 0; s < P.nseg; ++s) {
+    if (!encode_byte_map(&P.seg[s].wmap, w[s], (unsigned long long)P.seg[s].N, K * 2, P.mt, 1) ||
+        !encode_byte_map(&P.seg[s].xmap, x[s], (unsigned long long)rows_alloc, K * 2, P.Rt, 1)) {
+      *why = "cuTensorMapEncodeTiled failed";
+      return cudaErrorInvalidValue;
+    }
+    P.tiles_seg[s] = P.row_tiles * ((P.seg[s].N + P.mt - 1) / P.mt);
+    P.ntiles += P.tiles_seg[s];
+  }
+  const dim3 grid(P.ntiles < sms ? P.ntiles : sms);
+  return launch_chained(dense_tile_gemm_kernel, grid, dim3(kGemmThreads), size_t(kDgSmem), stream, P);
+}
+
+static void fill_dgemm_seg(DGemmSeg& s, int N, void* out, long long ldo, int act, int out_t) {
+  memset(&s, 0, sizeof(s));
+  s.N = N; s.out = out; s.ldo = ldo; s.act = act; s.out_t = out_t;
+}
+
 static const char* dense_model_problem(const b200rwkv_dense_model* m) {
   if (!m || !m->layers || !m->emb || !m->head || !m->ln0_w || !m->ln0_b || !m->ln_out_w || !m->ln_out_b) return "null pointer in the model";
   if (m->n_layer < 1 || m->n_vocab < 1 || m->n_embd < 8 || m->n_ffn < 8) return "bad dimensions";
@@ -1680,5 +1756,140 @@ int b200rwkv_dense_step(const b200rwkv_dense_model* m, const int64_t* token, flo
   return dense_step_impl<float>(m, token, state, logits, ws, st);
 }
 
+
+size_t b200rwkv_dense_rows_workspace_bytes(const b200rwkv_dense_model* m, int streams, int tokens_per_stream) {
+  if (!m || m->n_embd < 1 || m->n_ffn < 1 || streams < 1 || tokens_per_stream < 1) return 0;
+  if ((long long)streams * tokens_per_stream > 65535) return 0;
+  return dense_carve_rows(m, streams, tokens_per_stream, nullptr).bytes;
+}
+
+int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* tokens, int streams, int tokens_per_stream,
+                                float* state, int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  if (const char* why = dense_model_problem(m)) return fail(B200RWKV_EINVAL, "dense_forward_rows: %s", why);
+  if (m->dtype != B200RWKV_BF16 && m->dtype != B200RWKV_F16)
+    return fail(B200RWKV_EINVAL, "dense_forward_rows: the tensor-core rows path takes bf16 or fp16 matrices (fp32: feed tokens one by one)");
+  const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab, L = m->n_layer, B = streams, T = tokens_per_stream;
+  if (!tokens || !state || !workspace) return fail(B200RWKV_EINVAL, "dense_forward_rows: null argument");
+  if ((D % 64) != 0 || (F % 64) != 0) return fail(B200RWKV_EINVAL, "dense_forward_rows: n_embd and n_ffn must be multiples of 64");
+  if (B < 1 || T < 1 || (long long)B * T > 65535) return fail(B200RWKV_EINVAL, "dense_forward_rows: streams x tokens must be 1..65535 rows");
+  if (state_stride < (int64_t)L * 5 * D) return fail(B200RWKV_EINVAL, "dense_forward_rows: state_stride below n_layer*5*n_embd");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || !aligned16(state))
+    return fail(B200RWKV_EINVAL, "dense_forward_rows: workspace must be 256-byte and state 16-byte aligned");
+  DenseRowsWorkspace ws = dense_carve_rows(m, B, T, workspace);
+  if (workspace_bytes < ws.bytes) return fail(B200RWKV_EINVAL, "dense_forward_rows: workspace %zu < %zu bytes", workspace_bytes, ws.bytes);
+  const int R = B * T, Rpad = gemm_padded_rows(R), bf = m->dtype == B200RWKV_BF16 ? 1 : 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const char* why = "";
+  cudaError_t e;
+  g_chain_rows = R <= 1024;
+  static bool prep_configured[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !prep_configured[dev]) {
+    if (cudaFuncSetAttribute(dense_rows_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDsMaxEmbd * 4) != cudaSuccess)
+      return fail(B200RWKV_ECUDA, "dense_forward_rows: cannot size the preparation kernel's shared memory");
+    prep_configured[dev] = true;
+  }
+#define B200_DR_CHECK(call, what)                                                                      \
+  do {                                                                                                 \
+    e = (call);                                                                                        \
+    if (e != cudaSuccess)                                                                              \
+      return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "dense_forward_rows: %s: %s (%s)", what, why, \
+                  cudaGetErrorString(e));                                                              \
+  } while (0)
+  B200_DR_CHECK(launch_chained(embed_ln0_rows_kernel, dim3(R), dim3(256), 0, s, m->emb, reinterpret_cast<const long long*>(tokens),
+                               D, V, m->ln0_w, m->ln0_b, ws.xa), "embedding");
+  DRowsPrepParams Q;
+  DGemmParams P;
+  auto prep = [&](const float* x, const float* lw, const float* lb, const float* carry, int nmix, const float* const* mix,
+                  unsigned short* const* out, int last_only) -> cudaError_t {
+    memset(&Q, 0, sizeof(Q));
+    Q.x = x; Q.ln_w = lw; Q.ln_b = lb; Q.carry = carry; Q.carry_stride = state_stride; Q.carry_out = carry ? ws.carry_new : nullptr;
+    Q.nmix = nmix; Q.D = D; Q.Tn = T; Q.last_only = last_only; Q.is_bf16 = bf;
+    for (int i = 0; i < (nmix > 0 ? nmix : 1); ++i) { Q.mix[i] = mix ? mix[i] : nullptr; Q.out[i] = out[i]; }
+    return launch_chained(dense_rows_prep_kernel, dim3(last_only ? B : R), dim3(256), size_t(2) * D * 4, s, Q);
+  };
+  auto commit = [&](float* row) -> cudaError_t {      // parked layer norm of every stream's last row -> its state row
+    return cudaMemcpy2DAsync(row, size_t(state_stride) * 4, ws.carry_new, size_t(D) * 4, size_t(D) * 4, size_t(B),
+                             cudaMemcpyDeviceToDevice, s);
+  };
+  for (int l = 0; l < L; ++l) {
+    const b200rwkv_dense_layer& ly = m->layers[l];
+    float* st = state + size_t(l) * 5 * D;
+    // 1. ln1 + token-shift mix -> key, value, sigmoid(receptance)
+    { const float* mix[3] = {ly.att_mix_k, ly.att_mix_v, ly.att_mix_r};
+      unsigned short* out[3] = {ws.t0, ws.t1, ws.t2};
+      B200_DR_CHECK(prep(ws.xa, ly.ln1_w, ly.ln1_b, st, 3, mix, out, 0), "attention mix"); }
+    B200_DR_CHECK(commit(st), "attention carry");
+    memset(&P, 0, sizeof(P));
+    P.nseg = 3; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    fill_dgemm_seg(P.seg[0], D, ws.kb, D, ACT_NONE, 0);
+    fill_dgemm_seg(P.seg[1], D, ws.vb, D, ACT_NONE, 0);
+    fill_dgemm_seg(P.seg[2], D, ws.rb, D, ACT_SIGMOID, 0);
+    { const void* w[3] = {ly.att_key, ly.att_value, ly.att_receptance};
+      const unsigned short* x[3] = {ws.t0, ws.t1, ws.t2};
+      B200_DR_CHECK(launch_dense_gemm(P, w, x, D, Rpad, s, &why), "key/value/receptance"); }
+    // 2. WKV recurrence over each stream's rows; kb <- sigmoid(r) * wkv
+    why = "wkv launch";
+    if (T <= 2 * kWkvChunk) {
+      e = launch_chained(wkv_rows_kernel, dim3((B * D + 127) / 128), dim3(128), 0, s, B, T, D, ly.time_decay, ly.time_first, ws.kb,
+                         (const float*)ws.vb, (const float*)ws.rb, st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D),
+                         (long long)state_stride);
+    } else {
+      const int NC = (T + kWkvChunk - 1) / kWkvChunk;
+      const long long n1 = (long long)B * (NC - 1) * D, n2 = (long long)B * NC * D;
+      e = launch_chained(wkv_chunk_state_kernel, dim3((unsigned)((n1 + 127) / 128)), dim3(128), 0, s, B, T, D, NC, ly.time_decay,
+                         (const float*)ws.kb, (const float*)ws.vb, ws.wkv_loc, (const float*)(st + 2 * size_t(D)),
+                         (const float*)(st + 3 * size_t(D)), (const float*)(st + 4 * size_t(D)), (long long)state_stride);
+      if (e == cudaSuccess)
+        e = launch_chained(wkv_chunk_output_kernel, dim3((unsigned)((n2 + 127) / 128)), dim3(128), 0, s, B, T, D, NC, ly.time_decay,
+                           ly.time_first, ws.kb, (const float*)ws.vb, (const float*)ws.rb, (const float*)ws.wkv_loc,
+                           st + 2 * size_t(D), st + 3 * size_t(D), st + 4 * size_t(D), (long long)state_stride);
+    }
+    B200_DR_CHECK(e, "wkv");
+    // 3. attention output + residual -> xb
+    B200_DR_CHECK(launch_chained(dense_rows_cast_kernel, dim3(unsigned(std::min<long long>((long long)R * D / 4 / 256 + 1, 4096))), dim3(256), 0, s,
+                                 (const float*)ws.kb, ws.t0, (long long)R * D / 4, bf), "cast");
+    memset(&P, 0, sizeof(P));
+    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    fill_dgemm_seg(P.seg[0], D, ws.xb, D, ACT_NONE, 0);
+    P.seg[0].res = ws.xa; P.seg[0].ldres = D;
+    { const void* w[1] = {ly.att_output};
+      const unsigned short* x[1] = {ws.t0};
+      B200_DR_CHECK(launch_dense_gemm(P, w, x, D, Rpad, s, &why), "attention output"); }
+    // 4. ln2 + token-shift mix -> relu(key)^2 (kept in the matrices' type), sigmoid(receptance)
+    { const float* mix[2] = {ly.ffn_mix_k, ly.ffn_mix_r};
+      unsigned short* out[2] = {ws.t0, ws.t1};
+      B200_DR_CHECK(prep(ws.xb, ly.ln2_w, ly.ln2_b, st + D, 2, mix, out, 0), "ffn mix"); }
+    B200_DR_CHECK(commit(st + D), "ffn carry");
+    memset(&P, 0, sizeof(P));
+    P.nseg = 2; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    fill_dgemm_seg(P.seg[0], F, ws.kk, F, ACT_RELUSQ, 1);
+    fill_dgemm_seg(P.seg[1], D, ws.rb, D, ACT_SIGMOID, 0);
+    { const void* w[2] = {ly.ffn_key, ly.ffn_receptance};
+      const unsigned short* x[2] = {ws.t0, ws.t1};
+      B200_DR_CHECK(launch_dense_gemm(P, w, x, D, Rpad, s, &why), "ffn key and receptance"); }
+    // 5. ffn value, gated, + residual -> xa
+    memset(&P, 0, sizeof(P));
+    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    fill_dgemm_seg(P.seg[0], D, ws.xa, D, ACT_NONE, 0);
+    P.seg[0].res = ws.xb; P.seg[0].ldres = D; P.seg[0].gate = ws.rb; P.seg[0].ldgate = D;
+    { const void* w[1] = {ly.ffn_value};
+      const unsigned short* x[1] = {ws.kk};
+      B200_DR_CHECK(launch_dense_gemm(P, w, x, F, Rpad, s, &why), "ffn value"); }
+  }
+  if (logits) {
+    unsigned short* out[1] = {ws.hx};
+    B200_DR_CHECK(prep(ws.xa, m->ln_out_w, m->ln_out_b, nullptr, 0, nullptr, out, 1), "output layer norm");
+    memset(&P, 0, sizeof(P));
+    P.nseg = 1; P.R = B; P.is_bf16 = bf; P.status = ws.status;
+    fill_dgemm_seg(P.seg[0], V, logits, V, ACT_NONE, 0);
+    const void* w[1] = {m->head};
+    const unsigned short* x[1] = {ws.hx};
+    B200_DR_CHECK(launch_dense_gemm(P, w, x, D, gemm_padded_rows(B), s, &why), "head");
+  }
+#undef B200_DR_CHECK
+  return B200RWKV_OK;
+}
 
 }  // extern "C"

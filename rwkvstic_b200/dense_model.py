@@ -12,8 +12,10 @@ call of ``b200rwkv_dense_step`` (6 kernels per block, replayed from a CUDA graph
 
 ``forward(tokens int64[T], state f32[L,5,D]) -> (logits f32[V] on the device, state)``; the state is
 the reference's own (max-trick WKV rows 2..4, ``-1e30`` in row 4 when empty) and is updated in
-place.  Several tokens are fed one after another.  There is no CPU fallback: without the CUDA
-library the constructor raises.
+place.  From ``rows_threshold`` tokens on, bf16 / fp16 models apply every matrix to all rows at once
+on the tensor cores (``forward_rows``, ``b200rwkv_dense_forward_rows``: ``tcgen05.mma kind::f16``), as
+the reference does with a sequence; fp32 models and shorter inputs are fed token by token.  There is
+no CPU fallback: without the CUDA library the constructor raises.
 """
 from __future__ import annotations
 
@@ -82,6 +84,9 @@ class B200DenseRWKV:
         self._graphs: Dict[Tuple[int, bool], torch.cuda.CUDAGraph] = {}
         self._seen: Dict[Tuple[int, bool], int] = {}
         self.launches_per_step = 6 * self.n_layer + 3
+        self.rows_threshold = 4          # tokens per call from which the tensor-core rows path is used
+        self.rows_per_call = 4096        # rows one rows call handles; longer prompts are fed in pieces
+        self._rows_ws: Dict[Tuple[int, int], torch.Tensor] = {}
         self._status_host, self._status_event, self._status_pending = None, None, False
         self.launch_count = 0
 
@@ -136,18 +141,20 @@ class B200DenseRWKV:
 
     def check_status(self) -> None:
         """Raise if a kernel gave up a bounded device-side wait (synchronises).  The state the failed
-        step was given is undefined after that."""
-        bits = int(self._ws[:4].view(torch.int32).cpu()[0])
-        if bits:
-            self._ws[:4].zero_()
-            raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
+        call was given is undefined after that."""
+        for buf in [self._ws, *self._rows_ws.values()]:
+            bits = int(buf[:4].view(torch.int32).cpu()[0])
+            if bits:
+                buf[:4].zero_()
+                raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
 
-    def _queue_status(self) -> None:
-        """Non-blocking copy of the status word to pinned memory; looked at by a later call once it has landed."""
+    def _queue_status(self, buf: Optional[torch.Tensor] = None) -> None:
+        """Non-blocking copy of a workspace's status word to pinned memory; looked at by a later call once it has landed."""
+        buf = self._ws if buf is None else buf
         if self._status_host is None:
             self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
             self._status_event = torch.cuda.Event()
-        self._status_host.copy_(self._ws[:4].view(torch.int32), non_blocking=True)
+        self._status_host.copy_(buf[:4].view(torch.int32), non_blocking=True)
         self._status_event.record(torch.cuda.current_stream(self.device))
         self._status_pending = True
 
@@ -157,6 +164,48 @@ class B200DenseRWKV:
         self._status_pending = False
         if int(self._status_host[0]):
             self.check_status()
+
+    # ------------------------------------------------------------------ many rows at once
+    def empty_batch_state(self, B: int) -> torch.Tensor:
+        return self.emptyState.unsqueeze(0).repeat(B, 1, 1, 1).contiguous()
+
+    def forward_rows(self, tokens: torch.Tensor, state: torch.Tensor) -> torch.Tensor:
+        """``tokens [B,T]`` int64, ``state [B,L,5,D]`` fp32 contiguous on the device (updated in place):
+        B independent sequences, every matrix applied to all B*T rows at once.  Returns the logits
+        ``[B,V]`` after each sequence's last token.  bf16 / fp16 models only."""
+        if self.dtype == torch.float32:
+            raise ValueError("forward_rows needs bf16 or fp16 matrices; feed an fp32 model token by token")
+        if tokens.dim() != 2 or tokens.numel() == 0:
+            raise ValueError("forward_rows needs tokens [B,T] with at least one token")
+        B, T = tokens.shape
+        if (state.dtype != torch.float32 or state.device != self.device or not state.is_contiguous()
+                or tuple(state.shape) != (B, self.n_layer, 5, self.n_embd)):
+            raise ValueError(f"forward_rows needs a contiguous fp32 state [{B},{self.n_layer},5,{self.n_embd}] on the model's device")
+        self._raise_status()
+        out = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device)
+        piece = max(1, self.rows_per_call // B)
+        with torch.cuda.device(self.device):
+            toks = tokens.to(self.device, non_blocking=True)
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            for t0 in range(0, T, piece):
+                tp = min(piece, T - t0)
+                ws = self._rows_ws.get((B, tp))
+                if ws is None:
+                    if len(self._rows_ws) >= 4:
+                        self._rows_ws.clear()
+                    need = int(self._L.b200rwkv_dense_rows_workspace_bytes(C.byref(self._cmodel), B, tp))
+                    if need == 0:
+                        raise ValueError("forward_rows: at most 65535 rows per call")
+                    ws = self._rows_ws[(B, tp)] = torch.zeros(need, dtype=torch.uint8, device=self.device)
+                part = toks[:, t0:t0 + tp].contiguous()
+                last = t0 + tp == T
+                _lib.check(self._L.b200rwkv_dense_forward_rows(C.byref(self._cmodel), part.data_ptr(), B, tp, state.data_ptr(),
+                                                               state.stride(0), out.data_ptr() if last else None,
+                                                               ws.data_ptr(), ws.numel(), stream))
+                self.launch_count += 12 * self.n_layer + 3
+                self._rows_status_src = ws
+            self._queue_status(self._rows_status_src)
+        return out
 
     def forward(self, tokens, state: torch.Tensor):
         if not torch.is_tensor(tokens):
@@ -168,6 +217,8 @@ class B200DenseRWKV:
             raise ValueError(f"state must be [{self.n_layer},5,{self.n_embd}], got {tuple(state.shape)}")
         if state.dtype != torch.float32 or state.device != self.device or not state.is_contiguous():
             state = state.to(device=self.device, dtype=torch.float32).contiguous()
+        if tokens.numel() >= self.rows_threshold and self.dtype != torch.float32 and self.n_embd % 64 == 0 and self.n_ffn % 64 == 0:
+            return self.forward_rows(tokens.reshape(1, -1), state.unsqueeze(0))[0], state
         self._raise_status()
         with torch.cuda.device(self.device):
             toks = tokens.to(self.device, non_blocking=True)

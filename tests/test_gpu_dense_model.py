@@ -46,10 +46,21 @@ def test_dense_model_against_the_reference_outputs(golden, shape, name):
     print(f"{shape} {name}: worst |dlogit| / max |logit| over {n_tok} tokens = {worst:.2e}")
     assert worst <= REL_TOL[name], worst
     assert state_excess(state, torch.from_numpy(g[f"{shape}_{name}_state_tok"]), REL_TOL[name]) <= 0
-    # several tokens in one call are fed one after another: same result as the calls above
+    # Several tokens in one call.  fp32: fed one after another, the same result bit for bit.  bf16 / fp16: all rows
+    # at once on the tensor cores (another summation order), against the reference's own sequence-mode outputs.
     again = model.emptyState.clone()
     got2, _ = model.forward(toks, again)
-    assert torch.equal(got2, got) and torch.equal(again, state)
+    if name == "f32":
+        assert torch.equal(got2, got) and torch.equal(again, state)
+    else:
+        assert model.launch_count > 0 and len(model._rows_ws) == 1
+        seq = torch.from_numpy(g[f"{shape}_{name}_logits_seq"]) if shape == "tiny" else want[-1]
+        err = float((got2.cpu() - seq).abs().max()) / float(seq.abs().max())
+        print(f"{shape} {name}: rows path |dlogit| / max |logit| = {err:.2e}")
+        assert err <= REL_TOL[name], err
+        ref_state = torch.from_numpy(g[f"{shape}_{name}_state_seq"]) if shape == "tiny" else torch.from_numpy(g[f"{shape}_{name}_state_tok"])
+        assert state_excess(again, ref_state, REL_TOL[name]) <= 0
+    model.check_status()
 
 
 @pytest.mark.parametrize("embed,name", [(2048, "bf16"), (2560, "f16"), (4096, "bf16"), (5120, "bf16"), (4096, "f32")])
@@ -145,3 +156,49 @@ def test_loader_hook_with_dtype_builds_the_unquantised_model():
     want, _ = ref.forward(toks, ref.emptyState.clone())
     got, _ = model.forward(toks, model.emptyState.clone())
     assert float((got.cpu() - want).abs().max()) <= REL_TOL["bf16"] * float(want.abs().max())
+
+
+@pytest.mark.parametrize("embed,name,B,T", [(2048, "bf16", 3, 40), (2560, "f16", 2, 17), (4096, "bf16", 2, 300), (5120, "f16", 1, 130)])
+def test_dense_rows_path_against_the_oracle(embed, name, B, T):
+    """B sequences of T tokens in one call through the tensor-core rows path (T = 300 and 130 take the
+    chunk-parallel WKV scan) against the oracle's sequence mode, one sequence at a time: logits after the
+    last token and the final state; then one more token through the one-row step from that state."""
+    V = 1024
+    ck = synth_checkpoint(2, embed, vocab=V, seed=70 + embed % 13)
+    ref = OracleTorchMode(ck, TYPES[name])
+    model = B200DenseRWKV.from_checkpoint(ck, dtype=TYPES[name], device=DEV, use_graph=False)
+    toks = synth_tokens(B * T, seed=embed + 3, vocab=V).reshape(B, T)
+    state = model.empty_batch_state(B)
+    out = model.forward_rows(toks.to(DEV), state)
+    model.check_status()
+    worst = 0.0
+    for b in range(B):
+        want, wstate = ref.forward(toks[b], ref.emptyState.clone())
+        worst = max(worst, float((out[b].cpu() - want).abs().max()) / float(want.abs().max()))
+        assert state_excess(state[b], wstate, REL_TOL[name]) <= 0, b
+        if b == 0:
+            nxt = torch.tensor([5])
+            w2, _ = ref.forward(nxt, wstate)
+            g2, _ = model.forward(nxt, state[0].clone())
+            assert float((g2.cpu() - w2).abs().max()) / float(w2.abs().max()) <= REL_TOL[name]
+    print(f"D={embed} {name} rows path {B}x{T}: |dlogit| / max |logit| = {worst:.2e}")
+    assert worst <= REL_TOL[name], worst
+
+
+def test_dense_rows_path_arguments():
+    m = B200DenseRWKV.synthetic(1, 128, vocab=300, seed=1, dtype=torch.float32, device=DEV, use_graph=False)
+    with pytest.raises(ValueError):
+        m.forward_rows(torch.zeros(1, 4, dtype=torch.int64), m.empty_batch_state(1))        # fp32 matrices
+    h = B200DenseRWKV.synthetic(1, 128, vocab=300, seed=1, dtype=torch.float16, device=DEV, use_graph=False)
+    with pytest.raises(ValueError):
+        h.forward_rows(torch.zeros(2, 4, dtype=torch.int64), h.empty_batch_state(1))        # state of another batch size
+    L = h._L
+    st = h.empty_batch_state(1)
+    tok = torch.zeros(1, 4, dtype=torch.int64, device=DEV)
+    need = int(L.b200rwkv_dense_rows_workspace_bytes(C.byref(h._cmodel), 1, 4))
+    ws = torch.zeros(need, dtype=torch.uint8, device=DEV)
+    assert L.b200rwkv_dense_forward_rows(C.byref(h._cmodel), tok.data_ptr(), 1, 4, st.data_ptr(), st.stride(0), None,
+                                         ws.data_ptr(), need - 1, None) == _lib.EINVAL
+    assert L.b200rwkv_dense_forward_rows(C.byref(m._cmodel), tok.data_ptr(), 1, 4, st.data_ptr(), st.stride(0), None,
+                                         ws.data_ptr(), need, None) == _lib.EINVAL
+    assert int(L.b200rwkv_dense_rows_workspace_bytes(C.byref(h._cmodel), 300, 300)) == 0

@@ -372,7 +372,41 @@ def time_dense_decode(shape, dev, dtype=torch.bfloat16, steps=64, warm=6):
     torch.cuda.synchronize(dev)
     lib_ms = e0.elapsed_time(e1) / 3
     name = str(dtype).replace("torch.", "")
+    prompt = None
+    if dtype != torch.float32:
+        # a 1024-token prompt through the tensor-core rows path, and the same matrices through cuBLAS
+        ptoks = torch.randint(0, VOCAB, (1, 1024), generator=torch.Generator().manual_seed(13), dtype=torch.int64).to(dev)
+        pstate = model.empty_batch_state(1)
+        model.forward_rows(ptoks, pstate)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(3):
+            model.forward_rows(ptoks, pstate)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        model.check_status()
+        p_ms = e0.elapsed_time(e1) / 3
+        blocks = [m for m in mats if m.shape[0] != VOCAB]
+        rows = {n: torch.randn(1024, n, device=dev).to(dtype) for n in {m.shape[1] for m in blocks}}
+        for m in blocks[:4]:
+            torch.matmul(rows[m.shape[1]], m.t())
+        torch.cuda.synchronize(dev)
+        e0.record()
+        for _ in range(3):
+            for m in blocks:
+                torch.matmul(rows[m.shape[1]], m.t())
+        e1.record()
+        torch.cuda.synchronize(dev)
+        plib_ms = e0.elapsed_time(e1) / 3
+        flops = 2.0 * sum(m.numel() for m in blocks) * 1024 + 2.0 * VOCAB * D
+        tf_peak = measured_tensor_peak()
+        prompt = {"tokens": 1024, "ms": p_ms, "tokens_per_s": 1024 / (p_ms * 1e-3), "kernel": "dense_tile_gemm_kernel (tcgen05 kind::f16)",
+                  "tensor": {"algorithmic_tflops": flops / (p_ms * 1e-3) / 1e12, "peak_bf16_tflops": tf_peak,
+                             "frac_of_measured_bf16": flops / (p_ms * 1e-3) / 1e12 / tf_peak if tf_peak else None},
+                  "library_baseline": {"what": "the blocks' matrices through torch.matmul (cuBLAS) on 1024 rows, no layer norm / "
+                                               "mix / WKV work", "ms": plib_ms, "ours_over_library": p_ms / plib_ms}}
     return {"workload": f"RWKV-4 {shape} shape L={L} D={D} V={VOCAB}, {name} weights unquantised (TORCH mode), batch-1 decode",
+            "prompt_1024": prompt,
             "value": 1e3 / ms, "unit": UNIT, "ms_per_step": ms, "steps": steps, "dtype": name,
             "gpu_launches_per_step": model.launches_per_step, "kernel": "dense_rows_kernel + dense_vec_kernel",
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,

@@ -961,8 +961,7 @@ static DenseRowsWorkspace dense_carve_rows(const b200rwkv_dense_model* m, int B,
   return w;
 }
 
-// Picks the tile (all rows in one row tile up to 240, else equal row tiles; 256 weight rows per tile when
-// that still gives every SM a tile), encodes the tensor maps and launches.  w[s]: [N_s][K] of the 16-bit
+// Picks the tile, encodes the tensor maps and launches.  w[s]: [N_s][K] of the 16-bit
 // type; x[s]: [rows_alloc][K] of the same type.
 static cudaError_t launch_dense_gemm(DGemmParams& P, const void* const* w, const unsigned short* const* x, int K, int rows_alloc,
                                      cudaStream_t stream, const char** why) {
@@ -977,13 +976,25 @@ static cudaError_t launch_dense_gemm(DGemmParams& P, const void* const* w, const
     configured[dev] = true;
   }
   const int sms = device_sms();
-  const int row_tiles = (P.R + kDgRowsMax - 1) / kDgRowsMax;
-  P.Rt = gemm_padded_rows((P.R + row_tiles - 1) / row_tiles);
-  P.row_tiles = (P.R + P.Rt - 1) / P.Rt;
-  int t256 = 0;
-  for (int s = 0; s < P.nseg; ++s) t256 += P.row_tiles * ((P.seg[s].N + 255) / 256);
-  P.mt = t256 >= sms ? 256 : 128;
   P.ksteps = K * 2 / 128;
+  // Tile: rounds of tiles per CTA x (operand bytes of a tile + a fixed cost per tile), over both tile
+  // widths and every height that splits the rows evenly.
+  double best = 0.0;
+  for (int mt = 128; mt <= 256; mt += 128) {
+    for (int rt_rows = 1; rt_rows <= (P.R + 15) / 16; ++rt_rows) {
+      const int rt = gemm_padded_rows((P.R + rt_rows - 1) / rt_rows);
+      if (rt > kDgRowsMax) continue;
+      const int row_tiles = (P.R + rt - 1) / rt;
+      if (row_tiles != rt_rows) continue;
+      long long tiles = 0;
+      for (int s = 0; s < P.nseg; ++s) tiles += (long long)row_tiles * ((P.seg[s].N + mt - 1) / mt);
+      const double rounds = double((tiles + sms - 1) / sms);
+      const double cost = rounds * (double(P.ksteps) * 128.0 * (mt + rt) + 48.0 * 1024);
+      if (best == 0.0 || cost < best) { best = cost; P.mt = mt; P.Rt = rt; }
+    }
+  }
+  if (best == 0.0) { *why = "no tile fits"; return cudaErrorInvalidValue; }
+  P.row_tiles = (P.R + P.Rt - 1) / P.Rt;
   P.ntiles = 0;
   for (int s = 0; s < P.nseg; ++s) {
     if (!encode_byte_map(&P.seg[s].wmap, w[s], (unsigned long long)P.seg[s].N, K * 2, P.mt, 1) ||

@@ -12,7 +12,9 @@ With ``--dense bf16|fp16|fp32`` the first matrix of the shape is streamed unquan
 (``dense_gemv_kernel``), and with ``--sampler`` one row of V logits goes through the typical
 sampling kernel (``sample_typical_kernel``).  ``--dense-step bf16|fp16|fp32`` runs --launches
 tokens through the unquantised model of --shape (``dense_rows_kernel``, ``dense_vec_kernel``;
-``--network LAYERS`` truncates it), graph-replayed, and prints the time per token.
+``--network LAYERS`` truncates it), graph-replayed, and prints the time per token; with
+``--dense-rows`` it makes --launches calls of --streams x --tokens rows through the unquantised
+tensor-core rows path instead (``dense_tile_gemm_kernel``, ``dense_rows_prep_kernel``).
 """
 from __future__ import annotations
 
@@ -52,6 +54,7 @@ def main():
                     help="stream the first matrix of --matrix unquantised in this type (dense_gemv_kernel)")
     ap.add_argument("--dense-step", default=None, choices=["bf16", "fp16", "fp32"],
                     help="decode --launches tokens with the unquantised model of --shape in this type")
+    ap.add_argument("--dense-rows", action="store_true", help="with --dense-step: --streams x --tokens rows per call through the rows path")
     ap.add_argument("--sampler", action="store_true", help="typical sampling of one row of V logits")
     ap.add_argument("--trace", default=None, choices=["chained", "persistent"],
                     help="print the %%globaltimer timeline of one block of a graph-replayed decode step of --shape "
@@ -64,6 +67,22 @@ def main():
         dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dense_step]
         L, D = SHAPES[args.shape]
         model = B200DenseRWKV.synthetic(args.network or L, D, dtype=dt, device="cuda:0")
+        if args.dense_rows:
+            toks = torch.randint(0, VOCAB, (args.streams, args.tokens), generator=torch.Generator().manual_seed(3)).to("cuda:0")
+            bstate = model.empty_batch_state(args.streams)
+            model.forward_rows(toks, bstate)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.launches):
+                model.forward_rows(toks, bstate)
+            e1.record()
+            torch.cuda.synchronize()
+            model.check_status()
+            ms = e0.elapsed_time(e1) / args.launches
+            print(f"unquantised {args.dense_step} rows path, {args.shape} width, {model.n_layer} blocks, {args.streams} x {args.tokens} rows: "
+                  f"{ms:.3f} ms per call, {args.streams * args.tokens / ms * 1e3:.0f} tokens/s")
+            return
         state = model.emptyState.clone()
         tok = torch.tensor([17])
         for _ in range(3):                                   # the third call replays the graph

@@ -388,6 +388,21 @@ int b200rwkv_dense_step(const b200rwkv_dense_model* m, const int64_t* token, flo
  * Enqueues about 12 kernels per block on `stream`; no allocation, no host synchronisation.
  */
 size_t b200rwkv_dense_rows_workspace_bytes(const b200rwkv_dense_model* m, int streams, int tokens_per_stream);
+/*
+ * The two calls above for the blocks [layer_begin, layer_end) only, so that a host can keep some blocks'
+ * matrices in pinned host memory and bring them to the device while earlier blocks compute (the
+ * reference README's TORCH_STREAM mode: "matrixes will be stored in ram and moved to the GPU as needed").
+ * The embedding (+ ln0) runs when layer_begin == 0, the head when layer_end == n_layer and logits is
+ * not NULL; the residual stream stays in the workspace between calls, which must therefore be the same
+ * buffer (and, for rows, the same streams x tokens_per_stream) for all ranges of one token / one call.
+ * Only the layers of the range are dereferenced on the device; all entries of m->layers must still be
+ * filled in (they are checked for NULL and alignment).
+ */
+int b200rwkv_dense_step_layers(const b200rwkv_dense_model* m, int layer_begin, int layer_end, const int64_t* token, float* state,
+                               float* logits, void* workspace, size_t workspace_bytes, void* stream);
+int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_begin, int layer_end, const int64_t* tokens,
+                                       int streams, int tokens_per_stream, float* state, int64_t state_stride, float* logits,
+                                       void* workspace, size_t workspace_bytes, void* stream);
 int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* tokens, int streams, int tokens_per_stream,
                                 float* state, int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes,
                                 void* stream);

@@ -23,6 +23,7 @@ EXPORTS = (
     "b200rwkv_gemm_workspace_bytes", "b200rwkv_gemm_u8", "b200rwkv_rows_workspace_bytes", "b200rwkv_forward_rows", "b200rwkv_forward_rows_stage", "b200rwkv_argmax",
     "b200rwkv_sample_typical", "b200rwkv_gemv_dense",
     "b200rwkv_dense_workspace_bytes", "b200rwkv_dense_step", "b200rwkv_dense_rows_workspace_bytes", "b200rwkv_dense_forward_rows",
+    "b200rwkv_dense_step_layers", "b200rwkv_dense_forward_rows_layers",
     "b200rwkv_step_plan_bytes", "b200rwkv_step_plan_init", "b200rwkv_decode_step_persistent", "b200rwkv_step_geometry",
 )
 
@@ -144,6 +145,12 @@ def lib() -> C.CDLL:
     L.b200rwkv_dense_forward_rows.restype = C.c_int
     L.b200rwkv_dense_forward_rows.argtypes = [C.POINTER(DenseModel), C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int64,
                                               C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.b200rwkv_dense_step_layers.restype = C.c_int
+    L.b200rwkv_dense_step_layers.argtypes = [C.POINTER(DenseModel), C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_size_t, C.c_void_p]
+    L.b200rwkv_dense_forward_rows_layers.restype = C.c_int
+    L.b200rwkv_dense_forward_rows_layers.argtypes = [C.POINTER(DenseModel), C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
+                                                     C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     _lib = L
     return L
 

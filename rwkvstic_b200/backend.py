@@ -17,7 +17,9 @@ here imports the reference at module import time; ``install()`` needs it to be i
 The reference's TORCH mode takes ``dtype=`` for the matrices (agnostic/backends/torch.py:8-22).  The
 same keyword selects the model here: ``dtype=torch.bfloat16`` / ``float16`` / ``float32`` keeps the
 weights unquantised (``B200DenseRWKV``, the arithmetic of torch.py:125-166), no ``dtype`` or
-``torch.uint8`` gives the FASTQUANT model (``B200RWKV``).
+``torch.uint8`` gives the FASTQUANT model (``B200RWKV``).  With ``target=GB`` (and ``pinMem=``), the
+keywords of the TORCH_STREAM mode the reference's README describes, only that many GB of the unquantised
+model's matrices stay on the GPU and the other blocks are streamed from (pinned) host memory.
 """
 from __future__ import annotations
 
@@ -50,8 +52,9 @@ def make_ops_class(base_module, model_factory: Optional[Callable] = None, device
     """Subclass of the reference's ``agnostic.backends.base.module`` for ``Backends[MODE]``."""
 
     class RWKVB200Ops(base_module):
-        def __init__(self, layers, embed, *args, dtype=None, **kwargs):
+        def __init__(self, layers, embed, *args, dtype=None, target=None, pinMem=True, **kwargs):
             super().__init__(layers, embed, *args, **kwargs)
+            self.target, self.pinMem = target, pinMem        # TORCH_STREAM's keywords: GB of matrices kept on the GPU, pinned host copies
             if dtype not in (None, torch.uint8, torch.float32, torch.bfloat16, torch.float16):
                 raise ValueError("dtype must be torch.uint8 (FASTQUANT), torch.float32, torch.bfloat16 or torch.float16")
             self.dtype = dtype
@@ -73,7 +76,7 @@ def make_ops_class(base_module, model_factory: Optional[Callable] = None, device
                     new = factory(ck)
                 elif self.dtype in (torch.float32, torch.bfloat16, torch.float16):
                     from .dense_model import B200DenseRWKV
-                    new = B200DenseRWKV(ck.items(), dtype=self.dtype, device=device)
+                    new = B200DenseRWKV(ck.items(), dtype=self.dtype, device=device, target_gb=self.target, pin_memory=self.pinMem)
                 else:
                     from .model import B200RWKV
                     new = B200RWKV.from_checkpoint(ck, device=device, scheme=scheme)

@@ -854,7 +854,7 @@ static cudaError_t dense_launch_rows(DenseRowsParams& P, cudaStream_t stream) {
 }
 
 template <typename T>
-static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, float* state, float* logits,
+static int dense_step_impl(const b200rwkv_dense_model* m, int l0, int l1, const int64_t* token, float* state, float* logits,
                            const DenseWorkspace& ws, cudaStream_t st) {
   const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab;
   cudaError_t e;
@@ -867,8 +867,8 @@ static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, 
   memset(&vp, 0, sizeof(vp));
   vp.emb = m->emb; vp.token = reinterpret_cast<const long long*>(token);
   vp.ln_w = m->ln0_w; vp.ln_b = m->ln0_b; vp.x_out = ws.x; vp.D = D;
-  B200_DS_CHECK(dense_launch_vec<T>(vp, false, st), "embedding");
-  for (int l = 0; l < m->n_layer; ++l) {
+  if (l0 == 0) B200_DS_CHECK(dense_launch_vec<T>(vp, false, st), "embedding");
+  for (int l = l0; l < l1; ++l) {
     const b200rwkv_dense_layer& Lr = m->layers[l];
     float* sl = state + size_t(l) * 5 * D;
     memset(&vp, 0, sizeof(vp));
@@ -914,7 +914,7 @@ static int dense_step_impl(const b200rwkv_dense_model* m, const int64_t* token, 
     rp.resid = ws.x; rp.gate = ws.gate;
     B200_DS_CHECK((dense_launch_rows<T, 2>(rp, st)), "ffn value rows");
   }
-  if (logits) {
+  if (logits && l1 == m->n_layer) {
     memset(&vp, 0, sizeof(vp));
     vp.x = ws.x; vp.ln_w = m->ln_out_w; vp.ln_b = m->ln_out_b; vp.D = D; vp.out[0] = ws.hx;
     B200_DS_CHECK(dense_launch_vec<T>(vp, true, st), "output layer norm");
@@ -1753,18 +1753,25 @@ size_t b200rwkv_dense_workspace_bytes(const b200rwkv_dense_model* m) {
   return dense_carve(m, nullptr).bytes;
 }
 
-int b200rwkv_dense_step(const b200rwkv_dense_model* m, const int64_t* token, float* state, float* logits,
-                        void* workspace, size_t workspace_bytes, void* stream) {
+int b200rwkv_dense_step_layers(const b200rwkv_dense_model* m, int layer_begin, int layer_end, const int64_t* token, float* state,
+                               float* logits, void* workspace, size_t workspace_bytes, void* stream) {
   if (const char* why = dense_model_problem(m)) return fail(B200RWKV_EINVAL, "dense_step: %s", why);
   if (!token || !state || !workspace || !aligned16(workspace))
     return fail(B200RWKV_EINVAL, "dense_step: token, state and a 16-byte aligned workspace are required");
+  if (layer_begin < 0 || layer_begin > layer_end || layer_end > m->n_layer)
+    return fail(B200RWKV_EINVAL, "dense_step: layers [%d, %d) outside 0..%d", layer_begin, layer_end, m->n_layer);
   const DenseWorkspace ws = dense_carve(m, workspace);
   if (workspace_bytes < ws.bytes)
     return fail(B200RWKV_EINVAL, "dense_step: workspace of %zu bytes, %zu needed", workspace_bytes, ws.bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (m->dtype == B200RWKV_BF16) return dense_step_impl<__nv_bfloat16>(m, token, state, logits, ws, st);
-  if (m->dtype == B200RWKV_F16) return dense_step_impl<__half>(m, token, state, logits, ws, st);
-  return dense_step_impl<float>(m, token, state, logits, ws, st);
+  if (m->dtype == B200RWKV_BF16) return dense_step_impl<__nv_bfloat16>(m, layer_begin, layer_end, token, state, logits, ws, st);
+  if (m->dtype == B200RWKV_F16) return dense_step_impl<__half>(m, layer_begin, layer_end, token, state, logits, ws, st);
+  return dense_step_impl<float>(m, layer_begin, layer_end, token, state, logits, ws, st);
+}
+
+int b200rwkv_dense_step(const b200rwkv_dense_model* m, const int64_t* token, float* state, float* logits,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  return b200rwkv_dense_step_layers(m, 0, m ? m->n_layer : 0, token, state, logits, workspace, workspace_bytes, stream);
 }
 
 
@@ -1777,7 +1784,16 @@ size_t b200rwkv_dense_rows_workspace_bytes(const b200rwkv_dense_model* m, int st
 int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* tokens, int streams, int tokens_per_stream,
                                 float* state, int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes,
                                 void* stream) {
+  return b200rwkv_dense_forward_rows_layers(m, 0, m ? m->n_layer : 0, tokens, streams, tokens_per_stream, state, state_stride, logits,
+                                            workspace, workspace_bytes, stream);
+}
+
+int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_begin, int layer_end, const int64_t* tokens,
+                                       int streams, int tokens_per_stream, float* state, int64_t state_stride, float* logits,
+                                       void* workspace, size_t workspace_bytes, void* stream) {
   if (const char* why = dense_model_problem(m)) return fail(B200RWKV_EINVAL, "dense_forward_rows: %s", why);
+  if (layer_begin < 0 || layer_begin > layer_end || layer_end > m->n_layer)
+    return fail(B200RWKV_EINVAL, "dense_forward_rows: layers [%d, %d) outside 0..%d", layer_begin, layer_end, m->n_layer);
   if (m->dtype != B200RWKV_BF16 && m->dtype != B200RWKV_F16)
     return fail(B200RWKV_EINVAL, "dense_forward_rows: the tensor-core rows path takes bf16 or fp16 matrices (fp32: feed tokens one by one)");
   const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab, L = m->n_layer, B = streams, T = tokens_per_stream;
@@ -1808,8 +1824,9 @@ int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* to
       return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "dense_forward_rows: %s: %s (%s)", what, why, \
                   cudaGetErrorString(e));                                                              \
   } while (0)
-  B200_DR_CHECK(launch_chained(embed_ln0_rows_kernel, dim3(R), dim3(256), 0, s, m->emb, reinterpret_cast<const long long*>(tokens),
-                               D, V, m->ln0_w, m->ln0_b, ws.xa), "embedding");
+  if (layer_begin == 0)
+    B200_DR_CHECK(launch_chained(embed_ln0_rows_kernel, dim3(R), dim3(256), 0, s, m->emb, reinterpret_cast<const long long*>(tokens),
+                                 D, V, m->ln0_w, m->ln0_b, ws.xa), "embedding");
   DRowsPrepParams Q;
   DGemmParams P;
   auto prep = [&](const float* x, const float* lw, const float* lb, const float* carry, int nmix, const float* const* mix,
@@ -1824,7 +1841,7 @@ int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* to
     return cudaMemcpy2DAsync(row, size_t(state_stride) * 4, ws.carry_new, size_t(D) * 4, size_t(D) * 4, size_t(B),
                              cudaMemcpyDeviceToDevice, s);
   };
-  for (int l = 0; l < L; ++l) {
+  for (int l = layer_begin; l < layer_end; ++l) {
     const b200rwkv_dense_layer& ly = m->layers[l];
     float* st = state + size_t(l) * 5 * D;
     // 1. ln1 + token-shift mix -> key, value, sigmoid(receptance)
@@ -1889,7 +1906,7 @@ int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* to
       const unsigned short* x[1] = {ws.kk};
       B200_DR_CHECK(launch_dense_gemm(P, w, x, F, Rpad, s, &why), "ffn value"); }
   }
-  if (logits) {
+  if (logits && layer_end == L) {
     unsigned short* out[1] = {ws.hx};
     B200_DR_CHECK(prep(ws.xa, m->ln_out_w, m->ln_out_b, nullptr, 0, nullptr, out, 1), "output layer norm");
     memset(&P, 0, sizeof(P));

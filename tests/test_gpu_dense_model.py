@@ -202,3 +202,33 @@ def test_dense_rows_path_arguments():
     assert L.b200rwkv_dense_forward_rows(C.byref(m._cmodel), tok.data_ptr(), 1, 4, st.data_ptr(), st.stride(0), None,
                                          ws.data_ptr(), need, None) == _lib.EINVAL
     assert int(L.b200rwkv_dense_rows_workspace_bytes(C.byref(h._cmodel), 300, 300)) == 0
+
+
+@pytest.mark.parametrize("target_blocks", [0, 2])
+def test_blocks_streamed_from_pinned_host_memory_give_the_same_bits(target_blocks):
+    """``target_gb`` keeps only the first blocks' matrices on the device; the others are copied from pinned
+    host memory into two staging buffers one block ahead of their kernels.  Same kernels on the same
+    bytes: logits and states must equal the resident model's bit for bit, one token at a time (7 tokens:
+    the three streamed blocks take the two buffers in turn across tokens) and through the rows path."""
+    L, D, V = 5, 256, 300
+    ck = synth_checkpoint(L, D, vocab=V, seed=12)
+    block_bytes = (5 * D * D + 2 * D * 4 * D) * 2
+    resident = B200DenseRWKV.from_checkpoint(ck, dtype=torch.float16, device=DEV, use_graph=False)
+    streamed = B200DenseRWKV.from_checkpoint(ck, dtype=torch.float16, device=DEV, target_gb=(target_blocks + 0.5) * block_bytes / 1e9)
+    assert streamed.n_res == target_blocks and len(streamed._blob) == L - target_blocks
+    assert streamed.weight_bytes() == resident.weight_bytes()
+    toks = synth_tokens(7, seed=8, vocab=V)
+    sr, ss = resident.emptyState.clone(), streamed.emptyState.clone()
+    for t in toks:
+        lr, _ = resident.forward(t.reshape(1), sr)
+        ls, _ = streamed.forward(t.reshape(1), ss)
+        assert torch.equal(lr, ls)
+    assert torch.equal(sr, ss)
+    assert streamed.h2d_bytes >= 7 * (L - target_blocks) * streamed._blob[L - 1].numel()
+    rows = synth_tokens(2 * 9, seed=9, vocab=V).reshape(2, 9)
+    br, bs = resident.empty_batch_state(2), streamed.empty_batch_state(2)
+    assert torch.equal(resident.forward_rows(rows.to(DEV), br), streamed.forward_rows(rows.to(DEV), bs))
+    assert torch.equal(br, bs)
+    streamed.check_status()
+    full = B200DenseRWKV.from_checkpoint(ck, dtype=torch.float16, device=DEV, target_gb=1.0)      # everything fits: nothing streamed
+    assert full.n_res is None and not full._blob

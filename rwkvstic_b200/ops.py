@@ -160,6 +160,19 @@ def sample_typical(logits: torch.Tensor, temp: float = 1.0, tau: float = 0.95, u
     return (out, probs) if return_probs else out
 
 
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    """Index of the largest value of every row of ``logits [rows,V]`` (fp32, CUDA, contiguous rows), on the
+    device: int64 [rows]; ties go to the lowest index like ``torch.argmax`` on a CPU tensor."""
+    x = logits if logits.dim() == 2 else logits.reshape(1, -1)
+    if x.dtype != torch.float32 or x.device.type != "cuda" or x.stride(1) != 1:
+        raise ValueError("argmax_rows needs fp32 CUDA logits with contiguous rows")
+    rows, n = x.shape
+    out = torch.empty(rows, dtype=torch.int64, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().b200rwkv_argmax(x.data_ptr(), rows, n, x.stride(0), out.data_ptr(), None, None, 0, _stream(x.device)))
+    return out
+
+
 _DENSE_DTYPES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
 

@@ -458,9 +458,22 @@ def time_config4_one_gpu(dev, streams=64, steps=16):
     torch.cuda.synchronize(dev)
     model.check_rows_status()
     pre_ms = e0.elapsed_time(e1)
+    # one stream, one token per step: the one-row streaming path
+    st1 = model.emptyState.clone()
+    t1 = torch.tensor([7], dtype=torch.int64, device=dev)
+    for _ in range(4):
+        model.forward(t1, st1)
+    torch.cuda.synchronize(dev)
+    e0.record()
+    for _ in range(32):
+        model.forward(t1, st1)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    model.check_status()
+    b1_ms = e0.elapsed_time(e1) / 32
     return {"workload": f"RWKV-4 14b shape L={L} D={D}, all blocks on one GPU", "streams": streams, "decode_ms_per_step": dec_ms,
             "decode_tokens_per_s": streams / (dec_ms * 1e-3), "prefill_tokens": 2048, "prefill_ms": pre_ms,
-            "prefill_tokens_per_s": 2048 / (pre_ms * 1e-3)}
+            "prefill_tokens_per_s": 2048 / (pre_ms * 1e-3), "b1_decode_ms_per_step": b1_ms}
 
 
 def time_layer_split(rank, world, dev, streams=64, steps=16):
@@ -494,11 +507,18 @@ def time_layer_split(rank, world, dev, streams=64, steps=16):
     pipe.forward_rows(prompt, pstate)
     pre_ms = timed(lambda: pipe.forward_rows(prompt, pstate))
     model.check_rows_status()
-    del model, pipe, state, pstate
+    # one stream, one token per step: every stage runs the one-row streaming step on its blocks
+    s1 = LS.empty_stage_state(model, 1)
+    one = torch.full((1, 1), 7, dtype=torch.int64)
+    pipe.decode_greedy(one, s1, 3, 1)
+    b1_ms = timed(lambda: pipe.decode_greedy(one, s1, 32, 1)) / 32
+    model.check_status()
+    del model, pipe, state, pstate, s1
     torch.cuda.empty_cache()
     return {"workload": f"RWKV-4 14b shape L={L} D={D}, blocks split contiguously over {world} GPUs, {streams} streams, "
                         "one stream group", "decode_ms_per_step": dec_ms, "decode_tokens_per_s": streams / (dec_ms * 1e-3),
             "prefill_tokens": 2048, "prefill_ms": pre_ms, "prefill_tokens_per_s": 2048 / (pre_ms * 1e-3),
+            "b1_decode_ms_per_step": b1_ms,
             "handoff": "NCCL send/recv of the fp32 residual stream [rows, D] between consecutive ranks; sampled ids last -> first rank",
             "limit": "a decode step is a chain through all stages (each streams its blocks' weights once), so the split adds "
                      "capacity, not decode speed; the prompt's 512-token pieces pipeline across the stages"}

@@ -182,6 +182,21 @@ int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* s
  * receptance, attention output, ffn key+receptance, ffn value; then the head) and the preparation
  * kernel in front of it fill trace[i] as described at b200rwkv_gemv_u8_traced.  No counterpart in the reference.
  */
+/*
+ * One pipeline stage of the step above, for a model object that holds a contiguous range of blocks
+ * only (blocks placed on different devices: the TORCH_SPLIT placement; in-tree the hop between
+ * devices is modules/matmul.py:154-163).  The one-row streaming path for a single row, where
+ * b200rwkv_forward_rows_stage would run the tensor-core tiles.
+ *   token   device int64[1] on the first stage (m->emb set): embedding + ln0 produce the row; NULL on
+ *           later stages, where the row is read from x
+ *   x       device f32 [n_embd], 16-byte aligned: the residual stream handed over by the previous
+ *           stage (read when token is NULL) and, on return, this stage's result for the next one
+ *   logits  device f32 [n_vocab] on the last stage (m->head set), else NULL
+ * Same workspace, state rows and error convention as b200rwkv_decode_step; results are bit-identical
+ * to the unsplit step (same kernels on the same values).
+ */
+int b200rwkv_decode_step_stage(const b200rwkv_model* m, const int64_t* token, float* x, float* state, float* logits,
+                               void* workspace, size_t workspace_bytes, void* stream);
 int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
                                 void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream);
 

@@ -19,7 +19,7 @@ STATUS_WAIT_FULL, STATUS_WAIT_EMPTY, STATUS_WAIT_PEER = 1, 2, 4
 EXPORTS = (
     "b200rwkv_version", "b200rwkv_last_error", "b200rwkv_gemv_u8", "b200rwkv_wkv_scan", "b200rwkv_gemv_plan",
     "b200rwkv_gemv_u8_traced", "b200rwkv_gemv_workspace_bytes", "b200rwkv_gemv_u8_static",
-    "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step", "b200rwkv_decode_step_traced",
+    "b200rwkv_decode_workspace_bytes", "b200rwkv_decode_step", "b200rwkv_decode_step_traced", "b200rwkv_decode_step_stage",
     "b200rwkv_gemm_workspace_bytes", "b200rwkv_gemm_u8", "b200rwkv_rows_workspace_bytes", "b200rwkv_forward_rows", "b200rwkv_forward_rows_stage", "b200rwkv_argmax",
     "b200rwkv_sample_typical", "b200rwkv_gemv_dense",
     "b200rwkv_dense_workspace_bytes", "b200rwkv_dense_step", "b200rwkv_dense_rows_workspace_bytes", "b200rwkv_dense_forward_rows",
@@ -101,6 +101,9 @@ def lib() -> C.CDLL:
     L.b200rwkv_decode_step.restype = C.c_int
     L.b200rwkv_decode_step.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_size_t, C.c_void_p]
+    L.b200rwkv_decode_step_stage.restype = C.c_int
+    L.b200rwkv_decode_step_stage.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                             C.c_size_t, C.c_void_p]
     L.b200rwkv_decode_step_traced.restype = C.c_int
     L.b200rwkv_decode_step_traced.argtypes = [C.POINTER(Model), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_size_t, C.c_void_p, C.c_void_p]

@@ -182,11 +182,12 @@ static bool wants_sums(const b200rwkv_matrix& m) { return m.rx || m.mx || m.half
 // ---------------------------------------------------------------------------------------- small kernels
 // x = LayerNorm(emb[token]) (the reference's emb.py:8-9 gather followed by ln_in, opt.py:63-64).
 // First kernel of a decode step: it also clears the step's publication slots and publishes the sum
-// and sum of squares of x for the first block's layer norm (slot 0).
+// and sum of squares of x for the first block's layer norm (slot 0).  With x_in set (a pipeline stage
+// behind the first one) the row is the residual stream handed over by the previous stage, taken as it is.
 __global__ void __launch_bounds__(512, 1)
 embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ token, int D, int V,
                  const float* __restrict__ w, const float* __restrict__ b, float* __restrict__ out,
-                 PubSlot* __restrict__ pub, int npub) {
+                 PubSlot* __restrict__ pub, int npub, const float* __restrict__ x_in) {
   __shared__ float red[16];
   __shared__ long long redl[48];
   __shared__ float bc;
@@ -194,9 +195,9 @@ embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ to
   griddep_wait();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   for (int i = tid; i < npub * 16; i += 512) reinterpret_cast<long long*>(pub)[i] = 0;
-  long long tok = *token;
+  long long tok = x_in ? 0 : *token;
   tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
-  const float* row = emb + size_t(tok) * D;
+  const float* row = x_in ? x_in : emb + size_t(tok) * D;
   auto block_sum = [&](float v) -> float {
     v = warp_sum(v);
     if (lane == 0) red[warp] = v;
@@ -211,15 +212,18 @@ embed_ln0_kernel(const float* __restrict__ emb, const long long* __restrict__ to
     __syncthreads();
     return r;
   };
-  float s = 0.f;
-  for (int i = tid; i < D; i += 512) s += row[i];
-  const float mean = block_sum(s) / float(D);
-  s = 0.f;
-  for (int i = tid; i < D; i += 512) { const float c = row[i] - mean; s += c * c; }
-  const float sdev = sqrtf(block_sum(s) / float(D) + 1e-5f);
+  float mean = 0.f, sdev = 1.f;
+  if (!x_in) {
+    float s = 0.f;
+    for (int i = tid; i < D; i += 512) s += row[i];
+    mean = block_sum(s) / float(D);
+    s = 0.f;
+    for (int i = tid; i < D; i += 512) { const float c = row[i] - mean; s += c * c; }
+    sdev = sqrtf(block_sum(s) / float(D) + 1e-5f);
+  }
   long long p_sum = 0, p_sq = 0, p_sqlo = 0;
   for (int i = tid; i < D; i += 512) {
-    const float y = w[i] * ((row[i] - mean) / sdev) + b[i];
+    const float y = x_in ? __ldcg(x_in + i) : w[i] * ((row[i] - mean) / sdev) + b[i];
     out[i] = y;
     p_sum += __float2ll_rn(y * kPubSumScale);
     square_limbs(y, p_sq, p_sqlo);
@@ -1172,12 +1176,15 @@ size_t b200rwkv_decode_workspace_bytes(const b200rwkv_model* m) {
   return carve(m, nullptr).bytes;
 }
 
-static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float* state, float* logits, void* workspace,
+// x_io: null for a whole model.  Else the step is one pipeline stage: without `token` the residual stream
+// is read from x_io instead of the embedding, and in any case the stage's result is left in x_io.
+static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float* x_io, float* state, float* logits, void* workspace,
                             size_t workspace_bytes, unsigned long long* trace, void* stream) {
-  if (!m || !token || !state || !workspace || !m->layers || !m->emb)
+  if (!m || (!token && !x_io) || !state || !workspace || !m->layers || (token && !m->emb))
     return fail(B200RWKV_EINVAL, "decode_step: null argument");
+  if (x_io && !aligned16(x_io)) return fail(B200RWKV_EINVAL, "decode_step: x must be 16-byte aligned");
   const int D = m->n_embd, F = m->n_ffn, V = m->n_vocab, L = m->n_layer;
-  if (D <= 0 || (D % 128) != 0 || F <= 0 || (F % 128) != 0 || V <= 0 || L <= 0)
+  if (D <= 0 || (D % 128) != 0 || F <= 0 || (F % 128) != 0 || ((token || logits) && V <= 0) || L <= 0)
     return fail(B200RWKV_EINVAL, "decode_step: n_embd=%d n_ffn=%d must be positive multiples of 128", D, F);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0 || !aligned16(state))
     return fail(B200RWKV_EINVAL, "decode_step: workspace must be 256-byte and state 16-byte aligned");
@@ -1198,7 +1205,7 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     e = cudaLaunchKernelEx(&cfg, embed_ln0_kernel, m->emb, reinterpret_cast<const long long*>(token), D, V, m->ln0_w,
-                           m->ln0_b, ws.xa, ws.pub, 4 * L + 1);
+                           m->ln0_b, ws.xa, ws.pub, 4 * L + 1, token ? static_cast<const float*>(nullptr) : static_cast<const float*>(x_io));
     if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "decode_step: embed launch: %s", cudaGetErrorString(e));
   }
 
@@ -1311,6 +1318,10 @@ static int decode_step_impl(const b200rwkv_model* m, const int64_t* token, float
     P.status = ws.status; P.trace = trace_slice();
     if ((e = launch_stream_gemv(P, V, true, s, &why)) != cudaSuccess) goto launch_failed;
   }
+  if (x_io) {      // hand the residual stream to the next stage
+    why = "copy of the residual stream";
+    if ((e = cudaMemcpyAsync(x_io, ws.xa, size_t(D) * 4, cudaMemcpyDeviceToDevice, s)) != cudaSuccess) goto launch_failed;
+  }
   return B200RWKV_OK;
 launch_failed:
   return fail(e == cudaErrorInvalidValue ? B200RWKV_EINVAL : B200RWKV_ECUDA, "decode_step: %s (%s)", why, cudaGetErrorString(e));
@@ -1318,13 +1329,21 @@ launch_failed:
 
 int b200rwkv_decode_step(const b200rwkv_model* m, const int64_t* token, float* state, float* logits, void* workspace,
                          size_t workspace_bytes, void* stream) {
-  return decode_step_impl(m, token, state, logits, workspace, workspace_bytes, nullptr, stream);
+  if (!token) return fail(B200RWKV_EINVAL, "decode_step: null argument");
+  return decode_step_impl(m, token, nullptr, state, logits, workspace, workspace_bytes, nullptr, stream);
+}
+
+int b200rwkv_decode_step_stage(const b200rwkv_model* m, const int64_t* token, float* x, float* state, float* logits,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x) return fail(B200RWKV_EINVAL, "decode_step_stage: null x");
+  return decode_step_impl(m, token, x, state, logits, workspace, workspace_bytes, nullptr, stream);
 }
 
 int b200rwkv_decode_step_traced(const b200rwkv_model* m, const int64_t* token, float* state, float* logits,
                                 void* workspace, size_t workspace_bytes, uint64_t* trace, void* stream) {
   if (!trace) return fail(B200RWKV_EINVAL, "decode_step_traced: null trace buffer");
-  return decode_step_impl(m, token, state, logits, workspace, workspace_bytes, reinterpret_cast<unsigned long long*>(trace), stream);
+  if (!token) return fail(B200RWKV_EINVAL, "decode_step_traced: null argument");
+  return decode_step_impl(m, token, nullptr, state, logits, workspace, workspace_bytes, reinterpret_cast<unsigned long long*>(trace), stream);
 }
 
 

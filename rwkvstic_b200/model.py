@@ -178,6 +178,7 @@ class B200RWKV:
         self.emptyState = torch.zeros(self.n_layer, 5, self.n_embd, dtype=torch.float32, device=self.device)
         self.emptyState[:, 4] = -1e30
         self._build_descriptor()
+        self.stage_stream_rows = 2     # forward_rows_stage: up to this many rows go through the one-row step
         nbytes = int(self._L.b200rwkv_decode_workspace_bytes(C.byref(self._cmodel)))
         self._ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
         self._plan = None
@@ -506,6 +507,20 @@ class B200RWKV:
         if want_logits and self.w.head is None:
             raise ValueError("this stage holds no head")
         out = torch.empty(B, self.n_vocab, dtype=torch.float32, device=self.device) if want_logits else None
+        if B * T <= self.stage_stream_rows:
+            # one or two rows: the one-row streaming step per row (reads the stage's weights at HBM speed)
+            # instead of tensor-core tiles that would be almost empty
+            with torch.cuda.device(self.device):
+                stream = torch.cuda.current_stream(self.device).cuda_stream
+                for b in range(B):
+                    for t in range(T):
+                        r = b * T + t
+                        lp = out[b].data_ptr() if (want_logits and t == T - 1) else None
+                        _lib.check(self._L.b200rwkv_decode_step_stage(
+                            C.byref(self._cmodel), None if tokens is None else tokens[b, t:t + 1].data_ptr(), x[r].data_ptr(),
+                            state[b].data_ptr(), lp, self._ws.data_ptr(), self._ws.numel(), stream))
+                        self.launch_count += self.launches_per_step - (0 if lp is not None else 2)
+            return out
         with torch.cuda.device(self.device):
             ws = self._rows_ws.get((B, T))
             if ws is None:

@@ -144,6 +144,10 @@ constexpr int kDrWarps = 16;
 constexpr int kDrThreads = kDrWarps * 32;
 constexpr int kDrSlots = 2;                            // ring slots per warp
 constexpr int kDrStages = kDrWarps * kDrSlots;
+#ifndef B200_DR_EARLY
+#define B200_DR_EARLY 2
+#endif
+constexpr int kDrEarly = B200_DR_EARLY;               // slots per warp requested before the dependency wait
 constexpr int kDrOffFull = 0, kDrOffAbort = 512, kDrOffData = 1024;
 constexpr int kDrSmemLimit = 227 * 1024;
 
@@ -309,7 +313,7 @@ dense_rows_kernel(const DenseRowsParams P) {
   int rlt = lt, rpart = part;                          // the next item to request
   if (lane == 0) {
 #pragma unroll
-    for (int k = 0; k < kDrSlots; ++k) {
+    for (int k = 0; k < kDrEarly; ++k) {
       request(k, rlt, rpart);
       advance(rlt, rpart);
     }
@@ -338,6 +342,13 @@ dense_rows_kernel(const DenseRowsParams P) {
     for (int c = tid; c < pieces; c += kDrThreads) xs[v * pieces + c] = ld_act_u4(src + c);
   }
   __syncthreads();
+  if (lane == 0) {
+#pragma unroll
+    for (int k = kDrEarly; k < kDrSlots; ++k) {
+      request(k, rlt, rpart);
+      advance(rlt, rpart);
+    }
+  }
 
   int k = 0;
   bool dead = false;

@@ -870,7 +870,7 @@ static int dense_step_impl(const b200rwkv_dense_model* m, int l0, int l1, const 
   DenseVecParams vp;
   memset(&vp, 0, sizeof(vp));
   vp.emb = m->emb; vp.token = reinterpret_cast<const long long*>(token);
-  vp.ln_w = m->ln0_w; vp.ln_b = m->ln0_b; vp.x_out = ws.x; vp.D = D;
+  vp.ln_w = m->ln0_w; vp.ln_b = m->ln0_b; vp.x_out = ws.x; vp.D = D; vp.V = V;
   if (l0 == 0) B200_DS_CHECK(dense_launch_vec<T>(vp, false, st), "embedding");
   for (int l = l0; l < l1; ++l) {
     const b200rwkv_dense_layer& Lr = m->layers[l];

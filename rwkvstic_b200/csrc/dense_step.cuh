@@ -53,6 +53,7 @@ struct DenseVecParams {
   const float* mix[3];
   void* out[3];             // out[m] = T(lerp(carry, ln, mix[m])); with nmix == 0 and out[0] set: out[0] = T(ln)
   int nmix, D;
+  int V;                    // rows of emb: a token outside 0..V-1 is clamped into the table
 };
 
 __device__ __forceinline__ float block_sum_1024(float v, float* red) {
@@ -94,7 +95,9 @@ dense_vec_kernel(const DenseVecParams P) {
     lb[i] = in ? ld_param_v4(reinterpret_cast<const float4*>(P.ln_b) + g) : zero;
   }
   griddep_wait();
-  const float4* src = reinterpret_cast<const float4*>(P.x ? P.x : P.emb + size_t(*P.token) * P.D);
+  long long tok = P.x ? 0 : *P.token;
+  tok = tok < 0 ? 0 : (tok >= P.V ? P.V - 1 : tok);
+  const float4* src = reinterpret_cast<const float4*>(P.x ? P.x : P.emb + size_t(tok) * P.D);
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {

@@ -105,6 +105,12 @@ def test_dense_step_without_logits_and_bad_arguments():
         m._step(a, want_logits=True)
         m._step(b, want_logits=False)
     assert torch.equal(a, b)
+    # a token outside the table is clamped into it (as the quantised step does), not read out of bounds
+    for bad, same_as in ((300 + 5, 299), (-3, 0)):
+        x, y = m.emptyState.clone(), m.emptyState.clone()
+        lx, _ = m.forward(torch.tensor([bad]), x)
+        ly, _ = m.forward(torch.tensor([same_as]), y)
+        assert torch.equal(lx, ly) and torch.equal(x, y)
     L = m._L
     args = (m._tok.data_ptr(), a.data_ptr(), None, m._ws.data_ptr(), m._ws.numel(), None)
     assert L.b200rwkv_dense_step(None, *args) == _lib.EINVAL

@@ -422,6 +422,22 @@ int b200rwkv_dense_forward_rows(const b200rwkv_dense_model* m, const int64_t* to
                                 float* state, int64_t state_stride, float* logits, void* workspace, size_t workspace_bytes,
                                 void* stream);
 
+/*
+ * The time-out path under test.  Every device-side wait of the library is bounded; these two calls let a
+ * test make a bound run out without faulting anything.  No counterpart in the reference (its kernels do
+ * not wait on one another).
+ *   b200rwkv_wait_selftest: one small kernel waits, with the given bound, for bytes that are announced to
+ *     an mbarrier and never delivered; on expiry it ORs B200RWKV_STATUS_WAIT_FULL into *status (device
+ *     int) and returns.  The kernel ends limit_ns after it started.
+ *   b200rwkv_debug_expire_waits(1, limit_ns): process-wide switch; while on, the rows kernels of
+ *     b200rwkv_dense_step* announce their ring slots but withhold the copies, with limit_ns as the bound of
+ *     every wait: each launch gives up after limit_ns, sets the status word of the workspace and runs to
+ *     its end (results of such a step are undefined).  b200rwkv_debug_expire_waits(0, 0) switches it off.
+ * limit_ns between 1 us and 1 s.
+ */
+int b200rwkv_wait_selftest(uint64_t limit_ns, int* status, void* stream);
+int b200rwkv_debug_expire_waits(int enable, uint64_t limit_ns);
+
 #ifdef __cplusplus
 }
 #endif

@@ -23,7 +23,7 @@ EXPORTS = (
     "b200rwkv_gemm_workspace_bytes", "b200rwkv_gemm_u8", "b200rwkv_rows_workspace_bytes", "b200rwkv_forward_rows", "b200rwkv_forward_rows_stage", "b200rwkv_argmax",
     "b200rwkv_sample_typical", "b200rwkv_gemv_dense",
     "b200rwkv_dense_workspace_bytes", "b200rwkv_dense_step", "b200rwkv_dense_rows_workspace_bytes", "b200rwkv_dense_forward_rows",
-    "b200rwkv_dense_step_layers", "b200rwkv_dense_forward_rows_layers",
+    "b200rwkv_dense_step_layers", "b200rwkv_dense_forward_rows_layers", "b200rwkv_wait_selftest", "b200rwkv_debug_expire_waits",
     "b200rwkv_step_plan_bytes", "b200rwkv_step_plan_init", "b200rwkv_decode_step_persistent", "b200rwkv_step_geometry",
 )
 
@@ -154,6 +154,10 @@ def lib() -> C.CDLL:
     L.b200rwkv_dense_forward_rows_layers.restype = C.c_int
     L.b200rwkv_dense_forward_rows_layers.argtypes = [C.POINTER(DenseModel), C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_void_p,
                                                      C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+    L.b200rwkv_wait_selftest.restype = C.c_int
+    L.b200rwkv_wait_selftest.argtypes = [C.c_uint64, C.c_void_p, C.c_void_p]
+    L.b200rwkv_debug_expire_waits.restype = C.c_int
+    L.b200rwkv_debug_expire_waits.argtypes = [C.c_int, C.c_uint64]
     _lib = L
     return L
 

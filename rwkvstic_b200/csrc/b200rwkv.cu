@@ -753,6 +753,29 @@ using namespace b200;
 static int dense_elem_bytes(int dtype) { return dtype == B200RWKV_F32 ? 4 : (dtype == B200RWKV_BF16 || dtype == B200RWKV_F16) ? 2 : 0; }
 
 // ---- unquantised weights: one token through the network -------------------------------------------
+// Testing the time-out path (b200rwkv_debug_expire_waits): while enabled, the rows launches of the
+// unquantised step announce their ring slots but withhold the copies, with this bound on every wait.
+static int g_expire_waits = 0;
+static unsigned long long g_expire_limit_ns = 0;
+
+// A wait that nothing satisfies: one mbarrier expecting bytes that never come, every thread waits for it
+// with the given bound and reports the expiry.
+__global__ void __launch_bounds__(64) wait_selftest_kernel(unsigned long long limit_ns, int* status) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    mbar_init(b, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_arrive_expect_tx(b, 16);
+  __syncthreads();
+  const bool ok = mbar_wait_limited(b, 0, &abort_flag, limit_ns);
+  if (!ok && threadIdx.x == 0 && status) atomicOr(status, B200RWKV_STATUS_WAIT_FULL);
+}
+
 struct DenseWorkspace {
   int* status;
   float *x, *gate;
@@ -846,6 +869,8 @@ static cudaError_t dense_launch_rows(DenseRowsParams& P, cudaStream_t stream) {
   int grid = 0;
   size_t smem = 0;
   if (!dense_rows_geometry(P, R, int(sizeof(T)), device_sms(), &grid, &smem)) return cudaErrorInvalidValue;
+  P.withhold_copies = g_expire_waits;
+  P.wait_limit_ns = g_expire_waits ? g_expire_limit_ns : 0;
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kDrThreads);
@@ -1936,6 +1961,24 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
     B200_DR_CHECK(launch_dense_gemm(P, w, x, D, gemm_padded_rows(B), s, &why), "head");
   }
 #undef B200_DR_CHECK
+  return B200RWKV_OK;
+}
+
+// ---- time-out path under test ----------------------------------------------------------------------------
+int b200rwkv_debug_expire_waits(int enable, uint64_t limit_ns) {
+  if (enable && (limit_ns < 1000ull || limit_ns > 1000ull * 1000ull * 1000ull))
+    return fail(B200RWKV_EINVAL, "debug_expire_waits: limit must be between 1 us and 1 s");
+  g_expire_waits = enable ? 1 : 0;
+  g_expire_limit_ns = enable ? limit_ns : 0;
+  return B200RWKV_OK;
+}
+
+int b200rwkv_wait_selftest(uint64_t limit_ns, int* status, void* stream) {
+  if (!status || limit_ns < 1000ull || limit_ns > 1000ull * 1000ull * 1000ull)
+    return fail(B200RWKV_EINVAL, "wait_selftest: status pointer and a limit between 1 us and 1 s are required");
+  wait_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200RWKV_ECUDA, "wait_selftest: %s", cudaGetErrorString(e));
   return B200RWKV_OK;
 }
 

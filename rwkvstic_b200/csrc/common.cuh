@@ -52,19 +52,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Wait for `parity` of `bar`, at most kWaitLimitNs.  Returns false (and raises *abort_flag) when
+// Wait for `parity` of `bar`, at most limit_ns.  Returns false (and raises *abort_flag) when
 // the limit is hit or another thread already raised the flag.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+    if (globaltimer_ns() - t0 > limit_ns) {
       *abort_flag = 1;
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, kWaitLimitNs);
 }
 
 // ---- TMA bulk copy (1-D, global -> shared), completion counted in bytes on an mbarrier ----------

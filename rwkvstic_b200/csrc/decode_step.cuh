@@ -126,20 +126,6 @@ __device__ __forceinline__ unsigned ld_relaxed_u32(const unsigned* p) {
   return v;
 }
 
-__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                                  unsigned long long limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  for (unsigned it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if ((it & 63u) == 0u && globaltimer_ns() - t0 > limit_ns) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-
 // Exchange words are read and written with strong (relaxed, gpu-scope) accesses: a weak load, even
 // one that bypasses L1, may be served from a stale copy for microseconds.
 __device__ __forceinline__ float4 ld_xchg_v4(const float4* p) {

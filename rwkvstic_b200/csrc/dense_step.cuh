@@ -174,6 +174,8 @@ struct DenseRowsParams {
   const float *decay, *first;
   void* wkv_out;           // WKV launch: T[n] = sigmoid(r) * wkv
   int* status;             // device status word (B200RWKV_STATUS_* bits)
+  unsigned long long wait_limit_ns;   // bound of every wait of the kernel (0: the library default of one second)
+  int withhold_copies;     // testing the time-out path: slots are announced but never filled, so every wait expires
 #ifdef B200_DENSE_TRACE
   unsigned long long* trace;   // profiling builds: CTA 0, [warp][item 0..63][8] %globaltimer stamps
 #endif
@@ -261,6 +263,7 @@ dense_rows_kernel(const DenseRowsParams P) {
   unsigned char* ring = ds_smem + lay.ring_off + size_t(warp * kDrSlots) * P.stage_bytes;   // this warp's slots
 
   griddep_launch_dependents();
+  const unsigned long long wait_limit = P.wait_limit_ns ? P.wait_limit_ns : kWaitLimitNs;
   const int t0 = int((long long)P.tasks * blockIdx.x / gridDim.x);
   const int t1 = int((long long)P.tasks * (blockIdx.x + 1) / gridDim.x);
   if (tid == 0) *abort_flag = 0;
@@ -302,14 +305,17 @@ dense_rows_kernel(const DenseRowsParams P) {
     if constexpr (R == 3) {
 #pragma unroll
       for (int r = 0; r < 3; ++r)
-        bulk_g2s(dst + r * P.row_stride,
-                 reinterpret_cast<const uint4*>(static_cast<const T*>(P.seg[r].w) + size_t(task) * P.seg[r].ldw) + c0, bytes, bar);
+        if (!P.withhold_copies)
+          bulk_g2s(dst + r * P.row_stride,
+                   reinterpret_cast<const uint4*>(static_cast<const T*>(P.seg[r].w) + size_t(task) * P.seg[r].ldw) + c0, bytes, bar);
     } else {
       const ulonglong2 rec = table[lt];
       const unsigned meta = unsigned(rec.y);
       const T* W = reinterpret_cast<const T*>(rec.x);
-      bulk_g2s(dst, reinterpret_cast<const uint4*>(W) + c0, bytes, bar);
-      bulk_g2s(dst + P.row_stride, reinterpret_cast<const uint4*>(W + ((meta >> 31) ? P.seg[meta & 3u].ldw : 0)) + c0, bytes, bar);
+      if (!P.withhold_copies) {
+        bulk_g2s(dst, reinterpret_cast<const uint4*>(W) + c0, bytes, bar);
+        bulk_g2s(dst + P.row_stride, reinterpret_cast<const uint4*>(W + ((meta >> 31) ? P.seg[meta & 3u].ldw : 0)) + c0, bytes, bar);
+      }
     }
   };
   int lt = warp / split, part = warp % split;          // the item being consumed
@@ -366,7 +372,7 @@ dense_rows_kernel(const DenseRowsParams P) {
     }
     const int slot = k % kDrSlots;
     B200_DENSE_STAMP(0);
-    const bool ok = mbar_wait_bounded(full0 + 8 * slot, uint32_t(k / kDrSlots) & 1u, abort_flag);
+    const bool ok = mbar_wait_limited(full0 + 8 * slot, uint32_t(k / kDrSlots) & 1u, abort_flag, wait_limit);
     if (!__all_sync(0xffffffffu, ok)) {
       if (lane == 0 && P.status) atomicOr(P.status, B200RWKV_STATUS_WAIT_FULL);
       dead = true;
@@ -469,7 +475,7 @@ dense_rows_kernel(const DenseRowsParams P) {
     const unsigned long long t_start = globaltimer_ns();
     for (int j = k; j < k + kDrSlots; ++j) {
       if (warp + j * kDrWarps >= (t1 - t0) * split) break;
-      while (!mbar_try_wait(full0 + 8 * (j % kDrSlots), uint32_t(j / kDrSlots) & 1u) && globaltimer_ns() - t_start < kWaitLimitNs / 10) {
+      while (!mbar_try_wait(full0 + 8 * (j % kDrSlots), uint32_t(j / kDrSlots) & 1u) && globaltimer_ns() - t_start < wait_limit / 10) {
       }
     }
   }

@@ -963,6 +963,8 @@ struct DenseRowsWorkspace {
   int* status;
   float *xa, *xb, *kb, *vb, *rb, *carry_new, *wkv_loc;
   unsigned short *t0, *t1, *t2, *kk, *hx;
+  float* sk_part;        // partial sums of K slices (launches with few rows)
+  unsigned* sk_count;    // their tickets, zero between launches
   size_t bytes;
 };
 
@@ -986,6 +988,8 @@ static DenseRowsWorkspace dense_carve_rows(const b200rwkv_dense_model* m, int B,
   w.t2 = reinterpret_cast<unsigned short*>(take(Rpad * D * 2));
   w.kk = reinterpret_cast<unsigned short*>(take(Rpad * F * 2));
   w.hx = reinterpret_cast<unsigned short*>(take(Bpad * D * 2));
+  w.sk_count = reinterpret_cast<unsigned*>(take(size_t(kDgSplitMaxItems) * 4));
+  w.sk_part = reinterpret_cast<float*>(take(R <= size_t(kDgSplitMaxRt) ? kDgSplitBytes : 0));   // only few-row calls split K
   w.bytes = off;
   return w;
 }
@@ -1017,13 +1021,21 @@ static cudaError_t launch_dense_gemm(DGemmParams& P, const void* const* w, const
       if (row_tiles != rt_rows) continue;
       long long tiles = 0;
       for (int s = 0; s < P.nseg; ++s) tiles += (long long)row_tiles * ((P.seg[s].N + mt - 1) / mt);
-      const double rounds = double((tiles + sms - 1) / sms);
-      const double cost = rounds * (double(P.ksteps) * 128.0 * (mt + rt) + 48.0 * 1024);
-      if (best == 0.0 || cost < best) { best = cost; P.mt = mt; P.Rt = rt; }
+      for (int ks = 1; ks <= 8; ks *= 2) {     // K slices: only where few tiles would leave most SMs idle
+        if (ks > 1 && (!P.sk_part || mt != 128 || rt > kDgSplitMaxRt || tiles * ks > kDgSplitMaxItems || P.ksteps % ks != 0 ||
+                       P.ksteps / ks < 4))
+          continue;
+        const double rounds = double((tiles * ks + sms - 1) / sms);
+        const double reduce = ks > 1 ? 2.0 * rt * 128 * 4 + 64.0 * 1024 : 0.0;   // partial sums out and back, ticket
+        const double cost = rounds * (double(P.ksteps / ks) * 128.0 * (mt + rt) + 48.0 * 1024 + reduce);
+        if (best == 0.0 || cost < best) { best = cost; P.mt = mt; P.Rt = rt; P.ksplit = ks; }
+      }
     }
   }
   if (best == 0.0) { *why = "no tile fits"; return cudaErrorInvalidValue; }
   P.row_tiles = (P.R + P.Rt - 1) / P.Rt;
+  P.stage_bytes = (P.mt + P.Rt) * 128;
+  P.stages = kDgRingBytes / P.stage_bytes < kDgMaxStages ? kDgRingBytes / P.stage_bytes : kDgMaxStages;
   P.ntiles = 0;
   for (int s = 0; s < P.nseg; ++s) {
     if (!encode_byte_map(&P.seg[s].wmap, w[s], (unsigned long long)P.seg[s].N, K * 2, P.mt, 1) ||
@@ -1034,7 +1046,8 @@ static cudaError_t launch_dense_gemm(DGemmParams& P, const void* const* w, const
     P.tiles_seg[s] = P.row_tiles * ((P.seg[s].N + P.mt - 1) / P.mt);
     P.ntiles += P.tiles_seg[s];
   }
-  const dim3 grid(P.ntiles < sms ? P.ntiles : sms);
+  const int items = P.ntiles * P.ksplit;
+  const dim3 grid(items < sms ? items : sms);
   return launch_chained(dense_tile_gemm_kernel, grid, dim3(kGemmThreads), size_t(kDgSmem), stream, P);
 }
 
@@ -1876,12 +1889,15 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
   auto prep = [&](const float* x, const float* lw, const float* lb, const float* carry, int nmix, const float* const* mix,
                   unsigned short* const* out, int last_only) -> cudaError_t {
     memset(&Q, 0, sizeof(Q));
-    Q.x = x; Q.ln_w = lw; Q.ln_b = lb; Q.carry = carry; Q.carry_stride = state_stride; Q.carry_out = carry ? ws.carry_new : nullptr;
+    Q.x = x; Q.ln_w = lw; Q.ln_b = lb; Q.carry = carry; Q.carry_stride = state_stride;
+    Q.carry_out = !carry ? nullptr : (T == 1 ? const_cast<float*>(carry) : ws.carry_new);
+    Q.carry_out_stride = T == 1 ? state_stride : D;
     Q.nmix = nmix; Q.D = D; Q.Tn = T; Q.last_only = last_only; Q.is_bf16 = bf;
     for (int i = 0; i < (nmix > 0 ? nmix : 1); ++i) { Q.mix[i] = mix ? mix[i] : nullptr; Q.out[i] = out[i]; }
     return launch_chained(dense_rows_prep_kernel, dim3(last_only ? B : R), dim3(256), size_t(2) * D * 4, s, Q);
   };
   auto commit = [&](float* row) -> cudaError_t {      // parked layer norm of every stream's last row -> its state row
+    if (T == 1) return cudaSuccess;                    // one row per stream: the preparation kernel wrote the state row itself
     return cudaMemcpy2DAsync(row, size_t(state_stride) * 4, ws.carry_new, size_t(D) * 4, size_t(D) * 4, size_t(B),
                              cudaMemcpyDeviceToDevice, s);
   };
@@ -1894,7 +1910,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
       B200_DR_CHECK(prep(ws.xa, ly.ln1_w, ly.ln1_b, st, 3, mix, out, 0), "attention mix"); }
     B200_DR_CHECK(commit(st), "attention carry");
     memset(&P, 0, sizeof(P));
-    P.nseg = 3; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    P.nseg = 3; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], D, ws.kb, D, ACT_NONE, 0);
     fill_dgemm_seg(P.seg[1], D, ws.vb, D, ACT_NONE, 0);
     fill_dgemm_seg(P.seg[2], D, ws.rb, D, ACT_SIGMOID, 0);
@@ -1923,7 +1939,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
     B200_DR_CHECK(launch_chained(dense_rows_cast_kernel, dim3(unsigned(std::min<long long>((long long)R * D / 4 / 256 + 1, 4096))), dim3(256), 0, s,
                                  (const float*)ws.kb, ws.t0, (long long)R * D / 4, bf), "cast");
     memset(&P, 0, sizeof(P));
-    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], D, ws.xb, D, ACT_NONE, 0);
     P.seg[0].res = ws.xa; P.seg[0].ldres = D;
     { const void* w[1] = {ly.att_output};
@@ -1935,7 +1951,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
       B200_DR_CHECK(prep(ws.xb, ly.ln2_w, ly.ln2_b, st + D, 2, mix, out, 0), "ffn mix"); }
     B200_DR_CHECK(commit(st + D), "ffn carry");
     memset(&P, 0, sizeof(P));
-    P.nseg = 2; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    P.nseg = 2; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], F, ws.kk, F, ACT_RELUSQ, 1);
     fill_dgemm_seg(P.seg[1], D, ws.rb, D, ACT_SIGMOID, 0);
     { const void* w[2] = {ly.ffn_key, ly.ffn_receptance};
@@ -1943,7 +1959,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
       B200_DR_CHECK(launch_dense_gemm(P, w, x, D, Rpad, s, &why), "ffn key and receptance"); }
     // 5. ffn value, gated, + residual -> xa
     memset(&P, 0, sizeof(P));
-    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status;
+    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], D, ws.xa, D, ACT_NONE, 0);
     P.seg[0].res = ws.xb; P.seg[0].ldres = D; P.seg[0].gate = ws.rb; P.seg[0].ldgate = D;
     { const void* w[1] = {ly.ffn_value};
@@ -1954,7 +1970,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
     unsigned short* out[1] = {ws.hx};
     B200_DR_CHECK(prep(ws.xa, m->ln_out_w, m->ln_out_b, nullptr, 0, nullptr, out, 1), "output layer norm");
     memset(&P, 0, sizeof(P));
-    P.nseg = 1; P.R = B; P.is_bf16 = bf; P.status = ws.status;
+    P.nseg = 1; P.R = B; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], V, logits, V, ACT_NONE, 0);
     const void* w[1] = {m->head};
     const unsigned short* x[1] = {ws.hx};

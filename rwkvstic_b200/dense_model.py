@@ -236,7 +236,7 @@ class B200DenseRWKV:
         for buf in [self._ws, *self._rows_ws.values()]:
             bits = int(buf[:4].view(torch.int32).cpu()[0])
             if bits:
-                buf[:4].zero_()
+                buf.zero_()                 # status word and, in a rows workspace, the tickets of an abandoned K split
                 raise _lib.B200RWKVError(_lib.ETIMEOUT, f"device-side wait expired, status bits 0x{bits:x}")
 
     def _queue_status(self, buf: Optional[torch.Tensor] = None) -> None:

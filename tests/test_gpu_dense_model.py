@@ -238,3 +238,22 @@ def test_blocks_streamed_from_pinned_host_memory_give_the_same_bits(target_block
     streamed.check_status()
     full = B200DenseRWKV.from_checkpoint(ck, dtype=torch.float16, device=DEV, target_gb=1.0)      # everything fits: nothing streamed
     assert full.n_res is None and not full._blob
+
+
+def test_few_rows_split_k_and_stay_deterministic():
+    """With few rows a launch has few tiles and cuts K into slices whose partial sums are added in slice
+    order: two runs agree bit for bit (whichever CTA finished last), and the result matches the oracle."""
+    V, Dm = 1024, 4096
+    ck = synth_checkpoint(1, Dm, vocab=V, seed=91)
+    model = B200DenseRWKV.from_checkpoint(ck, dtype=torch.bfloat16, device=DEV, use_graph=False)
+    toks = synth_tokens(24, seed=5, vocab=V).reshape(24, 1)           # 24 sequences, one token each: 32 weight tiles per matrix
+    outs = []
+    for _ in range(3):
+        st = model.empty_batch_state(24)
+        outs.append((model.forward_rows(toks.to(DEV), st).clone(), st.clone()))
+    assert all(torch.equal(outs[0][0], o[0]) and torch.equal(outs[0][1], o[1]) for o in outs[1:])
+    ref = OracleTorchMode(ck, torch.bfloat16)
+    for b in (0, 23):
+        want, _ = ref.forward(toks[b], ref.emptyState.clone())
+        assert float((outs[0][0][b].cpu() - want).abs().max()) / float(want.abs().max()) <= REL_TOL["bf16"]
+    model.check_status()

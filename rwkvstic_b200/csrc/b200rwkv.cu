@@ -989,7 +989,7 @@ static DenseRowsWorkspace dense_carve_rows(const b200rwkv_dense_model* m, int B,
   w.kk = reinterpret_cast<unsigned short*>(take(Rpad * F * 2));
   w.hx = reinterpret_cast<unsigned short*>(take(Bpad * D * 2));
   w.sk_count = reinterpret_cast<unsigned*>(take(size_t(kDgSplitMaxItems) * 4));
-  w.sk_part = reinterpret_cast<float*>(take(R <= size_t(kDgSplitMaxRt) ? kDgSplitBytes : 0));   // only few-row calls split K
+  w.sk_part = reinterpret_cast<float*>(take(R <= size_t(kDgSplitMaxRows) ? kDgSplitBytes : 0));   // only calls with few rows split K
   w.bytes = off;
   return w;
 }
@@ -1022,8 +1022,8 @@ static cudaError_t launch_dense_gemm(DGemmParams& P, const void* const* w, const
       long long tiles = 0;
       for (int s = 0; s < P.nseg; ++s) tiles += (long long)row_tiles * ((P.seg[s].N + mt - 1) / mt);
       for (int ks = 1; ks <= 8; ks *= 2) {     // K slices: only where few tiles would leave most SMs idle
-        if (ks > 1 && (!P.sk_part || mt != 128 || rt > kDgSplitMaxRt || tiles * ks > kDgSplitMaxItems || P.ksteps % ks != 0 ||
-                       P.ksteps / ks < 4))
+        if (ks > 1 && (!P.sk_part || mt != 128 || tiles * ks > kDgSplitMaxItems || tiles * ks * rt > kDgSplitMaxCells ||
+                       P.ksteps % ks != 0 || P.ksteps / ks < 4))
           continue;
         const double rounds = double((tiles * ks + sms - 1) / sms);
         const double reduce = ks > 1 ? 2.0 * rt * 128 * 4 + 64.0 * 1024 : 0.0;   // partial sums out and back, ticket
@@ -1910,7 +1910,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
       B200_DR_CHECK(prep(ws.xa, ly.ln1_w, ly.ln1_b, st, 3, mix, out, 0), "attention mix"); }
     B200_DR_CHECK(commit(st), "attention carry");
     memset(&P, 0, sizeof(P));
-    P.nseg = 3; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
+    P.nseg = 3; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRows ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], D, ws.kb, D, ACT_NONE, 0);
     fill_dgemm_seg(P.seg[1], D, ws.vb, D, ACT_NONE, 0);
     fill_dgemm_seg(P.seg[2], D, ws.rb, D, ACT_SIGMOID, 0);
@@ -1939,7 +1939,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
     B200_DR_CHECK(launch_chained(dense_rows_cast_kernel, dim3(unsigned(std::min<long long>((long long)R * D / 4 / 256 + 1, 4096))), dim3(256), 0, s,
                                  (const float*)ws.kb, ws.t0, (long long)R * D / 4, bf), "cast");
     memset(&P, 0, sizeof(P));
-    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
+    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRows ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], D, ws.xb, D, ACT_NONE, 0);
     P.seg[0].res = ws.xa; P.seg[0].ldres = D;
     { const void* w[1] = {ly.att_output};
@@ -1951,7 +1951,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
       B200_DR_CHECK(prep(ws.xb, ly.ln2_w, ly.ln2_b, st + D, 2, mix, out, 0), "ffn mix"); }
     B200_DR_CHECK(commit(st + D), "ffn carry");
     memset(&P, 0, sizeof(P));
-    P.nseg = 2; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
+    P.nseg = 2; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRows ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], F, ws.kk, F, ACT_RELUSQ, 1);
     fill_dgemm_seg(P.seg[1], D, ws.rb, D, ACT_SIGMOID, 0);
     { const void* w[2] = {ly.ffn_key, ly.ffn_receptance};
@@ -1959,7 +1959,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
       B200_DR_CHECK(launch_dense_gemm(P, w, x, D, Rpad, s, &why), "ffn key and receptance"); }
     // 5. ffn value, gated, + residual -> xa
     memset(&P, 0, sizeof(P));
-    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
+    P.nseg = 1; P.R = R; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRows ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], D, ws.xa, D, ACT_NONE, 0);
     P.seg[0].res = ws.xb; P.seg[0].ldres = D; P.seg[0].gate = ws.rb; P.seg[0].ldgate = D;
     { const void* w[1] = {ly.ffn_value};
@@ -1970,7 +1970,7 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
     unsigned short* out[1] = {ws.hx};
     B200_DR_CHECK(prep(ws.xa, m->ln_out_w, m->ln_out_b, nullptr, 0, nullptr, out, 1), "output layer norm");
     memset(&P, 0, sizeof(P));
-    P.nseg = 1; P.R = B; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRt ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
+    P.nseg = 1; P.R = B; P.is_bf16 = bf; P.status = ws.status; P.sk_part = R <= kDgSplitMaxRows ? ws.sk_part : nullptr; P.sk_count = ws.sk_count;
     fill_dgemm_seg(P.seg[0], V, logits, V, ACT_NONE, 0);
     const void* w[1] = {m->head};
     const unsigned short* x[1] = {ws.hx};

@@ -30,9 +30,10 @@ constexpr int kDgStageBytes = kGemmABytes + kDgRowsMax * 128;    // 62 KB
 constexpr int kDgRingBytes = kGemmStages * kDgStageBytes;          // 186 KB: three stages of the largest tile, up to eight of a small one
 constexpr int kDgMaxStages = 8;                                  // barriers: full 0..7, empty 8..15
 constexpr int kDgSmem = kGemmOffRing + kDgRingBytes;
-constexpr int kDgSplitMaxItems = 640;                            // tiles x slices of a split launch
-constexpr int kDgSplitMaxRt = 64;                                // and its tile height
-constexpr size_t kDgSplitBytes = size_t(kDgSplitMaxItems) * kDgSplitMaxRt * 128 * 4;   // 21 MB of partial sums
+constexpr int kDgSplitMaxItems = 640;                            // tiles x slices of a split launch (its tickets)
+constexpr int kDgSplitMaxRows = 1024;                            // calls of up to this many rows may split K
+constexpr long long kDgSplitMaxCells = 640ll * 64;               // tiles x slices x tile height that the scratch holds
+constexpr size_t kDgSplitBytes = size_t(kDgSplitMaxCells) * 128 * 4;   // 21 MB of partial sums
 
 struct DGemmSeg {
   CUtensorMap wmap;     // W as bytes [K*2/128][N][128 B], box [1][mt][128], 128-byte swizzle
@@ -53,7 +54,7 @@ struct DGemmParams {
   int is_bf16;
   int stages;           // ring depth: as many stages of stage_bytes as fit the ring, at most 8
   int stage_bytes;      // mt * 128 (weights) + Rt * 128 (rows), a multiple of 1024
-  int ksplit;           // K slices per tile (1: none; > 1 only with 128-row tiles and Rt <= 64; divides ksteps)
+  int ksplit;           // K slices per tile (1: none; > 1 only with 128-row tiles; divides ksteps)
   float* sk_part;       // [ntiles][ksplit][Rt][128] partial sums of the slices
   unsigned* sk_count;   // [ntiles] tickets, zero between launches
   int* status;

@@ -164,7 +164,8 @@ def test_loader_hook_with_dtype_builds_the_unquantised_model():
     assert float((got.cpu() - want).abs().max()) <= REL_TOL["bf16"] * float(want.abs().max())
 
 
-@pytest.mark.parametrize("embed,name,B,T", [(2048, "bf16", 3, 40), (2560, "f16", 2, 17), (4096, "bf16", 2, 300), (5120, "f16", 1, 130)])
+@pytest.mark.parametrize("embed,name,B,T", [(2048, "bf16", 3, 40), (2560, "f16", 2, 17), (4096, "bf16", 2, 300), (5120, "f16", 1, 130),
+                                            (2048, "f16", 3, 129), (2048, "bf16", 5, 128)])
 def test_dense_rows_path_against_the_oracle(embed, name, B, T):
     """B sequences of T tokens in one call through the tensor-core rows path (T = 300 and 130 take the
     chunk-parallel WKV scan) against the oracle's sequence mode, one sequence at a time: logits after the

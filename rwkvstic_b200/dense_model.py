@@ -42,6 +42,8 @@ _VECS = ("ln1.weight", "ln1.bias", "ln2.weight", "ln2.bias", "att.time_mix_k", "
 
 
 class B200DenseRWKV:
+    RnnOnly = False  # sequence mode is supported (rwkvMaster.py:97 looks this up)
+
     def __init__(self, tensors: Iterable[Tuple[str, torch.Tensor]], dtype: torch.dtype = torch.bfloat16, device="cuda:0",
                  use_graph: bool = True, decay_is_final: bool = False, target_gb: Optional[float] = None,
                  pin_memory: bool = True):

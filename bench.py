@@ -525,7 +525,7 @@ def time_layer_split(rank, world, dev, streams=64, steps=16):
 
 
 def time_split_decode(model, rank, world, dev, total_streams=256, steps=16):
-    """BASELINE config 3 as written: `total_streams` independent streams SPLIT over the ranks
+    """A fixed total of `total_streams` independent streams SPLIT over the ranks
     (strong scaling), each rank decoding its shard on a replica; no collective on the data path."""
     import torch.distributed as dist
     from rwkvstic_b200.parallel import decode_sharded, stream_shard

@@ -38,3 +38,27 @@ def test_full_depth_prompt_and_decode_against_the_oracle(shape):
     model.check_status()
     print(f"{shape} shape, {L} blocks: max |dlogit| over prompt + 4 decode steps {worst:.2e}; greedy token checked at {agree} steps")
     assert worst < 2e-3, worst
+
+
+def test_full_depth_unquantised_1b5_against_the_oracle():
+    """The unquantised bf16 model at the full 1.5B shape: prompt through the tensor-core rows path, decode steps
+    through the one-row step, against the TORCH-mode oracle."""
+    from oracle.torch_mode_oracle import OracleTorchMode
+    from rwkvstic_b200.dense_model import B200DenseRWKV
+    L, D = SHAPES["1b5"]
+    ck = synth_checkpoint(L, D, seed=1234)
+    ref = OracleTorchMode(ck, torch.bfloat16)
+    model = B200DenseRWKV.from_checkpoint(ck, dtype=torch.bfloat16, device=DEV)
+    del ck
+    prompt = synth_tokens(8, seed=22)
+    want, rstate = ref.forward(prompt, ref.emptyState.clone())
+    got, state = model.forward(prompt, model.emptyState.clone())
+    worst = float((got.cpu() - want).abs().max()) / float(want.abs().max())
+    for _ in range(3):
+        tok = int(torch.argmax(want))
+        want, rstate = ref.forward(torch.tensor([tok]), rstate)
+        got, state = model.forward(torch.tensor([tok]), state)
+        worst = max(worst, float((got.cpu() - want).abs().max()) / float(want.abs().max()))
+    model.check_status()
+    print(f"unquantised bf16, 1.5B shape, 24 blocks: worst |dlogit| / max |logit| {worst:.2e}")
+    assert worst <= 8 * 2.0 ** -8, worst      # 24 blocks of products rounded to 8 significant bits each

@@ -62,3 +62,30 @@ def test_full_depth_unquantised_1b5_against_the_oracle():
     model.check_status()
     print(f"unquantised bf16, 1.5B shape, 24 blocks: worst |dlogit| / max |logit| {worst:.2e}")
     assert worst <= 8 * 2.0 ** -8, worst      # 24 blocks of products rounded to 8 significant bits each
+
+
+def test_full_3b_prompt_of_1024_tokens_against_the_oracle():
+    """The 3B shape at full depth, 8 streams x 1024 tokens in sequence mode (tensor-core GEMMs + the
+    chunk-parallel WKV scan over T = 1024): logits after the last token and the final state of two of the
+    streams against the oracle's sequence mode (the streams are independent; the oracle needs about half a
+    minute per stream on the host)."""
+    L, D = SHAPES["3b"]
+    ck = synth_checkpoint(L, D, seed=1234)
+    ref = OracleRWKV(ck)
+    model = B200RWKV.from_checkpoint(ck, device=DEV)
+    del ck
+    B, T = 8, 1024
+    toks = synth_tokens(B * T, seed=33).reshape(B, T)
+    state = model.empty_batch_state(B)
+    out = model.forward_rows(toks.to(DEV), state)
+    model.check_rows_status()
+    worst = 0.0
+    for b in (0, 7):
+        want, wstate = ref.forward(toks[b], ref.emptyState.clone())
+        worst = max(worst, float((out[b].cpu().double() - want).abs().max()))
+        mine = model.to_reference_state(state[b]).cpu()[:, :4]
+        ref4 = wstate[:, :4]
+        excess = (mine - ref4).abs() - (2e-4 + 2e-3 * ref4.abs() + 2e-5 * ref4.abs().amax(dim=2, keepdim=True))
+        assert float(excess.max()) <= 0, (b, int(excess.argmax()))
+    print(f"3B shape, 32 blocks, 8 x 1024 tokens: max |dlogit| {worst:.2e}")
+    assert worst < 2e-3, worst

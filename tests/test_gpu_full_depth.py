@@ -1,8 +1,12 @@
 """Whole networks at their full depth and vocabulary (1.5B shape: 24 blocks, D = 2048; 3B: 32 blocks,
 D = 2560; 7B: 32 blocks, D = 4096; V = 50,277) against the CPU oracle: a short prompt through the rows path,
 then decode steps through the one-row path, logits at every step.  About 25, 30 and 105 seconds, most of it
-the host generating and quantising the weights and the oracle's tokens.  The 14B shape differs in width and
-block count only, which the two-block test at D = 5120 covers; its oracle run would take several minutes."""
+the host generating and quantising the weights and the oracle's tokens.  The 14B shape (40 blocks, D = 5120)
+takes about three minutes, nearly as long as the rest of the GPU suite, and therefore only runs when the
+environment variable B200RWKV_TEST_14B is set to 1 (measured: 5.2e-4); its width is always covered by the
+two-block test at D = 5120."""
+import os
+
 import pytest
 import torch
 
@@ -14,7 +18,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("shape", ["1b5", "3b", "7b"])
+_WITH_14B = os.environ.get("B200RWKV_TEST_14B") == "1"
+
+
+@pytest.mark.parametrize("shape", ["1b5", "3b", "7b", pytest.param(
+    "14b", marks=pytest.mark.skipif(not _WITH_14B, reason="three minutes: set B200RWKV_TEST_14B=1 to run"))])
 def test_full_depth_prompt_and_decode_against_the_oracle(shape):
     L, D = SHAPES[shape]
     ck = synth_checkpoint(L, D, seed=1234)

@@ -540,26 +540,38 @@ static cudaError_t launch_chained(Kernel kernel, dim3 grid, dim3 block, size_t s
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
-static cudaError_t launch_rows_prep(const RowsPrepParams& P, cudaStream_t stream, const char** why) {
+static cudaError_t launch_rows_prep(const RowsPrepParams& P_in, cudaStream_t stream, const char** why) {
   static bool configured[64];
+  static int sm_count[64];
   *why = "rows_prep launch failed";
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    e = cudaFuncSetAttribute(rows_prep_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
+    e = cudaFuncSetAttribute(rows_prep_kernel<256, ROWS_LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<512, ROWS_LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<256, ROWS_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<512, ROWS_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
   }
+  RowsPrepParams P = P_in;
+  rows_prep_grouping(P.nseg, P.K, P.mode, P.R, sm_count[dev], &P.segs_per_cta, &P.rows_per_cta);
   const size_t smem = rows_prep_smem(P.K, P.mode);
-  if (smem > 200 * 1024 || P.R > 65535) {
+  const int groups = (P.R + P.rows_per_cta - 1) / P.rows_per_cta;
+  if (smem > 200 * 1024 || groups > 65535) {
     *why = "unsupported shape: k_in too large for the row preparation kernel, or more than 65535 rows";
     return cudaErrorInvalidValue;
   }
+  const dim3 grid(P.segs_per_cta == 1 ? P.nseg : 1, groups);
+  const bool ln = P.mode == ROWS_LN;
   if (rows_prep_threads(P.K, P.mode) == 256)
-    return launch_chained(rows_prep_kernel<256>, dim3(P.nseg, P.R), dim3(256), smem, stream, P);
-  return launch_chained(rows_prep_kernel<512>, dim3(P.nseg, P.R), dim3(512), smem, stream, P);
+    return ln ? launch_chained(rows_prep_kernel<256, ROWS_LN>, grid, dim3(256), smem, stream, P)
+              : launch_chained(rows_prep_kernel<256, ROWS_PLAIN>, grid, dim3(256), smem, stream, P);
+  return ln ? launch_chained(rows_prep_kernel<512, ROWS_LN>, grid, dim3(512), smem, stream, P)
+            : launch_chained(rows_prep_kernel<512, ROWS_PLAIN>, grid, dim3(512), smem, stream, P);
 }
 
 // Fills the tensor maps of P (weights and digit rows) and launches the tile GEMM.  digits: [nseg][3][Rpad][K].

@@ -459,6 +459,9 @@ struct RowsPrepParams {
   float* commit_dst;
   long long commit_stride;
   int commit_n;
+  // Grouping of the work, filled in by the launcher: a CTA takes one matrix (blockIdx.x) or all of them,
+  // and rows_per_cta consecutive rows from blockIdx.y * rows_per_cta.
+  int segs_per_cta, rows_per_cta;
 };
 
 // Sums of four per-thread values over a CTA of NT threads; every thread gets the totals.
@@ -518,11 +521,161 @@ __device__ __forceinline__ float4 ln_apply(float4 x, float mean, float rstd, flo
                      w.z * ((x.z - mean) * rstd) + b.z, w.w * ((x.w - mean) * rstd) + b.w);
 }
 
-// One activation row per CTA.  REG = true keeps the row in registers (up to G groups of four inputs
-// per thread: one round trip to memory, then the reductions, then the digit stores); REG = false
-// is the any-length variant that re-reads the row and parks xs in shared memory.
-template <int NT, int G, bool REG>
-__device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* red, float4* park) {
+// A CTA prepares rows [blockIdx.y * rows_per_cta, ...) for the matrices of its range (one matrix per
+// blockIdx.x, or all of them), each row held in registers (up to G groups of four inputs per thread).
+// With thousands of rows a CTA walks several consecutive rows: the parameter vectors (layer norm,
+// mix, scale, offset: 5 to 11 vectors of K floats) then come from L1 instead of once per row and
+// matrix from L2, the layer norm of a row is computed once for all matrices, and its result stays in
+// registers as the token-shift carry of the next row.  The arithmetic of a row (which thread holds
+// which input, the order of every reduction) does not depend on how rows and matrices are grouped,
+// so a row's digits and scalars are the same bits in every grouping.
+template <int NT, int G, bool LN>
+__device__ __forceinline__ void rows_prep_span(const RowsPrepParams& P, float* red) {
+  const int tid = threadIdx.x;
+  const int K = P.K, NG = K / 4;
+  const int s0 = P.segs_per_cta == 1 ? int(blockIdx.x) : 0, s1 = P.segs_per_cta == 1 ? s0 + 1 : P.nseg;
+  const int r0 = int(blockIdx.y) * P.rows_per_cta, r1 = min(r0 + P.rows_per_cta, P.R);
+  const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float invk = 1.0f / float(K);
+  bool any_mix = false;
+  if (LN)
+    for (int s = s0; s < s1; ++s) any_mix = any_mix || P.seg[s].mix != nullptr;
+
+  float4 xv[G];               // the row: raw, then its layer norm (LN) or the matrix input (plain)
+  float4 pv[LN ? G : 1];      // token-shift partner: LN of the previous row, or the stream's state row
+  bool have_prev = false;     // pv holds LN(row r-1) from the previous turn of the loop
+
+  for (int r = r0; r < r1; ++r) {
+    const int b = r / P.T, t = r - b * P.T;
+    if (P.commit_n > 0 && s0 == 0 && t == P.T - 1) {
+      const float4* src = reinterpret_cast<const float4*>(P.commit_src + size_t(b) * P.commit_n);
+      float4* dst = reinterpret_cast<float4*>(P.commit_dst + size_t(b) * P.commit_stride);
+      for (int g = tid; g < P.commit_n / 4; g += NT) dst[g] = __ldcg(src + g);
+    }
+    if (LN) {
+      const float4* xr = reinterpret_cast<const float4*>(P.ln_x + size_t(r) * P.ldx);
+      const bool fetch_prev = any_mix && t > 0 && !have_prev;   // first row of this CTA inside a stream
+      const float4* xp = fetch_prev ? reinterpret_cast<const float4*>(P.ln_x + size_t(r - 1) * P.ldx) : nullptr;
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const int g = tid + i * NT;
+        xv[i] = g < NG ? __ldcg(xr + g) : zero4;
+        if (fetch_prev) pv[i] = g < NG ? __ldcg(xp + g) : zero4;
+      }
+      // mean of the row (and of the previous one when it has to be rebuilt), then the sums of squared
+      // deviations: two passes over registers and two block reductions, the centred form of
+      // modules/layernorm.py:11-20 (a single pass with E[x^2] - mean^2 cancels in fp32 when |mean| is
+      // large against the spread)
+      float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < G; ++i)
+        if (tid + i * NT < NG) {
+          s[0] += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
+          if (fetch_prev) s[2] += (pv[i].x + pv[i].y) + (pv[i].z + pv[i].w);
+        }
+      block_sum4<NT>(s, red);
+      const float mean = s[0] * invk, meanp = s[2] * invk;
+      float q[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < G; ++i)
+        if (tid + i * NT < NG) {
+          const float a0 = xv[i].x - mean, a1 = xv[i].y - mean, a2 = xv[i].z - mean, a3 = xv[i].w - mean;
+          q[0] += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+          if (fetch_prev) {
+            const float b0 = pv[i].x - meanp, b1 = pv[i].y - meanp, b2 = pv[i].z - meanp, b3 = pv[i].w - meanp;
+            q[2] += (b0 * b0 + b1 * b1) + (b2 * b2 + b3 * b3);
+          }
+        }
+      block_sum4<NT>(q, red);
+      const float rstd = 1.0f / sqrtf(q[0] * invk + 1e-5f), rstdp = 1.0f / sqrtf(q[2] * invk + 1e-5f);
+      const bool park_carry = s0 == 0 && P.shift_out && t == P.T - 1;
+      const float4* carry = (any_mix && t == 0 && P.shift) ? reinterpret_cast<const float4*>(P.shift + size_t(b) * P.shift_stride) : nullptr;
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const int g = tid + i * NT;
+        if (g < NG) {
+          const float4 w = __ldg(reinterpret_cast<const float4*>(P.ln_w) + g), bb = __ldg(reinterpret_cast<const float4*>(P.ln_b) + g);
+          xv[i] = ln_apply(xv[i], mean, rstd, w, bb);
+          if (park_carry) reinterpret_cast<float4*>(P.shift_out + size_t(b) * K)[g] = xv[i];
+          if (fetch_prev) pv[i] = ln_apply(pv[i], meanp, rstdp, w, bb);
+          else if (any_mix && t == 0) pv[i] = carry ? __ldcg(carry + g) : zero4;
+        }
+      }
+    }
+
+    for (int sidx = s0; sidx < s1; ++sidx) {
+      const PrepSeg& S = P.seg[sidx];
+      const bool mixing = LN && S.mix != nullptr;
+      float4 xs_ln[LN ? G : 1];
+      float4* xs = LN ? xs_ln : xv;   // scaled values: beside the layer-normed row, or in place of the plain input
+      if (!LN) {
+        const float4* xr = reinterpret_cast<const float4*>(S.xin + size_t(r) * P.ldx);
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+          const int g = tid + i * NT;
+          xv[i] = g < NG ? __ldcg(xr + g) : zero4;
+        }
+      }
+      float amax = 0.f, szp = 0.f, sxs = 0.f, sx = 0.f;
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const int g = tid + i * NT;
+        if (g < NG) {
+          float4 v = xv[i];
+          if (mixing) {
+            const float4 xy = xv[i], tc = pv[LN ? i : 0];
+            const float4 mu = __ldg(reinterpret_cast<const float4*>(S.mix) + g);
+            v.x = xy.x * mu.x + tc.x * (1.f - mu.x);
+            v.y = xy.y * mu.y + tc.y * (1.f - mu.y);
+            v.z = xy.z * mu.z + tc.z * (1.f - mu.z);
+            v.w = xy.w * mu.w + tc.w * (1.f - mu.w);
+          }
+          const float4 ry = __ldg(reinterpret_cast<const float4*>(S.ry) + g), my = __ldg(reinterpret_cast<const float4*>(S.my) + g);
+          const float4 y = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
+          amax = fmaxf(amax, fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w))));
+          szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
+          if (P.need_sums) {
+            sxs += (y.x + y.y) + (y.z + y.w);
+            sx += (v.x + v.y) + (v.z + v.w);
+          }
+          xs[i] = y;
+        }
+      }
+      {
+        float st[4] = {amax, szp, sxs, sx};
+        block_stats<NT>(st, red);
+        amax = st[0]; szp = st[1]; sxs = st[2]; sx = st[3];
+      }
+      const float inv = amax > 0.f ? kQMax / amax : 0.f;
+      if (tid == 0) {
+        SegScalars sc;
+        sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;   // IEEE fp32 division, no fp64 on this path
+        sc.zp = szp; sc.sumxs = sxs; sc.sumx = sx;
+        sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
+        P.scal[size_t(sidx) * P.R + r] = sc;
+      }
+      // digit d of row r of matrix s: digits[((s*3 + d) * Rpad + r) * K ...], four inputs per word
+      uint32_t* da = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 0) * P.Rpad + r) * K);
+      uint32_t* db = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 1) * P.Rpad + r) * K);
+      uint32_t* dc = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 2) * P.Rpad + r) * K);
+#pragma unroll
+      for (int i = 0; i < G; ++i) {
+        const int g = tid + i * NT;
+        if (g < NG) rows_store_digits(da, db, dc, g, xs[i], inv);
+      }
+    }
+    if (LN && any_mix) {
+#pragma unroll
+      for (int i = 0; i < G; ++i) pv[LN ? i : 0] = xv[i];
+      have_prev = true;
+    }
+  }
+}
+
+// Rows too long for the registers of a CTA: one row and one matrix per CTA, the row is re-read for
+// every pass and its scaled values are parked in shared memory between the statistics and the digits.
+template <int NT>
+__device__ __forceinline__ void rows_prep_long(const RowsPrepParams& P, float* red, float4* park) {
   const int tid = threadIdx.x;
   const int K = P.K, NG = K / 4;
   const int sidx = blockIdx.x, r = blockIdx.y;
@@ -543,136 +696,123 @@ __device__ __forceinline__ void rows_prep_body(const RowsPrepParams& P, float* r
     float4* dst = reinterpret_cast<float4*>(P.commit_dst + size_t(b) * P.commit_stride);
     for (int g = tid; g < P.commit_n / 4; g += NT) dst[g] = __ldcg(src + g);
   }
-
-  float4 xv[REG ? G : 1], pv[REG ? G : 1];
-  if (REG) {
-#pragma unroll
-    for (int i = 0; i < G; ++i) {
-      const int g = tid + i * NT;
-      xv[i] = g < NG ? __ldcg(xr + g) : zero4;
-      pv[i] = (g < NG && xp) ? __ldcg(xp + g) : ((g < NG && carry) ? __ldcg(carry + g) : zero4);
-    }
-  }
-  auto x_at = [&](int i, int g) -> float4 { return REG ? xv[i] : __ldcg(xr + g); };
-  auto p_at = [&](int i, int g) -> float4 { return REG ? pv[i] : (xp ? __ldcg(xp + g) : (carry ? __ldcg(carry + g) : zero4)); };
+  auto p_at = [&](int g) -> float4 { return xp ? __ldcg(xp + g) : (carry ? __ldcg(carry + g) : zero4); };
 
   float mean = 0.f, rstd = 1.f, meanp = 0.f, rstdp = 1.f;
   if (ln) {
-    // mean of this row and of the previous one, then the sums of squared deviations: two passes over
-    // registers and two block reductions, the centred form of modules/layernorm.py:11-20 (a single
-    // pass with E[x^2] - mean^2 cancels in fp32 when |mean| is large against the spread)
     float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < (REG ? G : 1); ++i)
-      for (int g = tid + i * NT; g < NG; g += REG ? NG : NT) {
-        const float4 x = x_at(i, g);
-        s[0] += (x.x + x.y) + (x.z + x.w);
-        if (xp) {
-          const float4 y = p_at(i, g);
-          s[2] += (y.x + y.y) + (y.z + y.w);
-        }
+    for (int g = tid; g < NG; g += NT) {
+      const float4 x = __ldcg(xr + g);
+      s[0] += (x.x + x.y) + (x.z + x.w);
+      if (xp) {
+        const float4 y = __ldcg(xp + g);
+        s[2] += (y.x + y.y) + (y.z + y.w);
       }
+    }
     block_sum4<NT>(s, red);
     const float invk = 1.0f / float(K);
     mean = s[0] * invk; meanp = s[2] * invk;
     float q[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < (REG ? G : 1); ++i)
-      for (int g = tid + i * NT; g < NG; g += REG ? NG : NT) {
-        const float4 x = x_at(i, g);
-        const float a0 = x.x - mean, a1 = x.y - mean, a2 = x.z - mean, a3 = x.w - mean;
-        q[0] += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
-        if (xp) {
-          const float4 y = p_at(i, g);
-          const float b0 = y.x - meanp, b1 = y.y - meanp, b2 = y.z - meanp, b3 = y.w - meanp;
-          q[2] += (b0 * b0 + b1 * b1) + (b2 * b2 + b3 * b3);
-        }
+    for (int g = tid; g < NG; g += NT) {
+      const float4 x = __ldcg(xr + g);
+      const float a0 = x.x - mean, a1 = x.y - mean, a2 = x.z - mean, a3 = x.w - mean;
+      q[0] += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+      if (xp) {
+        const float4 y = __ldcg(xp + g);
+        const float b0 = y.x - meanp, b1 = y.y - meanp, b2 = y.z - meanp, b3 = y.w - meanp;
+        q[2] += (b0 * b0 + b1 * b1) + (b2 * b2 + b3 * b3);
       }
+    }
     block_sum4<NT>(q, red);
     rstd = 1.0f / sqrtf(q[0] * invk + 1e-5f);
     rstdp = 1.0f / sqrtf(q[2] * invk + 1e-5f);
-    __syncthreads();   // red is reused by the statistics reduction below
   }
 
   float amax = 0.f, szp = 0.f, sxs = 0.f, sx = 0.f;
   const bool last_of_stream = ln && sidx == 0 && P.shift_out && t == P.T - 1;
-#pragma unroll
-  for (int i = 0; i < (REG ? G : 1); ++i)
-    for (int g = tid + i * NT; g < NG; g += REG ? NG : NT) {
-      float4 v = x_at(i, g);
-      if (ln) {
-        const float4 w = __ldg(reinterpret_cast<const float4*>(P.ln_w) + g), bb = __ldg(reinterpret_cast<const float4*>(P.ln_b) + g);
-        const float4 xy = ln_apply(v, mean, rstd, w, bb);
-        if (last_of_stream) reinterpret_cast<float4*>(P.shift_out + size_t(b) * K)[g] = xy;
-        v = xy;
-        if (mixing) {
-          float4 tc = p_at(i, g);
-          if (xp) tc = ln_apply(tc, meanp, rstdp, w, bb);
-          const float4 mu = __ldg(reinterpret_cast<const float4*>(S.mix) + g);
-          v.x = xy.x * mu.x + tc.x * (1.f - mu.x);
-          v.y = xy.y * mu.y + tc.y * (1.f - mu.y);
-          v.z = xy.z * mu.z + tc.z * (1.f - mu.z);
-          v.w = xy.w * mu.w + tc.w * (1.f - mu.w);
-        }
+  for (int g = tid; g < NG; g += NT) {
+    float4 v = __ldcg(xr + g);
+    if (ln) {
+      const float4 w = __ldg(reinterpret_cast<const float4*>(P.ln_w) + g), bb = __ldg(reinterpret_cast<const float4*>(P.ln_b) + g);
+      const float4 xy = ln_apply(v, mean, rstd, w, bb);
+      if (last_of_stream) reinterpret_cast<float4*>(P.shift_out + size_t(b) * K)[g] = xy;
+      v = xy;
+      if (mixing) {
+        float4 tc = p_at(g);
+        if (xp) tc = ln_apply(tc, meanp, rstdp, w, bb);
+        const float4 mu = __ldg(reinterpret_cast<const float4*>(S.mix) + g);
+        v.x = xy.x * mu.x + tc.x * (1.f - mu.x);
+        v.y = xy.y * mu.y + tc.y * (1.f - mu.y);
+        v.z = xy.z * mu.z + tc.z * (1.f - mu.z);
+        v.w = xy.w * mu.w + tc.w * (1.f - mu.w);
       }
-      const float4 ry = __ldg(reinterpret_cast<const float4*>(S.ry) + g), my = __ldg(reinterpret_cast<const float4*>(S.my) + g);
-      const float4 xs = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
-      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xs.x), fabsf(xs.y)), fmaxf(fabsf(xs.z), fabsf(xs.w))));
-      szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
-      if (P.need_sums) {
-        sxs += (xs.x + xs.y) + (xs.z + xs.w);
-        sx += (v.x + v.y) + (v.z + v.w);
-      }
-      if (REG) xv[i] = xs; else park[g] = xs;
     }
+    const float4 ry = __ldg(reinterpret_cast<const float4*>(S.ry) + g), my = __ldg(reinterpret_cast<const float4*>(S.my) + g);
+    const float4 xs = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
+    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(xs.x), fabsf(xs.y)), fmaxf(fabsf(xs.z), fabsf(xs.w))));
+    szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
+    if (P.need_sums) {
+      sxs += (xs.x + xs.y) + (xs.z + xs.w);
+      sx += (v.x + v.y) + (v.z + v.w);
+    }
+    park[g] = xs;
+  }
   {
     float st[4] = {amax, szp, sxs, sx};
     block_stats<NT>(st, red);
     amax = st[0]; szp = st[1]; sxs = st[2]; sx = st[3];
   }
-
   const float inv = amax > 0.f ? kQMax / amax : 0.f;
   if (tid == 0) {
     SegScalars sc;
-    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;   // IEEE fp32 division, no fp64 on this path
+    sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;
     sc.zp = szp; sc.sumxs = sxs; sc.sumx = sx;
     sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
     P.scal[size_t(sidx) * P.R + r] = sc;
   }
-  // digit d of row r of matrix s: digits[((s*3 + d) * Rpad + r) * K ...], four inputs per word
   uint32_t* da = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 0) * P.Rpad + r) * K);
   uint32_t* db = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 1) * P.Rpad + r) * K);
   uint32_t* dc = reinterpret_cast<uint32_t*>(P.digits + (size_t(sidx * kDigits + 2) * P.Rpad + r) * K);
-#pragma unroll
-  for (int i = 0; i < (REG ? G : 1); ++i)
-    for (int g = tid + i * NT; g < NG; g += REG ? NG : NT)
-      rows_store_digits(da, db, dc, g, REG ? xv[i] : park[g], inv);
+  for (int g = tid; g < NG; g += NT) rows_store_digits(da, db, dc, g, park[g], inv);
 }
 
-// 256 threads per row while the row fits their registers (more rows in flight per SM: the kernel is
-// a chain of load -> reduce -> reduce -> store per row), 512 threads for longer rows.
-template <int NT>
-__global__ void __launch_bounds__(NT, NT == 256 ? 4 : 2) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
+// Register-resident rows: up to 4 groups of four inputs per thread with the layer norm (row, carry and
+// scaled values live at once), 8 without.  256 threads while a row fits, else 512.
+constexpr int kRowsPrepGroupsLn = 4, kRowsPrepGroupsPlain = 8;
+constexpr int rows_prep_min_ctas(int NT, int mode) { return mode == ROWS_LN ? (NT == 256 ? 3 : 1) : (NT == 256 ? 4 : 2); }
+
+template <int NT, int MODE>
+__global__ void __launch_bounds__(NT, rows_prep_min_ctas(NT, MODE)) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
   extern __shared__ __align__(128) unsigned char prep_smem[];
   float* red = reinterpret_cast<float*>(prep_smem);
   float4* park = reinterpret_cast<float4*>(prep_smem + kPrepRedBytes);
   griddep_launch_dependents();
   griddep_wait();
-  const int NG = P.K / 4;
-  if (P.mode == ROWS_LN) {
-    if (NG <= 4 * NT) rows_prep_body<NT, 4, true>(P, red, park);
-    else rows_prep_body<NT, 1, false>(P, red, park);
-  } else {
-    if (NG <= 8 * NT) rows_prep_body<NT, 8, true>(P, red, park);
-    else rows_prep_body<NT, 1, false>(P, red, park);
-  }
+  constexpr int G = MODE == ROWS_LN ? kRowsPrepGroupsLn : kRowsPrepGroupsPlain;
+  if (P.K / 4 <= G * NT) rows_prep_span<NT, G, MODE == ROWS_LN>(P, red);
+  else rows_prep_long<NT>(P, red, park);
 }
 
-inline int rows_prep_threads(int K, int mode) { return K / 4 <= (mode == ROWS_LN ? 4 : 8) * 256 ? 256 : 512; }
+inline bool rows_prep_in_regs(int K, int mode, int threads) {
+  return K / 4 <= (mode == ROWS_LN ? kRowsPrepGroupsLn : kRowsPrepGroupsPlain) * threads;
+}
+inline int rows_prep_threads(int K, int mode) { return rows_prep_in_regs(K, mode, 256) ? 256 : 512; }
 
 // Shared memory: the reduction scratch, plus 4*K bytes of parked xs when the row does not fit the registers.
 inline size_t rows_prep_smem(int K, int mode) {
-  const bool in_regs = K / 4 <= (mode == ROWS_LN ? 4 : 8) * rows_prep_threads(K, mode);
-  return size_t(kPrepRedBytes) + (in_regs ? 0 : size_t(4) * K);
+  return size_t(kPrepRedBytes) + (rows_prep_in_regs(K, mode, rows_prep_threads(K, mode)) ? 0 : size_t(4) * K);
+}
+
+// How a launch groups its work: while one CTA per (matrix, row) does not fill the GPU twice over, keep
+// that (shortest chain per CTA); beyond, one CTA takes all matrices of ceil(R / resident CTAs) consecutive
+// rows, so that the whole launch is one wave.
+inline void rows_prep_grouping(int nseg, int K, int mode, int R, int sms, int* segs_per_cta, int* rows_per_cta) {
+  *segs_per_cta = 1; *rows_per_cta = 1;
+  const int threads = rows_prep_threads(K, mode);
+  if (!rows_prep_in_regs(K, mode, threads)) return;
+  const long long slots = (long long)sms * rows_prep_min_ctas(threads, mode);
+  if ((long long)nseg * R <= 2 * slots) return;
+  *segs_per_cta = nseg;
+  *rows_per_cta = int((R + slots - 1) / slots);
 }
 }  // namespace b200

@@ -258,3 +258,23 @@ def test_rows_path_agrees_with_one_row_path_at_the_1b5_shape():
     lg64 = model.forward_rows(tok, st64)
     assert bool((lg64 == lg64[0]).all())
     model.check_status()
+
+
+def test_row_preparation_gives_the_same_bits_however_rows_are_grouped():
+    """With thousands of rows a preparation CTA walks several consecutive rows for all matrices and keeps the
+    layer norm of a row as the next row's token-shift partner; with few rows there is one CTA per (matrix, row).
+    Six streams of 280 tokens in one call (1680 rows: groups of four rows that straddle the stream boundaries)
+    must give exactly the logits and states of the same streams run one per call (280 rows: one CTA per row)."""
+    model = B200RWKV.synthetic(2, 512, vocab=1000, seed=9, device=DEV)
+    B, T = 6, 280
+    toks = synth_tokens(B * T, seed=44, vocab=1000).reshape(B, T)
+    start = model.empty_batch_state(B)
+    start[:, :, :2] = torch.randn(B, model.n_layer, 2, model.n_embd, device=DEV)      # token-shift carries in use
+    st_all = start.clone()
+    lg_all = model.forward_rows(toks, st_all)
+    for b in range(B):
+        st = start[b:b + 1].clone()
+        lg = model.forward_rows(toks[b:b + 1], st)
+        assert torch.equal(lg[0], lg_all[b]), b
+        assert torch.equal(st[0], st_all[b]), b
+    model.check_status()

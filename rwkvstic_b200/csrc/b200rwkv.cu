@@ -540,6 +540,11 @@ static cudaError_t launch_chained(Kernel kernel, dim3 grid, dim3 block, size_t s
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+template <int NT, int MODE, int G>
+static cudaError_t launch_rows_prep_as(const RowsPrepParams& P, dim3 grid, size_t smem, cudaStream_t stream) {
+  return launch_chained(rows_prep_kernel<NT, MODE, G>, grid, dim3(NT), smem, stream, P);
+}
+
 static cudaError_t launch_rows_prep(const RowsPrepParams& P_in, cudaStream_t stream, const char** why) {
   static bool configured[64];
   static int sm_count[64];
@@ -549,10 +554,7 @@ static cudaError_t launch_rows_prep(const RowsPrepParams& P_in, cudaStream_t str
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
   if (!configured[dev]) {
-    e = cudaFuncSetAttribute(rows_prep_kernel<256, ROWS_LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<512, ROWS_LN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<256, ROWS_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(rows_prep_kernel<512, ROWS_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    e = cudaFuncSetAttribute(rows_prep_long_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
     configured[dev] = true;
@@ -567,11 +569,31 @@ static cudaError_t launch_rows_prep(const RowsPrepParams& P_in, cudaStream_t str
   }
   const dim3 grid(P.segs_per_cta == 1 ? P.nseg : 1, groups);
   const bool ln = P.mode == ROWS_LN;
-  if (rows_prep_threads(P.K, P.mode) == 256)
-    return ln ? launch_chained(rows_prep_kernel<256, ROWS_LN>, grid, dim3(256), smem, stream, P)
-              : launch_chained(rows_prep_kernel<256, ROWS_PLAIN>, grid, dim3(256), smem, stream, P);
-  return ln ? launch_chained(rows_prep_kernel<512, ROWS_LN>, grid, dim3(512), smem, stream, P)
-            : launch_chained(rows_prep_kernel<512, ROWS_PLAIN>, grid, dim3(512), smem, stream, P);
+  const int threads = rows_prep_threads(P.K, P.mode);
+  if (!rows_prep_in_regs(P.K, P.mode, threads)) return launch_chained(rows_prep_long_kernel, grid, dim3(512), smem, stream, P);
+  const int G = rows_prep_groups(P.K, threads);
+  if (ln) {
+    if (threads == 256) switch (G) {
+      case 1: return launch_rows_prep_as<256, ROWS_LN, 1>(P, grid, smem, stream);
+      case 2: return launch_rows_prep_as<256, ROWS_LN, 2>(P, grid, smem, stream);
+      case 3: return launch_rows_prep_as<256, ROWS_LN, 3>(P, grid, smem, stream);
+      default: return launch_rows_prep_as<256, ROWS_LN, 4>(P, grid, smem, stream);
+    }
+    return G <= 3 ? launch_rows_prep_as<512, ROWS_LN, 3>(P, grid, smem, stream) : launch_rows_prep_as<512, ROWS_LN, 4>(P, grid, smem, stream);
+  }
+  if (threads == 256) switch (G) {
+    case 1: return launch_rows_prep_as<256, ROWS_PLAIN, 1>(P, grid, smem, stream);
+    case 2: return launch_rows_prep_as<256, ROWS_PLAIN, 2>(P, grid, smem, stream);
+    case 3: return launch_rows_prep_as<256, ROWS_PLAIN, 3>(P, grid, smem, stream);
+    case 4: return launch_rows_prep_as<256, ROWS_PLAIN, 4>(P, grid, smem, stream);
+    case 5: case 6: return launch_rows_prep_as<256, ROWS_PLAIN, 6>(P, grid, smem, stream);
+    default: return launch_rows_prep_as<256, ROWS_PLAIN, 8>(P, grid, smem, stream);
+  }
+  switch (G) {
+    case 5: return launch_rows_prep_as<512, ROWS_PLAIN, 5>(P, grid, smem, stream);
+    case 6: return launch_rows_prep_as<512, ROWS_PLAIN, 6>(P, grid, smem, stream);
+    default: return launch_rows_prep_as<512, ROWS_PLAIN, 8>(P, grid, smem, stream);
+  }
 }
 
 // Fills the tensor maps of P (weights and digit rows) and launches the tile GEMM.  digits: [nseg][3][Rpad][K].

@@ -504,8 +504,9 @@ __device__ __forceinline__ void rows_store_digits(uint32_t* da, uint32_t* db, ui
   uint32_t y[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const int mag = rint_nonneg(__fmul_rn(fabsf(v[i]), inv));
-    const int X = v[i] < 0.f ? -mag : mag;
+    // round to nearest even of the fp32 product, sign included (|v * inv| <= kQMax < 2^23): one conversion
+    // instead of the five instructions of the magnitude-and-sign form, same integer
+    const int X = __float2int_rn(__fmul_rn(v[i], inv));
     y[i] = uint32_t(X + 0x8080) ^ 0x8080u;   // bytes: (c, b, a, sign extension)
   }
   const uint32_t c01 = __byte_perm(y[0], y[1], 0x0040), c23 = __byte_perm(y[2], y[3], 0x0040);
@@ -521,14 +522,45 @@ __device__ __forceinline__ float4 ln_apply(float4 x, float mean, float rstd, flo
                      w.z * ((x.z - mean) * rstd) + b.z, w.w * ((x.w - mean) * rstd) + b.w);
 }
 
+// Totals of NV per-thread values over a CTA of NT threads, in every thread: sums, except that v[0] is a
+// maximum when MAX0.  Warp butterflies, one float4 slot per warp in shared memory, one barrier: the
+// slots alternate between two buffers (phase), so the next reduction cannot overwrite partials that
+// a slower warp is still reading.
+template <int NT, int NV, bool MAX0>
+__device__ __forceinline__ void span_reduce(float (&v)[NV], float* red, int& phase) {
+  constexpr int NW = NT / 32;
+  static_assert(NV <= 4 && (NW == 8 || NW == 16), "one float4 slot per warp, 8 or 16 warps");
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) v[k] = (MAX0 && k == 0) ? warp_max(v[k]) : warp_sum(v[k]);
+  float* slots = red + phase * (NW * 4);
+  phase ^= 1;
+  if (lane == 0) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) slots[warp * 4 + k] = v[k];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    float t = slots[(lane & (NW - 1)) * 4 + k];   // every aligned group of NW lanes holds all partials
+#pragma unroll
+    for (int o = NW / 2; o > 0; o >>= 1) {
+      const float u = __shfl_xor_sync(0xffffffffu, t, o);
+      t = (MAX0 && k == 0) ? fmaxf(t, u) : t + u;
+    }
+    v[k] = t;
+  }
+}
+
 // A CTA prepares rows [blockIdx.y * rows_per_cta, ...) for the matrices of its range (one matrix per
 // blockIdx.x, or all of them), each row held in registers (up to G groups of four inputs per thread).
-// With thousands of rows a CTA walks several consecutive rows: the parameter vectors (layer norm,
-// mix, scale, offset: 5 to 11 vectors of K floats) then come from L1 instead of once per row and
-// matrix from L2, the layer norm of a row is computed once for all matrices, and its result stays in
-// registers as the token-shift carry of the next row.  The arithmetic of a row (which thread holds
-// which input, the order of every reduction) does not depend on how rows and matrices are grouped,
-// so a row's digits and scalars are the same bits in every grouping.
+// With thousands of rows a CTA walks several consecutive rows: the layer norm of a row is computed
+// once for all matrices, its result stays in registers as the token-shift carry of the next row, and
+// the parameter vectors come from L1.  The kernel is bound by instruction issue, so groups beyond the
+// row's end are skipped by a CTA-uniform test and the reductions carry only the values in use.
+// The arithmetic of a row (which thread holds which input, the order of every reduction) does not
+// depend on how rows and matrices are grouped, so a row's digits and scalars are the same bits in
+// every grouping.
 template <int NT, int G, bool LN>
 __device__ __forceinline__ void rows_prep_span(const RowsPrepParams& P, float* red) {
   const int tid = threadIdx.x;
@@ -537,6 +569,8 @@ __device__ __forceinline__ void rows_prep_span(const RowsPrepParams& P, float* r
   const int r0 = int(blockIdx.y) * P.rows_per_cta, r1 = min(r0 + P.rows_per_cta, P.R);
   const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
   const float invk = 1.0f / float(K);
+  const bool sums = P.need_sums != 0;
+  int phase = 0;
   bool any_mix = false;
   if (LN)
     for (int s = s0; s < s1; ++s) any_mix = any_mix || P.seg[s].mix != nullptr;
@@ -557,25 +591,27 @@ __device__ __forceinline__ void rows_prep_span(const RowsPrepParams& P, float* r
       const bool fetch_prev = any_mix && t > 0 && !have_prev;   // first row of this CTA inside a stream
       const float4* xp = fetch_prev ? reinterpret_cast<const float4*>(P.ln_x + size_t(r - 1) * P.ldx) : nullptr;
 #pragma unroll
-      for (int i = 0; i < G; ++i) {
-        const int g = tid + i * NT;
-        xv[i] = g < NG ? __ldcg(xr + g) : zero4;
-        if (fetch_prev) pv[i] = g < NG ? __ldcg(xp + g) : zero4;
-      }
+      for (int i = 0; i < G; ++i)
+        if (i * NT < NG) {
+          const int g = tid + i * NT;
+          xv[i] = g < NG ? __ldcg(xr + g) : zero4;
+          if (fetch_prev) pv[i] = g < NG ? __ldcg(xp + g) : zero4;
+        }
       // mean of the row (and of the previous one when it has to be rebuilt), then the sums of squared
-      // deviations: two passes over registers and two block reductions, the centred form of
+      // deviations: two passes over registers and two reductions, the centred form of
       // modules/layernorm.py:11-20 (a single pass with E[x^2] - mean^2 cancels in fp32 when |mean| is
       // large against the spread)
-      float s[4] = {0.f, 0.f, 0.f, 0.f};
+      float s[2] = {0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < G; ++i)
-        if (tid + i * NT < NG) {
-          s[0] += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);
-          if (fetch_prev) s[2] += (pv[i].x + pv[i].y) + (pv[i].z + pv[i].w);
+        if (i * NT < NG) {
+          s[0] += (xv[i].x + xv[i].y) + (xv[i].z + xv[i].w);     // groups past the end hold zeros
+          if (fetch_prev) s[1] += (pv[i].x + pv[i].y) + (pv[i].z + pv[i].w);
         }
-      block_sum4<NT>(s, red);
-      const float mean = s[0] * invk, meanp = s[2] * invk;
-      float q[4] = {0.f, 0.f, 0.f, 0.f};
+      if (fetch_prev) span_reduce<NT, 2, false>(s, red, phase);
+      else { float s1v[1] = {s[0]}; span_reduce<NT, 1, false>(s1v, red, phase); s[0] = s1v[0]; }
+      const float mean = s[0] * invk, meanp = s[1] * invk;
+      float q[2] = {0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < G; ++i)
         if (tid + i * NT < NG) {
@@ -583,11 +619,12 @@ __device__ __forceinline__ void rows_prep_span(const RowsPrepParams& P, float* r
           q[0] += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
           if (fetch_prev) {
             const float b0 = pv[i].x - meanp, b1 = pv[i].y - meanp, b2 = pv[i].z - meanp, b3 = pv[i].w - meanp;
-            q[2] += (b0 * b0 + b1 * b1) + (b2 * b2 + b3 * b3);
+            q[1] += (b0 * b0 + b1 * b1) + (b2 * b2 + b3 * b3);
           }
         }
-      block_sum4<NT>(q, red);
-      const float rstd = 1.0f / sqrtf(q[0] * invk + 1e-5f), rstdp = 1.0f / sqrtf(q[2] * invk + 1e-5f);
+      if (fetch_prev) span_reduce<NT, 2, false>(q, red, phase);
+      else { float q1v[1] = {q[0]}; span_reduce<NT, 1, false>(q1v, red, phase); q[0] = q1v[0]; }
+      const float rstd = 1.0f / sqrtf(q[0] * invk + 1e-5f), rstdp = 1.0f / sqrtf(q[1] * invk + 1e-5f);
       const bool park_carry = s0 == 0 && P.shift_out && t == P.T - 1;
       const float4* carry = (any_mix && t == 0 && P.shift) ? reinterpret_cast<const float4*>(P.shift + size_t(b) * P.shift_stride) : nullptr;
 #pragma unroll
@@ -613,10 +650,10 @@ __device__ __forceinline__ void rows_prep_span(const RowsPrepParams& P, float* r
 #pragma unroll
         for (int i = 0; i < G; ++i) {
           const int g = tid + i * NT;
-          xv[i] = g < NG ? __ldcg(xr + g) : zero4;
+          if (g < NG) xv[i] = __ldcg(xr + g);
         }
       }
-      float amax = 0.f, szp = 0.f, sxs = 0.f, sx = 0.f;
+      float st[4] = {0.f, 0.f, 0.f, 0.f};   // max |xs|, sum v*my, sum xs, sum v
 #pragma unroll
       for (int i = 0; i < G; ++i) {
         const int g = tid + i * NT;
@@ -632,25 +669,23 @@ __device__ __forceinline__ void rows_prep_span(const RowsPrepParams& P, float* r
           }
           const float4 ry = __ldg(reinterpret_cast<const float4*>(S.ry) + g), my = __ldg(reinterpret_cast<const float4*>(S.my) + g);
           const float4 y = make_float4(v.x * ry.x, v.y * ry.y, v.z * ry.z, v.w * ry.w);
-          amax = fmaxf(amax, fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w))));
-          szp += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
-          if (P.need_sums) {
-            sxs += (y.x + y.y) + (y.z + y.w);
-            sx += (v.x + v.y) + (v.z + v.w);
+          st[0] = fmaxf(st[0], fmaxf(fmaxf(fabsf(y.x), fabsf(y.y)), fmaxf(fabsf(y.z), fabsf(y.w))));
+          st[1] += (v.x * my.x + v.y * my.y) + (v.z * my.z + v.w * my.w);
+          if (sums) {
+            st[2] += (y.x + y.y) + (y.z + y.w);
+            st[3] += (v.x + v.y) + (v.z + v.w);
           }
           xs[i] = y;
         }
       }
-      {
-        float st[4] = {amax, szp, sxs, sx};
-        block_stats<NT>(st, red);
-        amax = st[0]; szp = st[1]; sxs = st[2]; sx = st[3];
-      }
+      if (sums) span_reduce<NT, 4, true>(st, red, phase);
+      else { float st2[2] = {st[0], st[1]}; span_reduce<NT, 2, true>(st2, red, phase); st[0] = st2[0]; st[1] = st2[1]; }
+      const float amax = st[0];
       const float inv = amax > 0.f ? kQMax / amax : 0.f;
       if (tid == 0) {
         SegScalars sc;
         sc.sd = amax > 0.f ? __fdiv_rn(1.0f, inv) : 0.f;   // IEEE fp32 division, no fp64 on this path
-        sc.zp = szp; sc.sumxs = sxs; sc.sumx = sx;
+        sc.zp = st[1]; sc.sumxs = st[2]; sc.sumx = st[3];
         sc.pad[0] = sc.pad[1] = sc.pad[2] = sc.pad[3] = 0.f;
         P.scal[size_t(sidx) * P.R + r] = sc;
       }
@@ -777,26 +812,35 @@ __device__ __forceinline__ void rows_prep_long(const RowsPrepParams& P, float* r
 }
 
 // Register-resident rows: up to 4 groups of four inputs per thread with the layer norm (row, carry and
-// scaled values live at once), 8 without.  256 threads while a row fits, else 512.
+// scaled values live at once), 8 without; the kernel is instantiated for the exact number of groups a
+// row needs (fewer registers, more resident CTAs).  256 threads while a row fits, else 512.
 constexpr int kRowsPrepGroupsLn = 4, kRowsPrepGroupsPlain = 8;
-constexpr int rows_prep_min_ctas(int NT, int mode) { return mode == ROWS_LN ? (NT == 256 ? 3 : 1) : (NT == 256 ? 4 : 2); }
+constexpr int rows_prep_min_ctas(int NT, int mode, int G) {
+  return mode == ROWS_LN ? (NT == 256 ? (G <= 2 ? 5 : G == 3 ? 4 : 3) : (G <= 3 ? 2 : 1))
+                         : (NT == 256 ? (G <= 4 ? 5 : 4) : 2);
+}
 
-template <int NT, int MODE>
-__global__ void __launch_bounds__(NT, rows_prep_min_ctas(NT, MODE)) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
+template <int NT, int MODE, int G>
+__global__ void __launch_bounds__(NT, rows_prep_min_ctas(NT, MODE, G)) rows_prep_kernel(const __grid_constant__ RowsPrepParams P) {
   extern __shared__ __align__(128) unsigned char prep_smem[];
-  float* red = reinterpret_cast<float*>(prep_smem);
-  float4* park = reinterpret_cast<float4*>(prep_smem + kPrepRedBytes);
   griddep_launch_dependents();
   griddep_wait();
-  constexpr int G = MODE == ROWS_LN ? kRowsPrepGroupsLn : kRowsPrepGroupsPlain;
-  if (P.K / 4 <= G * NT) rows_prep_span<NT, G, MODE == ROWS_LN>(P, red);
-  else rows_prep_long<NT>(P, red, park);
+  rows_prep_span<NT, G, MODE == ROWS_LN>(P, reinterpret_cast<float*>(prep_smem));
+}
+
+// Rows beyond the registers: one CTA of 512 threads per (matrix, row).
+__global__ void __launch_bounds__(512, 2) rows_prep_long_kernel(const __grid_constant__ RowsPrepParams P) {
+  extern __shared__ __align__(128) unsigned char prep_smem[];
+  griddep_launch_dependents();
+  griddep_wait();
+  rows_prep_long<512>(P, reinterpret_cast<float*>(prep_smem), reinterpret_cast<float4*>(prep_smem + kPrepRedBytes));
 }
 
 inline bool rows_prep_in_regs(int K, int mode, int threads) {
   return K / 4 <= (mode == ROWS_LN ? kRowsPrepGroupsLn : kRowsPrepGroupsPlain) * threads;
 }
 inline int rows_prep_threads(int K, int mode) { return rows_prep_in_regs(K, mode, 256) ? 256 : 512; }
+inline int rows_prep_groups(int K, int threads) { return (K / 4 + threads - 1) / threads; }
 
 // Shared memory: the reduction scratch, plus 4*K bytes of parked xs when the row does not fit the registers.
 inline size_t rows_prep_smem(int K, int mode) {
@@ -810,7 +854,7 @@ inline void rows_prep_grouping(int nseg, int K, int mode, int R, int sms, int* s
   *segs_per_cta = 1; *rows_per_cta = 1;
   const int threads = rows_prep_threads(K, mode);
   if (!rows_prep_in_regs(K, mode, threads)) return;
-  const long long slots = (long long)sms * rows_prep_min_ctas(threads, mode);
+  const long long slots = (long long)sms * rows_prep_min_ctas(threads, mode, rows_prep_groups(K, threads));
   if ((long long)nseg * R <= 2 * slots) return;
   *segs_per_cta = nseg;
   *rows_per_cta = int((R + slots - 1) / slots);

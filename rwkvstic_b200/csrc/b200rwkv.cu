@@ -1902,12 +1902,20 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
   cudaError_t e;
   g_chain_rows = R <= 1024;
   static bool prep_configured[64];
+  static int prep_sms[64];
   int dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !prep_configured[dev]) {
-    if (cudaFuncSetAttribute(dense_rows_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDsMaxEmbd * 4) != cudaSuccess)
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(B200RWKV_ECUDA, "dense_forward_rows: no current device");
+  if (!prep_configured[dev]) {
+    if (cudaFuncSetAttribute(dense_rows_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kDsMaxEmbd * 4) != cudaSuccess ||
+        cudaDeviceGetAttribute(&prep_sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
       return fail(B200RWKV_ECUDA, "dense_forward_rows: cannot size the preparation kernel's shared memory");
     prep_configured[dev] = true;
   }
+  // preparation CTAs resident at once (registers, and two rows of shared memory each)
+  int prep_per_sm = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&prep_per_sm, dense_rows_prep_kernel, 256, size_t(2) * D * 4) != cudaSuccess || prep_per_sm < 1)
+    prep_per_sm = 1;
+  const int prep_slots = prep_sms[dev] * prep_per_sm;
 #define B200_DR_CHECK(call, what)                                                                      \
   do {                                                                                                 \
     e = (call);                                                                                        \
@@ -1928,7 +1936,10 @@ int b200rwkv_dense_forward_rows_layers(const b200rwkv_dense_model* m, int layer_
     Q.carry_out_stride = T == 1 ? state_stride : D;
     Q.nmix = nmix; Q.D = D; Q.Tn = T; Q.last_only = last_only; Q.is_bf16 = bf;
     for (int i = 0; i < (nmix > 0 ? nmix : 1); ++i) { Q.mix[i] = mix ? mix[i] : nullptr; Q.out[i] = out[i]; }
-    return launch_chained(dense_rows_prep_kernel, dim3(last_only ? B : R), dim3(256), size_t(2) * D * 4, s, Q);
+    // one row per CTA while that fits the GPU at once; beyond, a CTA walks consecutive rows and takes each layer norm once
+    Q.R = last_only ? B : R;
+    Q.rows_per_cta = (Q.R + prep_slots - 1) / prep_slots;
+    return launch_chained(dense_rows_prep_kernel, dim3((Q.R + Q.rows_per_cta - 1) / Q.rows_per_cta), dim3(256), size_t(2) * D * 4, s, Q);
   };
   auto commit = [&](float* row) -> cudaError_t {      // parked layer norm of every stream's last row -> its state row
     if (T == 1) return cudaSuccess;                    // one row per stream: the preparation kernel wrote the state row itself

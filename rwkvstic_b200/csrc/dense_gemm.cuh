@@ -333,9 +333,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) dense_tile_gemm_kernel(const 
 }
 
 // ---- rows in front of the GEMMs ---------------------------------------------------------------------
-// One CTA per activation row r (stream r / Tn, position r % Tn): layer norm of x[r]; the token-shift
-// carry is the stream's state row for its first row and the layer norm of x[r - 1] otherwise
-// (agnosticRwkv.py:125-127: roll + push); out[m][r] = T(lerp(carry, ln, mix[m])).  The layer norm of
+// A CTA takes rows_per_cta consecutive activation rows (row r: stream r / Tn, position r % Tn): layer
+// norm of x[r]; the token-shift carry is the stream's state row for its first row and the layer norm of
+// x[r - 1] otherwise (agnosticRwkv.py:125-127: roll + push); out[m][r] = T(lerp(carry, ln, mix[m])).
+// Walking consecutive rows, the CTA already holds the layer norm of x[r - 1] from its previous turn (the
+// two shared-memory rows swap roles) and only rebuilds it for the first row it takes; a row's arithmetic
+// is the same either way.  The layer norm of
 // every stream's last row is the stream's next carry: with one row per stream the CTA that read the
 // state row writes it back itself; with more rows it is parked in a scratch row that the caller copies
 // to the state once this launch is over (sibling CTAs still read the old row).
@@ -351,6 +354,7 @@ struct DRowsPrepParams {
   const float* mix[3];
   void* out[3];              // T [Rpad][D]
   int nmix, D, Tn, last_only, is_bf16, is_f32;
+  int R, rows_per_cta;       // rows of the call (streams with last_only); consecutive rows per CTA
 };
 
 __global__ void __launch_bounds__(256)
@@ -360,8 +364,6 @@ dense_rows_prep_kernel(const DRowsPrepParams P) {
   griddep_launch_dependents();
   griddep_wait();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, D = P.D, D4 = P.D >> 2;
-  const int r = P.last_only ? (blockIdx.x + 1) * P.Tn - 1 : blockIdx.x;
-  const int pos = r % P.Tn, stream = r / P.Tn;
   auto block_sum = [&](float v) -> float {
     v = warp_sum(v);
     __syncthreads();
@@ -393,39 +395,45 @@ dense_rows_prep_kernel(const DRowsPrepParams P) {
   };
   float* cur = rp_smem;
   float* prev = rp_smem + D;
-  layer_norm(P.x + size_t(r) * D, cur);
   const bool shift = !P.last_only && P.nmix > 0;
-  if (shift) {
-    if (pos == 0) {
-      const float4* c4 = reinterpret_cast<const float4*>(P.carry + size_t(stream) * P.carry_stride);
-      for (int i = tid; i < D4; i += 256) reinterpret_cast<float4*>(prev)[i] = __ldcg(c4 + i);
-    } else {
-      layer_norm(P.x + size_t(r - 1) * D, prev);
+  const int first = blockIdx.x * P.rows_per_cta, end = min(first + P.rows_per_cta, P.R);
+  for (int idx = first; idx < end; ++idx) {
+    const int r = P.last_only ? (idx + 1) * P.Tn - 1 : idx;
+    const int pos = r % P.Tn, stream = r / P.Tn;
+    if (idx > first) { float* t = cur; cur = prev; prev = t; }     // prev now holds the layer norm of row r - 1
+    layer_norm(P.x + size_t(r) * D, cur);
+    if (shift) {
+      if (pos == 0) {
+        const float4* c4 = reinterpret_cast<const float4*>(P.carry + size_t(stream) * P.carry_stride);
+        for (int i = tid; i < D4; i += 256) reinterpret_cast<float4*>(prev)[i] = __ldcg(c4 + i);
+      } else if (idx == first) {
+        layer_norm(P.x + size_t(r - 1) * D, prev);
+      }
+      if (pos == P.Tn - 1 && P.carry_out)
+        for (int i = tid; i < D4; i += 256) reinterpret_cast<float4*>(P.carry_out + size_t(stream) * P.carry_out_stride)[i] = reinterpret_cast<const float4*>(cur)[i];
     }
-    if (pos == P.Tn - 1 && P.carry_out)
-      for (int i = tid; i < D4; i += 256) reinterpret_cast<float4*>(P.carry_out + size_t(stream) * P.carry_out_stride)[i] = reinterpret_cast<const float4*>(cur)[i];
-  }
-  const size_t orow = size_t(blockIdx.x) * D;
-  auto store4 = [&](void* out, int i, float a, float b, float c, float d) {
-    if (P.is_f32) {
-      reinterpret_cast<float4*>(static_cast<float*>(out) + orow)[i] = make_float4(a, b, c, d);
+    const size_t orow = size_t(idx) * D;
+    auto store4 = [&](void* out, int i, float a, float b, float c, float d) {
+      if (P.is_f32) {
+        reinterpret_cast<float4*>(static_cast<float*>(out) + orow)[i] = make_float4(a, b, c, d);
+      } else {
+        ushort4 o;
+        o.x = bits16(a, P.is_bf16); o.y = bits16(b, P.is_bf16); o.z = bits16(c, P.is_bf16); o.w = bits16(d, P.is_bf16);
+        reinterpret_cast<ushort4*>(static_cast<unsigned short*>(out) + orow)[i] = o;
+      }
+    };
+    if (!shift) {
+      for (int i = tid; i < D4; i += 256) { const float4 v = reinterpret_cast<const float4*>(cur)[i]; store4(P.out[0], i, v.x, v.y, v.z, v.w); }
     } else {
-      ushort4 o;
-      o.x = bits16(a, P.is_bf16); o.y = bits16(b, P.is_bf16); o.z = bits16(c, P.is_bf16); o.w = bits16(d, P.is_bf16);
-      reinterpret_cast<ushort4*>(static_cast<unsigned short*>(out) + orow)[i] = o;
-    }
-  };
-  if (!shift) {
-    for (int i = tid; i < D4; i += 256) { const float4 v = reinterpret_cast<const float4*>(cur)[i]; store4(P.out[0], i, v.x, v.y, v.z, v.w); }
-  } else {
-    for (int i = tid; i < D4; i += 256) {
-      const float4 c = reinterpret_cast<const float4*>(cur)[i], p = reinterpret_cast<const float4*>(prev)[i];
+      for (int i = tid; i < D4; i += 256) {
+        const float4 c = reinterpret_cast<const float4*>(cur)[i], p = reinterpret_cast<const float4*>(prev)[i];
 #pragma unroll
-      for (int m = 0; m < 3; ++m) {
-        if (m < P.nmix) {
-          const float4 w = __ldg(reinterpret_cast<const float4*>(P.mix[m]) + i);
-          store4(P.out[m], i, lerp_like_torch(p.x, c.x, w.x), lerp_like_torch(p.y, c.y, w.y), lerp_like_torch(p.z, c.z, w.z),
-                 lerp_like_torch(p.w, c.w, w.w));
+        for (int m = 0; m < 3; ++m) {
+          if (m < P.nmix) {
+            const float4 w = __ldg(reinterpret_cast<const float4*>(P.mix[m]) + i);
+            store4(P.out[m], i, lerp_like_torch(p.x, c.x, w.x), lerp_like_torch(p.y, c.y, w.y), lerp_like_torch(p.z, c.z, w.z),
+                   lerp_like_torch(p.w, c.w, w.w));
+          }
         }
       }
     }

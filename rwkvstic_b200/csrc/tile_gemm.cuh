@@ -44,6 +44,8 @@ constexpr int kGemmAcc1Col = 256;                        // first column of the 
 constexpr int kGemmEpiWarps = 16;                        // four per TMEM lane quadrant
 constexpr int kGemmThreads = 128 + kGemmEpiWarps * 32;   // warp 0 TMA, 1 MMA, 2 TMEM allocation, 4.. epilogue
 constexpr int kGemmChunk = 8;                            // activation rows an epilogue warp handles per TMEM read
+// 8-row chunks of both 128-row sub-tiles that one epilogue warp takes at most (every fourth of its lane quadrant's)
+constexpr int kGemmItemsPerWarp = (2 * (kGemmRowsMax / kGemmChunk) + kGemmEpiWarps / 4 - 1) / (kGemmEpiWarps / 4);
 constexpr int kSplitMaxTiles = 320;                      // tiles a split-K launch may have
 constexpr int kSplitMaxRt = 32;                          // and its tile height
 constexpr size_t kSplitAccBytes = size_t(kSplitMaxTiles) * kDigits * kSplitMaxRt * 128 * 4;   // 15.7 MB
@@ -303,8 +305,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
         tc_fence_before();
         if (lane == 0) mbar_arrive(acc_empty);
       }
-      // affine terms + fused element-wise op for 8 rows of one output column, from the digit sums
-      auto finish = [&](const int (&da)[CH], const int (&db)[CH], const int (&dc)[CH], int h, int j0) {
+      // exact dot products of 8 rows of one output column from their three digit sums, as fp32
+      auto recombine = [&](const int (&da)[CH], const int (&db)[CH], const int (&dc)[CH], float (&yf)[CH]) {
+#pragma unroll
+        for (int j = 0; j < CH; ++j)
+          yf[j] = __ll2float_rn((long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j]);
+      };
+      // affine terms + fused element-wise op for 8 rows of one output column
+      auto finish = [&](const float (&yf)[CH], int h, int j0) {
         const int n = n0 + h * 128 + q * 32 + lane;
         const bool nvalid = n < Sg.N;
         const int nc = nvalid ? n : Sg.N - 1;   // clamped: loads stay in bounds, the store is predicated
@@ -314,8 +322,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
           const float4 sc = *reinterpret_cast<const float4*>(&scal[j0 + j]);   // sd, zp, sumxs, sumx
-          const long long I = (long long)da[j] * 65536 + (long long)db[j] * 256 + (long long)dc[j];
-          float y = __fmul_rn(__ll2float_rn(I), sc.x) + Sg.half * sc.z;
+          float y = __fmul_rn(yf[j], sc.x) + Sg.half * sc.z;
           y *= rx;               // rx = 1, mx = 0 when the matrix has no per-output terms: exact no-ops
           y += sc.y;
           y += mx * sc.w;
@@ -351,23 +358,55 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
       };
       // split-K scratch of this tile: [column = digit*Rt + row][128 weight rows] (mt = 128 only)
       int* sk = S > 1 ? P.sk_acc + size_t(tile) * (kDigits * Rt) * 128 + q * 32 + lane : nullptr;
-#pragma unroll 1
-      for (int item = eg; item < nitems; item += EG) {
-        const int h = item / nchunks, j0 = (item - h * nchunks) * CH;
-        if (row0 + j0 >= P.R) continue;   // warp-uniform
-        const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t((h + buf) * kGemmAcc1Col + j0);
-        int da[CH], db[CH], dc[CH];
-        tmem_ld8(tbase, da);
-        tmem_ld8(tbase + uint32_t(Rt), db);
-        tmem_ld8(tbase + uint32_t(2 * Rt), dc);
-        tmem_ld_wait();
-        if (item == last_item) {   // the rest of this item works from registers: let the next tile's MMAs start
-          tc_fence_before();
-          if (lane == 0) mbar_arrive(acc_empty);
+      if (S == 1) {
+        // Two passes, so that the accumulators are free again as early as possible (a 256-row tile has no
+        // second buffer: the next tile's MMAs wait for this): first every item of this warp leaves TMEM and
+        // is recombined to one fp32 per output (40 registers at most), then the affine terms, the gate and
+        // residual loads and the stores run from registers under the next tile's MMAs.
+        float yf[kGemmItemsPerWarp][CH];
+#pragma unroll
+        for (int u = 0; u < kGemmItemsPerWarp; ++u) {
+          const int item = eg + u * EG;
+          if (item < nitems) {
+            const int h = item / nchunks, j0 = (item - h * nchunks) * CH;
+            if (row0 + j0 < P.R) {   // warp-uniform
+              const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t((h + buf) * kGemmAcc1Col + j0);
+              int da[CH], db[CH], dc[CH];
+              tmem_ld8(tbase, da);
+              tmem_ld8(tbase + uint32_t(Rt), db);
+              tmem_ld8(tbase + uint32_t(2 * Rt), dc);
+              tmem_ld_wait();
+              if (item == last_item) {
+                tc_fence_before();
+                if (lane == 0) mbar_arrive(acc_empty);
+              }
+              recombine(da, db, dc, yf[u]);
+            }
+          }
         }
-        if (S == 1) {
-          finish(da, db, dc, h, j0);
-        } else {
+#pragma unroll
+        for (int u = 0; u < kGemmItemsPerWarp; ++u) {
+          const int item = eg + u * EG;
+          if (item < nitems) {
+            const int h = item / nchunks, j0 = (item - h * nchunks) * CH;
+            if (row0 + j0 < P.R) finish(yf[u], h, j0);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int item = eg; item < nitems; item += EG) {
+          const int h = item / nchunks, j0 = (item - h * nchunks) * CH;
+          if (row0 + j0 >= P.R) continue;   // warp-uniform
+          const uint32_t tbase = tmem + (uint32_t(q * 32) << 16) + uint32_t((h + buf) * kGemmAcc1Col + j0);
+          int da[CH], db[CH], dc[CH];
+          tmem_ld8(tbase, da);
+          tmem_ld8(tbase + uint32_t(Rt), db);
+          tmem_ld8(tbase + uint32_t(2 * Rt), dc);
+          tmem_ld_wait();
+          if (item == last_item) {   // the rest works from registers: let the next tile's MMAs start
+            tc_fence_before();
+            if (lane == 0) mbar_arrive(acc_empty);
+          }
 #pragma unroll
           for (int j = 0; j < CH; ++j) {   // 32 lanes = 32 consecutive ints per atomic instruction
             atomicAdd(sk + size_t(j0 + j) * 128, da[j]);
@@ -401,7 +440,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid
             for (int j = 0; j < CH; ++j) {   // leave the scratch zero for the next launch
               sk[size_t(j0 + j) * 128] = 0; sk[size_t(Rt + j0 + j) * 128] = 0; sk[size_t(2 * Rt + j0 + j) * 128] = 0;
             }
-            finish(da, db, dc, 0, j0);
+            float yf[CH];
+            recombine(da, db, dc, yf);
+            finish(yf, 0, j0);
           }
           if (et == 0) P.sk_count[tile] = 0u;
         }

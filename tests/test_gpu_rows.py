@@ -260,12 +260,15 @@ def test_rows_path_agrees_with_one_row_path_at_the_1b5_shape():
     model.check_status()
 
 
-def test_row_preparation_gives_the_same_bits_however_rows_are_grouped():
+@pytest.mark.parametrize("embed", [512, 2048, 4096, 5120])
+def test_row_preparation_gives_the_same_bits_however_rows_are_grouped(embed):
     """With thousands of rows a preparation CTA walks several consecutive rows for all matrices and keeps the
     layer norm of a row as the next row's token-shift partner; with few rows there is one CTA per (matrix, row).
-    Six streams of 280 tokens in one call (1680 rows: groups of four rows that straddle the stream boundaries)
-    must give exactly the logits and states of the same streams run one per call (280 rows: one CTA per row)."""
-    model = B200RWKV.synthetic(2, 512, vocab=1000, seed=9, device=DEV)
+    Six streams of 280 tokens in one call (1680 rows: groups of rows that straddle the stream boundaries)
+    must give exactly the logits and states of the same streams run one per call.  The widths cover every
+    instantiation family: 1, 2 and 4 register groups per thread at 256 threads, 512 threads at 5120 inputs,
+    and for the ffn value input (4 x embed) 256 threads, 512 threads and the rows too long for registers."""
+    model = B200RWKV.synthetic(2, embed, vocab=1000, seed=9, device=DEV)
     B, T = 6, 280
     toks = synth_tokens(B * T, seed=44, vocab=1000).reshape(B, T)
     start = model.empty_batch_state(B)

@@ -165,10 +165,11 @@ def test_loader_hook_with_dtype_builds_the_unquantised_model():
 
 
 @pytest.mark.parametrize("embed,name,B,T", [(2048, "bf16", 3, 40), (2560, "f16", 2, 17), (4096, "bf16", 2, 300), (5120, "f16", 1, 130),
-                                            (2048, "f16", 3, 129), (2048, "bf16", 5, 128)])
+                                            (2048, "f16", 3, 129), (2048, "bf16", 5, 128), (512, "bf16", 6, 280)])
 def test_dense_rows_path_against_the_oracle(embed, name, B, T):
-    """B sequences of T tokens in one call through the tensor-core rows path (T = 300 and 130 take the
-    chunk-parallel WKV scan) against the oracle's sequence mode, one sequence at a time: logits after the
+    """B sequences of T tokens in one call through the tensor-core rows path (T = 300, 280 and 130 take the
+    chunk-parallel WKV scan; 6 x 280 = 1680 rows are more than the GPU holds preparation CTAs, so each CTA
+    walks three consecutive rows across the sequence boundaries) against the oracle's sequence mode, one sequence at a time: logits after the
     last token and the final state; then one more token through the one-row step from that state."""
     V = 1024
     ck = synth_checkpoint(2, embed, vocab=V, seed=70 + embed % 13)

@@ -646,6 +646,7 @@ static cudaError_t launch_tile_gemm(GemmParams& P, const b200rwkv_matrix* const*
     }
   }
   P.row_tiles = (P.R + P.Rt - 1) / P.Rt;
+  P.block_tiles = gemm_block_tiles(P.row_tiles, P.Rt, P.K);
   P.ntiles = 0;
   for (int s = 0; s < P.nseg; ++s) {
     P.tiles_seg[s] = P.row_tiles * ((P.seg[s].N + P.mt - 1) / P.mt);

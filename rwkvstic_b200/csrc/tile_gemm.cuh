@@ -79,6 +79,7 @@ struct GemmParams {
   int Rt;              // activation rows per tile (multiple of 16, <= 80)
   int mt;              // weight rows per tile: 256 (two accumulators) or 128 (small grids: more CTAs)
   int row_tiles;       // ceil(R / Rt)
+  int block_tiles;     // row tiles per row block (tile order below); row_tiles when all digit rows fit L2 at once
   int tiles_seg[kMaxSeg];  // tiles per matrix = row_tiles * ceil(N / mt)
   int ntiles;          // all tiles of the launch; the grid is min(ntiles * ksplit, SMs), CTAs loop over work items
   // Split-K for launches with few tiles (few activation rows): work item = (tile, K slice); every
@@ -143,14 +144,29 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, int (&v)[8]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Tile t of a launch -> (segment, first weight row, first activation row).  Tiles that share a weight
-// tile are consecutive, so CTAs working side by side read it from L2.
+// Tile t of a launch -> (segment, first weight row, first activation row).  Within a matrix the order is
+// row block, weight tile, row tile of the block: the CTAs working side by side share a weight tile, and
+// all weight tiles sweep over one block of digit rows (sized by the launcher to stay in L2) before the
+// next block is touched, so the digit rows come from DRAM once instead of once per few weight tiles.
 struct GemmTile { int seg, n0, row0; };
 __device__ __forceinline__ GemmTile gemm_tile(const GemmParams& P, int t) {
   int s = 0;
   while (s < P.nseg - 1 && t >= P.tiles_seg[s]) { t -= P.tiles_seg[s]; ++s; }
-  const int wt = t / P.row_tiles;
-  return {s, wt * P.mt, (t - wt * P.row_tiles) * P.Rt};
+  const int wtiles = P.tiles_seg[s] / P.row_tiles;
+  const int per_block = P.block_tiles * wtiles;
+  const int blk = t / per_block, first = blk * P.block_tiles;
+  const int nb = min(P.block_tiles, P.row_tiles - first);     // row tiles of this (maybe last, shorter) block
+  const int idx = t - blk * per_block;
+  const int wt = idx / nb;
+  return {s, wt * P.mt, (first + idx - wt * nb) * P.Rt};
+}
+
+// Row tiles per block: three digit planes of a block's rows take at most kGemmDigitBlockBytes.
+constexpr long long kGemmDigitBlockBytes = 16ll << 20;   // measured best of 8 / 16 / 24 / 32 / 48 MB on the 126 MB L2
+inline int gemm_block_tiles(int row_tiles, int Rt, int K) {
+  const long long per_tile = (long long)kDigits * Rt * K;
+  const long long fit = per_tile > 0 ? kGemmDigitBlockBytes / per_tile : row_tiles;
+  return int(fit < 1 ? 1 : fit > row_tiles ? row_tiles : fit);
 }
 
 __global__ void __launch_bounds__(kGemmThreads, 1) tile_gemm_kernel(const __grid_constant__ GemmParams P) {
